@@ -1,0 +1,578 @@
+// Flash attention backward for sm_100a, as two deterministic kernels (no float atomics):
+//
+//   flash_bwd_q   one CTA per 128 query rows of a (batch, head): for each key block recompute
+//                 S = Q K^T and dP = dO V^T into TMEM, form dS = P * (dP - delta) * scale in registers,
+//                 stage it as a bf16 operand and accumulate dQ += dS K in TMEM.
+//   flash_bwd_kv  one CTA per 128 keys of a (batch, kv head): for every query head of the group and every
+//                 query block that can see these keys recompute S^T = K Q^T and dP^T = V dO^T (so a
+//                 thread owns a key row), form P^T and dS^T, and accumulate dV += P^T dO and
+//                 dK += dS^T Q in TMEM. Grouped-query heads are summed inside the CTA.
+//   flash_delta   delta[b,h,s] = sum_d dO * O.
+//
+// Warp roles match the forward kernel: warp 0 feeds shared memory with TMA, warp 1 issues tcgen05.mma,
+// warps 2..5 do the element-wise work one row per thread. The same 128B-swizzled tile serves as a
+// K-major operand for one product and as an MN-major operand for the other, so nothing is transposed.
+//
+// Reference counterparts: flash_tc_bwd_q_d{64,128}, flash_tc_bwd_kv_d{64,128}, flash_tc_delta
+// (src/Idrak.Gpu/Cuda/PtxKernels.FlashTensorCore.cs) and attn_bwd_{d,kv,q}_f32 (PtxKernels.Rows.cs:1222-1750).
+#include "flash_common.cuh"
+
+namespace idrak {
+
+constexpr float kLog2e = 1.4426950408889634f;
+
+__device__ __forceinline__ void softmax_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Write 32 consecutive columns [c*32, c*32+32) of row r of a 128x128 bf16 K-major operand tile.
+__device__ __forceinline__ void store_operand_chunk(uint8_t* tile, int r, int c, const float (&v)[32]) {
+  uint8_t* atom = tile + (c >> 1) * 16384 + r * 128;
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
+    uint4 o;
+    o.x = pack_bf16x2(v[g * 8 + 0], v[g * 8 + 1]);
+    o.y = pack_bf16x2(v[g * 8 + 2], v[g * 8 + 3]);
+    o.z = pack_bf16x2(v[g * 8 + 4], v[g * 8 + 5]);
+    o.w = pack_bf16x2(v[g * 8 + 6], v[g * 8 + 7]);
+    *reinterpret_cast<uint4*>(atom + chunk * 16) = o;
+  }
+}
+
+// K-major operand tile [128 rows][D]: descriptor for k-step kk (16 columns)
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t base, int kk) {
+  return make_smem_desc_sw128(base + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+}
+// The same tile read as an MN-major operand (N = D, contraction over its 128 rows): k-step kk = 16 rows
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t base, int kk) {
+  return make_smem_desc_sw128(base + kk * 2048, 16384, 1024);
+}
+
+// ---------------------------------------------------------------------------
+// delta
+// ---------------------------------------------------------------------------
+__global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dO,
+                                   float* __restrict__ delta, int B, int S, int H, int D) {
+  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * S * H;
+  if (w >= total) return;
+  const int h = int(w % H);
+  const long long bs = w / H;
+  const int s = int(bs % S);
+  const int b = int(bs / S);
+  const __nv_bfloat16* po = o + (bs * H + h) * D;
+  const __nv_bfloat16* pd = dO + (bs * H + h) * D;
+  float acc = 0.f;
+  for (int i = lane * 2; i < D; i += 64) {
+    float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(po + i));
+    float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pd + i));
+    acc += a.x * g.x + a.y * g.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) delta[((long long)b * H + h) * S + s] = acc;
+}
+
+// ---------------------------------------------------------------------------
+// dQ
+// ---------------------------------------------------------------------------
+template <int D>
+struct BwdQSmem {
+  static constexpr int kTile = 128 * D * 2;
+  static constexpr int kStages = (D == 64) ? 2 : 1;
+  static constexpr int kQ = 0;
+  static constexpr int kDO = kQ + kTile;
+  static constexpr int kK = kDO + kTile;
+  static constexpr int kV = kK + kStages * kTile;
+  static constexpr int kDS = kV + kStages * kTile;
+  static constexpr int kBar = kDS + 32768;
+  static constexpr int kTotal = kBar + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                   const FlashParams p) {
+  using L = BwdQSmem<D>;
+  constexpr int NS = L::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  uint64_t* qdo_full = bars + 0;
+  uint64_t* kv_full = bars + 1;     // [2]
+  uint64_t* kv_empty = bars + 3;    // [2]
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* ds_ready = bars + 6;
+  uint64_t* dq_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int kv_head = head / (p.H / p.Hkv);
+  const int q0 = qb * 128;
+  const int off = p.Skv - p.Sq;
+  int nkv = (p.Skv + 127) / 128;
+  if (p.causal) nkv = min(nkv, (q0 + 127 + off) / 128 + 1);
+  if (nkv < 0) nkv = 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(qdo_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_ready, 128);
+    mbar_init(dq_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  constexpr uint32_t kTmemCols = 512;   // S [0,128) | dP [128,256) | dQ [256, 256+D)
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dQ = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0 && nkv > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmDO);
+      mbar_expect_tx(qdo_full, 2 * L::kTile);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_4d(smem + L::kQ + c * 16384, &tmQ, qdo_full, c * 64, q0, head, batch);
+        tma_load_4d(smem + L::kDO + c * 16384, &tmDO, qdo_full, c * 64, q0, head, batch);
+      }
+      for (int j = 0; j < nkv; ++j) {
+        const int st = j % NS;
+        const uint32_t ph = (j / NS) & 1;
+        if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (3u << 16) | st)) break;
+        mbar_expect_tx(&kv_full[st], 2 * L::kTile);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_4d(smem + L::kK + st * L::kTile + c * 16384, &tmK, &kv_full[st], c * 64, j * 128, kv_head, batch);
+          tma_load_4d(smem + L::kV + st * L::kTile + c * 16384, &tmV, &kv_full[st], c * 64, j * 128, kv_head, batch);
+        }
+      }
+      if (*abort_flag) __nanosleep(50000);
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nkv > 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0, 1);
+      constexpr uint32_t idesc_dq = make_idesc_f16(128, D, 0, 1, 1);
+      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.st, kTimeoutSmemFull, (3u << 16) | 8);
+      const uint32_t sq = smem_u32(smem + L::kQ), sdo = smem_u32(smem + L::kDO), sds = smem_u32(smem + L::kDS);
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int st = j % NS;
+        const uint32_t ph = (j / NS) & 1;
+        if (!mbar_wait(&kv_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (3u << 16) | st)) break;
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + L::kK + st * L::kTile), sv = smem_u32(smem + L::kV + st * L::kTile);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          tc_mma_f16_ss(tmem_S, kmajor_desc(sq, kk), kmajor_desc(sk, kk), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          tc_mma_f16_ss(tmem_dP, kmajor_desc(sdo, kk), kmajor_desc(sv, kk), idesc_s, kk > 0 ? 1u : 0u);
+        tc_commit(sdp_full);
+        if (!mbar_wait(ds_ready, j & 1, abort_flag, p.st, kTimeoutGeneric, (3u << 16) | 9)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tc_mma_f16_ss(tmem_dQ, kmajor_desc(sds, kk), mnmajor_desc(sk, kk), idesc_dq, (j > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&kv_empty[st]);
+        tc_commit(dq_done);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int row = q0 + r;
+    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    uint8_t* sDS = smem + L::kDS;
+    float lse2 = INFINITY, dlt = 0.f;
+    if (row < p.Sq) {
+      const size_t idx = (size_t(batch) * p.H + head) * p.Sq + row;
+      const float l = p.lse[idx];
+      lse2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+      dlt = p.delta[idx];
+    }
+    bool ok = nkv > 0;
+    for (int j = 0; j < nkv && ok; ++j) {
+      if (!mbar_wait(sdp_full, j & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 10)) { ok = false; break; }
+      tc_fence_after();
+      if (j > 0) {
+        // the previous dQ product still reads the dS tile until dq_done completes
+        if (!mbar_wait(dq_done, (j - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 11)) { ok = false; break; }
+      }
+      const int k0 = j * 128;
+      int lim = p.Skv - k0;
+      if (p.causal) lim = min(lim, row + off - k0 + 1);
+      lim = max(0, min(128, lim));
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32], dp[32];
+        tmem_ld_32x32b_x32(tmem_S + lane_addr + c * 32, s);
+        tmem_ld_32x32b_x32(tmem_dP + lane_addr + c * 32, dp);
+        tmem_ld_wait();
+        float ds[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float pr = exp2f(__uint_as_float(s[i]) * p.scale_log2 - lse2);
+          float v = pr * (__uint_as_float(dp[i]) - dlt) * p.scale;
+          ds[i] = (c * 32 + i < lim) ? v : 0.f;
+        }
+        store_operand_chunk(sDS, r, c, ds);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(ds_ready);
+    }
+    if (ok && nkv > 0) {
+      if (!mbar_wait(dq_done, (nkv - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 12)) ok = false;
+    }
+    tc_fence_after();
+    if (ok || nkv == 0) {     // warp-uniform: every thread of the warp waited on the same barriers
+      __nv_bfloat16* drow = p.dQ + (size_t(batch) * p.Sq + row) * p.dq_row_stride + size_t(head) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (nkv > 0) {
+          tmem_ld_32x32b_x32(tmem_dQ + lane_addr + c * 32, o);   // aligned: all 32 lanes take part
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (row >= p.Sq) continue;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(o[g * 8 + 0]), __uint_as_float(o[g * 8 + 1]));
+          w.y = pack_bf16x2(__uint_as_float(o[g * 8 + 2]), __uint_as_float(o[g * 8 + 3]));
+          w.z = pack_bf16x2(__uint_as_float(o[g * 8 + 4]), __uint_as_float(o[g * 8 + 5]));
+          w.w = pack_bf16x2(__uint_as_float(o[g * 8 + 6]), __uint_as_float(o[g * 8 + 7]));
+          *reinterpret_cast<uint4*>(drow + c * 32 + g * 8) = w;
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// dK, dV
+// ---------------------------------------------------------------------------
+template <int D>
+struct BwdKVSmem {
+  static constexpr int kTile = 128 * D * 2;
+  static constexpr int kStages = (D == 64) ? 2 : 1;
+  static constexpr int kK = 0;
+  static constexpr int kV = kK + kTile;
+  static constexpr int kQ = kV + kTile;
+  static constexpr int kDO = kQ + kStages * kTile;
+  static constexpr int kPT = kDO + kStages * kTile;
+  static constexpr int kDST = kPT + 32768;
+  static constexpr int kStat = kDST + 32768;       // lse2[128], delta[128]
+  static constexpr int kBar = kStat + 1024;
+  static constexpr int kTotal = kBar + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                    const FlashParams p) {
+  using L = BwdKVSmem<D>;
+  constexpr int NS = L::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  uint64_t* kv_full = bars + 0;
+  uint64_t* qdo_full = bars + 1;    // [2]
+  uint64_t* qdo_empty = bars + 3;   // [2]
+  uint64_t* sdp_full = bars + 5;
+  uint64_t* pds_ready = bars + 6;
+  uint64_t* acc_done = bars + 7;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+  float* s_lse2 = reinterpret_cast<float*>(smem + L::kStat);
+  float* s_delta = s_lse2 + 128;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int kb = blockIdx.x, kv_head = blockIdx.y, batch = blockIdx.z;
+  const int group = p.H / p.Hkv;
+  const int k0 = kb * 128;
+  const int off = p.Skv - p.Sq;
+  const int nq = (p.Sq + 127) / 128;
+  int i_min = 0;
+  if (p.causal) i_min = max(0, (k0 - off) / 128);
+  const int per_head = max(0, nq - i_min);
+  const int iters = per_head * group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&qdo_full[s], 1);
+      mbar_init(&qdo_empty[s], 1);
+    }
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_ready, 128);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  constexpr uint32_t kTmemCols = 512;   // S^T [0,128) | dP^T [128,256) | dV [256,256+D) | dK [256+D, 256+2D)
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_ST = tmem_base, tmem_dPT = tmem_base + 128, tmem_dV = tmem_base + 256,
+                 tmem_dK = tmem_base + 256 + D;
+
+  if (warp == 0) {
+    if (lane == 0 && iters > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmDO);
+      mbar_expect_tx(kv_full, 2 * L::kTile);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_4d(smem + L::kK + c * 16384, &tmK, kv_full, c * 64, k0, kv_head, batch);
+        tma_load_4d(smem + L::kV + c * 16384, &tmV, kv_full, c * 64, k0, kv_head, batch);
+      }
+      for (int it = 0; it < iters; ++it) {
+        const int st = it % NS;
+        const uint32_t ph = (it / NS) & 1;
+        const int head = kv_head * group + it / per_head;
+        const int qi = i_min + it % per_head;
+        if (!mbar_wait(&qdo_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (4u << 16) | st)) break;
+        mbar_expect_tx(&qdo_full[st], 2 * L::kTile);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c) {
+          tma_load_4d(smem + L::kQ + st * L::kTile + c * 16384, &tmQ, &qdo_full[st], c * 64, qi * 128, head, batch);
+          tma_load_4d(smem + L::kDO + st * L::kTile + c * 16384, &tmDO, &qdo_full[st], c * 64, qi * 128, head, batch);
+        }
+      }
+      if (*abort_flag) __nanosleep(50000);
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && iters > 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0, 1);
+      constexpr uint32_t idesc_acc = make_idesc_f16(128, D, 0, 1, 1);
+      bool ok = mbar_wait(kv_full, 0, abort_flag, p.st, kTimeoutSmemFull, (4u << 16) | 8);
+      const uint32_t sk = smem_u32(smem + L::kK), sv = smem_u32(smem + L::kV);
+      const uint32_t spt = smem_u32(smem + L::kPT), sdst = smem_u32(smem + L::kDST);
+      for (int it = 0; it < iters && ok; ++it) {
+        const int st = it % NS;
+        const uint32_t ph = (it / NS) & 1;
+        if (!mbar_wait(&qdo_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (4u << 16) | st)) break;
+        tc_fence_after();
+        const uint32_t sq = smem_u32(smem + L::kQ + st * L::kTile), sdo = smem_u32(smem + L::kDO + st * L::kTile);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          tc_mma_f16_ss(tmem_ST, kmajor_desc(sk, kk), kmajor_desc(sq, kk), idesc_s, kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          tc_mma_f16_ss(tmem_dPT, kmajor_desc(sv, kk), kmajor_desc(sdo, kk), idesc_s, kk > 0 ? 1u : 0u);
+        tc_commit(sdp_full);
+        if (!mbar_wait(pds_ready, it & 1, abort_flag, p.st, kTimeoutGeneric, (4u << 16) | 9)) break;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tc_mma_f16_ss(tmem_dV, kmajor_desc(spt, kk), mnmajor_desc(sdo, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk)
+          tc_mma_f16_ss(tmem_dK, kmajor_desc(sdst, kk), mnmajor_desc(sq, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+        tc_commit(&qdo_empty[st]);
+        tc_commit(acc_done);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;       // key row within the block
+    const int key = k0 + r;
+    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    uint8_t* sPT = smem + L::kPT;
+    uint8_t* sDST = smem + L::kDST;
+    bool ok = true;
+    for (int it = 0; it < iters && ok; ++it) {
+      const int head = kv_head * group + it / per_head;
+      const int qi = i_min + it % per_head;
+      const int qrow0 = qi * 128;
+      // stage this query block's row statistics (thread r loads query r)
+      softmax_bar_sync();    // readers of the previous block's statistics are done
+      {
+        const int qr = qrow0 + r;
+        float l2 = INFINITY, dl = 0.f;
+        if (qr < p.Sq) {
+          const size_t idx = (size_t(batch) * p.H + head) * p.Sq + qr;
+          const float l = p.lse[idx];
+          l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+          dl = p.delta[idx];
+        }
+        s_lse2[r] = l2;
+        s_delta[r] = dl;
+      }
+      softmax_bar_sync();
+      if (!mbar_wait(sdp_full, it & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 10)) { ok = false; break; }
+      tc_fence_after();
+      if (it > 0) {
+        if (!mbar_wait(acc_done, (it - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 11)) { ok = false; break; }
+      }
+      // query q (column) sees this key iff key <= q + off  <=>  q >= key - off
+      const int first_q = p.causal ? (key - off - qrow0) : 0;    // columns below this are masked
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32], dp[32];
+        tmem_ld_32x32b_x32(tmem_ST + lane_addr + c * 32, s);
+        tmem_ld_32x32b_x32(tmem_dPT + lane_addr + c * 32, dp);
+        tmem_ld_wait();
+        float pt[32], dst[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int col = c * 32 + i;
+          float pr = exp2f(__uint_as_float(s[i]) * p.scale_log2 - s_lse2[col]);
+          if (col < first_q) pr = 0.f;
+          pt[i] = pr;
+          dst[i] = pr * (__uint_as_float(dp[i]) - s_delta[col]) * p.scale;
+        }
+        store_operand_chunk(sPT, r, c, pt);
+        store_operand_chunk(sDST, r, c, dst);
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(pds_ready);
+    }
+    if (ok && iters > 0) {
+      if (!mbar_wait(acc_done, (iters - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 12)) ok = false;
+    }
+    tc_fence_after();
+    if (ok || iters == 0) {   // warp-uniform
+      __nv_bfloat16* dkrow = p.dK + (size_t(batch) * p.Skv + key) * p.dk_row_stride + size_t(kv_head) * D;
+      __nv_bfloat16* dvrow = p.dV + (size_t(batch) * p.Skv + key) * p.dv_row_stride + size_t(kv_head) * D;
+#pragma unroll 1
+      for (int which = 0; which < 2; ++which) {
+        __nv_bfloat16* drow = which ? dkrow : dvrow;
+        const uint32_t t = which ? tmem_dK : tmem_dV;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          if (iters > 0) {
+            tmem_ld_32x32b_x32(t + lane_addr + c * 32, o);
+            tmem_ld_wait();
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = 0u;
+          }
+          if (key >= p.Skv) continue;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[g * 8 + 0]), __uint_as_float(o[g * 8 + 1]));
+            w.y = pack_bf16x2(__uint_as_float(o[g * 8 + 2]), __uint_as_float(o[g * 8 + 3]));
+            w.z = pack_bf16x2(__uint_as_float(o[g * 8 + 4]), __uint_as_float(o[g * 8 + 5]));
+            w.w = pack_bf16x2(__uint_as_float(o[g * 8 + 6]), __uint_as_float(o[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(drow + c * 32 + g * 8) = w;
+          }
+        }
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int D>
+static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
+                      const FlashParams& p, cudaStream_t stream) {
+  auto kq = flash_bwd_q_kernel<D>;
+  auto kkv = flash_bwd_kv_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdQSmem<D>::kTotal);
+    if (e != cudaSuccess) return int(e);
+    e = cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdKVSmem<D>::kTotal);
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  dim3 gq((p.Sq + 127) / 128, p.H, p.B);
+  kq<<<gq, 192, BwdQSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  int rc = int(cudaGetLastError());
+  if (rc) return rc;
+  dim3 gkv((p.Skv + 127) / 128, p.Hkv, p.B);
+  kkv<<<gkv, 192, BwdKVSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  return int(cudaGetLastError());
+}
+
+}  // namespace idrak
+
+using namespace idrak;
+
+// out / dout: contiguous [B, Sq, H, D]; dq [B,Sq,H,D], dk / dv [B,Skv,Hkv,D] contiguous; lse, delta [B,H,Sq].
+IDRAK_API int idrak_flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                              const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int H, int Hkv,
+                              int Sq, int Skv, int D, long long q_row_stride, long long k_row_stride,
+                              long long v_row_stride, long long q_batch_stride, long long k_batch_stride,
+                              long long v_batch_stride, float scale, int causal, void* stream_) {
+  if (D != 64 && D != 128) return -2;
+  if (H % Hkv) return -3;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  {
+    const long long warps = (long long)B * Sq * H;
+    const int threads = 256;
+    const long long blocks = (warps * 32 + threads - 1) / threads;
+    flash_delta_kernel<<<unsigned(blocks), threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(out),
+                                                                 static_cast<const __nv_bfloat16*>(dout), delta, B,
+                                                                 Sq, H, D);
+    int rc = int(cudaGetLastError());
+    if (rc) return rc;
+  }
+  FlashParams p;
+  p.O = nullptr;
+  p.o_row_stride = 0;
+  p.lse = const_cast<float*>(lse);
+  p.delta = delta;
+  p.B = B; p.H = H; p.Hkv = Hkv; p.Sq = Sq; p.Skv = Skv;
+  p.scale = scale;
+  p.scale_log2 = scale * kLog2e;
+  p.causal = causal;
+  p.st = status_device_ptr();
+  p.dQ = static_cast<__nv_bfloat16*>(dq);
+  p.dK = static_cast<__nv_bfloat16*>(dk);
+  p.dV = static_cast<__nv_bfloat16*>(dv);
+  p.dq_row_stride = (long long)H * D;
+  p.dk_row_stride = (long long)Hkv * D;
+  p.dv_row_stride = (long long)Hkv * D;
+  CUtensorMap tq, tk, tv, tdo;
+  if (make_head_map(&tq, q, D, Sq, H, B, q_row_stride, q_batch_stride)) return -10;
+  if (make_head_map(&tk, k, D, Skv, Hkv, B, k_row_stride, k_batch_stride)) return -11;
+  if (make_head_map(&tv, v, D, Skv, Hkv, B, v_row_stride, v_batch_stride)) return -12;
+  if (make_head_map(&tdo, dout, D, Sq, H, B, (long long)H * D, (long long)Sq * H * D)) return -13;
+  return D == 64 ? launch_bwd<64>(tq, tk, tv, tdo, p, stream) : launch_bwd<128>(tq, tk, tv, tdo, p, stream);
+}

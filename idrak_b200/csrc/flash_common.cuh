@@ -1,0 +1,34 @@
+// Shared by the flash-attention forward and backward kernels.
+#pragma once
+#include "common.cuh"
+
+namespace idrak {
+
+struct FlashParams {
+  __nv_bfloat16* O;
+  long long o_row_stride;
+  float* lse;          // [B, H, Sq]
+  int B, H, Hkv, Sq, Skv;
+  float scale, scale_log2;
+  int causal;
+  Status* st;
+  // backward only
+  const float* delta;  // [B, H, Sq] rowsum(dO * O)
+  __nv_bfloat16* dQ;
+  __nv_bfloat16* dK;
+  __nv_bfloat16* dV;
+  long long dq_row_stride, dk_row_stride, dv_row_stride;
+};
+
+// 4-D map (d, position, head, batch) over a buffer whose rows hold heads packed as [heads, D].
+// Box = 64 d x 128 positions: one 128-byte-swizzled operand tile column block.
+static inline int make_head_map(CUtensorMap* tm, const void* ptr, int D, int S, int heads, int B,
+                                long long row_stride, long long batch_stride) {
+  uint64_t dims[4] = {uint64_t(D), uint64_t(S), uint64_t(heads), uint64_t(B)};
+  uint64_t strides[3] = {uint64_t(row_stride) * 2, uint64_t(D) * 2, uint64_t(batch_stride) * 2};
+  uint32_t box[4] = {64, 128, 1, 1};
+  return encode_tensor_map(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box,
+                           CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace idrak

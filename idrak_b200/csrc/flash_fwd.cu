@@ -1,0 +1,344 @@
+// Flash attention forward for sm_100a (prefill / training): O = softmax(scale * Q K^T + mask) V without
+// ever forming the score matrix in memory. Causal or full, grouped-query heads, head size 64 or 128.
+//
+// One CTA owns 128 query rows of one (batch, head) and walks the key/value sequence in blocks of 128:
+//   warp 0      TMA producer: Q once, then K and V blocks through two-stage rings (128B swizzle)
+//   warp 1      MMA issuer:   S = Q K^T into TMEM (tcgen05.mma, K-major x K-major), then O += P V
+//                             (P from shared memory, V as an MN-major operand, accumulator kept in TMEM)
+//   warps 2..5  softmax:      one thread per query row reads its row of S with tcgen05.ld (no shuffles),
+//                             online max / sum in the log2 domain, writes P as bf16 into the swizzled
+//                             operand layout, rescales the TMEM accumulator only when the running max
+//                             moved by more than 2^8 (warp-uniform decision), and finally normalises
+//                             and stores O plus the row log-sum-exp for the backward pass.
+// Q, K and V are addressed through 4-D tensor maps (d, position, head, batch) so fused-QKV buffers and
+// cache layouts need no copy.
+//
+// Reference counterparts: flash_tc_fwd_d{64,128} (src/Idrak.Gpu/Cuda/PtxKernels.FlashTensorCore.cs:318-321)
+// and Tensor.CausalAttention (src/Idrak.Abstraction/Tensors/Tensor.Decoding.cs:132).
+#include "flash_common.cuh"
+
+namespace idrak {
+
+template <int D>
+struct FwdSmem {
+  static constexpr int kTile = 128 * D * 2;        // one 128-row operand tile
+  static constexpr int kP = 128 * 128 * 2;
+  static constexpr int kQ = 0;
+  static constexpr int kK = kQ + kTile;            // two stages
+  static constexpr int kV = kK + 2 * kTile;        // two stages
+  static constexpr int kPOff = kV + 2 * kTile;
+  static constexpr int kBar = kPOff + kP;
+  static constexpr int kTotal = kBar + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(192, (D == 64) ? 2 : 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
+  using L = FwdSmem<D>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
+  uint64_t* q_full = bars + 0;
+  uint64_t* k_full = bars + 1;    // [2]
+  uint64_t* v_full = bars + 3;    // [2]
+  uint64_t* k_empty = bars + 5;   // [2]
+  uint64_t* v_empty = bars + 7;   // [2]
+  uint64_t* s_full = bars + 9;
+  uint64_t* p_ready = bars + 10;
+  uint64_t* o_done = bars + 11;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heavier (later) causal row blocks are scheduled first
+  const int qb = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
+  const int head = blockIdx.y, batch = blockIdx.z;
+  const int kv_head = head / (p.H / p.Hkv);
+  const int q0 = qb * 128;
+  const int off = p.Skv - p.Sq;   // causal: query row r sees keys <= r + off
+  int nkv = (p.Skv + 127) / 128;
+  if (p.causal) nkv = min(nkv, (q0 + 127 + off) / 128 + 1);
+  if (nkv < 0) nkv = 0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_empty[s], 1);
+    }
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 128);
+    mbar_init(o_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  constexpr uint32_t kTmemCols = 256;   // S: columns [0,128), O: [128, 128+D)
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+
+  if (warp == 0) {
+    if (lane == 0 && nkv > 0) {
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, L::kTile);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) tma_load_4d(smem + L::kQ + c * 16384, &tmQ, q_full, c * 64, q0, head, batch);
+      uint32_t inflight = 0;
+      bool ok = true;
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (2u << 16) | st)) { ok = false; break; }
+        mbar_expect_tx(&k_full[st], L::kTile);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_4d(smem + L::kK + st * L::kTile + c * 16384, &tmK, &k_full[st], c * 64, j * 128, kv_head, batch);
+        inflight |= 1u << st;
+        if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (2u << 16) | (2 + st))) { ok = false; break; }
+        mbar_expect_tx(&v_full[st], L::kTile);
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_4d(smem + L::kV + st * L::kTile + c * 16384, &tmV, &v_full[st], c * 64, j * 128, kv_head, batch);
+        inflight |= 4u << st;
+      }
+      if (!ok || *abort_flag) {
+        // let copies already issued land before shared memory is released (bounded)
+        for (int i = 0; i < (1 << 16); ++i) {
+          if (!mbar_try_wait(q_full, 0)) continue;
+          break;
+        }
+        __nanosleep(20000);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && nkv > 0) {
+      constexpr uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0, 1);
+      constexpr uint32_t idesc_o = make_idesc_f16(128, D, 0, 1, 1);
+      bool ok = mbar_wait(q_full, 0, abort_flag, p.st, kTimeoutSmemFull, (2u << 16) | 8);
+      const uint32_t sq = smem_u32(smem + L::kQ);
+      const uint32_t sp = smem_u32(smem + L::kPOff);
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(&k_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (2u << 16) | st)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sk = smem_u32(smem + L::kK + st * L::kTile);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const uint32_t o = (kk >> 2) * 16384 + (kk & 3) * 32;
+          tc_mma_f16_ss(tmem_S, make_smem_desc_sw128(sq + o, 16, 1024), make_smem_desc_sw128(sk + o, 16, 1024),
+                        idesc_s, kk > 0 ? 1u : 0u);
+        }
+        tc_commit(s_full);
+        tc_commit(&k_empty[st]);
+        if (!mbar_wait(p_ready, j & 1, abort_flag, p.st, kTimeoutGeneric, (2u << 16) | 9)) { ok = false; break; }
+        if (!mbar_wait(&v_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (2u << 16) | (2 + st))) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t sv = smem_u32(smem + L::kV + st * L::kTile);
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+          const uint64_t da = make_smem_desc_sw128(sp + (kk >> 2) * 16384 + (kk & 3) * 32, 16, 1024);
+          const uint64_t db = make_smem_desc_sw128(sv + kk * 2048, 16384, 1024);
+          tc_mma_f16_ss(tmem_O, da, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        tc_commit(&v_empty[st]);
+        tc_commit(o_done);
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax / correction / epilogue
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;           // row within the tile == TMEM lane
+    const int row = q0 + r;                      // query position
+    const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
+    uint8_t* sP = smem + L::kPOff;
+    float m_used = -INFINITY;                    // max the accumulator and the running sum are scaled by
+    float l = 0.f;
+    bool ok = nkv > 0;
+    for (int j = 0; j < nkv && ok; ++j) {
+      if (!mbar_wait(s_full, j & 1, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 10)) { ok = false; break; }
+      tc_fence_after();
+      const int k0 = j * 128;
+      // keys visible to this row in this block: columns [0, lim)
+      int lim = p.Skv - k0;
+      if (p.causal) lim = min(lim, row + off - k0 + 1);
+      lim = max(0, min(128, lim));
+      const bool need_mask = lim < 128;
+      // pass 1: row max
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        tmem_ld_32x32b_x32(tmem_S + lane_addr + c * 32, s);
+        tmem_ld_wait();
+        if (!need_mask) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i)
+            if (c * 32 + i < lim) mx = fmaxf(mx, __uint_as_float(s[i]));
+        }
+      }
+      mx *= p.scale_log2;
+      const float m_new = fmaxf(m_used, mx);
+      // the accumulator is rescaled only when some row of this warp moved its max by more than 2^8
+      const bool need = (j > 0) && (m_new - m_used > 8.0f);
+      const bool warp_rescale = __any_sync(0xffffffffu, need);
+      if (j > 0) {
+        // P of the previous block is still being read by its MMA until o_done completes
+        if (!mbar_wait(o_done, (j - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 11)) { ok = false; break; }
+        tc_fence_after();
+      }
+      if (j == 0) {
+        m_used = m_new;
+      } else if (warp_rescale) {
+        const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_used - m_new);
+        m_used = m_new;
+        l *= alpha;
+#pragma unroll 1
+        for (int c = 0; c < D / 32; ++c) {
+          uint32_t o[32];
+          tmem_ld_32x32b_x32(tmem_O + lane_addr + c * 32, o);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st_32x32b_x32(tmem_O + lane_addr + c * 32, o);
+        }
+        tmem_st_wait();
+      }
+      const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
+      // pass 2: probabilities -> bf16 operand tile (K-major, 128B swizzle: chunk ^= row % 8)
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        uint32_t s[32];
+        tmem_ld_32x32b_x32(tmem_S + lane_addr + c * 32, s);
+        tmem_ld_wait();
+        float pv[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          float e = exp2f(__uint_as_float(s[i]) * p.scale_log2 - m_sub);
+          if (need_mask && (c * 32 + i >= lim)) e = 0.f;
+          pv[i] = e;
+          l += e;
+        }
+        uint8_t* atom = sP + (c >> 1) * 16384 + r * 128;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
+          uint4 o;
+          o.x = pack_bf16x2(pv[g * 8 + 0], pv[g * 8 + 1]);
+          o.y = pack_bf16x2(pv[g * 8 + 2], pv[g * 8 + 3]);
+          o.z = pack_bf16x2(pv[g * 8 + 4], pv[g * 8 + 5]);
+          o.w = pack_bf16x2(pv[g * 8 + 6], pv[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(atom + chunk * 16) = o;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(p_ready);
+    }
+    if (ok) {
+      if (!mbar_wait(o_done, (nkv - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 12)) ok = false;
+    }
+    tc_fence_after();
+    if (nkv == 0) {
+      // no visible key: output zeros, lse = -inf
+      if (row < p.Sq) {
+        __nv_bfloat16* orow = p.O + (size_t(batch) * p.Sq + row) * p.o_row_stride + size_t(head) * D;
+        for (int i = 0; i < D; i += 8) *reinterpret_cast<uint4*>(orow + i) = make_uint4(0, 0, 0, 0);
+        if (p.lse) p.lse[(size_t(batch) * p.H + head) * p.Sq + row] = -INFINITY;
+      }
+    } else if (ok) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = p.O + (size_t(batch) * p.Sq + row) * p.o_row_stride + size_t(head) * D;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        tmem_ld_32x32b_x32(tmem_O + lane_addr + c * 32, o);
+        tmem_ld_wait();
+        if (row < p.Sq) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 w;
+            w.x = pack_bf16x2(__uint_as_float(o[g * 8 + 0]) * inv, __uint_as_float(o[g * 8 + 1]) * inv);
+            w.y = pack_bf16x2(__uint_as_float(o[g * 8 + 2]) * inv, __uint_as_float(o[g * 8 + 3]) * inv);
+            w.z = pack_bf16x2(__uint_as_float(o[g * 8 + 4]) * inv, __uint_as_float(o[g * 8 + 5]) * inv);
+            w.w = pack_bf16x2(__uint_as_float(o[g * 8 + 6]) * inv, __uint_as_float(o[g * 8 + 7]) * inv);
+            *reinterpret_cast<uint4*>(orow + c * 32 + g * 8) = w;
+          }
+        }
+      }
+      if (row < p.Sq && p.lse) {
+        // natural-log LSE of the scaled scores
+        p.lse[(size_t(batch) * p.H + head) * p.Sq + row] =
+            (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+template <int D>
+static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FlashParams& p,
+                      cudaStream_t stream) {
+  using L = FwdSmem<D>;
+  auto kern = flash_fwd_kernel<D>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  dim3 grid((p.Sq + 127) / 128, p.H, p.B);
+  kern<<<grid, 192, L::kTotal, stream>>>(tq, tk, tv, p);
+  return int(cudaGetLastError());
+}
+
+}  // namespace idrak
+
+using namespace idrak;
+
+// q: rows of (batch, position) with `q_row_stride` elements between positions and heads packed as
+// [H, D] inside a row; likewise k, v with Hkv heads. o: [B*Sq, o_row_stride] with heads packed [H, D].
+// lse: [B, H, Sq] fp32 (may be null). Pointers 16-byte aligned, strides multiples of 8 elements.
+IDRAK_API int idrak_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
+                              int Hkv, int Sq, int Skv, int D, long long q_row_stride, long long k_row_stride,
+                              long long v_row_stride, long long o_row_stride, long long q_batch_stride,
+                              long long k_batch_stride, long long v_batch_stride, float scale, int causal,
+                              void* stream_) {
+  if (D != 64 && D != 128) return -2;
+  if (H % Hkv) return -3;
+  FlashParams p;
+  p.O = static_cast<__nv_bfloat16*>(o);
+  p.o_row_stride = o_row_stride;
+  p.lse = lse;
+  p.B = B; p.H = H; p.Hkv = Hkv; p.Sq = Sq; p.Skv = Skv;
+  p.scale = scale;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  p.causal = causal;
+  p.st = status_device_ptr();
+  CUtensorMap tq, tk, tv;
+  if (make_head_map(&tq, q, D, Sq, H, B, q_row_stride, q_batch_stride)) return -10;
+  if (make_head_map(&tk, k, D, Skv, Hkv, B, k_row_stride, k_batch_stride)) return -11;
+  if (make_head_map(&tv, v, D, Skv, Hkv, B, v_row_stride, v_batch_stride)) return -12;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  return D == 64 ? launch_fwd<64>(tq, tk, tv, p, stream) : launch_fwd<128>(tq, tk, tv, p, stream);
+}

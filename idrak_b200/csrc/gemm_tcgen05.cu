@@ -1,0 +1,536 @@
+// Dense bf16/fp16 GEMM for sm_100a: C[M,N] = epilogue(A · B), fp32 accumulation in TMEM.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer   (cp.async.bulk.tensor into a 128B-swizzled shared-memory ring)
+//   warp 1      MMA issuer     (one thread issues tcgen05.mma; owns the TMEM allocation)
+//   warps 2..5  epilogue       (tcgen05.ld the fp32 accumulator, fuse bias / GELU / GELU' / residual /
+//                               accumulate, write bf16 or fp32)
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps the
+// main loop of tile i+1. Both operands may be K-major or MN-major in memory, which gives the four
+// BLAS transposition cases without a transposed copy:
+//   A K-major : A is [M,K] row-major          A MN-major : A is stored as [K,M] row-major
+//   B K-major : B is [N,K] row-major          B MN-major : B is stored as [K,N] row-major
+// (Linear forward = K/K, input gradient = K/MN, weight gradient = MN/MN.)
+// Split-K writes fp32 partials to a workspace and a second kernel sums them in split order, so the
+// result does not depend on scheduling.
+//
+// Covers the reference's tensor-core family gemm_tc_{nn,nt,tn,tt}_f32 and its bias / GELU / GELU-grad /
+// residual epilogues (src/Idrak.Gpu/Cuda/PtxKernels.TensorCore.cs:24-29,80-144) and the host dispatch
+// of CudaBackend.cs:1306-1471.
+#include "common.cuh"
+
+namespace idrak {
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;          // 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;
+constexpr int kGemmThreads = 192;
+constexpr int kGroupM = 16;      // raster: 16 row-tiles share the resident column tiles in L2
+
+enum GemmAct : int { kActNone = 0, kActGelu = 1, kActGeluGrad = 2 };
+
+struct GemmParams {
+  int M, N, K;
+  void* C;              // bf16 or fp32 [M, ldc]
+  int ldc;
+  int c_fp32;
+  const __nv_bfloat16* bias;      // [N] or null
+  const __nv_bfloat16* residual;  // [M, ldr] or null
+  int ldr;
+  int act;                        // GemmAct
+  __nv_bfloat16* aux;             // kActGelu: pre-activation out; kActGeluGrad: pre-activation in. [M, ld_aux]
+  int ld_aux;
+  int beta;                       // 1: add the old contents of C
+  float alpha;                    // scale on the accumulator
+  int splits;                     // split-K factor (1 = direct epilogue)
+  float* workspace;               // [splits, M, N] fp32 when splits > 1
+  int m_tiles, n_tiles;
+  Status* st;
+};
+
+// Epilogue on 8 consecutive columns of one row. `v` holds alpha-scaled accumulators on entry.
+__device__ __forceinline__ void epilogue8(const GemmParams& p, int row, int col, float (&v)[8], int nvalid) {
+  const bool vec = (nvalid == 8);
+  if (p.bias) {
+    if (vec && ((reinterpret_cast<uintptr_t>(p.bias + col) & 15) == 0)) {
+      uint4 b = __ldg(reinterpret_cast<const uint4*>(p.bias + col));
+      float2 f;
+      f = unpack_bf16x2(b.x); v[0] += f.x; v[1] += f.y;
+      f = unpack_bf16x2(b.y); v[2] += f.x; v[3] += f.y;
+      f = unpack_bf16x2(b.z); v[4] += f.x; v[5] += f.y;
+      f = unpack_bf16x2(b.w); v[6] += f.x; v[7] += f.y;
+    } else {
+      for (int i = 0; i < nvalid; ++i) v[i] += __bfloat162float(p.bias[col + i]);
+    }
+  }
+  if (p.act != kActNone) {
+    __nv_bfloat16* ax = p.aux + size_t(row) * p.ld_aux + col;
+    const bool axvec = vec && ((reinterpret_cast<uintptr_t>(ax) & 15) == 0);
+    if (p.act == kActGelu) {
+      if (axvec) {
+        uint4 o;
+        o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+        o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+        *reinterpret_cast<uint4*>(ax) = o;
+      } else {
+        for (int i = 0; i < nvalid; ++i) ax[i] = __float2bfloat16(v[i]);
+      }
+      // the activation sees the value as it was stored (bf16), so forward and backward agree
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
+    } else {
+      float x[8];
+      if (axvec) {
+        uint4 a = *reinterpret_cast<const uint4*>(ax);
+        float2 f;
+        f = unpack_bf16x2(a.x); x[0] = f.x; x[1] = f.y;
+        f = unpack_bf16x2(a.y); x[2] = f.x; x[3] = f.y;
+        f = unpack_bf16x2(a.z); x[4] = f.x; x[5] = f.y;
+        f = unpack_bf16x2(a.w); x[6] = f.x; x[7] = f.y;
+      } else {
+        for (int i = 0; i < 8; ++i) x[i] = i < nvalid ? __bfloat162float(ax[i]) : 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] *= gelu_tanh_grad(x[i]);
+    }
+  }
+  if (p.residual) {
+    const __nv_bfloat16* r = p.residual + size_t(row) * p.ldr + col;
+    if (vec && ((reinterpret_cast<uintptr_t>(r) & 15) == 0)) {
+      uint4 a = *reinterpret_cast<const uint4*>(r);
+      float2 f;
+      f = unpack_bf16x2(a.x); v[0] += f.x; v[1] += f.y;
+      f = unpack_bf16x2(a.y); v[2] += f.x; v[3] += f.y;
+      f = unpack_bf16x2(a.z); v[4] += f.x; v[5] += f.y;
+      f = unpack_bf16x2(a.w); v[6] += f.x; v[7] += f.y;
+    } else {
+      for (int i = 0; i < nvalid; ++i) v[i] += __bfloat162float(r[i]);
+    }
+  }
+  if (p.c_fp32) {
+    float* c = reinterpret_cast<float*>(p.C) + size_t(row) * p.ldc + col;
+    if (vec && ((reinterpret_cast<uintptr_t>(c) & 15) == 0)) {
+      float4* c4 = reinterpret_cast<float4*>(c);
+      if (p.beta) {
+        float4 o0 = c4[0], o1 = c4[1];
+        v[0] += o0.x; v[1] += o0.y; v[2] += o0.z; v[3] += o0.w;
+        v[4] += o1.x; v[5] += o1.y; v[6] += o1.z; v[7] += o1.w;
+      }
+      c4[0] = make_float4(v[0], v[1], v[2], v[3]);
+      c4[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+      for (int i = 0; i < nvalid; ++i) c[i] = p.beta ? c[i] + v[i] : v[i];
+    }
+  } else {
+    __nv_bfloat16* c = reinterpret_cast<__nv_bfloat16*>(p.C) + size_t(row) * p.ldc + col;
+    if (vec && ((reinterpret_cast<uintptr_t>(c) & 15) == 0)) {
+      if (p.beta) {
+        uint4 a = *reinterpret_cast<const uint4*>(c);
+        float2 f;
+        f = unpack_bf16x2(a.x); v[0] += f.x; v[1] += f.y;
+        f = unpack_bf16x2(a.y); v[2] += f.x; v[3] += f.y;
+        f = unpack_bf16x2(a.z); v[4] += f.x; v[5] += f.y;
+        f = unpack_bf16x2(a.w); v[6] += f.x; v[7] += f.y;
+      }
+      uint4 o;
+      o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+      o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(c) = o;
+    } else {
+      for (int i = 0; i < nvalid; ++i) {
+        float o = v[i] + (p.beta ? __bfloat162float(c[i]) : 0.f);
+        c[i] = __float2bfloat16(o);
+      }
+    }
+  }
+}
+
+__device__ __forceinline__ void unit_to_tile(const GemmParams& p, int unit, int& tm, int& tn, int& split) {
+  const int tiles = p.m_tiles * p.n_tiles;
+  split = unit / tiles;
+  int t = unit - split * tiles;
+  const int per_group = kGroupM * p.n_tiles;
+  int group = t / per_group;
+  int first_m = group * kGroupM;
+  int gsz = min(p.m_tiles - first_m, kGroupM);
+  int r = t - group * per_group;
+  tm = first_m + (r % gsz);
+  tn = r / gsz;
+}
+
+template <int BN>
+struct GemmSmem {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+};
+
+template <int BN, int A_MN, int B_MN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+  using L = GemmSmem<BN>;
+  constexpr int kStages = L::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* bar_base = smem + kStages * L::kStageBytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);
+  uint64_t* empty = full + kStages;
+  uint64_t* tmem_full = empty + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int k_blocks_total = (p.K + kBK - 1) / kBK;
+  const int kb_per_split = (k_blocks_total + p.splits - 1) / p.splits;
+  const int units = p.m_tiles * p.n_tiles * p.splits;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&tmem_full[b], 1);
+      mbar_init(&tmem_empty[b], 128);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 2 * BN);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tmA);
+      tma_prefetch_desc(&tmB);
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t issued_mask = 0, issued_phase = 0;   // which stages have a copy in flight and on which parity
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        int tm, tn, split;
+        unit_to_tile(p, unit, tm, tn, split);
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(k_blocks_total, kb0 + kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (1u << 16) | stage)) {
+            ok = false;
+            break;
+          }
+          uint8_t* sa = smem + stage * L::kStageBytes;
+          uint8_t* sb = sa + L::kABytes;
+          mbar_expect_tx(&full[stage], L::kStageBytes);
+          if (A_MN) {
+#pragma unroll
+            for (int j = 0; j < kBM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full[stage], tm * kBM + j * 64, kb * kBK);
+          } else {
+            tma_load_2d(sa, &tmA, &full[stage], kb * kBK, tm * kBM);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[stage], tn * BN + j * 64, kb * kBK);
+          } else {
+            tma_load_2d(sb, &tmB, &full[stage], kb * kBK, tn * BN);
+          }
+          issued_mask |= 1u << stage;
+          issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // give up: let the copies already issued land before the CTA's shared memory goes away
+        for (int s = 0; s < kStages; ++s) {
+          if (issued_mask & (1u << s)) {
+            uint32_t par = (issued_phase >> s) & 1u;
+            for (int i = 0; i < (1 << 20); ++i)
+              if (mbar_try_wait(&full[s], par)) break;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(kBM, BN, A_MN, B_MN, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++local) {
+        int tm, tn, split;
+        unit_to_tile(p, unit, tm, tn, split);
+        const int kb0 = split * kb_per_split;
+        const int kb1 = min(k_blocks_total, kb0 + kb_per_split);
+        const int buf = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1;
+        if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1, abort_flag, p.st, kTimeoutTmemEmpty, (1u << 16) | buf)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, p.st, kTimeoutSmemFull, (1u << 16) | stage)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
+          const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+          for (int kk = 0; kk < kBK / kUmmaK; ++kk) {
+            const uint64_t da = A_MN ? make_smem_desc_sw128(sa + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(sa + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc_sw128(sb + kk * 2048, 8192, 1024)
+                                     : make_smem_desc_sw128(sb + kk * 32, 16, 1024);
+            tc_mma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+          }
+          tc_commit(&empty[stage]);   // releases the stage once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(&tmem_full[buf]);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (4 warps, 128 rows)
+    const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const int row_in_tile = quarter * 32 + lane;
+    int local = 0;
+    bool ok = true;
+    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++local) {
+      int tm, tn, split;
+      unit_to_tile(p, unit, tm, tn, split);
+      const int buf = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1;
+      const int kb0 = split * kb_per_split;
+      const bool has_k = kb0 < k_blocks_total;   // a split past the end of K contributes zeros
+      if (!mbar_wait(&tmem_full[buf], acc_phase, abort_flag, p.st, kTimeoutTmemFull, (1u << 16) | buf)) {
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = tm * kBM + row_in_tile;
+      const int n0 = tn * BN;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        if (has_k) {
+          tmem_ld_32x32b_x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + c * 32, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) r[i] = 0u;
+        }
+        const int col0 = n0 + c * 32;
+        if (row < p.M && col0 < p.N) {
+          if (p.splits > 1) {
+            float* w = p.workspace + (size_t(split) * p.M + row) * p.N + col0;
+            if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(w) & 15) == 0)) {
+#pragma unroll
+              for (int i = 0; i < 8; ++i)
+                reinterpret_cast<float4*>(w)[i] =
+                    make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
+                                __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
+            } else {
+              for (int i = 0; i < 32 && col0 + i < p.N; ++i) w[i] = __uint_as_float(r[i]);
+            }
+          } else {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = col0 + g * 8;
+              if (col < p.N) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * p.alpha;
+                epilogue8(p, row, col, v, min(8, p.N - col));
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(&tmem_empty[buf]);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// Sum split-K partials in split order and run the fused epilogue. One thread per 8 columns.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) {
+  const int groups_per_row = (p.N + 7) / 8;
+  const long long total = (long long)p.M * groups_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const int row = int(i / groups_per_row);
+    const int col = int(i - (long long)row * groups_per_row) * 8;
+    const int nvalid = min(8, p.N - col);
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.f;
+    for (int s = 0; s < p.splits; ++s) {
+      const float* w = p.workspace + (size_t(s) * p.M + row) * p.N + col;
+      if (nvalid == 8 && ((reinterpret_cast<uintptr_t>(w) & 15) == 0)) {
+        float4 a = reinterpret_cast<const float4*>(w)[0], b = reinterpret_cast<const float4*>(w)[1];
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+        v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+      } else {
+        for (int j = 0; j < nvalid; ++j) v[j] += w[j];
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= p.alpha;
+    epilogue8(p, row, col, v, nvalid);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// host launcher
+// ---------------------------------------------------------------------------
+template <int BN, int A_MN, int B_MN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
+                       cudaStream_t stream) {
+  using L = GemmSmem<BN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
+    if (e != cudaSuccess) return int(e);
+    configured = true;
+  }
+  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, p);
+  return int(cudaGetLastError());
+}
+
+static int make_operand_map(CUtensorMap* tm, const void* ptr, int mn_extent, int k_extent, int ld, int mn_major,
+                            int box_mn, int fp16) {
+  // K-major : memory [mn_extent rows][k_extent contiguous], row stride ld   -> box {64 k, box_mn rows}
+  // MN-major: memory [k_extent rows][mn_extent contiguous], row stride ld   -> box {64 mn, 64 k rows}
+  uint64_t dims[2], strides[1];
+  uint32_t box[2];
+  if (mn_major) {
+    dims[0] = uint64_t(mn_extent);
+    dims[1] = uint64_t(k_extent);
+    box[0] = 64;
+    box[1] = kBK;
+  } else {
+    dims[0] = uint64_t(k_extent);
+    dims[1] = uint64_t(mn_extent);
+    box[0] = kBK;
+    box[1] = uint32_t(box_mn);
+  }
+  strides[0] = uint64_t(ld) * 2;
+  return encode_tensor_map(tm, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                           const_cast<void*>(ptr), dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace idrak
+
+using namespace idrak;
+
+// Number of fp32 workspace elements a call with these sizes needs (0 when it will not split K).
+IDRAK_API long long idrak_gemm_workspace_elems(int M, int N, int K, int splits) {
+  if (splits <= 1) return 0;
+  return (long long)splits * M * N;
+}
+
+// Pick a split-K factor so a small output still fills the machine. Deterministic in (M, N, K, sms).
+IDRAK_API int idrak_gemm_pick_splits(int M, int N, int K, int bn) {
+  const int sms = sm_count();
+  const int tiles = ((M + kBM - 1) / kBM) * ((N + bn - 1) / bn);
+  const int kblocks = (K + kBK - 1) / kBK;
+  if (tiles * 2 > sms || kblocks < 16) return 1;
+  int s = sms / tiles;
+  s = max(1, min(s, kblocks / 8));
+  return min(s, 16);
+}
+
+// C = epilogue(alpha * op(A) op(B)).
+//   a_mn = 0: A is [M,K] row-major (lda >= K); a_mn = 1: A is stored [K,M] row-major (lda >= M)
+//   b_mn = 0: B is [N,K] row-major (ldb >= K); b_mn = 1: B is stored [K,N] row-major (ldb >= N)
+// Leading dimensions are in elements and must be multiples of 8 for A and B (TMA strides are 16-byte
+// multiples). C, aux and residual may have any leading dimension; unaligned rows take a scalar path.
+// Returns 0, a cudaError, or a negative argument error.
+IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc,
+                              int c_fp32, int M, int N, int K, const void* bias, const void* residual, int ldr,
+                              int act, void* aux, int ld_aux, int beta, float alpha, int splits, float* workspace,
+                              int fp16, void* stream_) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7)) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  if (act != kActNone && aux == nullptr) return -4;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int bn = (N <= 128) ? 128 : 256;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.act = act;
+  p.aux = static_cast<__nv_bfloat16*>(aux);
+  p.ld_aux = ld_aux;
+  p.beta = beta;
+  p.alpha = alpha;
+  p.splits = (splits > 1 && workspace) ? splits : 1;
+  {
+    // every split must own at least one k-block
+    const int kblocks = (K + kBK - 1) / kBK;
+    if (p.splits > kblocks) p.splits = kblocks;
+    const int per = (kblocks + p.splits - 1) / p.splits;
+    p.splits = (kblocks + per - 1) / per;
+  }
+  p.workspace = workspace;
+  p.m_tiles = (M + kBM - 1) / kBM;
+  p.n_tiles = (N + bn - 1) / bn;
+  p.st = status_device_ptr();
+
+  CUtensorMap tmA, tmB;
+  int e = make_operand_map(&tmA, A, M, K, lda, a_mn, kBM, fp16);
+  if (e) return -10 - (e > 0 ? 0 : 1);
+  e = make_operand_map(&tmB, B, N, K, ldb, b_mn, bn, fp16);
+  if (e) return -12;
+
+  const int units = p.m_tiles * p.n_tiles * p.splits;
+  const int grid = min(units, sm_count());
+  int rc;
+#define IDRAK_GEMM_CASE(BN_, AM_, BM_) rc = launch_gemm<BN_, AM_, BM_>(tmA, tmB, p, grid, stream)
+  if (bn == 256) {
+    if (!a_mn && !b_mn) IDRAK_GEMM_CASE(256, 0, 0);
+    else if (!a_mn && b_mn) IDRAK_GEMM_CASE(256, 0, 1);
+    else if (a_mn && !b_mn) IDRAK_GEMM_CASE(256, 1, 0);
+    else IDRAK_GEMM_CASE(256, 1, 1);
+  } else {
+    if (!a_mn && !b_mn) IDRAK_GEMM_CASE(128, 0, 0);
+    else if (!a_mn && b_mn) IDRAK_GEMM_CASE(128, 0, 1);
+    else if (a_mn && !b_mn) IDRAK_GEMM_CASE(128, 1, 0);
+    else IDRAK_GEMM_CASE(128, 1, 1);
+  }
+#undef IDRAK_GEMM_CASE
+  if (rc) return rc;
+  if (p.splits > 1) {
+    const long long groups = (long long)M * ((N + 7) / 8);
+    long long want = (groups + 255) / 256, cap = (long long)sm_count() * 8;
+    int blocks = int(want < cap ? want : cap);
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p);
+    rc = int(cudaGetLastError());
+  }
+  return rc;
+}

@@ -1,0 +1,105 @@
+"""Flash attention (training / prefill) on the tcgen05 kernels, with a plain PyTorch reference.
+
+Tensors are ``[batch, seq, heads, head_dim]`` views; the last dim must be contiguous and the head dim
+stride must equal ``head_dim`` (heads packed inside a row), which is what a fused QKV projection
+produces — so q, k, v may be slices of one ``[B, S, 3*H*D]`` buffer and no copy is made.
+
+Reference: Tensor.CausalAttention (src/Idrak.Abstraction/Tensors/Tensor.Decoding.cs:132),
+flash_tc_{fwd,bwd_q,bwd_kv,delta} (src/Idrak.Gpu/Cuda/PtxKernels.FlashTensorCore.cs).
+"""
+from __future__ import annotations
+
+import math
+
+import torch
+
+from .. import _native
+from ._util import ptr, stream_ptr
+
+
+def attention_reference(q, k, v, causal=True, scale=None):
+    """fp32 softmax(QK^T)V with grouped heads. q: [B,Sq,H,D], k/v: [B,Skv,Hkv,D]."""
+    B, Sq, H, D = q.shape
+    Skv, Hkv = k.shape[1], k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(H // Hkv, dim=1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(H // Hkv, dim=1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if causal:
+        off = Skv - Sq
+        i = torch.arange(Sq, device=q.device)[:, None]
+        j = torch.arange(Skv, device=q.device)[None, :]
+        s = s.masked_fill(j > i + off, float("-inf"))
+    p = torch.softmax(s, dim=-1)
+    o = torch.matmul(p, vf)
+    return o.permute(0, 2, 1, 3).to(q.dtype)
+
+
+def _check_layout(t: torch.Tensor, name: str):
+    B, S, H, D = t.shape
+    assert t.dtype == torch.bfloat16, f"{name}: bf16 required"
+    assert t.stride(3) == 1 and t.stride(2) == D, f"{name}: heads must be packed [H, D] inside a row"
+    assert t.stride(1) % 8 == 0 and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0, f"{name}: alignment"
+
+
+def flash_forward(q, k, v, causal=True, scale=None):
+    """Returns (out [B,Sq,H,D] contiguous, lse [B,H,Sq] fp32)."""
+    B, Sq, H, D = q.shape
+    Skv, Hkv = k.shape[1], k.shape[2]
+    for t, n in ((q, "q"), (k, "k"), (v, "v")):
+        _check_layout(t, n)
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    out = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+    lse = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    rc = _native.lib().idrak_flash_fwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), B, H, Hkv, Sq, Skv, D,
+        q.stride(1), k.stride(1), v.stride(1), H * D, q.stride(0), k.stride(0), v.stride(0),
+        float(scale), int(causal), stream_ptr())
+    _native.check(rc, "idrak_flash_fwd")
+    return out, lse
+
+
+def flash_backward(dout, q, k, v, out, lse, causal=True, scale=None):
+    """Returns (dq, dk, dv) shaped like q, k, v (contiguous)."""
+    B, Sq, H, D = q.shape
+    Skv, Hkv = k.shape[1], k.shape[2]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    lib = _native.lib()
+    dout = dout.contiguous()
+    delta = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
+    dq = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+    dk = torch.empty((B, Skv, Hkv, D), dtype=q.dtype, device=q.device)
+    dv = torch.empty((B, Skv, Hkv, D), dtype=q.dtype, device=q.device)
+    rc = lib.idrak_flash_bwd(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
+        delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H, Hkv, Sq, Skv, D,
+        q.stride(1), k.stride(1), v.stride(1), q.stride(0), k.stride(0), v.stride(0),
+        float(scale), int(causal), stream_ptr())
+    _native.check(rc, "idrak_flash_bwd")
+    return dq, dk, dv
+
+
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, causal, scale):
+        out, lse = flash_forward(q, k, v, causal, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.causal, ctx.scale = causal, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = flash_backward(dout, q, k, v, out, lse, ctx.causal, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def attention(q, k, v, causal: bool = True, scale: float | None = None) -> torch.Tensor:
+    """Scaled dot-product attention; q [B,Sq,H,D], k/v [B,Skv,Hkv,D]; returns [B,Sq,H,D]."""
+    D = q.shape[-1]
+    if q.is_cuda and q.dtype == torch.bfloat16 and D in (64, 128):
+        return _FlashAttention.apply(q, k, v, causal, scale)
+    if q.is_cuda:
+        raise NotImplementedError(f"attention on CUDA needs bf16 and head_dim 64 or 128 (got {q.dtype}, {D})")
+    return attention_reference(q, k, v, causal, scale)

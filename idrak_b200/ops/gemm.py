@@ -1,0 +1,162 @@
+"""Dense GEMM on the tcgen05 kernel, and the ``Linear`` autograd function built on it.
+
+``gemm`` exposes the kernel's full contract (operand majors, fused epilogue, split-K).
+``linear`` is the layer-level entry: ``y = act(x @ W^T + b) (+ residual)`` with a backward pass that
+runs the input gradient (K-major x MN-major) and the weight gradient (MN-major x MN-major, split-K) on
+the same kernel, so no transposed copy of an activation or a weight is ever made.
+
+On CPU tensors the same functions compute in plain PyTorch (fp32 for config-1-style CPU runs and as
+the oracle the GPU tests compare against).
+
+Reference: Tensor.MatMul (src/Idrak.Abstraction/Tensors/Tensor.Advanced.cs:31), Linear.ForwardCore
+(src/Idrak/Layers/Linear.cs:165), GEMM dispatch (src/Idrak.Gpu/Cuda/CudaBackend.cs:1306-1471).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import _native
+from ._util import ptr, scratch, stream_ptr
+
+ACT_NONE, ACT_GELU, ACT_GELU_GRAD = 0, 1, 2
+_ACT_IDS = {None: ACT_NONE, "none": ACT_NONE, "gelu": ACT_GELU, "gelu_grad": ACT_GELU_GRAD}
+
+
+def _gelu_tanh(x: torch.Tensor) -> torch.Tensor:
+    return torch.nn.functional.gelu(x, approximate="tanh")
+
+
+def _gelu_tanh_grad(x: torch.Tensor) -> torch.Tensor:
+    k0, k1 = 0.7978845608028654, 0.044715
+    u = k0 * (x + k1 * x ** 3)
+    t = torch.tanh(u)
+    return 0.5 * (1 + t) + 0.5 * x * (1 - t * t) * k0 * (1 + 3 * k1 * x * x)
+
+
+def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, residual=None, act=None, aux=None,
+                   out=None, beta=False, alpha=1.0, out_dtype=None):
+    """Plain PyTorch statement of the kernel's contract (fp32 math)."""
+    A = a.float().t() if a_mn else a.float()          # [M, K]
+    Bt = b.float() if b_mn else b.float().t()         # [K, N]
+    v = (A @ Bt) * alpha
+    if bias is not None:
+        v = v + bias.float()
+    aux_out = None
+    if _ACT_IDS[act] == ACT_GELU:
+        aux_out = v.to(a.dtype)
+        v = _gelu_tanh(aux_out.float())
+    elif _ACT_IDS[act] == ACT_GELU_GRAD:
+        v = v * _gelu_tanh_grad(aux.float())
+    if residual is not None:
+        v = v + residual.float()
+    dtype = out_dtype or (out.dtype if out is not None else a.dtype)
+    if out is not None:
+        if beta:
+            v = v + out.float()
+        out.copy_(v.to(dtype))
+        res = out
+    else:
+        res = v.to(dtype)
+    return (res, aux_out) if _ACT_IDS[act] == ACT_GELU else res
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
+         bias: torch.Tensor | None = None, residual: torch.Tensor | None = None, act: str | None = None,
+         aux: torch.Tensor | None = None, out: torch.Tensor | None = None, beta: bool = False,
+         alpha: float = 1.0, out_dtype: torch.dtype | None = None, splits: int | None = None):
+    """``C = epilogue(alpha * op(A) @ op(B))``.
+
+    ``a``: ``[M, K]`` (``a_mn=False``) or stored ``[K, M]`` (``a_mn=True``).
+    ``b``: ``[N, K]`` (``b_mn=False``, the ``nn.Linear`` weight layout) or stored ``[K, N]`` (``b_mn=True``).
+    ``act='gelu'`` returns ``(C, pre_activation)``; ``act='gelu_grad'`` multiplies by ``gelu'(aux)``.
+    ``beta=True`` accumulates into ``out``. ``splits=None`` lets the library choose a split-K factor.
+    """
+    if not a.is_cuda:
+        return gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, bias=bias, residual=residual, act=act, aux=aux,
+                              out=out, beta=beta, alpha=alpha, out_dtype=out_dtype)
+    assert a.dtype == b.dtype and a.dtype in (torch.bfloat16, torch.float16), (a.dtype, b.dtype)
+    assert a.dim() == 2 and b.dim() == 2
+    if a.stride(1) != 1:
+        a = a.contiguous()
+    if b.stride(1) != 1:
+        b = b.contiguous()
+    K, M = (a.shape if a_mn else (a.shape[1], a.shape[0]))
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    lib = _native.lib()
+    act_id = _ACT_IDS[act]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype or a.dtype, device=a.device)
+        assert not beta
+    assert out.stride(1) == 1 and out.shape == (M, N)
+    c_fp32 = 1 if out.dtype == torch.float32 else 0
+    assert c_fp32 or out.dtype == torch.bfloat16
+    aux_t = aux
+    if act_id == ACT_GELU and aux_t is None:
+        aux_t = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    bn = 128 if N <= 128 else 256
+    if splits is None:
+        splits = lib.idrak_gemm_pick_splits(M, N, K, bn)
+    ws = None
+    if splits > 1:
+        ws = scratch("gemm_splitk", splits * M * N, torch.float32, a.device)
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and residual.stride(1) == 1
+    rc = lib.idrak_gemm_bf16(
+        a.data_ptr(), a.stride(0), int(a_mn), b.data_ptr(), b.stride(0), int(b_mn),
+        out.data_ptr(), out.stride(0), c_fp32, M, N, K,
+        ptr(bias), ptr(residual), residual.stride(0) if residual is not None else 0,
+        act_id, ptr(aux_t), aux_t.stride(0) if aux_t is not None else 0,
+        int(beta), float(alpha), int(splits), ptr(ws), 1 if a.dtype == torch.float16 else 0, stream_ptr())
+    _native.check(rc, "idrak_gemm_bf16")
+    return (out, aux_t) if act_id == ACT_GELU else out
+
+
+class _Linear(torch.autograd.Function):
+    """y = x @ W^T (+ b) (+ residual); W is [out, in] as in ``nn.Linear``."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        r2 = residual.reshape(-1, weight.shape[0]) if residual is not None else None
+        y = gemm(x2, weight, bias=bias, residual=r2)
+        ctx.save_for_backward(x2, weight)
+        ctx.has_bias = bias is not None
+        ctx.has_res = residual is not None
+        return y.reshape(*shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight = ctx.saved_tensors
+        dy2 = dy.reshape(-1, weight.shape[0])
+        if dy2.stride(1) != 1 or dy2.stride(0) != dy2.shape[1]:
+            dy2 = dy2.contiguous()
+        dx = dw = db = dres = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, weight, b_mn=True).reshape(*dy.shape[:-1], weight.shape[1])
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            from .rowops import colsum
+            db = colsum(dy2)
+        if ctx.has_res and ctx.needs_input_grad[3]:
+            dres = dy
+        return dx, dw, db, dres
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = None,
+           residual: torch.Tensor | None = None) -> torch.Tensor:
+    if not x.is_cuda:
+        y = torch.nn.functional.linear(x, weight, bias)
+        return y + residual if residual is not None else y
+    return _Linear.apply(x, weight, bias, residual)

@@ -1,0 +1,79 @@
+"""tcgen05 GEMM against a plain PyTorch fp32 statement of the same contract."""
+import pytest
+import torch
+
+from idrak_b200.ops import gemm, gemm_reference, linear
+
+pytestmark = pytest.mark.gpu
+
+
+def _rand(shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return (torch.randn(shape, generator=g, device="cuda") * scale).to(torch.bfloat16)
+
+
+def _check(out, ref, tol=2e-2):
+    out, ref = out.float(), ref.float()
+    err = (out - ref).abs().max().item()
+    denom = ref.abs().max().item() + 1e-6
+    assert err / denom < tol, f"max err {err} vs scale {denom}"
+
+
+SHAPES = [(128, 256, 64), (256, 512, 128), (384, 768, 768), (1024, 2304, 768), (200, 136, 72), (64, 64, 64),
+          (130, 100, 1000), (4096, 768, 3072), (128, 50304, 768)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+def test_gemm_majors(M, N, K, a_mn, b_mn):
+    if (a_mn and M % 8) or (b_mn and N % 8) or K % 8:
+        pytest.skip("leading dimension must be a multiple of 8")
+    a = _rand((K, M) if a_mn else (M, K), 1.0, 1)
+    b = _rand((K, N) if b_mn else (N, K), 1.0, 2)
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, splits=1)
+    ref = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    _check(out, ref)
+
+
+@pytest.mark.parametrize("splits", [2, 3, 8])
+def test_gemm_splitk_matches_and_is_deterministic(splits):
+    M, N, K = 768, 768, 4096
+    a, b = _rand((K, M), 1.0, 3), _rand((K, N), 1.0, 4)
+    ref = gemm_reference(a, b, a_mn=True, b_mn=True, out_dtype=torch.float32)
+    o1 = gemm(a, b, a_mn=True, b_mn=True, splits=splits, out_dtype=torch.float32)
+    o2 = gemm(a, b, a_mn=True, b_mn=True, splits=splits, out_dtype=torch.float32)
+    _check(o1, ref, 5e-3)
+    assert torch.equal(o1, o2)
+
+
+def test_gemm_epilogues():
+    M, N, K = 512, 1024, 256
+    a, b = _rand((M, K), 1.0, 5), _rand((N, K), 0.1, 6)
+    bias, res = _rand((N,), 1.0, 7), _rand((M, N), 1.0, 8)
+    out = gemm(a, b, bias=bias, residual=res)
+    _check(out, gemm_reference(a, b, bias=bias, residual=res, out_dtype=torch.float32))
+    out, pre = gemm(a, b, bias=bias, act="gelu")
+    ref, ref_pre = gemm_reference(a, b, bias=bias, act="gelu", out_dtype=torch.float32)
+    _check(pre, ref_pre)
+    _check(out, ref)
+    g = gemm(a, b, act="gelu_grad", aux=pre)
+    _check(g, gemm_reference(a, b, act="gelu_grad", aux=pre, out_dtype=torch.float32))
+    acc = torch.ones((M, N), dtype=torch.float32, device="cuda")
+    gemm(a, b, out=acc, beta=True, alpha=0.5)
+    _check(acc, gemm_reference(a, b, alpha=0.5, out_dtype=torch.float32) + 1.0)
+
+
+def test_linear_autograd_matches_torch():
+    x = _rand((4, 96, 256), 1.0, 9).requires_grad_()
+    w = _rand((384, 256), 0.05, 10).requires_grad_()
+    b = _rand((384,), 0.1, 11).requires_grad_()
+    y = linear(x, w, b)
+    dy = _rand(y.shape, 1.0, 12)
+    y.backward(dy)
+    xr, wr, br = (t.detach().float().requires_grad_() for t in (x, w, b))
+    yr = torch.nn.functional.linear(xr, wr, br)
+    yr.backward(dy.float())
+    _check(y, yr)
+    _check(x.grad, xr.grad)
+    _check(w.grad, wr.grad)
+    _check(b.grad, br.grad)
