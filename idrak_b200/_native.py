@@ -35,6 +35,7 @@ _SIGNATURES = {
     "idrak_status_take": (c_int, [C.POINTER(C.c_uint32)]),
     "idrak_sm_count": (c_int, []),
     "idrak_last_error": (C.c_char_p, []),
+    "idrak_launch_count": (c_ll, []),
     "idrak_build_info": (C.c_char_p, []),
     "idrak_gemm_workspace_elems": (c_ll, [c_int, c_int, c_int, c_int]),
     "idrak_gemm_pick_splits": (c_int, [c_int, c_int, c_int, c_int]),
@@ -69,7 +70,7 @@ _SIGNATURES = {
     "idrak_opt_adamw": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]),
     "idrak_opt_sgd": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_void_p]),
     "idrak_flash_fwd": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 7 + [c_float, c_int, c_void_p]),
-    "idrak_flash_bwd": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 6 + [c_float, c_int, c_void_p]),
+    "idrak_flash_bwd": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 9 + [c_float, c_int, c_void_p]),
 }
 
 

@@ -166,7 +166,9 @@ IDRAK_API int idrak_opt_grad_norm(const void* tensors, const void* chunks, int n
   if (n_chunks > 0)
     multi_sumsq_kernel<<<n_chunks, kOptThreads, 0, s>>>(static_cast<const OptTensor*>(tensors),
                                                         static_cast<const OptChunk*>(chunks), partial);
+    note_launches(1);
   clip_factor_kernel<<<1, 1024, 0, s>>>(partial, n_chunks, extra_sumsq, hyper);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 
@@ -175,6 +177,7 @@ IDRAK_API int idrak_opt_adamw(const void* tensors, const void* chunks, int n_chu
   if (n_chunks <= 0) return 0;
   multi_adamw_kernel<<<n_chunks, kOptThreads, 0, static_cast<cudaStream_t>(stream_)>>>(
       static_cast<const OptTensor*>(tensors), static_cast<const OptChunk*>(chunks), hyper, zero_grad);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 
@@ -183,5 +186,6 @@ IDRAK_API int idrak_opt_sgd(const void* tensors, const void* chunks, int n_chunk
   if (n_chunks <= 0) return 0;
   multi_sgd_kernel<<<n_chunks, kOptThreads, 0, static_cast<cudaStream_t>(stream_)>>>(
       static_cast<const OptTensor*>(tensors), static_cast<const OptChunk*>(chunks), hyper, momentum, zero_grad);
+  note_launches(1);
   return int(cudaGetLastError());
 }

@@ -332,4 +332,6 @@ int encode_tensor_map(CUtensorMap* out, CUtensorMapDataType dtype, int rank, voi
                       const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle);
 int sm_count();
 const char* last_error();
+// Every kernel launch made by this library is counted (read with idrak_launch_count()).
+void note_launches(int n);
 }  // namespace idrak

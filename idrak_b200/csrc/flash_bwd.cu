@@ -523,10 +523,12 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   }
   dim3 gq((p.Sq + 127) / 128, p.H, p.B);
   kq<<<gq, 192, BwdQSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  note_launches(1);
   int rc = int(cudaGetLastError());
   if (rc) return rc;
   dim3 gkv((p.Skv + 127) / 128, p.Hkv, p.B);
   kkv<<<gkv, 192, BwdKVSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 
@@ -534,12 +536,15 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
 
 using namespace idrak;
 
-// out / dout: contiguous [B, Sq, H, D]; dq [B,Sq,H,D], dk / dv [B,Skv,Hkv,D] contiguous; lse, delta [B,H,Sq].
+// out / dout: contiguous [B, Sq, H, D]; lse, delta [B,H,Sq]. dq / dk / dv rows hold heads packed [heads, D] with
+// the given row strides in elements (0 = contiguous), so they may be slices of one fused d(QKV) buffer;
+// their batch stride is rows * row stride.
 IDRAK_API int idrak_flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
                               const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int H, int Hkv,
                               int Sq, int Skv, int D, long long q_row_stride, long long k_row_stride,
                               long long v_row_stride, long long q_batch_stride, long long k_batch_stride,
-                              long long v_batch_stride, float scale, int causal, void* stream_) {
+                              long long v_batch_stride, long long dq_row_stride, long long dk_row_stride,
+                              long long dv_row_stride, float scale, int causal, void* stream_) {
   if (D != 64 && D != 128) return -2;
   if (H % Hkv) return -3;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
@@ -550,6 +555,7 @@ IDRAK_API int idrak_flash_bwd(const void* q, const void* k, const void* v, const
     flash_delta_kernel<<<unsigned(blocks), threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(out),
                                                                  static_cast<const __nv_bfloat16*>(dout), delta, B,
                                                                  Sq, H, D);
+    note_launches(1);
     int rc = int(cudaGetLastError());
     if (rc) return rc;
   }
@@ -566,9 +572,9 @@ IDRAK_API int idrak_flash_bwd(const void* q, const void* k, const void* v, const
   p.dQ = static_cast<__nv_bfloat16*>(dq);
   p.dK = static_cast<__nv_bfloat16*>(dk);
   p.dV = static_cast<__nv_bfloat16*>(dv);
-  p.dq_row_stride = (long long)H * D;
-  p.dk_row_stride = (long long)Hkv * D;
-  p.dv_row_stride = (long long)Hkv * D;
+  p.dq_row_stride = dq_row_stride > 0 ? dq_row_stride : (long long)H * D;
+  p.dk_row_stride = dk_row_stride > 0 ? dk_row_stride : (long long)Hkv * D;
+  p.dv_row_stride = dv_row_stride > 0 ? dv_row_stride : (long long)Hkv * D;
   CUtensorMap tq, tk, tv, tdo;
   if (make_head_map(&tq, q, D, Sq, H, B, q_row_stride, q_batch_stride)) return -10;
   if (make_head_map(&tk, k, D, Skv, Hkv, B, k_row_stride, k_batch_stride)) return -11;

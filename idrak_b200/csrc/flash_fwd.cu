@@ -309,6 +309,7 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
   }
   dim3 grid((p.Sq + 127) / 128, p.H, p.B);
   kern<<<grid, 192, L::kTotal, stream>>>(tq, tk, tv, p);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 

@@ -416,6 +416,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     configured = true;
   }
   kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, p);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 
@@ -530,6 +531,7 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
     long long want = (groups + 255) / 256, cap = (long long)sm_count() * 8;
     int blocks = int(want < cap ? want : cap);
     splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p);
+    note_launches(1);
     rc = int(cudaGetLastError());
   }
   return rc;

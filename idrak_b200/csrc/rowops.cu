@@ -520,6 +520,7 @@ IDRAK_API int idrak_norm_fwd(const void* x, const void* residual, const void* w,
   else if (nvec <= 32 * 16) NF(16);
   else NF(32);
 #undef NF
+  note_launches(1);
   return int(cudaGetLastError());
 }
 
@@ -543,10 +544,13 @@ IDRAK_API int idrak_norm_bwd(const void* dy, const void* x, const void* w, const
   else if (nvec <= 128 * 4) NB(4);
   else NB(8);
 #undef NB
+  note_launches(1);
   int rc = int(cudaGetLastError());
   if (rc) return rc;
   colsum_final_kernel<<<(C + 255) / 256, 256, 0, s>>>(dw_part, blocks, C, dw, grads_fp32, accumulate);
+  note_launches(1);
   if (!rms && db) colsum_final_kernel<<<(C + 255) / 256, 256, 0, s>>>(db_part, blocks, C, db, grads_fp32, accumulate);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 
@@ -563,25 +567,30 @@ IDRAK_API int idrak_colsum(const void* x, int rows, int C, int ld, float* part, 
   const int rpb = (rows + yb - 1) / yb;
   dim3 grid((C + 63) / 64, yb);
   colsum_part_kernel<<<grid, 256, 0, s>>>(CBF(x), rows, C, ld, rpb, part);
+  note_launches(1);
   colsum_final_kernel<<<(C + 255) / 256, 256, 0, s>>>(part, yb, C, out, out_fp32, accumulate);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 
 IDRAK_API int idrak_gelu_fwd(const void* x, void* y, long long n, void* stream_) {
   if (n % 8) return -2;
   gelu_fwd_kernel<<<grid_for(n / 8, 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(CBF(x), BF(y), n / 8);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_gelu_bwd(const void* x, const void* dy, void* dx, long long n, void* stream_) {
   if (n % 8) return -2;
   gelu_bwd_kernel<<<grid_for(n / 8, 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(CBF(x), CBF(dy), BF(dx),
                                                                                        n / 8);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_gated_fwd(const void* gu, void* out, int rows, int H, int kind, void* stream_) {
   if (H % 8) return -2;
   gated_fwd_kernel<<<grid_for(size_t(rows) * (H / 8), 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
       CBF(gu), BF(out), rows, H, kind);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_gated_bwd(const void* gu, const void* dout, void* dgu, int rows, int H, int kind,
@@ -589,19 +598,23 @@ IDRAK_API int idrak_gated_bwd(const void* gu, const void* dout, void* dgu, int r
   if (H % 8) return -2;
   gated_bwd_kernel<<<grid_for(size_t(rows) * (H / 8), 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
       CBF(gu), CBF(dout), BF(dgu), rows, H, kind);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_add(const void* a, const void* b, void* y, long long n, void* stream_) {
   if (n % 8) return -2;
   add_kernel<<<grid_for(n / 8, 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(CBF(a), CBF(b), BF(y), n / 8);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_f32_to_bf16(const float* x, void* y, long long n, void* stream_) {
   f32_to_bf16_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(x, BF(y), n);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_bf16_to_f32(const void* x, float* y, long long n, void* stream_) {
   bf16_to_f32_kernel<<<grid_for((n + 3) / 4, 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(CBF(x), y, n);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_rope(void* x, const int* positions, int tokens, int heads, int D, int row_stride, int rot_dim,
@@ -610,6 +623,7 @@ IDRAK_API int idrak_rope(void* x, const int* positions, int tokens, int heads, i
   rope_kernel<<<grid_for(size_t(tokens) * heads * (rot_dim / 2), 256), 256, 0,
                 static_cast<cudaStream_t>(stream_)>>>(BF(x), positions, tokens, heads, D, row_stride, rot_dim, theta,
                                                      freq_scale, inverse);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_embedding_fwd(const int* ids, const void* wte, const void* wpe, void* out, int tokens, int seq,
@@ -617,6 +631,7 @@ IDRAK_API int idrak_embedding_fwd(const int* ids, const void* wte, const void* w
   if (C % 8) return -2;
   embedding_fwd_kernel<<<grid_for(size_t(tokens) * (C / 8), 256), 256, 0, static_cast<cudaStream_t>(stream_)>>>(
       ids, CBF(wte), CBF(wpe), BF(out), tokens, seq, C);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_wpe_bwd(const void* dout, void* dwpe, int batch, int seq, int C, int out_fp32, int accumulate,
@@ -624,6 +639,7 @@ IDRAK_API int idrak_wpe_bwd(const void* dout, void* dwpe, int batch, int seq, in
   if (C % 8) return -2;
   wpe_bwd_kernel<<<grid_for(size_t(seq) * (C / 8), 128), 128, 0, static_cast<cudaStream_t>(stream_)>>>(
       CBF(dout), dwpe, batch, seq, C, out_fp32, accumulate);
+  note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_wte_bwd(const int* sorted_ids, const int* order, const void* dout, void* dwte, int tokens, int C,
@@ -632,5 +648,6 @@ IDRAK_API int idrak_wte_bwd(const int* sorted_ids, const int* order, const void*
   int threads = C / 8 < 128 ? ((C / 8 + 31) / 32) * 32 : 128;
   wte_bwd_kernel<<<tokens, threads, 0, static_cast<cudaStream_t>(stream_)>>>(sorted_ids, order, CBF(dout), dwte,
                                                                             tokens, C, out_fp32);
+  note_launches(1);
   return int(cudaGetLastError());
 }

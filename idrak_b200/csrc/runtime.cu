@@ -8,6 +8,7 @@
 // compiled library still needs at run time remain.
 #include "common.cuh"
 #include <cudaTypedefs.h>
+#include <atomic>
 #include <mutex>
 #include <cstdio>
 #include <cstring>
@@ -89,6 +90,10 @@ int encode_tensor_map(CUtensorMap* out, CUtensorMapDataType dtype, int rank, voi
   return r == CUDA_SUCCESS ? 0 : int(r);
 }
 
+static std::atomic<long long> g_launches{0};
+void note_launches(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
+long long launches() { return g_launches.load(std::memory_order_relaxed); }
+
 int sm_count() {
   static int cached[16] = {0};
   int dev = 0;
@@ -130,6 +135,9 @@ IDRAK_API int idrak_status_take(uint32_t* out4) {
 IDRAK_API const char* idrak_last_error() { return idrak::last_error(); }
 
 IDRAK_API int idrak_sm_count() { return idrak::sm_count(); }
+
+// Kernels launched by this library in this process so far.
+IDRAK_API long long idrak_launch_count() { return idrak::launches(); }
 
 IDRAK_API const char* idrak_build_info() {
   return "idrak_b200 native kernels, sm_100a, built " __DATE__ " " __TIME__;

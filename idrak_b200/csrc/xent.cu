@@ -35,7 +35,7 @@ __global__ void __launch_bounds__(kXentThreads) xent_kernel(__nv_bfloat16* __res
   const int row = blockIdx.x;
   __nv_bfloat16* lrow = logits + size_t(row) * ld;
   const int target = targets[row];
-  const int nvec = (vocab + 7) >> 3;
+  const int nvec = ld >> 3;   // whole row stride: padding columns get gradient 0
   uint4 raw[NV];
   float mx = -INFINITY;
 #pragma unroll
@@ -102,8 +102,6 @@ __global__ void __launch_bounds__(kXentThreads) xent_kernel(__nv_bfloat16* __res
       *reinterpret_cast<uint4*>(lrow + vi * 8) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
-  // columns between the last full vector and the row stride stay as the GEMM wrote them only if they are
-  // past nvec*8; those in [vocab, nvec*8) were zeroed above.
 }
 
 // Rows too wide for registers: same arithmetic, the row is read from memory in each of the three passes
@@ -117,7 +115,7 @@ __global__ void __launch_bounds__(kXentThreads) xent_stream_kernel(__nv_bfloat16
   const int row = blockIdx.x;
   __nv_bfloat16* lrow = logits + size_t(row) * ld;
   const int target = targets[row];
-  const int nvec = (vocab + 7) >> 3;
+  const int nvec = ld >> 3;
   const float l2e = 1.4426950408889634f;
   float mx = -INFINITY;
   for (int vi = threadIdx.x; vi < nvec; vi += kXentThreads) {
@@ -193,12 +191,13 @@ using namespace idrak;
 IDRAK_API int idrak_softmax_xent(void* logits, const int* targets, float* losses, float* lse, int rows, int vocab,
                                  int ld, float scale, int ignore_index, int write_grad, void* stream_) {
   if (ld % 8 || ld < ((vocab + 7) / 8) * 8) return -2;
-  const int nvec = (vocab + 7) / 8;
+  const int nvec = ld / 8;
   const int nv = (nvec + kXentThreads - 1) / kXentThreads;
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   __nv_bfloat16* l = static_cast<__nv_bfloat16*>(logits);
   if (nv > kXentMaxVec) {
     xent_stream_kernel<<<rows, kXentThreads, 0, s>>>(l, targets, losses, lse, vocab, ld, scale, ignore_index, write_grad);
+    note_launches(1);
     return int(cudaGetLastError());
   }
 #define XE(V) xent_kernel<V><<<rows, kXentThreads, 0, s>>>(l, targets, losses, lse, vocab, ld, scale, ignore_index, write_grad)
@@ -213,10 +212,12 @@ IDRAK_API int idrak_softmax_xent(void* logits, const int* targets, float* losses
     default: XE(8); break;
   }
 #undef XE
+  note_launches(1);
   return int(cudaGetLastError());
 }
 
 IDRAK_API int idrak_sum_rows(const float* v, int n, float scale, float* out, void* stream_) {
   sum_rows_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream_)>>>(v, n, scale, out);
+  note_launches(1);
   return int(cudaGetLastError());
 }

@@ -1,0 +1,347 @@
+"""The decoder-only transformer every supported family is an instance of, built from a ``DecoderSpec``.
+
+Parameters are kept in the layout the kernels want: one packed QKV projection ``[(H + 2*Hkv)*D, dim]``,
+one packed gate/up projection ``[2*ff, dim]`` (``nn.Linear`` orientation, K-major for the GEMM), an
+embedding table padded to a multiple of 64 rows. ``checkpoint_names`` maps these to the reference's
+per-matrix names and ``[in, out]`` orientation for file I/O.
+
+Training forward on the GPU goes through the fused functions of ``idrak_b200.ops`` (bias / GELU /
+residual inside GEMM epilogues, RoPE in place, flash attention, chunked head + loss). The same module
+runs on the CPU in fp32 with plain PyTorch math.
+
+Reference: DecoderBuilder.Build (src/Idrak/Layers/DecoderBuilder.cs:23), CausalSelfAttention /
+FeedForward / DecoderBlock (src/Idrak/Layers/Decoder.cs:108,820,969), PositionEmbedding (:1251).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+from torch import nn
+
+from .. import ops
+from .spec import DecoderSpec
+
+
+class Norm(nn.Module):
+    def __init__(self, dim: int, kind: str, eps: float, offset: float = 0.0):
+        super().__init__()
+        self.kind, self.eps, self.offset = kind, eps, offset
+        self.weight = nn.Parameter(torch.ones(dim) if offset == 0.0 else torch.zeros(dim))
+        self.bias = nn.Parameter(torch.zeros(dim)) if kind == "layer" else None
+
+    def effective_weight(self):
+        return self.weight if self.offset == 0.0 else self.weight + self.offset
+
+    def forward(self, x):
+        w = self.effective_weight()
+        if self.kind == "layer":
+            return ops.layer_norm(x, w, self.bias, self.eps)
+        return ops.rms_norm(x, w, self.eps)
+
+
+class SelfAttention(nn.Module):
+    def __init__(self, spec: DecoderSpec, layer: int):
+        super().__init__()
+        self.spec, self.layer = spec, layer
+        H, Hkv, D, dim = spec.heads, spec.kv_heads, spec.head_dim, spec.dim
+        self.qkv_weight = nn.Parameter(torch.empty((H + 2 * Hkv) * D, dim))
+        self.qkv_bias = nn.Parameter(torch.zeros((H + 2 * Hkv) * D)) if spec.qkv_bias else None
+        self.o_weight = nn.Parameter(torch.empty(dim, H * D))
+        self.o_bias = nn.Parameter(torch.zeros(dim)) if spec.output_bias else None
+        if spec.qk_norm:
+            self.q_norm = Norm(D, "rms", spec.norm_epsilon, spec.norm_offset)
+            self.k_norm = Norm(D, "rms", spec.norm_epsilon, spec.norm_offset)
+        self.scale = spec.attention_scale if spec.attention_scale is not None else 1.0 / math.sqrt(D)
+        rope = spec.sliding_window_rope if (spec.is_windowed(layer) and spec.sliding_window_rope) else spec.rope
+        self.rope = rope
+
+    def forward(self, x, residual=None, positions=None):
+        spec = self.spec
+        H, Hkv, D = spec.heads, spec.kv_heads, spec.head_dim
+        qkv = ops.linear(x, self.qkv_weight, self.qkv_bias)
+        window = spec.sliding_window if spec.is_windowed(self.layer) else None
+        simple = not spec.qk_norm and window is None and spec.attention_softcap is None and (
+            self.rope is None or self.rope.scaling is None)
+        if simple:
+            theta = self.rope.theta if self.rope is not None else None
+            rdim = self.rope.rotary_dim if self.rope is not None else None
+            a = ops.qkv_attention(qkv, H, Hkv, D, True, self.scale, theta, rdim, 1.0, positions)
+        else:
+            a = self._general(qkv, positions, window)
+        return ops.linear(a, self.o_weight, self.o_bias, residual)
+
+    def _general(self, qkv, positions, window):
+        """qk-norm, scaled RoPE tables, sliding windows and soft-capping: composed from primitives."""
+        from ..ops.fused import _split_qkv
+        spec = self.spec
+        B, S, _ = qkv.shape
+        q, k, v = _split_qkv(qkv, spec.heads, spec.kv_heads, spec.head_dim)
+        if spec.qk_norm:
+            q, k = self.q_norm(q.contiguous()), self.k_norm(k.contiguous())
+        if self.rope is not None:
+            q, k = apply_rope_table(q, self.rope, positions), apply_rope_table(k, self.rope, positions)
+        if window is None and spec.attention_softcap is None:
+            a = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), True, self.scale)
+        else:
+            a = masked_attention(q, k, v, self.scale, window, spec.attention_softcap)
+        return a.reshape(B, S, spec.heads * spec.head_dim)
+
+
+def apply_rope_table(x, rope, positions=None):
+    """RoPE with an explicit (possibly scaled) frequency table; x: [B, S, H, D]. Differentiable."""
+    B, S, H, D = x.shape
+    inv, mscale = rope.inv_freq(D, S)
+    rot = rope.rotary_dim or D
+    half = rot // 2
+    inv_t = torch.tensor(inv, device=x.device, dtype=torch.float32)
+    pos = (positions.reshape(B, S).float() if positions is not None
+           else torch.arange(S, device=x.device, dtype=torch.float32)[None, :].expand(B, S))
+    ang = pos[..., None] * inv_t
+    c, s = (torch.cos(ang) * mscale)[:, :, None, :], (torch.sin(ang) * mscale)[:, :, None, :]
+    xf = x.float()
+    a, b = xf[..., :half], xf[..., half:rot]
+    out = torch.cat([a * c - b * s, b * c + a * s, xf[..., rot:]], dim=-1)
+    return out.to(x.dtype)
+
+
+def masked_attention(q, k, v, scale, window=None, softcap=None):
+    """Causal attention with a sliding window and/or tanh soft-capping (fp32 math)."""
+    B, S, H, D = q.shape
+    Hkv = k.shape[2]
+    qf = q.float().permute(0, 2, 1, 3)
+    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(H // Hkv, 1)
+    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(H // Hkv, 1)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    if softcap:
+        s = torch.tanh(s / softcap) * softcap
+    i = torch.arange(S, device=q.device)[:, None]
+    j = torch.arange(k.shape[1], device=q.device)[None, :]
+    off = k.shape[1] - S
+    mask = j > i + off
+    if window is not None:
+        mask = mask | (j <= i + off - window)
+    s = s.masked_fill(mask, float("-inf"))
+    o = torch.matmul(torch.softmax(s, -1), vf)
+    return o.permute(0, 2, 1, 3).to(q.dtype)
+
+
+class FeedForward(nn.Module):
+    def __init__(self, spec: DecoderSpec, ff_dim: Optional[int] = None):
+        super().__init__()
+        self.spec = spec
+        ff = ff_dim or spec.ff_dim
+        mult = 2 if spec.gated else 1
+        self.up_weight = nn.Parameter(torch.empty(mult * ff, spec.dim))      # gated: [gate; up]
+        self.up_bias = nn.Parameter(torch.zeros(mult * ff)) if spec.feed_forward_bias else None
+        self.down_weight = nn.Parameter(torch.empty(spec.dim, ff))
+        self.down_bias = nn.Parameter(torch.zeros(spec.dim)) if spec.feed_forward_bias else None
+
+    def forward(self, x, residual=None):
+        spec = self.spec
+        if spec.gated:
+            kind = {"silu": "silu", "gelu": "gelu", "relu": "relu"}.get(spec.activation)
+            if kind is None:   # tanh(gate) * sigmoid(up)
+                gu = ops.linear(x, self.up_weight, self.up_bias)
+                ff = gu.shape[-1] // 2
+                h = torch.tanh(gu[..., :ff]) * torch.sigmoid(gu[..., ff:])
+                return ops.linear(h, self.down_weight, self.down_bias, residual)
+            return ops.mlp_gated(x, self.up_weight, self.up_bias, self.down_weight, self.down_bias, residual, kind)
+        if spec.activation == "gelu":
+            return ops.mlp_gelu(x, self.up_weight, self.up_bias, self.down_weight, self.down_bias, residual)
+        h = ops.linear(x, self.up_weight, self.up_bias)
+        h = torch.relu(h) if spec.activation == "relu" else torch.nn.functional.silu(h)
+        return ops.linear(h, self.down_weight, self.down_bias, residual)
+
+
+class MixtureOfExperts(nn.Module):
+    """Top-k routed experts (+ optional shared expert). Single-device, as in the reference
+    (src/Idrak/Layers/MixtureOfExperts.cs:34): ties go to the lowest index, weights optionally renormalised."""
+
+    def __init__(self, spec: DecoderSpec):
+        super().__init__()
+        self.spec = spec
+        self.router = nn.Parameter(torch.empty(spec.experts, spec.dim))
+        self.experts = nn.ModuleList([FeedForward(spec, spec.expert_hidden) for _ in range(spec.experts)])
+        if spec.shared_expert_ff_dim:
+            self.shared = FeedForward(spec, spec.shared_expert_ff_dim)
+            self.shared_gate = nn.Parameter(torch.empty(1, spec.dim))
+        else:
+            self.shared = None
+
+    def forward(self, x, residual=None):
+        spec = self.spec
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        logits = torch.nn.functional.linear(x2.float(), self.router.float())
+        probs = torch.softmax(logits, -1)
+        top_p, top_i = torch.topk(probs, spec.experts_per_token, dim=-1)
+        if spec.normalize_top_k:
+            top_p = top_p / top_p.sum(-1, keepdim=True)
+        out = torch.zeros_like(x2, dtype=torch.float32)
+        for e, expert in enumerate(self.experts):
+            rows, slot = torch.nonzero(top_i == e, as_tuple=True)
+            if rows.numel() == 0:
+                continue
+            y = expert(x2[rows])
+            out.index_add_(0, rows, y.float() * top_p[rows, slot][:, None])
+        if self.shared is not None:
+            g = torch.sigmoid(torch.nn.functional.linear(x2.float(), self.shared_gate.float()))
+            out = out + self.shared(x2).float() * g
+        out = out.to(x.dtype).reshape(shape)
+        return out + residual if residual is not None else out
+
+
+class DecoderBlock(nn.Module):
+    def __init__(self, spec: DecoderSpec, layer: int):
+        super().__init__()
+        self.spec, self.layer = spec, layer
+        self.attn_norm = Norm(spec.dim, spec.norm, spec.norm_epsilon, spec.norm_offset)
+        self.attn = SelfAttention(spec, layer)
+        self.mlp_norm = Norm(spec.dim, spec.norm, spec.norm_epsilon, spec.norm_offset)
+        self.mlp = MixtureOfExperts(spec) if spec.is_expert_layer(layer) else FeedForward(spec)
+        if spec.post_norms:
+            self.post_attn_norm = Norm(spec.dim, spec.norm, spec.norm_epsilon, spec.norm_offset)
+            self.post_mlp_norm = Norm(spec.dim, spec.norm, spec.norm_epsilon, spec.norm_offset)
+        self.drop = spec.dropout
+
+    def forward(self, x, positions=None):
+        spec = self.spec
+        if spec.parallel_blocks:
+            h = self.attn_norm(x)
+            return x + self._drop(self.attn(h, None, positions)) + self._drop(self.mlp(h))
+        if spec.post_norms or self.drop > 0:
+            a = self.attn(self.attn_norm(x), None, positions)
+            if spec.post_norms:
+                a = self.post_attn_norm(a)
+            x = x + self._drop(a)
+            m = self.mlp(self.mlp_norm(x))
+            if spec.post_norms:
+                m = self.post_mlp_norm(m)
+            return x + self._drop(m)
+        # plain pre-norm block: residual additions happen inside the GEMM epilogues
+        x = self.attn(self.attn_norm(x), x, positions)
+        return self.mlp(self.mlp_norm(x), x)
+
+    def _drop(self, t):
+        if self.drop > 0 and self.training:
+            return torch.nn.functional.dropout(t, self.drop, True)
+        return t
+
+
+class Decoder(nn.Module):
+    """Token embedding -> blocks -> final norm -> head. ``loss`` runs the head and the cross-entropy fused."""
+
+    def __init__(self, spec: DecoderSpec):
+        super().__init__()
+        self.spec = spec
+        vp = spec.padded_vocabulary
+        self.embed = nn.Parameter(torch.empty(vp, spec.dim))
+        self.pos = nn.Parameter(torch.empty(spec.max_positions, spec.dim)) if spec.learned_positions else None
+        self.blocks = nn.ModuleList([DecoderBlock(spec, i) for i in range(spec.layers)])
+        self.norm = Norm(spec.dim, spec.norm, spec.norm_epsilon, spec.norm_offset)
+        self.head = None if spec.tie_embeddings else nn.Parameter(torch.empty(vp, spec.dim))
+        self.head_bias = nn.Parameter(torch.zeros(vp)) if spec.head_bias else None
+        self.checkpoint_blocks = False
+        self.loss_chunk_rows: Optional[int] = None
+        self.reset_parameters()
+
+    # ------------------------------------------------------------------ init
+    @torch.no_grad()
+    def reset_parameters(self, seed: Optional[int] = None):
+        spec = self.spec
+        g = torch.Generator().manual_seed(seed) if seed is not None else None
+        std = spec.init_std
+        resid_std = std / math.sqrt(2 * spec.layers)
+
+        def normal_(p, s):
+            p.copy_(torch.randn(p.shape, generator=g, dtype=torch.float32).mul_(s).to(p.dtype))
+
+        normal_(self.embed, std)
+        self.embed[spec.vocabulary:].zero_()
+        if self.pos is not None:
+            normal_(self.pos, std)
+        if self.head is not None:
+            normal_(self.head, std)
+            self.head[spec.vocabulary:].zero_()
+        for blk in self.blocks:
+            normal_(blk.attn.qkv_weight, std)
+            normal_(blk.attn.o_weight, resid_std)
+            mlps = [blk.mlp] if isinstance(blk.mlp, FeedForward) else list(blk.mlp.experts) + (
+                [blk.mlp.shared] if blk.mlp.shared is not None else [])
+            for m in mlps:
+                normal_(m.up_weight, std)
+                normal_(m.down_weight, resid_std)
+            if isinstance(blk.mlp, MixtureOfExperts):
+                normal_(blk.mlp.router, std)
+                if blk.mlp.shared is not None:
+                    normal_(blk.mlp.shared_gate, std)
+
+    # ------------------------------------------------------------------ forward
+    def hidden(self, ids: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+        spec = self.spec
+        B, S = ids.shape
+        if self.pos is not None and positions is None:
+            x = ops.embedding(ids, self.embed, self.pos)
+        else:
+            x = ops.embedding(ids, self.embed, None)
+            if self.pos is not None:
+                x = x + self.pos[positions.reshape(B, S).long()]
+        if spec.embedding_scale is not None:
+            x = x * spec.embedding_scale
+        if spec.dropout > 0 and self.training:
+            x = torch.nn.functional.dropout(x, spec.dropout, True)
+        for blk in self.blocks:
+            if self.checkpoint_blocks and self.training and torch.is_grad_enabled():
+                from ..core.checkpointing import checkpoint
+                x = checkpoint(blk, x, positions)
+            else:
+                x = blk(x, positions)
+        return self.norm(x)
+
+    def head_weight(self) -> torch.Tensor:
+        return self.embed if self.head is None else self.head
+
+    def forward(self, ids: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Logits ``[B, S, vocabulary]``."""
+        h = self.hidden(ids, positions)
+        logits = ops.linear(h, self.head_weight(), self.head_bias)[..., : self.spec.vocabulary]
+        if self.spec.logit_softcap:
+            c = self.spec.logit_softcap
+            logits = torch.tanh(logits.float() / c).mul(c).to(logits.dtype)
+        return logits
+
+    def loss(self, ids: torch.Tensor, targets: torch.Tensor, positions: Optional[torch.Tensor] = None,
+             ignore_index: Optional[int] = None) -> torch.Tensor:
+        """Mean next-token cross-entropy; the logits matrix is never materialised beyond one row chunk."""
+        h = self.hidden(ids, positions)
+        if self.spec.logit_softcap or self.head_bias is not None:
+            logits = self.forward_from_hidden(h)
+            return torch.nn.functional.cross_entropy(
+                logits.reshape(-1, logits.shape[-1]).float(), targets.reshape(-1).long(),
+                ignore_index=-100 if ignore_index is None else ignore_index)
+        return ops.token_cross_entropy(h, self.head_weight(), targets, self.spec.vocabulary,
+                                       self.loss_chunk_rows, ignore_index)
+
+    def forward_from_hidden(self, h):
+        logits = ops.linear(h, self.head_weight(), self.head_bias)[..., : self.spec.vocabulary]
+        if self.spec.logit_softcap:
+            c = self.spec.logit_softcap
+            logits = torch.tanh(logits.float() / c).mul(c).to(logits.dtype)
+        return logits
+
+    # ------------------------------------------------------------------ parameter groups
+    def decay_groups(self, weight_decay: float):
+        """Matrices decay; biases, norms and 1-D tensors do not (the usual GPT recipe)."""
+        decay, no_decay = [], []
+        for _, p in self.named_parameters():
+            (decay if p.dim() >= 2 else no_decay).append(p)
+        return [{"params": decay, "weight_decay": weight_decay}, {"params": no_decay, "weight_decay": 0.0}]
+
+
+def build_decoder(spec: DecoderSpec, seed: Optional[int] = None) -> Decoder:
+    model = Decoder(spec)
+    if seed is not None:
+        model.reset_parameters(seed)
+    return model

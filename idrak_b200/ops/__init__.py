@@ -12,3 +12,6 @@ __all__ = [
     "attention_reference", "flash_backward", "flash_forward", "cross_entropy_logits", "softmax_xent_",
     "token_cross_entropy", "FusedAdamW", "FusedSGD",
 ]
+from .fused import mlp_gated, mlp_gelu, qkv_attention  # noqa: E402
+
+__all__ += ["mlp_gated", "mlp_gelu", "qkv_attention"]

@@ -60,22 +60,28 @@ def flash_forward(q, k, v, causal=True, scale=None):
     return out, lse
 
 
-def flash_backward(dout, q, k, v, out, lse, causal=True, scale=None):
-    """Returns (dq, dk, dv) shaped like q, k, v (contiguous)."""
+def flash_backward(dout, q, k, v, out, lse, causal=True, scale=None, grads=None):
+    """Returns (dq, dk, dv) shaped like q, k, v. ``grads`` may supply the three output views (rows holding
+    heads packed [heads, D], any row stride, batch stride = rows * row stride), e.g. slices of one d(QKV)."""
     B, Sq, H, D = q.shape
     Skv, Hkv = k.shape[1], k.shape[2]
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     lib = _native.lib()
     dout = dout.contiguous()
     delta = torch.empty((B, H, Sq), dtype=torch.float32, device=q.device)
-    dq = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
-    dk = torch.empty((B, Skv, Hkv, D), dtype=q.dtype, device=q.device)
-    dv = torch.empty((B, Skv, Hkv, D), dtype=q.dtype, device=q.device)
+    if grads is None:
+        dq = torch.empty((B, Sq, H, D), dtype=q.dtype, device=q.device)
+        dk = torch.empty((B, Skv, Hkv, D), dtype=q.dtype, device=q.device)
+        dv = torch.empty((B, Skv, Hkv, D), dtype=q.dtype, device=q.device)
+    else:
+        dq, dk, dv = grads
+        for g, rows in ((dq, Sq), (dk, Skv), (dv, Skv)):
+            assert g.stride(3) == 1 and g.stride(2) == D and g.stride(0) == rows * g.stride(1)
     rc = lib.idrak_flash_bwd(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), dout.data_ptr(), lse.data_ptr(),
         delta.data_ptr(), dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), B, H, Hkv, Sq, Skv, D,
         q.stride(1), k.stride(1), v.stride(1), q.stride(0), k.stride(0), v.stride(0),
-        float(scale), int(causal), stream_ptr())
+        dq.stride(1), dk.stride(1), dv.stride(1), float(scale), int(causal), stream_ptr())
     _native.check(rc, "idrak_flash_bwd")
     return dq, dk, dv
 

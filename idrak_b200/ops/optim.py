@@ -120,8 +120,21 @@ class FusedOptimizerBase:
             self._hyper_dev = torch.zeros(H_COUNT, dtype=torch.float32, device=dev)
         return self._tables
 
+    def _hyper_values(self) -> dict:
+        raise NotImplementedError
+
+    def advance_for_replay(self):
+        """A recorded CUDA graph replays the launches of ``step``; the host side of a step (count the step,
+        refresh the pinned hyper-parameter block the graph copies from) is this call."""
+        self.step_count += 1
+        h = self._hyper_host[0]
+        for k, v in self._hyper_values().items():
+            h[k] = v
+
     def _upload_hyper(self, values: dict):
-        h = self._hyper_host[self.step_count % 16]
+        # under graph capture the copy node must always read the same pinned block
+        slot = 0 if torch.cuda.is_current_stream_capturing() else 1 + self.step_count % 15
+        h = self._hyper_host[slot]
         for k, v in values.items():
             h[k] = v
         # clip scale / norm slots are written by the device; do not overwrite them mid-step
@@ -151,8 +164,7 @@ class FusedAdamW(FusedOptimizerBase):
             return self._step_cpu(bc1, bc2)
         lib = _native.lib()
         t_dev, c_dev, n_chunks, partial = self._build_tables()
-        self._upload_hyper({H_LR: self.lr, H_B1: b1, H_B2: b2, H_EPS: self.eps, H_BC1: bc1, H_BC2: bc2,
-                            H_MAXNORM: self.max_grad_norm, H_GSCALE: self.grad_scale})
+        self._upload_hyper(self._hyper_values())
         s = stream_ptr()
         rc = lib.idrak_opt_grad_norm(t_dev.data_ptr(), c_dev.data_ptr(), n_chunks, partial.data_ptr(),
                                      extra_sumsq.data_ptr() if extra_sumsq is not None else None,
@@ -161,6 +173,11 @@ class FusedAdamW(FusedOptimizerBase):
         rc = lib.idrak_opt_adamw(t_dev.data_ptr(), c_dev.data_ptr(), n_chunks, self._hyper_dev.data_ptr(),
                                  int(self.zero_grad_in_step), s)
         _native.check(rc, "idrak_opt_adamw")
+
+    def _hyper_values(self) -> dict:
+        b1, b2 = self.betas
+        return {H_LR: self.lr, H_B1: b1, H_B2: b2, H_EPS: self.eps, H_BC1: 1.0 - b1 ** self.step_count,
+                H_BC2: 1.0 - b2 ** self.step_count, H_MAXNORM: self.max_grad_norm, H_GSCALE: self.grad_scale}
 
     def _step_cpu(self, bc1, bc2):
         b1, b2 = self.betas
@@ -242,13 +259,16 @@ class FusedSGD(FusedOptimizerBase):
             return
         lib = _native.lib()
         t_dev, c_dev, n_chunks, partial = self._build_tables()
-        self._upload_hyper({H_LR: self.lr, H_MAXNORM: self.max_grad_norm, H_GSCALE: self.grad_scale})
+        self._upload_hyper(self._hyper_values())
         s = stream_ptr()
         _native.check(lib.idrak_opt_grad_norm(t_dev.data_ptr(), c_dev.data_ptr(), n_chunks, partial.data_ptr(),
                                               extra_sumsq.data_ptr() if extra_sumsq is not None else None,
                                               self._hyper_dev.data_ptr(), s), "idrak_opt_grad_norm")
         _native.check(lib.idrak_opt_sgd(t_dev.data_ptr(), c_dev.data_ptr(), n_chunks, self._hyper_dev.data_ptr(),
                                         float(self.momentum), int(self.zero_grad_in_step), s), "idrak_opt_sgd")
+
+    def _hyper_values(self) -> dict:
+        return {H_LR: self.lr, H_MAXNORM: self.max_grad_norm, H_GSCALE: self.grad_scale}
 
     def state_dict(self):
         out = {"step": torch.tensor(float(self.step_count))}
