@@ -36,6 +36,7 @@ _SIGNATURES = {
     "idrak_sm_count": (c_int, []),
     "idrak_last_error": (C.c_char_p, []),
     "idrak_launch_count": (c_ll, []),
+    "idrak_bind_device": (c_int, [c_int]),
     "idrak_build_info": (C.c_char_p, []),
     "idrak_gemm_workspace_elems": (c_ll, [c_int, c_int, c_int, c_int]),
     "idrak_gemm_pick_splits": (c_int, [c_int, c_int, c_int, c_int]),

@@ -221,6 +221,7 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(CommCtx c, PeerPtrs
   // the peers may not overwrite their buffers until everyone has read them
   if (last_block(c, channel)) {
     signal_peers(c, channel + 1, e);
+    wait_peers(c, channel + 1, e, 29);   // when this kernel ends, every peer has finished reading my buffer
   }
 }
 

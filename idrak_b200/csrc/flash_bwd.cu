@@ -52,24 +52,30 @@ __device__ __forceinline__ uint64_t mnmajor_desc(uint32_t base, int kk) {
 // ---------------------------------------------------------------------------
 __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dO,
                                    float* __restrict__ delta, int B, int S, int H, int D) {
-  const long long w = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
-  const int lane = threadIdx.x & 31;
+  // D/8 lanes share one (b, s, h) row, each with one 128-bit load of O and of dO; a warp covers 256/D rows
+  const int lanes_per_row = D >> 3;
+  const long long t = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  const long long w = t / lanes_per_row;
+  const int sub = int(t - w * lanes_per_row);
   const long long total = (long long)B * S * H;
-  if (w >= total) return;
-  const int h = int(w % H);
-  const long long bs = w / H;
-  const int s = int(bs % S);
-  const int b = int(bs / S);
-  const __nv_bfloat16* po = o + (bs * H + h) * D;
-  const __nv_bfloat16* pd = dO + (bs * H + h) * D;
   float acc = 0.f;
-  for (int i = lane * 2; i < D; i += 64) {
-    float2 a = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(po + i));
-    float2 g = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(pd + i));
-    acc += a.x * g.x + a.y * g.y;
+  if (w < total) {
+    const uint4 a = *reinterpret_cast<const uint4*>(o + w * D + sub * 8);
+    const uint4 g = *reinterpret_cast<const uint4*>(dO + w * D + sub * 8);
+    float2 x, y;
+    x = unpack_bf16x2(a.x); y = unpack_bf16x2(g.x); acc += x.x * y.x + x.y * y.y;
+    x = unpack_bf16x2(a.y); y = unpack_bf16x2(g.y); acc += x.x * y.x + x.y * y.y;
+    x = unpack_bf16x2(a.z); y = unpack_bf16x2(g.z); acc += x.x * y.x + x.y * y.y;
+    x = unpack_bf16x2(a.w); y = unpack_bf16x2(g.w); acc += x.x * y.x + x.y * y.y;
   }
-  acc = warp_sum(acc);
-  if (lane == 0) delta[((long long)b * H + h) * S + s] = acc;
+  for (int o2 = lanes_per_row >> 1; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
+  if (w < total && sub == 0) {
+    const int h = int(w % H);
+    const long long bs = w / H;
+    const int s = int(bs % S);
+    const int b = int(bs / S);
+    delta[((long long)b * H + h) * S + s] = acc;
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -549,9 +555,9 @@ IDRAK_API int idrak_flash_bwd(const void* q, const void* k, const void* v, const
   if (H % Hkv) return -3;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   {
-    const long long warps = (long long)B * Sq * H;
+    const long long rows = (long long)B * Sq * H;
     const int threads = 256;
-    const long long blocks = (warps * 32 + threads - 1) / threads;
+    const long long blocks = (rows * (D / 8) + threads - 1) / threads;
     flash_delta_kernel<<<unsigned(blocks), threads, 0, stream>>>(static_cast<const __nv_bfloat16*>(out),
                                                                  static_cast<const __nv_bfloat16*>(dout), delta, B,
                                                                  Sq, H, D);

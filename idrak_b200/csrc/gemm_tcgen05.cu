@@ -18,6 +18,7 @@
 // residual epilogues (src/Idrak.Gpu/Cuda/PtxKernels.TensorCore.cs:24-29,80-144) and the host dispatch
 // of CudaBackend.cs:1306-1471.
 #include "common.cuh"
+#include <cstring>
 
 namespace idrak {
 
@@ -45,11 +46,15 @@ struct GemmParams {
   int splits;                     // split-K factor (1 = direct epilogue)
   float* workspace;               // [splits, M, N] fp32 when splits > 1
   int m_tiles, n_tiles;
+  int tma_store;                  // 1: bf16 C (and aux) leave through shared-memory staging + TMA stores
   Status* st;
 };
 
-// Epilogue on 8 consecutive columns of one row. `v` holds alpha-scaled accumulators on entry.
-__device__ __forceinline__ void epilogue8(const GemmParams& p, int row, int col, float (&v)[8], int nvalid) {
+// Element-wise part of the epilogue on 8 consecutive columns of one row: bias, activation, residual.
+// `v` holds alpha-scaled accumulators on entry and the values to store on return. With kActGelu the
+// pre-activation goes to `pre` (rounded to bf16 like the stored copy) and, when `store_aux`, to p.aux.
+__device__ __forceinline__ void epilogue_math8(const GemmParams& p, int row, int col, float (&v)[8], int nvalid,
+                                               bool store_aux, float (&pre)[8]) {
   const bool vec = (nvalid == 8);
   if (p.bias) {
     if (vec && ((reinterpret_cast<uintptr_t>(p.bias + col) & 15) == 0)) {
@@ -67,17 +72,22 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, int row, int col,
     __nv_bfloat16* ax = p.aux + size_t(row) * p.ld_aux + col;
     const bool axvec = vec && ((reinterpret_cast<uintptr_t>(ax) & 15) == 0);
     if (p.act == kActGelu) {
-      if (axvec) {
-        uint4 o;
-        o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-        o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-        *reinterpret_cast<uint4*>(ax) = o;
-      } else {
-        for (int i = 0; i < nvalid; ++i) ax[i] = __float2bfloat16(v[i]);
+      if (store_aux) {
+        if (axvec) {
+          uint4 o;
+          o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+          o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+          *reinterpret_cast<uint4*>(ax) = o;
+        } else {
+          for (int i = 0; i < nvalid; ++i) ax[i] = __float2bfloat16(v[i]);
+        }
       }
       // the activation sees the value as it was stored (bf16), so forward and backward agree
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(__bfloat162float(__float2bfloat16(v[i])));
+      for (int i = 0; i < 8; ++i) {
+        pre[i] = __bfloat162float(__float2bfloat16(v[i]));
+        v[i] = gelu_tanh(pre[i]);
+      }
     } else {
       float x[8];
       if (axvec) {
@@ -107,6 +117,13 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, int row, int col,
       for (int i = 0; i < nvalid; ++i) v[i] += __bfloat162float(r[i]);
     }
   }
+}
+
+// Full epilogue with direct global stores (any alignment, fp32 or bf16 output, optional accumulate).
+__device__ __forceinline__ void epilogue8(const GemmParams& p, int row, int col, float (&v)[8], int nvalid) {
+  const bool vec = (nvalid == 8);
+  float pre[8];
+  epilogue_math8(p, row, col, v, nvalid, true, pre);
   if (p.c_fp32) {
     float* c = reinterpret_cast<float*>(p.C) + size_t(row) * p.ldc + col;
     if (vec && ((reinterpret_cast<uintptr_t>(c) & 15) == 0)) {
@@ -164,18 +181,21 @@ struct GemmSmem {
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStagingBytes = 4 * 2 * 4096;   // per epilogue warp: two 32-row x 128-byte slabs
   static constexpr int kBarrierBytes = 256;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;  // + alignment slack
+  static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
 template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const GemmParams p) {
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
   using L = GemmSmem<BN>;
   constexpr int kStages = L::kStages;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  uint8_t* bar_base = smem + kStages * L::kStageBytes;
+  uint8_t* staging = smem + kStages * L::kStageBytes;        // 1024-byte aligned (stages are 16 KB multiples)
+  uint8_t* bar_base = staging + L::kStagingBytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(bar_base);
   uint64_t* empty = full + kStages;
   uint64_t* tmem_full = empty + kStages;
@@ -308,6 +328,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
     const int row_in_tile = quarter * 32 + lane;
     int local = 0;
+    int ring = 0;
     bool ok = true;
     for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++local) {
       int tm, tn, split;
@@ -323,6 +344,62 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_after();
       const int row = tm * kBM + row_in_tile;
       const int n0 = tn * BN;
+      if (p.tma_store && p.splits == 1) {
+        // ---- staged path: registers -> swizzled shared slab (32 rows x 64 columns) -> TMA store
+        const int row0 = tm * kBM + quarter * 32;
+        const bool gelu = (p.act == kActGelu);
+        uint8_t* my_stage = staging + quarter * 2 * 4096;
+#pragma unroll 1
+        for (int s64 = 0; s64 < BN / 64; ++s64) {
+          const int col0 = n0 + s64 * 64;
+          if (col0 >= p.N || row0 >= p.M) break;                      // warp-uniform
+          uint8_t* cbuf = my_stage + (gelu ? 0 : (ring & 1)) * 4096;
+          uint8_t* abuf = my_stage + 4096;
+          if (lane == 0) {
+            if (gelu) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
+          }
+          __syncwarp();
+#pragma unroll 1
+          for (int h = 0; h < 2; ++h) {
+            uint32_t r[32];
+            tmem_ld_32x32b_x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + s64 * 64 + h * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = col0 + h * 32 + g * 8;
+              float v[8], pre[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) { v[i] = __uint_as_float(r[g * 8 + i]) * p.alpha; pre[i] = 0.f; }
+              if (row < p.M && col < p.N) epilogue_math8(p, row, col, v, min(8, p.N - col), false, pre);
+              const int chunk = ((h * 4 + g) ^ (lane & 7)) << 4;
+              uint4 o;
+              o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
+              o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+              *reinterpret_cast<uint4*>(cbuf + lane * 128 + chunk) = o;
+              if (gelu) {
+                uint4 a;
+                a.x = pack_bf16x2(pre[0], pre[1]); a.y = pack_bf16x2(pre[2], pre[3]);
+                a.z = pack_bf16x2(pre[4], pre[5]); a.w = pack_bf16x2(pre[6], pre[7]);
+                *reinterpret_cast<uint4*>(abuf + lane * 128 + chunk) = a;
+              }
+            }
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            tma_store_2d(&tmC, cbuf, col0, row0);
+            tma_store_commit();
+            if (gelu) {
+              tma_store_2d(&tmAux, abuf, col0, row0);
+              tma_store_commit();
+            }
+          }
+          ++ring;
+        }
+        tc_fence_before();
+        mbar_arrive(&tmem_empty[buf]);
+        continue;
+      }
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -363,6 +440,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_before();
       mbar_arrive(&tmem_empty[buf]);
     }
+    if (p.tma_store && lane == 0) tma_store_wait<0>();   // staged slabs are read out before shared memory goes away
   }
 
   tc_fence_before();
@@ -405,8 +483,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) 
 // host launcher
 // ---------------------------------------------------------------------------
 template <int BN, int A_MN, int B_MN>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p, int grid,
-                       cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
+                       const CUtensorMap& tmAux, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = GemmSmem<BN>;
   auto kern = gemm_kernel<BN, A_MN, B_MN>;
   static bool configured = false;
@@ -415,7 +493,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     if (e != cudaSuccess) return int(e);
     configured = true;
   }
-  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, p);
+  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, tmC, tmAux, p);
   note_launches(1);
   return int(cudaGetLastError());
 }
@@ -509,10 +587,30 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
   e = make_operand_map(&tmB, B, N, K, ldb, b_mn, bn, fp16);
   if (e) return -12;
 
+  // Output through TMA when the layout allows: bf16, no accumulate, 16-byte aligned rows.
+  CUtensorMap tmC, tmAux;
+  memset(&tmC, 0, sizeof(tmC));
+  memset(&tmAux, 0, sizeof(tmAux));
+  p.tma_store = 0;
+  if (!c_fp32 && !beta && p.splits == 1 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+      (act != kActGelu || ((ld_aux % 8) == 0 && (reinterpret_cast<uintptr_t>(aux) & 15) == 0))) {
+    uint64_t dims[2] = {uint64_t(N), uint64_t(M)};
+    uint32_t box[2] = {64, 32};
+    uint64_t str_c[1] = {uint64_t(ldc) * 2};
+    int ok = encode_tensor_map(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, dims, str_c, box,
+                               CU_TENSOR_MAP_SWIZZLE_128B) == 0;
+    if (ok && act == kActGelu) {
+      uint64_t str_a[1] = {uint64_t(ld_aux) * 2};
+      ok = encode_tensor_map(&tmAux, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, aux, dims, str_a, box,
+                             CU_TENSOR_MAP_SWIZZLE_128B) == 0;
+    }
+    p.tma_store = ok ? 1 : 0;
+  }
+
   const int units = p.m_tiles * p.n_tiles * p.splits;
   const int grid = min(units, sm_count());
   int rc;
-#define IDRAK_GEMM_CASE(BN_, AM_, BM_) rc = launch_gemm<BN_, AM_, BM_>(tmA, tmB, p, grid, stream)
+#define IDRAK_GEMM_CASE(BN_, AM_, BM_) rc = launch_gemm<BN_, AM_, BM_>(tmA, tmB, tmC, tmAux, p, grid, stream)
   if (bn == 256) {
     if (!a_mn && !b_mn) IDRAK_GEMM_CASE(256, 0, 0);
     else if (!a_mn && b_mn) IDRAK_GEMM_CASE(256, 0, 1);

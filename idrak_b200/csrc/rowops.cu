@@ -196,26 +196,72 @@ __global__ void __launch_bounds__(128) norm_bwd_kernel(const __nv_bfloat16* __re
   }
 }
 
-// out[c] (+)= sum_p part[p, c], p ascending. Output bf16 or fp32.
-__global__ void colsum_final_kernel(const float* __restrict__ part, int parts, int C, void* __restrict__ out,
-                                    int out_fp32, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= C) return;
+// out[c] (+)= sum_p part[p, c]. Block = 32 columns x 8 part lanes: lane ty adds parts ty, ty+8, ... in
+// ascending order, then the 8 lane sums are added in lane order, so the result has one fixed order.
+__global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ part, int parts, int C,
+                                                           void* __restrict__ out, int out_fp32, int accumulate) {
+  __shared__ float sm[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + tx;
   float s = 0.f;
-  for (int p = 0; p < parts; ++p) s += part[size_t(p) * C + c];
-  if (out_fp32) {
-    float* o = static_cast<float*>(out);
-    o[c] = accumulate ? o[c] + s : s;
-  } else {
-    __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
-    o[c] = __float2bfloat16(accumulate ? __bfloat162float(o[c]) + s : s);
+  if (c < C)
+    for (int p = ty; p < parts; p += 8) s += part[size_t(p) * C + c];
+  sm[ty][tx] = s;
+  __syncthreads();
+  if (ty == 0 && c < C) {
+    float r = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) r += sm[k][tx];
+    if (out_fp32) {
+      float* o = static_cast<float*>(out);
+      o[c] = accumulate ? o[c] + r : r;
+    } else {
+      __nv_bfloat16* o = static_cast<__nv_bfloat16*>(out);
+      o[c] = __float2bfloat16(accumulate ? __bfloat162float(o[c]) + r : r);
+    }
   }
 }
 
 // Column sums of a bf16 matrix [rows, C] (ld elements per row) into per-block partials [gridDim.y, C].
-// Block = 32 x 8 threads: 32 lanes cover 64 columns (2 each), 8 row lanes stride the rows of the chunk.
+// Block = 32 x 8 threads: a lane owns 8 consecutive columns (one 128-bit load per row), 8 row lanes stride
+// the rows of the block's chunk. Needs ld % 8 == 0 and a 16-byte aligned base; C may be ragged.
 __global__ void __launch_bounds__(256) colsum_part_kernel(const __nv_bfloat16* __restrict__ x, int rows, int C,
                                                           int ld, int rows_per_block, float* __restrict__ part) {
+  __shared__ float sm[8][256];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int col = blockIdx.x * 256 + tx * 8;
+  const int row0 = blockIdx.y * rows_per_block;
+  const int row1 = min(rows, row0 + rows_per_block);
+  float a[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) a[j] = 0.f;
+  if (col + 8 <= C) {
+    for (int r = row0 + ty; r < row1; r += 8) {
+      float v[8];
+      load8(x + size_t(r) * ld + col, v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) a[j] += v[j];
+    }
+  } else if (col < C) {
+    for (int r = row0 + ty; r < row1; r += 8)
+      for (int j = 0; j < C - col; ++j) a[j] += __bfloat162float(x[size_t(r) * ld + col + j]);
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sm[ty][tx * 8 + j] = a[j];
+  __syncthreads();
+  const int c = threadIdx.x;          // 256 threads fold the 256 columns of the block
+  if (blockIdx.x * 256 + c < C) {
+    float r = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) r += sm[k][c];
+    part[size_t(blockIdx.y) * C + blockIdx.x * 256 + c] = r;
+  }
+}
+
+// Same contract for matrices whose rows are not 16-byte aligned: two columns per lane, scalar loads.
+__global__ void __launch_bounds__(256) colsum_part_scalar_kernel(const __nv_bfloat16* __restrict__ x, int rows,
+                                                                 int C, int ld, int rows_per_block,
+                                                                 float* __restrict__ part) {
   __shared__ float sm[8][64];
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
   const int col = blockIdx.x * 64 + tx * 2;
@@ -225,14 +271,8 @@ __global__ void __launch_bounds__(256) colsum_part_kernel(const __nv_bfloat16* _
   if (col < C) {
     for (int r = row0 + ty; r < row1; r += 8) {
       const __nv_bfloat16* p = x + size_t(r) * ld + col;
-      if (col + 1 < C && ((reinterpret_cast<uintptr_t>(p) & 3) == 0)) {
-        float2 f = unpack_bf16x2(*reinterpret_cast<const uint32_t*>(p));
-        a0 += f.x;
-        a1 += f.y;
-      } else {
-        a0 += __bfloat162float(p[0]);
-        if (col + 1 < C) a1 += __bfloat162float(p[1]);
-      }
+      a0 += __bfloat162float(p[0]);
+      if (col + 1 < C) a1 += __bfloat162float(p[1]);
     }
   }
   sm[ty][tx * 2] = a0;
@@ -244,6 +284,101 @@ __global__ void __launch_bounds__(256) colsum_part_kernel(const __nv_bfloat16* _
     for (int k = 0; k < 8; ++k) { s0 += sm[k][tx * 2]; s1 += sm[k][tx * 2 + 1]; }
     if (col < C) part[size_t(blockIdx.y) * C + col] = s0;
     if (col + 1 < C) part[size_t(blockIdx.y) * C + col + 1] = s1;
+  }
+}
+
+// LayerNorm / RMSNorm backward for rows that fit a warp's registers (C <= 256 * VPL): one warp per row, eight
+// warps per block walking the block's rows; per-lane dw / db sums are folded across the warps of a block in
+// warp order through shared memory, so the per-block partials have a fixed summation order.
+template <int VPL>
+__global__ void __launch_bounds__(256) norm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy,
+                                                            const __nv_bfloat16* __restrict__ x,
+                                                            const __nv_bfloat16* __restrict__ w,
+                                                            const float* __restrict__ mean_in,
+                                                            const float* __restrict__ rstd_in,
+                                                            const __nv_bfloat16* __restrict__ dres_in,
+                                                            __nv_bfloat16* __restrict__ dx,
+                                                            float* __restrict__ dw_part, float* __restrict__ db_part,
+                                                            int rows, int C, int rms, int rows_per_block) {
+  extern __shared__ float sm_acc[];   // [2][C]
+  float* sdw = sm_acc;
+  float* sdb = sm_acc + C;
+  const int wid = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nvec = C >> 3;
+  const int row0 = blockIdx.x * rows_per_block;
+  const int row1 = min(rows, row0 + rows_per_block);
+  float adw[VPL][8], adb[VPL][8], wv[VPL][8];
+#pragma unroll
+  for (int i = 0; i < VPL; ++i) {
+    const int vi = lane + i * 32;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { adw[i][j] = 0.f; adb[i][j] = 0.f; wv[i][j] = 0.f; }
+    if (vi < nvec) load8(w + vi * 8, wv[i]);
+  }
+  for (int row = row0 + wid; row < row1; row += 8) {
+    const size_t base = size_t(row) * C;
+    const float mean = rms ? 0.f : mean_in[row];
+    const float rstd = rstd_in[row];
+    float g[VPL][8], n[VPL][8];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float dyv[8], xv[8];
+        load8(dy + base + vi * 8, dyv);
+        load8(x + base + vi * 8, xv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          n[i][j] = (xv[j] - mean) * rstd;
+          g[i][j] = dyv[j] * wv[i][j];
+          s1 += g[i][j];
+          s2 += g[i][j] * n[i][j];
+          adw[i][j] += dyv[j] * n[i][j];
+          adb[i][j] += dyv[j];
+        }
+      }
+    }
+    s1 = rms ? 0.f : warp_sum(s1) / float(C);
+    s2 = warp_sum(s2) / float(C);
+#pragma unroll
+    for (int i = 0; i < VPL; ++i) {
+      const int vi = lane + i * 32;
+      if (vi < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = (g[i][j] - s1 - n[i][j] * s2) * rstd;
+        if (dres_in) {
+          float r[8];
+          load8(dres_in + base + vi * 8, r);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] += r[j];
+        }
+        store8(dx + base + vi * 8, o);
+      }
+    }
+  }
+  for (int i = threadIdx.x; i < 2 * C; i += blockDim.x) sm_acc[i] = 0.f;
+  __syncthreads();
+  for (int wsel = 0; wsel < 8; ++wsel) {
+    if (wid == wsel) {
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) {
+        const int vi = lane + i * 32;
+        if (vi < nvec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            sdw[vi * 8 + j] += adw[i][j];
+            sdb[vi * 8 + j] += adb[i][j];
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  for (int i = threadIdx.x; i < C; i += blockDim.x) {
+    dw_part[size_t(blockIdx.x) * C + i] = sdw[i];
+    if (db_part) db_part[size_t(blockIdx.x) * C + i] = sdb[i];
   }
 }
 
@@ -538,25 +673,30 @@ IDRAK_API int idrak_norm_bwd(const void* dy, const void* x, const void* w, const
   const int blocks = idrak_norm_bwd_blocks(rows);
   const int rpb = (rows + blocks - 1) / blocks;
   const int nvec = C / 8;
+#define NW(V) norm_bwd_warp_kernel<V><<<blocks, 256, size_t(2) * C * sizeof(float), s>>>(CBF(dy), CBF(x), CBF(w), mean, rstd, CBF(dres_in), BF(dx), dw_part, rms ? nullptr : db_part, rows, C, rms, rpb)
 #define NB(V) norm_bwd_kernel<V><<<blocks, 128, 0, s>>>(CBF(dy), CBF(x), CBF(w), mean, rstd, CBF(dres_in), BF(dx), dw_part, rms ? nullptr : db_part, rows, C, rms, rpb)
-  if (nvec <= 128 * 1) NB(1);
+  if (nvec <= 32 * 1) NW(1);
+  else if (nvec <= 32 * 2) NW(2);
+  else if (nvec <= 32 * 3) NW(3);
+  else if (nvec <= 32 * 4) NW(4);
   else if (nvec <= 128 * 2) NB(2);
   else if (nvec <= 128 * 4) NB(4);
   else NB(8);
+#undef NW
 #undef NB
   note_launches(1);
   int rc = int(cudaGetLastError());
   if (rc) return rc;
-  colsum_final_kernel<<<(C + 255) / 256, 256, 0, s>>>(dw_part, blocks, C, dw, grads_fp32, accumulate);
+  colsum_final_kernel<<<(C + 31) / 32, 256, 0, s>>>(dw_part, blocks, C, dw, grads_fp32, accumulate);
   note_launches(1);
-  if (!rms && db) colsum_final_kernel<<<(C + 255) / 256, 256, 0, s>>>(db_part, blocks, C, db, grads_fp32, accumulate);
+  if (!rms && db) colsum_final_kernel<<<(C + 31) / 32, 256, 0, s>>>(db_part, blocks, C, db, grads_fp32, accumulate);
   note_launches(1);
   return int(cudaGetLastError());
 }
 
 IDRAK_API int idrak_colsum_blocks(int rows) {
-  int b = (rows + 255) / 256;
-  return b < 1 ? 1 : (b > 64 ? 64 : b);
+  int b = (rows + 63) / 64;
+  return b < 1 ? 1 : (b > 128 ? 128 : b);
 }
 
 // out[c] (+)= sum_r x[r, c]; `part` holds [idrak_colsum_blocks(rows), C] floats.
@@ -565,10 +705,15 @@ IDRAK_API int idrak_colsum(const void* x, int rows, int C, int ld, float* part, 
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   const int yb = idrak_colsum_blocks(rows);
   const int rpb = (rows + yb - 1) / yb;
-  dim3 grid((C + 63) / 64, yb);
-  colsum_part_kernel<<<grid, 256, 0, s>>>(CBF(x), rows, C, ld, rpb, part);
+  if ((ld % 8) == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0) {
+    dim3 grid((C + 255) / 256, yb);
+    colsum_part_kernel<<<grid, 256, 0, s>>>(CBF(x), rows, C, ld, rpb, part);
+  } else {
+    dim3 grid((C + 63) / 64, yb);
+    colsum_part_scalar_kernel<<<grid, 256, 0, s>>>(CBF(x), rows, C, ld, rpb, part);
+  }
   note_launches(1);
-  colsum_final_kernel<<<(C + 255) / 256, 256, 0, s>>>(part, yb, C, out, out_fp32, accumulate);
+  colsum_final_kernel<<<(C + 31) / 32, 256, 0, s>>>(part, yb, C, out, out_fp32, accumulate);
   note_launches(1);
   return int(cudaGetLastError());
 }

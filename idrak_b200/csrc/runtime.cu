@@ -136,6 +136,10 @@ IDRAK_API const char* idrak_last_error() { return idrak::last_error(); }
 
 IDRAK_API int idrak_sm_count() { return idrak::sm_count(); }
 
+// Make `device`'s primary context current on the calling thread (threads PyTorch creates for the backward
+// pass may not have one yet, and this library's driver-level calls need it).
+IDRAK_API int idrak_bind_device(int device) { return int(cudaSetDevice(device)); }
+
 // Kernels launched by this library in this process so far.
 IDRAK_API long long idrak_launch_count() { return idrak::launches(); }
 

@@ -1,6 +1,8 @@
 """Helpers shared by the op wrappers: stream handles, pointers, scratch buffers."""
 from __future__ import annotations
 
+import threading
+
 import torch
 
 from .. import _native
@@ -8,7 +10,16 @@ from .. import _native
 _SCRATCH: dict[tuple, torch.Tensor] = {}
 
 
+_TLS = threading.local()
+
+
 def stream_ptr() -> int:
+    """The current stream's handle. Also binds the current device's context to this thread the first time
+    the thread comes through here: PyTorch's backward threads may not have a driver context yet."""
+    dev = torch.cuda.current_device()
+    if getattr(_TLS, "device", None) != dev:
+        _native.check(_native.lib().idrak_bind_device(dev), "idrak_bind_device")
+        _TLS.device = dev
     return torch.cuda.current_stream().cuda_stream
 
 
