@@ -60,7 +60,14 @@ class SelfAttention(nn.Module):
     def forward(self, x, residual=None, positions=None):
         spec = self.spec
         H, Hkv, D = spec.heads, spec.kv_heads, spec.head_dim
-        qkv = ops.linear(x, self.qkv_weight, self.qkv_bias)
+        adapters = getattr(self, "adapters", None)
+        if adapters is not None:
+            from ..adapters.lora import _slices_attention, project_with_adapters
+            qkv = project_with_adapters(x, self.qkv_weight, self.qkv_bias, adapters, _slices_attention(spec))
+            if not qkv.is_contiguous():
+                qkv = qkv.contiguous()
+        else:
+            qkv = ops.linear(x, self.qkv_weight, self.qkv_bias)
         window = spec.sliding_window if spec.is_windowed(self.layer) else None
         simple = not spec.qk_norm and window is None and spec.attention_softcap is None and (
             self.rope is None or self.rope.scaling is None)
@@ -70,6 +77,10 @@ class SelfAttention(nn.Module):
             a = ops.qkv_attention(qkv, H, Hkv, D, True, self.scale, theta, rdim, 1.0, positions)
         else:
             a = self._general(qkv, positions, window)
+        if adapters is not None and "o" in adapters:
+            from ..adapters.lora import project_with_adapters
+            return project_with_adapters(a, self.o_weight, self.o_bias, adapters,
+                                         {"o": (0, self.o_weight.shape[0])}, residual)
         return ops.linear(a, self.o_weight, self.o_bias, residual)
 
     def _general(self, qkv, positions, window):
@@ -140,6 +151,9 @@ class FeedForward(nn.Module):
 
     def forward(self, x, residual=None):
         spec = self.spec
+        adapters = getattr(self, "adapters", None)
+        if adapters is not None and len(adapters.items) > 0:
+            return self._forward_adapted(x, residual, adapters)
         if spec.gated:
             kind = {"silu": "silu", "gelu": "gelu", "relu": "relu"}.get(spec.activation)
             if kind is None:   # tanh(gate) * sigmoid(up)
@@ -153,6 +167,27 @@ class FeedForward(nn.Module):
         h = ops.linear(x, self.up_weight, self.up_bias)
         h = torch.relu(h) if spec.activation == "relu" else torch.nn.functional.silu(h)
         return ops.linear(h, self.down_weight, self.down_bias, residual)
+
+
+    def _forward_adapted(self, x, residual, adapters):
+        """The same block with low-rank adapters on gate / up / down: projections run one by one."""
+        from ..adapters.lora import project_with_adapters
+        spec = self.spec
+        hidden = self.down_weight.shape[1]
+        if spec.gated:
+            gu = project_with_adapters(x, self.up_weight, self.up_bias, adapters,
+                                       {"gate": (0, hidden), "up": (hidden, 2 * hidden)})
+            kind = {"silu": "silu", "gelu": "gelu", "relu": "relu"}.get(spec.activation)
+            if kind is None:
+                h = torch.tanh(gu[..., :hidden]) * torch.sigmoid(gu[..., hidden:])
+            else:
+                h = ops.gated_activation(gu.contiguous(), kind)
+        else:
+            h = project_with_adapters(x, self.up_weight, self.up_bias, adapters, {"up": (0, hidden)})
+            h = ops.gelu(h) if spec.activation == "gelu" else (
+                torch.relu(h) if spec.activation == "relu" else torch.nn.functional.silu(h))
+        return project_with_adapters(h, self.down_weight, self.down_bias, adapters,
+                                     {"down": (0, self.down_weight.shape[0])}, residual)
 
 
 class MixtureOfExperts(nn.Module):
@@ -243,6 +278,8 @@ class Decoder(nn.Module):
         self.norm = Norm(spec.dim, spec.norm, spec.norm_epsilon, spec.norm_offset)
         self.head = None if spec.tie_embeddings else nn.Parameter(torch.empty(vp, spec.dim))
         self.head_bias = nn.Parameter(torch.zeros(vp)) if spec.head_bias else None
+        if spec.tie_embeddings:
+            self.embed._idrak_writers = 2      # its gradient comes from the head and from the lookup
         self.checkpoint_blocks = False
         self.loss_chunk_rows: Optional[int] = None
         self.reset_parameters()

@@ -18,7 +18,7 @@ import torch
 
 from . import rowops
 from .attention import attention_reference, flash_backward, flash_forward
-from .gemm import gemm
+from .gemm import bias_grad, gemm, weight_grad
 from .rowops import GATE_KINDS, _gate_ref, colsum, rope_, rope_reference
 
 
@@ -89,6 +89,7 @@ class _MlpGelu(torch.autograd.Function):
         h, pre = gemm(x2, w1, bias=b1, act="gelu")
         y = gemm(h, w2, bias=b2, residual=r2)
         ctx.save_for_backward(x2, w1, w2, pre, h)
+        ctx.params = (w1, b1, w2, b2)
         ctx.flags = (b1 is not None, b2 is not None, residual is not None)
         return y.reshape(*shape[:-1], w2.shape[0])
 
@@ -99,11 +100,12 @@ class _MlpGelu(torch.autograd.Function):
         dy2 = dy.reshape(-1, w2.shape[0])
         if dy2.stride(1) != 1 or dy2.stride(0) != dy2.shape[1]:
             dy2 = dy2.contiguous()
-        dw2 = gemm(dy2, h, a_mn=True, b_mn=True)
-        db2 = colsum(dy2) if has_b2 else None
+        p_w1, p_b1, p_w2, p_b2 = ctx.params
+        dw2 = weight_grad(dy2, h, p_w2)
+        db2 = bias_grad(dy2, p_b2) if has_b2 else None
         dpre = gemm(dy2, w2, b_mn=True, act="gelu_grad", aux=pre)
-        dw1 = gemm(dpre, x2, a_mn=True, b_mn=True)
-        db1 = colsum(dpre) if has_b1 else None
+        dw1 = weight_grad(dpre, x2, p_w1)
+        db1 = bias_grad(dpre, p_b1) if has_b1 else None
         dx = gemm(dpre, w1, b_mn=True).reshape(*dy.shape[:-1], w1.shape[1])
         return dx, dw1, db1, dw2, db2, (dy if has_res else None)
 
@@ -132,6 +134,7 @@ class _MlpGated(torch.autograd.Function):
                                                     stream_ptr()), "gated_fwd")
         y = gemm(act, w2, bias=b2, residual=r2)
         ctx.save_for_backward(x2, wgu, w2, gu, act)
+        ctx.params = (wgu, bgu, w2, b2)
         ctx.flags = (bgu is not None, b2 is not None, residual is not None, kind)
         return y.reshape(*shape[:-1], w2.shape[0])
 
@@ -144,15 +147,16 @@ class _MlpGated(torch.autograd.Function):
         dy2 = dy.reshape(-1, w2.shape[0])
         if dy2.stride(1) != 1 or dy2.stride(0) != dy2.shape[1]:
             dy2 = dy2.contiguous()
-        dw2 = gemm(dy2, act, a_mn=True, b_mn=True)
-        db2 = colsum(dy2) if has_b2 else None
+        p_wgu, p_bgu, p_w2, p_b2 = ctx.params
+        dw2 = weight_grad(dy2, act, p_w2)
+        db2 = bias_grad(dy2, p_b2) if has_b2 else None
         dact = gemm(dy2, w2, b_mn=True)
         dgu = torch.empty_like(gu)
         Hd = gu.shape[1] // 2
         _native.check(_native.lib().idrak_gated_bwd(gu.data_ptr(), dact.data_ptr(), dgu.data_ptr(), gu.shape[0], Hd,
                                                     kind, stream_ptr()), "gated_bwd")
-        dwgu = gemm(dgu, x2, a_mn=True, b_mn=True)
-        dbgu = colsum(dgu) if has_bgu else None
+        dwgu = weight_grad(dgu, x2, p_wgu)
+        dbgu = bias_grad(dgu, p_bgu) if has_bgu else None
         dx = gemm(dgu, wgu, b_mn=True).reshape(*dy.shape[:-1], wgu.shape[1])
         return dx, dwgu, dbgu, dw2, db2, (dy if has_res else None), None
 

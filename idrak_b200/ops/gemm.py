@@ -121,6 +121,31 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     return (out, aux_t) if act_id == ACT_GELU else out
 
 
+def weight_grad(dy2: torch.Tensor, x2: torch.Tensor, param: torch.Tensor | None):
+    """dW = dy^T x for an ``nn.Linear``-layout weight. Written straight into ``param.grad`` (and ``None``
+    returned) when the parameter takes direct gradient writes, else returned as a new tensor."""
+    from . import _grad
+    tgt = _grad.target(param)
+    if tgt is None:
+        return gemm(dy2, x2, a_mn=True, b_mn=True)
+    g, accumulate = tgt
+    gemm(dy2, x2, a_mn=True, b_mn=True, out=g, beta=accumulate)
+    _grad.written(param)
+    return None
+
+
+def bias_grad(dy2: torch.Tensor, param: torch.Tensor | None):
+    from . import _grad
+    from .rowops import colsum
+    tgt = _grad.target(param)
+    if tgt is None:
+        return colsum(dy2)
+    g, accumulate = tgt
+    colsum(dy2, out=g, accumulate=accumulate)
+    _grad.written(param)
+    return None
+
+
 class _Linear(torch.autograd.Function):
     """y = x @ W^T (+ b) (+ residual); W is [out, in] as in ``nn.Linear``."""
 
@@ -131,13 +156,17 @@ class _Linear(torch.autograd.Function):
         r2 = residual.reshape(-1, weight.shape[0]) if residual is not None else None
         y = gemm(x2, weight, bias=bias, residual=r2)
         ctx.save_for_backward(x2, weight)
+        ctx.params = (weight, bias)          # the Parameter objects, for direct gradient writes
         ctx.has_bias = bias is not None
         ctx.has_res = residual is not None
         return y.reshape(*shape[:-1], weight.shape[0])
 
     @staticmethod
     def backward(ctx, dy):
+        from . import _grad
+        from .rowops import colsum
         x2, weight = ctx.saved_tensors
+        w_param, b_param = ctx.params
         dy2 = dy.reshape(-1, weight.shape[0])
         if dy2.stride(1) != 1 or dy2.stride(0) != dy2.shape[1]:
             dy2 = dy2.contiguous()
@@ -145,10 +174,9 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, weight, b_mn=True).reshape(*dy.shape[:-1], weight.shape[1])
         if ctx.needs_input_grad[1]:
-            dw = gemm(dy2, x2, a_mn=True, b_mn=True)
+            dw = weight_grad(dy2, x2, w_param)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            from .rowops import colsum
-            db = colsum(dy2)
+            db = bias_grad(dy2, b_param)
         if ctx.has_res and ctx.needs_input_grad[3]:
             dres = dy
         return dx, dw, db, dres

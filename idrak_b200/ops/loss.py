@@ -79,14 +79,27 @@ class _TokenCrossEntropy(torch.autograd.Function):
                     gemm(logits, h2[r0:r1], a_mn=True, b_mn=True, out=dw, beta=True)
         loss = torch.cat(losses).sum() * inv
         ctx.save_for_backward(dh, dw)
+        ctx.param = weight
         ctx.hshape, ctx.wdtype = hidden.shape, weight.dtype
         return loss
 
     @staticmethod
     def backward(ctx, dloss):
+        from . import _grad
         dh, dw = ctx.saved_tensors
         gh = (dh * dloss.to(dh.dtype)).reshape(ctx.hshape) if dh is not None and ctx.needs_input_grad[0] else None
-        gw = (dw * dloss).to(ctx.wdtype) if dw is not None and ctx.needs_input_grad[1] else None
+        gw = None
+        if dw is not None and ctx.needs_input_grad[1]:
+            tgt = _grad.target(ctx.param)
+            if tgt is not None:
+                g, accumulate = tgt
+                if accumulate:
+                    g.add_((dw * dloss).to(g.dtype))
+                else:
+                    torch.mul(dw, dloss.to(dw.dtype), out=g) if g.dtype == dw.dtype else g.copy_(dw * dloss)
+                _grad.written(ctx.param)
+            else:
+                gw = (dw * dloss).to(ctx.wdtype)
         return gh, gw, None, None, None, None
 
 

@@ -75,8 +75,10 @@ def norm_forward(x, weight, bias, eps, rms, residual=None):
     return out.reshape(x.shape), mean, rstd, (summed.reshape(x.shape) if summed is not None else None)
 
 
-def norm_backward(dy, x, weight, mean, rstd, rms, has_bias, dres=None):
-    """Returns (dx, dweight, dbias). ``x`` is the tensor that was normalised. ``dres`` is added to dx."""
+def norm_backward(dy, x, weight, mean, rstd, rms, has_bias, dres=None, w_param=None, b_param=None):
+    """Returns (dx, dweight, dbias). ``x`` is the tensor that was normalised. ``dres`` is added to dx.
+    When ``w_param`` (and ``b_param``) take direct gradient writes, dweight / dbias go straight into their
+    ``.grad`` and come back as None."""
     C = x.shape[-1]
     dy2, x2 = dy.reshape(-1, C), x.reshape(-1, C)
     rows = x2.shape[0]
@@ -97,13 +99,27 @@ def norm_backward(dy, x, weight, mean, rstd, rms, has_bias, dres=None):
     dx = torch.empty_like(x2)
     blocks = lib.idrak_norm_bwd_blocks(rows)
     part = scratch("norm_bwd", 2 * blocks * C, torch.float32, x.device)
-    dw = torch.empty_like(weight)
-    db = torch.empty_like(weight) if has_bias else None
+    from . import _grad
+    tw = _grad.target(w_param)
+    tb = _grad.target(b_param) if has_bias else None
+    direct = tw is not None and (not has_bias or tb is not None)
+    if direct:
+        dw, accumulate = tw
+        db = tb[0] if has_bias else None
+    else:
+        dw, accumulate = torch.empty_like(weight), False
+        db = torch.empty_like(weight) if has_bias else None
     d2 = dres.reshape(-1, C).contiguous() if dres is not None else None
     rc = lib.idrak_norm_bwd(dy2.data_ptr(), x2.data_ptr(), weight.data_ptr(), ptr(mean), rstd.data_ptr(), ptr(d2),
                             dx.data_ptr(), part.data_ptr(), part.data_ptr() + 4 * blocks * C, dw.data_ptr(),
-                            ptr(db), 0, 0, rows, C, int(rms), stream_ptr())
+                            ptr(db), 1 if dw.dtype == torch.float32 else 0, int(accumulate), rows, C, int(rms),
+                            stream_ptr())
     _native.check(rc, "idrak_norm_bwd")
+    if direct:
+        _grad.written(w_param)
+        if has_bias:
+            _grad.written(b_param)
+        return dx.reshape(x.shape), None, None
     return dx.reshape(x.shape), dw, db
 
 
@@ -112,13 +128,14 @@ class _Norm(torch.autograd.Function):
     def forward(ctx, x, weight, bias, eps, rms):
         out, mean, rstd, _ = norm_forward(x, weight, bias, eps, rms)
         ctx.save_for_backward(x, weight, mean, rstd)
+        ctx.params = (weight, bias)
         ctx.rms, ctx.has_bias = rms, bias is not None
         return out
 
     @staticmethod
     def backward(ctx, dy):
         x, weight, mean, rstd = ctx.saved_tensors
-        dx, dw, db = norm_backward(dy, x, weight, mean, rstd, ctx.rms, ctx.has_bias)
+        dx, dw, db = norm_backward(dy, x, weight, mean, rstd, ctx.rms, ctx.has_bias, None, *ctx.params)
         return dx, dw, db, None, None
 
 
@@ -274,6 +291,7 @@ class _Embedding(torch.autograd.Function):
                                                seq, C, stream_ptr())
         _native.check(rc, "idrak_embedding_fwd")
         ctx.save_for_backward(ids32)
+        ctx.params = (wte, wpe)
         ctx.wte_shape, ctx.wpe_shape, ctx.seq = wte.shape, (wpe.shape if wpe is not None else None), seq
         ctx.dtype = wte.dtype
         return out.reshape(*ids.shape, C)
@@ -285,17 +303,37 @@ class _Embedding(torch.autograd.Function):
         d2 = dout.reshape(-1, C).contiguous()
         tokens = d2.shape[0]
         lib = _native.lib()
-        dwte = torch.zeros(ctx.wte_shape, dtype=ctx.dtype, device=dout.device)
+        from . import _grad
+        p_wte, p_wpe = ctx.params
+        tgt = _grad.target(p_wte)
+        if tgt is not None:
+            dwte, accumulate = tgt
+            if not accumulate:
+                dwte.zero_()          # the kernel adds the rows of the tokens that occur
+        else:
+            dwte = torch.zeros(ctx.wte_shape, dtype=ctx.dtype, device=dout.device)
         sorted_ids, order = torch.sort(ids32, stable=True)
         order32 = order.to(torch.int32)
         rc = lib.idrak_wte_bwd(sorted_ids.data_ptr(), order32.data_ptr(), d2.data_ptr(), dwte.data_ptr(), tokens, C,
-                               0, stream_ptr())
+                               1 if dwte.dtype == torch.float32 else 0, stream_ptr())
         _native.check(rc, "idrak_wte_bwd")
+        if tgt is not None:
+            _grad.written(p_wte)
+            dwte = None
         dwpe = None
         if ctx.wpe_shape is not None:
-            dwpe = torch.zeros(ctx.wpe_shape, dtype=ctx.dtype, device=dout.device)
-            rc = lib.idrak_wpe_bwd(d2.data_ptr(), dwpe.data_ptr(), tokens // ctx.seq, ctx.seq, C, 0, 0, stream_ptr())
-            _native.check(rc, "idrak_wpe_bwd")
+            tp = _grad.target(p_wpe)
+            if tp is not None:
+                g, accumulate = tp
+                rc = lib.idrak_wpe_bwd(d2.data_ptr(), g.data_ptr(), tokens // ctx.seq, ctx.seq, C,
+                                       1 if g.dtype == torch.float32 else 0, int(accumulate), stream_ptr())
+                _native.check(rc, "idrak_wpe_bwd")
+                _grad.written(p_wpe)
+            else:
+                dwpe = torch.zeros(ctx.wpe_shape, dtype=ctx.dtype, device=dout.device)
+                rc = lib.idrak_wpe_bwd(d2.data_ptr(), dwpe.data_ptr(), tokens // ctx.seq, ctx.seq, C, 0, 0,
+                                       stream_ptr())
+                _native.check(rc, "idrak_wpe_bwd")
         return None, dwte, dwpe, None
 
 

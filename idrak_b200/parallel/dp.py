@@ -39,7 +39,7 @@ class _ShardedAdamW:
         self.weight_decay, self.max_grad_norm = weight_decay, max_grad_norm
         self.step_count = 0
         self.grad_scale = 1.0
-        self.zero_grad_in_step = True
+        self.zero_grad_in_step = False
         self._hyper_host = torch.zeros(16, H_COUNT, dtype=torch.float32).pin_memory()
         self._hyper_dev = torch.zeros(H_COUNT, dtype=torch.float32, device=device)
         self.master = self.m = self.v = None
@@ -173,6 +173,7 @@ class DataParallel:
         for p in params:
             i = index_of[id(p)]
             self._handles.append(p.register_post_accumulate_grad_hook(lambda _p, i=i: self._grad_ready(i)))
+            p._idrak_ready = (lambda i=i: self._grad_ready(i))     # called by direct gradient writes
 
     def _grad_ready(self, index: int):
         if not self._overlapping:
@@ -257,14 +258,12 @@ class DataParallel:
             # every peer's last update kernel has published "done": their stores into my parameters landed and
             # they no longer read my gradients
             _native.check(lib.idrak_comm_wait(self.comm.ctx, CH_STEP_DONE, 0, s_ptr), "comm_wait")
-            self.flat.grad.zero_()
         done = torch.cuda.Event()
         done.record(self._side)
         main.wait_event(done)
 
     def zero_grad(self):
-        if self.mode == "nccl":
-            self.flat.zero_grad()
+        self.flat.zero_grad()
 
     def close(self):
         for h in self._handles:

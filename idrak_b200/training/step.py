@@ -15,10 +15,13 @@ from typing import Callable, Optional
 
 import torch
 
+from ..ops import _grad
+
 
 class TrainStep:
     def __init__(self, model: torch.nn.Module, optimizer, *, sync=None, grad_accumulation: int = 1,
-                 use_graph: bool = False, loss_fn: Optional[Callable] = None, ignore_index: Optional[int] = None):
+                 use_graph: bool = False, loss_fn: Optional[Callable] = None, ignore_index: Optional[int] = None,
+                 direct_grads: bool = True):
         self.model, self.optimizer, self.sync = model, optimizer, sync
         self.grad_accumulation = max(1, grad_accumulation)
         self.use_graph = use_graph
@@ -34,6 +37,11 @@ class TrainStep:
         self._first_replay = False
         self.graph_kernels = 0
         self.replays = 0
+        self._direct = bool(direct_grads) and self.device.type == "cuda"
+        self._needs_zero = None
+        if self._direct:
+            _grad.enable(p for p in model.parameters() if p.requires_grad)
+            _grad.next_step()
 
     # ------------------------------------------------------------------ host -> device staging
     def stage(self, ids_host: torch.Tensor, targets_host: torch.Tensor):
@@ -78,6 +86,16 @@ class TrainStep:
         return loss
 
     def _zero_grads(self):
+        if self._direct:
+            # parameters whose gradient kernels store into .grad need no zero-fill: the first write of the next
+            # step overwrites. The rest (gradients that arrive through autograd's accumulate nodes) are zeroed.
+            if self._needs_zero is None:
+                self._needs_zero = [p for p in self.model.parameters()
+                                    if p.grad is not None and getattr(p, "_idrak_epoch", -1) != _grad._EPOCH]
+            for p in self._needs_zero:
+                p.grad.zero_()
+            _grad.next_step()
+            return
         if getattr(self.optimizer, "zero_grad_in_step", False):
             return
         if self.sync is not None and hasattr(self.sync, "zero_grad"):
