@@ -90,10 +90,11 @@ def _slices_attention(spec) -> Dict[str, Tuple[int, int]]:
 
 
 def _make(base_rows: torch.Tensor, rank, alpha, dora, rslora):
+    dtype = base_rows.dtype if base_rows.dtype != torch.float32 or not base_rows.is_cuda else torch.bfloat16
     if dora:
-        return DoraAdapter(base_rows.detach(), rank, alpha, rslora)
+        return DoraAdapter(base_rows.detach().to(dtype), rank, alpha, rslora)
     out_f, in_f = base_rows.shape
-    return LoraAdapter(in_f, out_f, rank, alpha, rslora, base_rows.dtype, base_rows.device)
+    return LoraAdapter(in_f, out_f, rank, alpha, rslora, dtype, base_rows.device)
 
 
 def add_adapters(model: Decoder, rank: int = 16, alpha: float = 32.0, targets: Sequence[str] = DEFAULT_TARGETS,
@@ -104,30 +105,33 @@ def add_adapters(model: Decoder, rank: int = 16, alpha: float = 32.0, targets: S
     if freeze_base:
         for p in model.parameters():
             p.requires_grad_(False)
+    from ..quant import dense_weight
     for blk in model.blocks:
         a: SelfAttention = blk.attn
         sl = _slices_attention(spec)
         aset = AdapterSet()
+        qkv_w = dense_weight(a, "qkv")
         for t in ("q", "k", "v"):
             if t in targets:
                 lo, hi = sl[t]
-                aset.items[t] = _make(a.qkv_weight[lo:hi], rank, alpha, dora, rslora)
+                aset.items[t] = _make(qkv_w[lo:hi], rank, alpha, dora, rslora)
         if "o" in targets:
-            aset.items["o"] = _make(a.o_weight, rank, alpha, dora, rslora)
+            aset.items["o"] = _make(dense_weight(a, "o"), rank, alpha, dora, rslora)
         a.adapters = aset
         if isinstance(blk.mlp, FeedForward):
             f: FeedForward = blk.mlp
             fset = AdapterSet()
-            hidden = f.down_weight.shape[1]
+            hidden = f.hidden
+            up_w = dense_weight(f, "up")
             if spec.gated:
                 if "gate" in targets:
-                    fset.items["gate"] = _make(f.up_weight[:hidden], rank, alpha, dora, rslora)
+                    fset.items["gate"] = _make(up_w[:hidden], rank, alpha, dora, rslora)
                 if "up" in targets:
-                    fset.items["up"] = _make(f.up_weight[hidden:], rank, alpha, dora, rslora)
+                    fset.items["up"] = _make(up_w[hidden:], rank, alpha, dora, rslora)
             elif "up" in targets:
-                fset.items["up"] = _make(f.up_weight, rank, alpha, dora, rslora)
+                fset.items["up"] = _make(up_w, rank, alpha, dora, rslora)
             if "down" in targets:
-                fset.items["down"] = _make(f.down_weight, rank, alpha, dora, rslora)
+                fset.items["down"] = _make(dense_weight(f, "down"), rank, alpha, dora, rslora)
             f.adapters = fset
     if "head" in targets and model.head is not None:
         hs = AdapterSet()
@@ -210,16 +214,24 @@ def _merged(w: torch.Tensor, ad: LoraAdapter) -> torch.Tensor:
 # --------------------------------------------------------------------------- forward helpers used by the decoder
 def project_with_adapters(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                           adapters: Optional[AdapterSet], slices: Dict[str, Tuple[int, int]],
-                          residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``x W^T + b`` with each adapter's contribution added to its column slice of the output."""
+                          residual: Optional[torch.Tensor] = None, packed=None) -> torch.Tensor:
+    """``x W^T + b`` with each adapter's contribution added to its column slice of the output.
+    ``packed`` is the int8 / int4 replacement of ``weight`` when the base has been quantised."""
+    def base(bias_, residual_):
+        if packed is not None:
+            from ..quant.weights import qlinear
+            return qlinear(x, packed, bias_, residual_)
+        return ops.linear(x, weight, bias_, residual_)
+
+    out_features = packed.cols if packed is not None else weight.shape[0]
     if adapters is None or len(adapters.items) == 0:
-        return ops.linear(x, weight, bias, residual)
+        return base(bias, residual)
     has_dora = any(isinstance(ad, DoraAdapter) for ad in adapters.items.values())
     if not has_dora:
-        y = ops.linear(x, weight, bias, residual)
+        y = base(bias, residual)
         parts, last = [], 0
         order = sorted(((lo, hi, n) for n, (lo, hi) in slices.items() if n in adapters), key=lambda t: t[0])
-        if len(order) == 1 and order[0][0] == 0 and order[0][1] == weight.shape[0]:
+        if len(order) == 1 and order[0][0] == 0 and order[0][1] == out_features:
             return y + adapters[order[0][2]].delta(x)
         for lo, hi, n in order:
             if lo > last:
@@ -230,7 +242,8 @@ def project_with_adapters(x: torch.Tensor, weight: torch.Tensor, bias: Optional[
             parts.append(y[..., last:])
         return torch.cat(parts, dim=-1)
     # DoRA rescales the base output, so bias and residual are applied after the rescale
-    y = ops.linear(x, weight)
+    y = base(None, None)
+    dense = weight if packed is None else packed.dequantize().t().to(x.dtype)      # [out, in]
     parts, last = [], 0
     for lo, hi, n in sorted(((lo, hi, n) for n, (lo, hi) in slices.items()), key=lambda t: t[0]):
         if lo > last:
@@ -238,7 +251,7 @@ def project_with_adapters(x: torch.Tensor, weight: torch.Tensor, bias: Optional[
         seg = y[..., lo:hi]
         if n in adapters:
             ad = adapters[n]
-            seg = ad.apply(x, weight[lo:hi], seg) if isinstance(ad, DoraAdapter) else seg + ad.delta(x)
+            seg = ad.apply(x, dense[lo:hi], seg) if isinstance(ad, DoraAdapter) else seg + ad.delta(x)
         parts.append(seg)
         last = hi
     if last < y.shape[-1]:

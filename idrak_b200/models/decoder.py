@@ -41,6 +41,14 @@ class Norm(nn.Module):
         return ops.rms_norm(x, w, self.eps)
 
 
+def project(x, weight, packed, bias=None, residual=None):
+    """``x W^T + b (+ residual)`` over the dense weight, or over its packed int8 / int4 replacement."""
+    if packed is not None:
+        from ..quant.weights import qlinear
+        return qlinear(x, packed, bias, residual)
+    return ops.linear(x, weight, bias, residual)
+
+
 class SelfAttention(nn.Module):
     def __init__(self, spec: DecoderSpec, layer: int):
         super().__init__()
@@ -61,13 +69,15 @@ class SelfAttention(nn.Module):
         spec = self.spec
         H, Hkv, D = spec.heads, spec.kv_heads, spec.head_dim
         adapters = getattr(self, "adapters", None)
+        packed = getattr(self, "packed", {})
         if adapters is not None:
             from ..adapters.lora import _slices_attention, project_with_adapters
-            qkv = project_with_adapters(x, self.qkv_weight, self.qkv_bias, adapters, _slices_attention(spec))
+            qkv = project_with_adapters(x, self.qkv_weight, self.qkv_bias, adapters, _slices_attention(spec),
+                                        packed=packed.get("qkv"))
             if not qkv.is_contiguous():
                 qkv = qkv.contiguous()
         else:
-            qkv = ops.linear(x, self.qkv_weight, self.qkv_bias)
+            qkv = project(x, self.qkv_weight, packed.get("qkv"), self.qkv_bias)
         window = spec.sliding_window if spec.is_windowed(self.layer) else None
         simple = not spec.qk_norm and window is None and spec.attention_softcap is None and (
             self.rope is None or self.rope.scaling is None)
@@ -80,8 +90,8 @@ class SelfAttention(nn.Module):
         if adapters is not None and "o" in adapters:
             from ..adapters.lora import project_with_adapters
             return project_with_adapters(a, self.o_weight, self.o_bias, adapters,
-                                         {"o": (0, self.o_weight.shape[0])}, residual)
-        return ops.linear(a, self.o_weight, self.o_bias, residual)
+                                         {"o": (0, spec.dim)}, residual, packed=packed.get("o"))
+        return project(a, self.o_weight, packed.get("o"), self.o_bias, residual)
 
     def _general(self, qkv, positions, window):
         """qk-norm, scaled RoPE tables, sliding windows and soft-capping: composed from primitives."""
@@ -143,6 +153,7 @@ class FeedForward(nn.Module):
         super().__init__()
         self.spec = spec
         ff = ff_dim or spec.ff_dim
+        self.hidden = ff
         mult = 2 if spec.gated else 1
         self.up_weight = nn.Parameter(torch.empty(mult * ff, spec.dim))      # gated: [gate; up]
         self.up_bias = nn.Parameter(torch.zeros(mult * ff)) if spec.feed_forward_bias else None
@@ -152,8 +163,9 @@ class FeedForward(nn.Module):
     def forward(self, x, residual=None):
         spec = self.spec
         adapters = getattr(self, "adapters", None)
-        if adapters is not None and len(adapters.items) > 0:
-            return self._forward_adapted(x, residual, adapters)
+        packed = getattr(self, "packed", {})
+        if (adapters is not None and len(adapters.items) > 0) or packed:
+            return self._forward_adapted(x, residual, adapters, packed)
         if spec.gated:
             kind = {"silu": "silu", "gelu": "gelu", "relu": "relu"}.get(spec.activation)
             if kind is None:   # tanh(gate) * sigmoid(up)
@@ -169,25 +181,28 @@ class FeedForward(nn.Module):
         return ops.linear(h, self.down_weight, self.down_bias, residual)
 
 
-    def _forward_adapted(self, x, residual, adapters):
-        """The same block with low-rank adapters on gate / up / down: projections run one by one."""
+    def _forward_adapted(self, x, residual, adapters, packed=None):
+        """The same block with low-rank adapters on gate / up / down and / or a packed (int8 / int4) base:
+        projections run one by one."""
         from ..adapters.lora import project_with_adapters
         spec = self.spec
-        hidden = self.down_weight.shape[1]
+        packed = packed or {}
+        hidden = self.hidden
         if spec.gated:
             gu = project_with_adapters(x, self.up_weight, self.up_bias, adapters,
-                                       {"gate": (0, hidden), "up": (hidden, 2 * hidden)})
+                                       {"gate": (0, hidden), "up": (hidden, 2 * hidden)}, packed=packed.get("up"))
             kind = {"silu": "silu", "gelu": "gelu", "relu": "relu"}.get(spec.activation)
             if kind is None:
                 h = torch.tanh(gu[..., :hidden]) * torch.sigmoid(gu[..., hidden:])
             else:
                 h = ops.gated_activation(gu.contiguous(), kind)
         else:
-            h = project_with_adapters(x, self.up_weight, self.up_bias, adapters, {"up": (0, hidden)})
+            h = project_with_adapters(x, self.up_weight, self.up_bias, adapters, {"up": (0, hidden)},
+                                      packed=packed.get("up"))
             h = ops.gelu(h) if spec.activation == "gelu" else (
                 torch.relu(h) if spec.activation == "relu" else torch.nn.functional.silu(h))
         return project_with_adapters(h, self.down_weight, self.down_bias, adapters,
-                                     {"down": (0, self.down_weight.shape[0])}, residual)
+                                     {"down": (0, spec.dim)}, residual, packed=packed.get("down"))
 
 
 class MixtureOfExperts(nn.Module):
