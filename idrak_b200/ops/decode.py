@@ -1,0 +1,168 @@
+"""Serving-side ops: paged KV cache writes, decode attention over block tables, device-side sampling.
+
+Each op runs the sm_100a kernel on CUDA tensors and a plain PyTorch statement of the same math on CPU
+tensors (the oracle of the GPU tests and the engine's CPU path).
+
+Reference: Tensor.AttentionRows / KeyValueWrite / SampleRows (src/Idrak.Abstraction/Tensors/Tensor.Decoding.cs),
+KeyValueCache (src/Idrak.Abstraction/Generation/Decoding.cs:243), TokenSampler (TokenSamplers.cs).
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Optional
+
+import torch
+
+from .. import _native
+from ._util import ptr, scratch, stream_ptr
+
+_BOUND = False
+
+
+def _bind():
+    global _BOUND
+    if _BOUND:
+        return
+    vp, i, f, ll = C.c_void_p, C.c_int, C.c_float, C.c_longlong
+    _native.bind("idrak_decode_partial_floats", ll, [i, i, i, i])
+    _native.bind("idrak_paged_decode", i, [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, i, vp])
+    _native.bind("idrak_kv_write_paged", i, [vp, vp, ll, vp, vp, vp, i, i, vp])
+    _native.bind("idrak_argmax_rows", i, [vp, i, i, i, ll, vp, vp])
+    _native.bind("idrak_sample_rows", i, [vp, i, i, i, ll, vp, vp, vp, vp, vp, vp, vp, i, vp, vp, vp, vp, C.c_uint, vp])
+    _BOUND = True
+
+
+# --------------------------------------------------------------------------- KV cache
+def kv_write_paged(k_src: torch.Tensor, v_src: torch.Tensor, slots: torch.Tensor, k_cache: torch.Tensor,
+                   v_cache: torch.Tensor) -> None:
+    """Write the new tokens' keys / values (``[tokens, Hkv, D]`` views with packed heads) into cache slots
+    ``slots[t] = block * block_size + offset`` (negative = skip)."""
+    tokens, Hkv, D = k_src.shape
+    row = Hkv * D
+    if not k_src.is_cuda:
+        flat_k, flat_v = k_cache.view(-1, row), v_cache.view(-1, row)
+        keep = slots >= 0
+        flat_k[slots[keep].long()] = k_src.reshape(tokens, row)[keep]
+        flat_v[slots[keep].long()] = v_src.reshape(tokens, row)[keep]
+        return
+    _bind()
+    assert k_src.stride(2) == 1 and k_src.stride(1) == D and v_src.stride(0) == k_src.stride(0)
+    assert slots.dtype == torch.int32
+    rc = _native.lib().idrak_kv_write_paged(k_src.data_ptr(), v_src.data_ptr(), k_src.stride(0), slots.data_ptr(),
+                                            k_cache.data_ptr(), v_cache.data_ptr(), tokens, row, stream_ptr())
+    _native.check(rc, "idrak_kv_write_paged")
+
+
+def paged_decode_reference(q, k_cache, v_cache, block_table, seq_lens, scale=None, window: int = 0):
+    seqs, H, D = q.shape
+    _, bs, Hkv, _ = k_cache.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    out = torch.zeros_like(q, dtype=torch.float32)
+    for s in range(seqs):
+        n = int(seq_lens[s])
+        if n == 0:
+            continue
+        blocks = block_table[s, : (n + bs - 1) // bs].long()
+        k = k_cache[blocks].reshape(-1, Hkv, D)[:n].float()
+        v = v_cache[blocks].reshape(-1, Hkv, D)[:n].float()
+        if window and n > window:
+            k, v = k[n - window:], v[n - window:]
+        k = k.repeat_interleave(H // Hkv, dim=1)
+        v = v.repeat_interleave(H // Hkv, dim=1)
+        sc = torch.einsum("hd,nhd->hn", q[s].float(), k) * scale
+        out[s] = torch.einsum("hn,nhd->hd", torch.softmax(sc, -1), v)
+    return out.to(q.dtype)
+
+
+def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
+                 seq_lens: torch.Tensor, scale: Optional[float] = None, window: int = 0,
+                 splits: Optional[int] = None, max_len_hint: Optional[int] = None) -> torch.Tensor:
+    """One query token per sequence against its cached keys / values. q: ``[seqs, H, D]``."""
+    if not q.is_cuda:
+        return paged_decode_reference(q, k_cache, v_cache, block_table, seq_lens, scale, window)
+    _bind()
+    seqs, H, D = q.shape
+    _, bs, Hkv, _ = k_cache.shape
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    lib = _native.lib()
+    if splits is None:
+        # fill the machine: sequences x kv heads CTAs may be few; long contexts split along the keys
+        ctas = seqs * Hkv
+        longest = max_len_hint if max_len_hint is not None else block_table.shape[1] * bs
+        splits = max(1, min(lib.idrak_sm_count() * 2 // max(ctas, 1), (longest + 255) // 256, 32))
+    out = torch.empty_like(q)
+    part = None
+    if splits > 1:
+        part = scratch("decode_partial", lib.idrak_decode_partial_floats(seqs, H, D, splits), torch.float32, q.device)
+    assert q.is_contiguous() and block_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
+    rc = lib.idrak_paged_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+                                seq_lens.data_ptr(), out.data_ptr(), ptr(part), seqs, H, Hkv, D, bs,
+                                block_table.shape[1], splits, float(scale), int(window), stream_ptr())
+    _native.check(rc, "idrak_paged_decode")
+    return out
+
+
+# --------------------------------------------------------------------------- sampling
+def argmax_rows(logits: torch.Tensor, vocab: Optional[int] = None) -> torch.Tensor:
+    """Greedy token per row (lowest id among ties). logits: ``[rows, ld]`` bf16 or fp32."""
+    rows, ld = logits.shape
+    vocab = vocab or ld
+    if not logits.is_cuda:
+        return logits[:, :vocab].float().argmax(-1).to(torch.int32)
+    _bind()
+    assert logits.stride(1) == 1 and logits.dtype in (torch.bfloat16, torch.float32)
+    ids = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    rc = _native.lib().idrak_argmax_rows(logits.data_ptr(), int(logits.dtype == torch.float32), rows, vocab,
+                                         logits.stride(0), ids.data_ptr(), stream_ptr())
+    _native.check(rc, "idrak_argmax_rows")
+    return ids
+
+
+def sample_rows_reference(logits, vocab, temperature, top_k, top_p, min_p, uniforms):
+    """Same filtering as the kernel; ``uniforms[row]`` in [0,1) picks along the kept, sorted candidates."""
+    out = []
+    for r in range(logits.shape[0]):
+        v = logits[r, :vocab].float() / max(float(temperature[r]), 1e-6)
+        k = int(top_k[r]) if int(top_k[r]) > 0 else 64
+        k = min(k, 64, vocab)
+        vals, idx = torch.sort(v, descending=True, stable=True)
+        vals, idx = vals[:k], idx[:k]
+        pr = torch.exp(vals - vals[0])
+        keep = k
+        if float(min_p[r]) > 0:
+            keep = max(int((pr >= float(min_p[r]) * pr[0]).sum()), 1)
+        if float(top_p[r]) < 1:
+            cum = torch.cumsum(pr[:keep] / pr.sum(), 0)
+            c = int((cum < float(top_p[r])).sum()) + 1
+            keep = max(min(c, keep), 1)
+        cum = torch.cumsum(pr[:keep], 0)
+        u = float(uniforms[r]) * float(cum[-1])
+        pick = int((cum <= u).sum())
+        out.append(int(idx[min(pick, keep - 1)]))
+    return torch.tensor(out, dtype=torch.int32)
+
+
+def sample_rows(logits: torch.Tensor, vocab: int, temperature: torch.Tensor, top_k: torch.Tensor,
+                top_p: torch.Tensor, min_p: torch.Tensor, seeds: torch.Tensor, step: int,
+                history: Optional[torch.Tensor] = None, repeat_penalty: Optional[torch.Tensor] = None,
+                presence_penalty: Optional[torch.Tensor] = None, frequency_penalty: Optional[torch.Tensor] = None,
+                return_logprobs: bool = False):
+    """Sample one token per row on the device. Per-row settings are tensors on the logits' device
+    (float32 / int32; ``seeds`` int64)."""
+    rows = logits.shape[0]
+    if not logits.is_cuda:
+        g = torch.Generator().manual_seed(int(seeds[0]) * 1000003 + step)
+        u = torch.rand(rows, generator=g)
+        ids = sample_rows_reference(logits, vocab, temperature, top_k, top_p, min_p, u)
+        return (ids, torch.zeros(rows)) if return_logprobs else ids
+    _bind()
+    ids = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    lp = torch.empty(rows, dtype=torch.float32, device=logits.device) if return_logprobs else None
+    rc = _native.lib().idrak_sample_rows(
+        logits.data_ptr(), int(logits.dtype == torch.float32), rows, vocab, logits.stride(0), ids.data_ptr(), ptr(lp),
+        temperature.data_ptr(), top_k.data_ptr(), top_p.data_ptr(), min_p.data_ptr(), ptr(history),
+        history.shape[1] if history is not None else 0, ptr(repeat_penalty), ptr(presence_penalty),
+        ptr(frequency_penalty), seeds.data_ptr(), int(step), stream_ptr())
+    _native.check(rc, "idrak_sample_rows")
+    return (ids, lp) if return_logprobs else ids

@@ -1,0 +1,242 @@
+"""Runs a decoder over the paged KV cache: packed prefill of several prompts, and batched one-token decode.
+
+Prefill packs the uncached tokens of every admitted prompt into one ``[1, T, dim]`` activation so each
+projection is a single GEMM; attention then runs per prompt (flash kernel over that prompt's keys) and the
+keys / values go to the prompt's cache blocks. Decode advances every running sequence by one token: one
+GEMM per projection over ``[n, dim]``, in-place RoPE at each sequence's position, a paged cache write, the
+split-KV decode-attention kernel over the block tables, the head GEMM, and the device sampler - the host
+reads one int per sequence and nothing else.
+
+Model features outside the kernels' fast path (attention soft-capping, scaled RoPE tables, query/key norms)
+are composed from primitives around the same cache; numerics equal the training forward.
+
+Reference: TextGenerator's prefill / decode loop (src/Idrak/Generation/TextGenerator.cs:569-623), KeyValueCache and
+decode primitives (src/Idrak.Abstraction/Generation/Decoding.cs:243, Tensors/Tensor.Decoding.cs).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence
+
+import torch
+
+from .. import ops
+from ..models.decoder import Decoder, FeedForward, apply_rope_table, masked_attention, project
+from ..ops import decode as dops
+
+
+@dataclass
+class PrefillItem:
+    tokens: List[int]          # the tokens to compute (positions start .. start + len - 1)
+    start: int                 # number of leading tokens already in the cache (shared prefix)
+    blocks: List[int]          # block table covering positions 0 .. start + len
+
+
+class ModelRunner:
+    def __init__(self, model: Decoder, num_blocks: int, block_size: int = 16, max_batch: int = 256,
+                 cache_dtype: Optional[torch.dtype] = None):
+        self.model = model.eval()
+        self.spec = model.spec
+        p = next(model.parameters())
+        self.device, self.dtype = p.device, p.dtype
+        self.block_size, self.num_blocks, self.max_batch = block_size, num_blocks, max_batch
+        s = self.spec
+        cd = cache_dtype or self.dtype
+        self.k_cache = [torch.zeros(num_blocks, block_size, s.kv_heads, s.head_dim, dtype=cd, device=self.device)
+                        for _ in range(s.layers)]
+        self.v_cache = [torch.zeros_like(k) for k in self.k_cache]
+        self.max_blocks_per_seq = (s.max_positions + block_size - 1) // block_size
+
+    # ------------------------------------------------------------------ sizing
+    @staticmethod
+    def blocks_that_fit(spec, bytes_available: int, block_size: int = 16, elem_bytes: int = 2) -> int:
+        per_block = 2 * spec.layers * block_size * spec.kv_heads * spec.head_dim * elem_bytes
+        return max(int(bytes_available // per_block), 1)
+
+    # ------------------------------------------------------------------ shared pieces
+    def _embed(self, ids: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        m, s = self.model, self.spec
+        x = ops.embedding(ids.view(1, -1), m.embed, None)
+        if m.pos is not None:
+            x = x + m.pos[positions.long()][None]
+        if s.embedding_scale is not None:
+            x = x * s.embedding_scale
+        return x
+
+    def _qkv(self, attn, x):
+        adapters = getattr(attn, "adapters", None)
+        packed = getattr(attn, "packed", {})
+        if adapters is not None:
+            from ..adapters.lora import _slices_attention, project_with_adapters
+            qkv = project_with_adapters(x, attn.qkv_weight, attn.qkv_bias, adapters, _slices_attention(self.spec),
+                                        packed=packed.get("qkv"))
+            return qkv.contiguous()
+        return project(x, attn.qkv_weight, packed.get("qkv"), attn.qkv_bias)
+
+    def _out(self, attn, a, residual):
+        adapters = getattr(attn, "adapters", None)
+        packed = getattr(attn, "packed", {})
+        if adapters is not None and "o" in adapters:
+            from ..adapters.lora import project_with_adapters
+            return project_with_adapters(a, attn.o_weight, attn.o_bias, adapters, {"o": (0, self.spec.dim)}, residual,
+                                         packed=packed.get("o"))
+        return project(a, attn.o_weight, packed.get("o"), attn.o_bias, residual)
+
+    def _rotate(self, attn, qkv2, positions):
+        """RoPE (and query / key norms) in place on the packed ``[T, (H + 2 Hkv) D]`` projection."""
+        s = self.spec
+        H, Hkv, D = s.heads, s.kv_heads, s.head_dim
+        T = qkv2.shape[0]
+        qk = qkv2[:, : (H + Hkv) * D].unflatten(-1, (H + Hkv, D))
+        if s.qk_norm:
+            q = attn.q_norm(qk[:, :H].contiguous())
+            k = attn.k_norm(qk[:, H:].contiguous())
+            qk[:, :H].copy_(q)
+            qk[:, H:].copy_(k)
+        rope = attn.rope
+        if rope is None:
+            return
+        if rope.scaling is None:
+            ops.rope_(qk, positions, rope.theta, rope.rotary_dim, 1.0)
+        else:
+            r = apply_rope_table(qk[None], rope, positions[None])
+            qk.copy_(r[0])
+
+    def _block(self, blk, x, attend):
+        """One decoder block around ``attend(attn_module, normed_x, residual_or_None)``; mirrors DecoderBlock.forward."""
+        s = self.spec
+        if s.parallel_blocks:
+            h = blk.attn_norm(x)
+            return x + attend(blk.attn, h, None) + blk.mlp(h)
+        if s.post_norms:
+            a = blk.post_attn_norm(attend(blk.attn, blk.attn_norm(x), None))
+            x = x + a
+            return x + blk.post_mlp_norm(blk.mlp(blk.mlp_norm(x)))
+        x = attend(blk.attn, blk.attn_norm(x), x)
+        return blk.mlp(blk.mlp_norm(x), x)
+
+    def _logits(self, h: torch.Tensor) -> torch.Tensor:
+        """``[rows, padded vocabulary]`` logits of already-normalised hidden rows."""
+        m, s = self.model, self.spec
+        logits = ops.linear(h, m.head_weight(), m.head_bias)
+        if s.logit_softcap:
+            c = s.logit_softcap
+            logits = torch.tanh(logits.float() / c).mul(c).to(logits.dtype)
+        return logits.reshape(-1, logits.shape[-1])
+
+    # ------------------------------------------------------------------ prefill
+    @torch.no_grad()
+    def prefill(self, items: Sequence[PrefillItem], all_logits: bool = False) -> torch.Tensor:
+        """Computes the listed tokens of every item, fills the cache, and returns the logits of each item's last
+        token ``[len(items), padded vocabulary]`` (or of every computed token, packed, when ``all_logits``)."""
+        s, dev, bs = self.spec, self.device, self.block_size
+        H, Hkv, D = s.heads, s.kv_heads, s.head_dim
+        ids, pos, slots, bounds = [], [], [], [0]
+        for it in items:
+            n = len(it.tokens)
+            ids += it.tokens
+            for j in range(n):
+                p = it.start + j
+                pos.append(p)
+                slots.append(it.blocks[p // bs] * bs + p % bs)
+            bounds.append(bounds[-1] + n)
+        ids_t = torch.tensor(ids, dtype=torch.int32, device=dev)
+        pos_t = torch.tensor(pos, dtype=torch.int32, device=dev)
+        slots_t = torch.tensor(slots, dtype=torch.int32, device=dev)
+        tables = [torch.tensor(it.blocks, dtype=torch.long, device=dev) if it.start > 0 else None for it in items]
+        x = self._embed(ids_t, pos_t)
+        layer_index = {id(blk.attn): i for i, blk in enumerate(self.model.blocks)}
+
+        def attend(attn, h, residual):
+            li = layer_index[id(attn)]
+            qkv = self._qkv(attn, h)
+            qkv2 = qkv.view(-1, qkv.shape[-1])
+            self._rotate(attn, qkv2, pos_t)
+            q = qkv2[:, : H * D].unflatten(-1, (H, D))
+            k = qkv2[:, H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D))
+            v = qkv2[:, (H + Hkv) * D:].unflatten(-1, (Hkv, D))
+            dops.kv_write_paged(k, v, slots_t, self.k_cache[li], self.v_cache[li])
+            window = s.sliding_window if s.is_windowed(attn.layer) else None
+            fast = window is None and s.attention_softcap is None
+            out = torch.empty(qkv2.shape[0], H * D, dtype=qkv.dtype, device=dev)
+            for i, it in enumerate(items):
+                a, b = bounds[i], bounds[i + 1]
+                qi = q[a:b][None]
+                if it.start > 0:     # queries see the shared prefix too: read keys / values back from the cache
+                    total = it.start + (b - a)
+                    ki = self.k_cache[li][tables[i]].reshape(-1, Hkv, D)[:total][None].to(qkv.dtype)
+                    vi = self.v_cache[li][tables[i]].reshape(-1, Hkv, D)[:total][None].to(qkv.dtype)
+                else:
+                    ki, vi = k[a:b][None], v[a:b][None]
+                if fast:
+                    o = ops.attention(qi, ki, vi, True, attn.scale)
+                else:
+                    o = masked_attention(qi, ki, vi, attn.scale, window, s.attention_softcap)
+                out[a:b] = o.reshape(b - a, H * D)
+            return self._out(attn, out[None], residual)
+
+        for blk in self.model.blocks:
+            x = self._block(blk, x, attend)
+        if all_logits:
+            return self._logits(self.model.norm(x))
+        last = torch.tensor([b - 1 for b in bounds[1:]], dtype=torch.long, device=dev)
+        h = self.model.norm(x[0, last].contiguous()[None])
+        return self._logits(h)
+
+    # ------------------------------------------------------------------ decode
+    @torch.no_grad()
+    def decode(self, tokens: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
+               max_len_hint: Optional[int] = None) -> torch.Tensor:
+        """One new token per sequence. ``tokens`` / ``positions`` int32 ``[n]`` (position = index of the new
+        token), ``block_table`` int32 ``[n, max_blocks]``. Returns logits ``[n, padded vocabulary]``."""
+        s, dev, bs = self.spec, self.device, self.block_size
+        H, Hkv, D = s.heads, s.kv_heads, s.head_dim
+        n = tokens.shape[0]
+        rows = torch.arange(n, device=dev)
+        blk_of = block_table[rows, (positions // bs).long()]
+        slots = (blk_of * bs + positions % bs).to(torch.int32)
+        lens = (positions + 1).to(torch.int32)
+        x = self._embed(tokens, positions)
+        layer_index = {id(blk.attn): i for i, blk in enumerate(self.model.blocks)}
+
+        def attend(attn, h, residual):
+            li = layer_index[id(attn)]
+            qkv = self._qkv(attn, h)
+            qkv2 = qkv.view(-1, qkv.shape[-1])
+            self._rotate(attn, qkv2, positions)
+            q = qkv2[:, : H * D].unflatten(-1, (H, D))
+            k = qkv2[:, H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D))
+            v = qkv2[:, (H + Hkv) * D:].unflatten(-1, (Hkv, D))
+            dops.kv_write_paged(k, v, slots, self.k_cache[li], self.v_cache[li])
+            window = s.sliding_window if s.is_windowed(attn.layer) else 0
+            if s.attention_softcap is None:
+                o = dops.paged_decode(q.contiguous(), self.k_cache[li], self.v_cache[li], block_table, lens,
+                                      attn.scale, window or 0, max_len_hint=max_len_hint)
+            else:
+                o = self._decode_softcap(q, li, block_table, lens, attn.scale, window or None)
+            return self._out(attn, o.reshape(1, n, H * D), residual)
+
+        for blk in self.model.blocks:
+            x = self._block(blk, x, attend)
+        return self._logits(self.model.norm(x))
+
+    def _decode_softcap(self, q, li, block_table, lens, scale, window):
+        """Soft-capped scores (Gemma-2 style) composed from primitives, one sequence at a time."""
+        s = self.spec
+        out = torch.empty_like(q)
+        for i in range(q.shape[0]):
+            n = int(lens[i])
+            blocks = block_table[i, : (n + self.block_size - 1) // self.block_size].long()
+            k = self.k_cache[li][blocks].reshape(-1, s.kv_heads, s.head_dim)[:n][None].to(q.dtype)
+            v = self.v_cache[li][blocks].reshape(-1, s.kv_heads, s.head_dim)[:n][None].to(q.dtype)
+            out[i] = masked_attention(q[i][None, None], k, v, scale, window, s.attention_softcap)[0, 0]
+        return out
+
+    # ------------------------------------------------------------------ embeddings endpoint
+    @torch.no_grad()
+    def embed_text(self, tokens: Sequence[int], pooling: str = "mean") -> torch.Tensor:
+        """A sentence vector from the final hidden states (mean over tokens, or the last token), L2-normalised."""
+        ids = torch.tensor([list(tokens)], dtype=torch.int32, device=self.device)
+        h = self.model.hidden(ids).float()[0]
+        v = h.mean(0) if pooling == "mean" else h[-1]
+        return torch.nn.functional.normalize(v, dim=0)

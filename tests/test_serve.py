@@ -1,0 +1,134 @@
+"""Continuous-batching engine on CPU: scheduler behaviour, and token-exact agreement of paged generation with
+the plain forward pass (greedy), under prefix sharing and under block pressure that forces preemption."""
+import pytest
+import torch
+
+from idrak_b200.models.decoder import build_decoder
+from idrak_b200.models.spec import DecoderSpec
+from idrak_b200.serve import GenerationOptions, LLMEngine, QueueFull, Scheduler
+from idrak_b200.serve.scheduler import DECODE, PREFILL
+
+
+def _model(kind="llama", **kw):
+    if kind == "llama":
+        import dataclasses
+        spec = DecoderSpec.llama(layers=2, dim=64, heads=4, kv_heads=2, ff_dim=128, vocab=200, max_positions=128)
+        spec = dataclasses.replace(spec, **kw)
+    else:
+        spec = DecoderSpec.gpt2(layers=2, dim=64, heads=4, vocab=200, max_positions=128)
+    m = build_decoder(spec, seed=1).float().eval()
+    for p in m.parameters():
+        p.data.mul_(3.0)          # sharper logits: arg-max is stable against summation order
+    return m
+
+
+def _naive(model, prompt, n):
+    ids = list(prompt)
+    for _ in range(n):
+        with torch.no_grad():
+            lg = model(torch.tensor([ids], dtype=torch.int32))
+        ids.append(int(lg[0, -1].argmax()))
+    return ids[len(prompt):]
+
+
+def test_scheduler_admission_queue_limit_and_deadline():
+    s = Scheduler(num_blocks=8, block_size=16, max_batch=2, max_prefill_tokens=64, queue_limit=3, prefix_sharing=False)
+    s.add(1, list(range(20)), 4)
+    s.add(2, list(range(20)), 4)
+    s.add(3, list(range(5)), 4, deadline=1.0)
+    with pytest.raises(QueueFull):
+        s.add(4, [1, 2], 2)
+    with pytest.raises(ValueError):
+        Scheduler(2, 16, 2, 64, 0, False).add(9, list(range(40)), 10)
+    kind, ids, expired = s.step(0.0)
+    assert kind == PREFILL and ids == [1, 2] and expired == []
+    assert s.commit(1, 7, False) is False and s.commit(2, 7, False) is False
+    kind, ids, expired = s.step(2.0)           # the batch is full; request 3 timed out waiting
+    assert kind == DECODE and ids == [1, 2] and expired == [3]
+    assert s.commit(1, 7, True) is True
+    st = s.stats()
+    assert st["running"] == 1 and st["rejected"] == 1 and st["free_blocks"] == 6
+
+
+def test_scheduler_shares_prompt_prefix_blocks():
+    s = Scheduler(8, 16, 4, 256, 0, True)
+    prompt = list(range(40))
+    s.add(1, prompt, 2)
+    assert s.step(0.0)[1] == [1]
+    s.commit(1, 5, False)
+    s.add(2, prompt[:33] + [99, 98], 2)
+    assert s.step(0.0)[1] == [2]
+    a, b = s.info(1), s.info(2)
+    assert b.cached_prefix == 32 and s.blocks(1, 8)[:2] == s.blocks(2, 8)[:2]
+    assert s.blocks(1, 8)[2] != s.blocks(2, 8)[2] and a.cached_prefix == 0
+
+
+@pytest.mark.parametrize("kind", ["llama", "gpt2"])
+def test_engine_matches_plain_forward(kind):
+    m = _model(kind)
+    eng = LLMEngine(m, num_blocks=12, block_size=16, max_batch=4, prefix_sharing=True)
+    prompts = [[5, 6, 7, 8, 9] * 4 + [i] for i in range(6)] + [[3, 4]]
+    outs = eng.generate(prompts, GenerationOptions.greedy_options(20))
+    for p, r in zip(prompts, outs):
+        assert r.output == _naive(m, p, 20) and r.finish_reason == "length"
+    st = eng.stats()
+    assert st["prefix_hits"] > 0 and st["free_blocks"] == 12
+
+
+def test_engine_preempts_and_recomputes_under_block_pressure():
+    m = _model()
+    eng = LLMEngine(m, num_blocks=6, block_size=16, max_batch=4, prefix_sharing=False)
+    prompts = [[10 + i, 11, 12, 13, 14, 15, 16, 17, 18, 19, 20, 21, 22, 23] for i in range(4)]
+    outs = eng.generate(prompts, GenerationOptions.greedy_options(30))
+    assert eng.stats()["preemptions"] > 0
+    for p, r in zip(prompts, outs):
+        assert r.output == _naive(m, p, 30)
+
+
+def test_engine_windowed_and_softcapped_attention_paths():
+    m = _model(sliding_window=8)
+    eng = LLMEngine(m, num_blocks=12, max_batch=2)
+    p = list(range(30, 50))
+    assert eng.generate([p], GenerationOptions.greedy_options(12))[0].output == _naive(m, p, 12)
+    m = _model(attention_softcap=20.0, logit_softcap=30.0)
+    eng = LLMEngine(m, num_blocks=12, max_batch=2)
+    outs = eng.generate([p, p[:17]], GenerationOptions.greedy_options(12))
+    assert outs[0].output == _naive(m, p, 12) and outs[1].output == _naive(m, p[:17], 12)
+
+
+def test_engine_stop_tokens_sampling_and_late_arrivals():
+    m = _model()
+    eng = LLMEngine(m, num_blocks=16, max_batch=4, eos_token_ids=[])
+    ref = _naive(m, [1, 2, 3], 10)
+    r = eng.generate([[1, 2, 3]], GenerationOptions.greedy_options(10, stop_token_ids=(ref[4],)))[0]
+    stop_at = ref.index(ref[4])
+    assert r.finish_reason == "stop" and r.output == ref[: stop_at + 1]
+    # sampled requests with one seed repeat exactly; a request added mid-flight joins the running batch
+    o = GenerationOptions(temperature=0.9, top_k=20, top_p=0.95, seed=7, max_tokens=12, return_logprobs=True)
+    a = eng.add_request([4, 5, 6], o)
+    for _ in range(3):
+        eng.step()
+    b = eng.add_request([9, 9, 9], GenerationOptions.greedy_options(5))
+    while not (eng.requests[a].finished and eng.requests[b].finished):
+        eng.step()
+    ra, rb = eng.release(a), eng.release(b)
+    assert len(ra.output) == 12 and len(ra.logprobs) == 12 and all(lp <= 0 for lp in ra.logprobs)
+    assert rb.output == _naive(m, [9, 9, 9], 5)
+    with pytest.raises(ValueError):
+        eng.add_request(list(range(128)))
+
+
+def test_engine_abort_and_queue_timeout():
+    m = _model()
+    t = [0.0]
+    eng = LLMEngine(m, num_blocks=16, max_batch=1, clock=lambda: t[0])
+    seen = []
+    a = eng.add_request([1, 2, 3], GenerationOptions.greedy_options(50))
+    b = eng.add_request([4, 5, 6], GenerationOptions.greedy_options(5, timeout=1.0), on_token=seen.append)
+    eng.step()
+    t[0] = 5.0
+    eng.step()
+    assert eng.requests[b].finish_reason == "timeout" and seen[-1].finished and seen[-1].token == -1
+    eng.abort(a)
+    assert eng.requests[a].finish_reason == "abort" and not eng.has_work()
+    assert eng.stats()["free_blocks"] == 16
