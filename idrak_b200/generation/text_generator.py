@@ -98,7 +98,10 @@ class TextGenerator:
             torch.cuda.set_device(dev)
         while not self._stopping:
             if self.engine.has_work():
-                self.engine.step()
+                try:
+                    self.engine.step()
+                except Exception as e:        # a failed step must not strand the callers waiting on their queues
+                    self.engine.fail_all(e)
             else:
                 self._wake.wait(0.05)
                 self._wake.clear()
@@ -150,6 +153,8 @@ class TextGenerator:
                 if out.finished:
                     done = True
                     res.finish_reason = "stop" if stops.hit else out.finish_reason
+                    if out.finish_reason == "error":
+                        raise RuntimeError(f"generation failed: {self.engine.last_error!r}") from self.engine.last_error
             if not stops.hit:
                 tail = stops.push(decoder.flush()) + stops.flush()
                 if tail:

@@ -143,6 +143,27 @@ def sample_rows_reference(logits, vocab, temperature, top_k, top_p, min_p, unifo
     return torch.tensor(out, dtype=torch.int32)
 
 
+def penalise_reference(logits, vocab, history, repeat_penalty=None, presence_penalty=None, frequency_penalty=None):
+    """The kernel's penalties: tokens seen in ``history`` (-1 = empty) are divided / multiplied by the repeat
+    penalty (positive / negative logits), then lose the presence penalty and count x the frequency penalty."""
+    out = logits[:, :vocab].float().clone()
+    for r in range(out.shape[0]):
+        h = history[r][history[r] >= 0].long()
+        if h.numel() == 0:
+            continue
+        ids, counts = torch.unique(h, return_counts=True)
+        v = out[r, ids]
+        rp = float(repeat_penalty[r]) if repeat_penalty is not None else 1.0
+        if rp != 1.0:
+            v = torch.where(v > 0, v / rp, v * rp)
+        if presence_penalty is not None:
+            v = v - float(presence_penalty[r])
+        if frequency_penalty is not None:
+            v = v - float(frequency_penalty[r]) * counts.float()
+        out[r, ids] = v
+    return out
+
+
 def sample_rows(logits: torch.Tensor, vocab: int, temperature: torch.Tensor, top_k: torch.Tensor,
                 top_p: torch.Tensor, min_p: torch.Tensor, seeds: torch.Tensor, step: int,
                 history: Optional[torch.Tensor] = None, repeat_penalty: Optional[torch.Tensor] = None,
@@ -152,8 +173,12 @@ def sample_rows(logits: torch.Tensor, vocab: int, temperature: torch.Tensor, top
     (float32 / int32; ``seeds`` int64)."""
     rows = logits.shape[0]
     if not logits.is_cuda:
-        g = torch.Generator().manual_seed(int(seeds[0]) * 1000003 + step)
-        u = torch.rand(rows, generator=g)
+        u = torch.empty(rows)
+        for r in range(rows):      # one stream per row, so a row's draw does not depend on its batch neighbours
+            g = torch.Generator().manual_seed((int(seeds[r]) * 1000003 + step) & 0x7FFFFFFFFFFFFFFF)
+            u[r] = torch.rand(1, generator=g)[0]
+        if history is not None:
+            logits = penalise_reference(logits, vocab, history, repeat_penalty, presence_penalty, frequency_penalty)
         ids = sample_rows_reference(logits, vocab, temperature, top_k, top_p, min_p, u)
         return (ids, torch.zeros(rows)) if return_logprobs else ids
     _bind()

@@ -126,6 +126,7 @@ class LLMEngine:
         self.tokens_generated = 0
         self.tokens_prefilled = 0
         self.steps = 0
+        self.last_error: Optional[BaseException] = None
 
     # ------------------------------------------------------------------ requests
     def add_request(self, prompt: Sequence[int], options: Optional[GenerationOptions] = None,
@@ -158,6 +159,17 @@ class LLMEngine:
             self._finish(r, "abort")
             if r.on_token:
                 r.on_token(StepOutput(r.id, -1, True, "abort"))
+
+    def fail_all(self, error: BaseException) -> None:
+        """End every unfinished request with reason "error" (a step raised): callers waiting on them wake up."""
+        with self._lock:
+            self.last_error = error
+            for r in list(self.requests.values()):
+                if not r.finished:
+                    self.sched.abort(r.id)
+                    self._finish(r, "error")
+                    if r.on_token:
+                        r.on_token(StepOutput(r.id, -1, True, "error"))
 
     def release(self, request_id: int) -> Optional[Request]:
         """Forget a finished request (its record is returned)."""

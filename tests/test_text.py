@@ -112,6 +112,20 @@ def test_tool_call_parsers_streaming():
         create_parser("nope")
 
 
+def test_failed_engine_step_wakes_callers_with_an_error():
+    gen, m, tok = _generator()
+    gen.start()
+    try:
+        def boom():
+            raise ValueError("kernel refused")
+        gen.engine._step = boom
+        with pytest.raises(RuntimeError, match="kernel refused"):
+            gen.generate("hello", GenerationOptions.greedy_options(4))
+        assert not gen.engine.has_work()
+    finally:
+        gen.close()
+
+
 def _generator(**kw):
     tok = ByteTokenizer()
     spec = DecoderSpec.llama(layers=2, dim=64, heads=4, kv_heads=2, ff_dim=128, vocab=tok.vocab_size, max_positions=256)
