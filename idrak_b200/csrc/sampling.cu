@@ -179,7 +179,8 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const Sampl
     float kept = 0.f;
     for (int a = 0; a < keep; ++a) kept += cand_v[a];
     const unsigned long long seed = p.seeds ? p.seeds[row] : 0ull;
-    uint32_t r = hash32(uint32_t(seed) ^ hash32(uint32_t(seed >> 32) + 0x9e3779b9u * (p.step + 1u)) ^ hash32(row * 0x85ebca6bu + 1u));
+    // the draw depends on the row's seed and the step only, never on where the row sits in the batch
+    uint32_t r = hash32(uint32_t(seed) ^ hash32(uint32_t(seed >> 32) + 0x9e3779b9u * (p.step + 1u)));
     const float u = (float(r >> 8) + 0.5f) * (1.0f / 16777216.0f) * kept;
     float cum = 0.f;
     int pick = keep - 1;

@@ -121,7 +121,6 @@ class LLMEngine:
         self.requests: Dict[int, Request] = {}
         self._ids = itertools.count(1)
         self._lock = threading.RLock()
-        self._sample_step = 0
         self.device = self.runner.device
         self.tokens_generated = 0
         self.tokens_prefilled = 0
@@ -189,7 +188,6 @@ class LLMEngine:
     def _sample(self, logits: torch.Tensor, reqs: List[Request]) -> Tuple[List[int], Optional[List[float]]]:
         """Pick one token per row on the device; one host read of ``len(reqs)`` ints."""
         vocab, dev = self.spec.vocabulary, logits.device
-        self._sample_step += 1
         want_lp = any(r.options.return_logprobs for r in reqs)
         if all(r.options.greedy and not r.options.penalised for r in reqs):
             ids = dops.argmax_rows(logits, vocab)
@@ -199,7 +197,9 @@ class LLMEngine:
             temperature = f32([1.0 if x.greedy else x.temperature for x in o])
             top_k = torch.tensor([1 if x.greedy else x.top_k for x in o], dtype=torch.int32, device=dev)
             top_p, min_p = f32([x.top_p for x in o]), f32([x.min_p for x in o])
-            seeds = torch.tensor([r.seed for r in reqs], dtype=torch.int64, device=dev)
+            # a request's draws depend on its seed and its own token index only, not on its batch neighbours
+            seeds = torch.tensor([(r.seed + 0x9E3779B97F4A7C15 * (len(r.output) + 1)) & 0x7FFFFFFFFFFFFFFF
+                                  for r in reqs], dtype=torch.int64, device=dev)
             history = rp = pp = fp = None
             if any(x.penalised for x in o):
                 width = max(max(x.repeat_last_n for x in o), 1)
@@ -211,7 +211,7 @@ class LLMEngine:
                 history = torch.tensor(rows, dtype=torch.int32, device=dev)
                 rp, pp, fp = (f32([x.repeat_penalty for x in o]), f32([x.presence_penalty for x in o]),
                               f32([x.frequency_penalty for x in o]))
-            ids = dops.sample_rows(logits, vocab, temperature, top_k, top_p, min_p, seeds, self._sample_step,
+            ids = dops.sample_rows(logits, vocab, temperature, top_k, top_p, min_p, seeds, 0,
                                    history, rp, pp, fp)
         lps = None
         if want_lp:
