@@ -161,7 +161,7 @@ class FusedAdamW(FusedOptimizerBase):
         bc1 = 1.0 - b1 ** self.step_count
         bc2 = 1.0 - b2 ** self.step_count
         if not self.cuda:
-            return self._step_cpu(bc1, bc2)
+            return self._step_cpu(bc1, bc2, extra_sumsq)
         lib = _native.lib()
         t_dev, c_dev, n_chunks, partial = self._build_tables()
         self._upload_hyper(self._hyper_values())
@@ -179,11 +179,13 @@ class FusedAdamW(FusedOptimizerBase):
         return {H_LR: self.lr, H_B1: b1, H_B2: b2, H_EPS: self.eps, H_BC1: 1.0 - b1 ** self.step_count,
                 H_BC2: 1.0 - b2 ** self.step_count, H_MAXNORM: self.max_grad_norm, H_GSCALE: self.grad_scale}
 
-    def _step_cpu(self, bc1, bc2):
+    def _step_cpu(self, bc1, bc2, extra_sumsq=None):
         b1, b2 = self.betas
         grads = [p.grad.float() * self.grad_scale if p.grad is not None else None for p in self.params]
         scale = 1.0
         sq = sum(float(g.pow(2).sum()) for g in grads if g is not None)
+        if extra_sumsq is not None:
+            sq += float(extra_sumsq.sum())
         norm = math.sqrt(sq)
         self._last_norm = norm
         if self.max_grad_norm > 0 and norm > self.max_grad_norm:
