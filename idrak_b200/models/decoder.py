@@ -65,7 +65,7 @@ class SelfAttention(nn.Module):
         rope = spec.sliding_window_rope if (spec.is_windowed(layer) and spec.sliding_window_rope) else spec.rope
         self.rope = rope
 
-    def forward(self, x, residual=None, positions=None):
+    def forward(self, x, residual=None, positions=None, spans=None):
         spec = self.spec
         H, Hkv, D = spec.heads, spec.kv_heads, spec.head_dim
         adapters = getattr(self, "adapters", None)
@@ -81,12 +81,23 @@ class SelfAttention(nn.Module):
         window = spec.sliding_window if spec.is_windowed(self.layer) else None
         simple = not spec.qk_norm and window is None and spec.attention_softcap is None and (
             self.rope is None or self.rope.scaling is None)
-        if simple:
-            theta = self.rope.theta if self.rope is not None else None
-            rdim = self.rope.rotary_dim if self.rope is not None else None
-            a = ops.qkv_attention(qkv, H, Hkv, D, True, self.scale, theta, rdim, 1.0, positions)
+        def attend(part, pos):
+            if simple:
+                theta = self.rope.theta if self.rope is not None else None
+                rdim = self.rope.rotary_dim if self.rope is not None else None
+                return ops.qkv_attention(part, H, Hkv, D, True, self.scale, theta, rdim, 1.0, pos)
+            return self._general(part, pos, window)
+
+        if spans is None:
+            a = attend(qkv, positions)
         else:
-            a = self._general(qkv, positions, window)
+            # several sequences packed into one row: attention runs per sequence, everything else over the pack
+            pieces = []
+            for lo, hi in spans:
+                pos = (positions.reshape(qkv.shape[0], -1)[:, lo:hi].reshape(-1).contiguous()
+                       if positions is not None else None)
+                pieces.append(attend(qkv[:, lo:hi].contiguous(), pos))
+            a = torch.cat(pieces, dim=1)
         if adapters is not None and "o" in adapters:
             from ..adapters.lora import project_with_adapters
             return project_with_adapters(a, self.o_weight, self.o_bias, adapters,
@@ -256,13 +267,13 @@ class DecoderBlock(nn.Module):
             self.post_mlp_norm = Norm(spec.dim, spec.norm, spec.norm_epsilon, spec.norm_offset)
         self.drop = spec.dropout
 
-    def forward(self, x, positions=None):
+    def forward(self, x, positions=None, spans=None):
         spec = self.spec
         if spec.parallel_blocks:
             h = self.attn_norm(x)
-            return x + self._drop(self.attn(h, None, positions)) + self._drop(self.mlp(h))
+            return x + self._drop(self.attn(h, None, positions, spans)) + self._drop(self.mlp(h))
         if spec.post_norms or self.drop > 0:
-            a = self.attn(self.attn_norm(x), None, positions)
+            a = self.attn(self.attn_norm(x), None, positions, spans)
             if spec.post_norms:
                 a = self.post_attn_norm(a)
             x = x + self._drop(a)
@@ -271,7 +282,7 @@ class DecoderBlock(nn.Module):
                 m = self.post_mlp_norm(m)
             return x + self._drop(m)
         # plain pre-norm block: residual additions happen inside the GEMM epilogues
-        x = self.attn(self.attn_norm(x), x, positions)
+        x = self.attn(self.attn_norm(x), x, positions, spans)
         return self.mlp(self.mlp_norm(x), x)
 
     def _drop(self, t):
@@ -331,7 +342,7 @@ class Decoder(nn.Module):
                     normal_(blk.mlp.shared_gate, std)
 
     # ------------------------------------------------------------------ forward
-    def hidden(self, ids: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def hidden(self, ids: torch.Tensor, positions: Optional[torch.Tensor] = None, spans=None) -> torch.Tensor:
         spec = self.spec
         B, S = ids.shape
         if self.pos is not None and positions is None:
@@ -347,17 +358,18 @@ class Decoder(nn.Module):
         for blk in self.blocks:
             if self.checkpoint_blocks and self.training and torch.is_grad_enabled():
                 from ..core.checkpointing import checkpoint
-                x = checkpoint(blk, x, positions)
+                x = checkpoint(blk, x, positions, spans)
             else:
-                x = blk(x, positions)
+                x = blk(x, positions, spans)
         return self.norm(x)
 
     def head_weight(self) -> torch.Tensor:
         return self.embed if self.head is None else self.head
 
-    def forward(self, ids: torch.Tensor, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Logits ``[B, S, vocabulary]``."""
-        h = self.hidden(ids, positions)
+    def forward(self, ids: torch.Tensor, positions: Optional[torch.Tensor] = None, spans=None) -> torch.Tensor:
+        """Logits ``[B, S, vocabulary]``. ``spans``: ``[(lo, hi), ...]`` token ranges of the sequences packed into a
+        single row (B = 1); attention stays inside each range."""
+        h = self.hidden(ids, positions, spans)
         logits = ops.linear(h, self.head_weight(), self.head_bias)[..., : self.spec.vocabulary]
         if self.spec.logit_softcap:
             c = self.spec.logit_softcap
@@ -365,9 +377,9 @@ class Decoder(nn.Module):
         return logits
 
     def loss(self, ids: torch.Tensor, targets: torch.Tensor, positions: Optional[torch.Tensor] = None,
-             ignore_index: Optional[int] = None) -> torch.Tensor:
+             ignore_index: Optional[int] = None, spans=None) -> torch.Tensor:
         """Mean next-token cross-entropy; the logits matrix is never materialised beyond one row chunk."""
-        h = self.hidden(ids, positions)
+        h = self.hidden(ids, positions, spans)
         if self.spec.logit_softcap or self.head_bias is not None:
             logits = self.forward_from_hidden(h)
             return torch.nn.functional.cross_entropy(

@@ -1,0 +1,398 @@
+"""Supervised fine-tuning with LoRA / DoRA adapters over a frozen base (bf16, int8 or int4).
+
+    result = FineTuner.train(model, tokenizer, examples, options=FineTuningOptions(base="int4"), out_dir="out")
+
+Examples are dicts: ``{"text"}`` (every token is trained), ``{"prompt", "response"}`` (only the response is trained)
+or ``{"messages": [...]}`` (only assistant turns are trained; rendered through the chat template). Sequences are
+packed first-fit into rows of at most ``max_length`` tokens; a batch holds rows up to ``batch_tokens``. Inside a
+packed row attention stays within each sequence and positions restart. The step runs the frozen projections on
+the dequant-fused tcgen05 GEMM with the low-rank term added, adapters only are optimised (fused AdamW), gradients
+are clipped at 1.0, a non-finite loss skips the step, and the result is written as a PEFT adapter folder.
+
+Reference: FineTuner.Train and FineTuningOptions (src/Idrak.Text/FineTuning.cs:1176, :767-1007), ChatTranscriptEncoder
+(src/Idrak.Text/ChatTranscriptEncoder.cs:169), preference losses (src/Idrak.Text/FineTuningLosses.cs).
+"""
+from __future__ import annotations
+
+import contextlib
+import json
+import math
+import os
+import random
+from dataclasses import asdict, dataclass, field
+from typing import Any, Callable, Dict, Iterable, List, Optional, Sequence, Tuple
+
+import torch
+import torch.distributed as dist
+
+from ..adapters.lora import DEFAULT_TARGETS, add_adapters, adapter_parameters
+from ..adapters.peft import load_adapters, save_adapters
+from ..ops import FusedAdamW
+from .chat import ChatTemplate
+
+IGNORE = -100
+
+
+@dataclass
+class FineTuningOptions:
+    rank: int = 16
+    alpha: float = 32.0
+    targets: Tuple[str, ...] = tuple(DEFAULT_TARGETS)
+    dora: bool = False
+    rslora: bool = False
+    base: str = "bf16"                   # how the frozen base is held: bf16 | int8 | int4
+    learning_rate: float = 2e-4
+    weight_decay: float = 0.0
+    warmup_fraction: float = 0.03
+    schedule: str = "cosine"             # cosine | linear | constant
+    clip: float = 1.0
+    epochs: int = 1
+    max_steps: int = 0                   # 0 = run the epochs out
+    batch_tokens: int = 4096
+    max_length: int = 2048
+    packing: bool = True
+    accumulation: int = 1
+    loss_chunk_rows: int = 512
+    non_finite_steps: int = 8            # give up after this many skipped steps in a row
+    checkpoint_blocks: bool = False      # recompute block activations in backward
+    loss: str = "sft"                    # sft | dpo
+    dpo_beta: float = 0.1
+    save_every: int = 0                  # steps; 0 = only at the end
+    eval_every: int = 0
+    seed: int = 0
+    resume_from: Optional[str] = None
+
+
+@dataclass
+class FineTuningResult:
+    steps: int = 0
+    tokens: int = 0
+    losses: List[float] = field(default_factory=list)
+    eval_losses: List[Tuple[int, float]] = field(default_factory=list)
+    skipped_steps: int = 0
+    adapter_folder: Optional[str] = None
+
+
+# ------------------------------------------------------------------ examples -> token rows
+def encode_example(example: Dict[str, Any], tokenizer, template: Optional[ChatTemplate] = None,
+                   max_length: int = 2048) -> Tuple[List[int], List[bool]]:
+    """Token ids of one example and, per token, whether it is a training target."""
+    eos = list(tokenizer.eos_token_ids[:1])
+    if "messages" in example:
+        template = template or ChatTemplate.for_tokenizer(tokenizer)
+        ids: List[int] = []
+        train: List[bool] = []
+        msgs = example["messages"]
+        done = 0
+        for i, m in enumerate(msgs):
+            if m.get("role") != "assistant":
+                continue
+            # text up to this assistant turn (with the generation prompt) is context; the turn itself is trained
+            before = tokenizer.encode(template.render(msgs[:i], add_generation_prompt=True), add_special_tokens=False)
+            upto = tokenizer.encode(template.render(msgs[: i + 1], add_generation_prompt=False), add_special_tokens=False)
+            if upto[: len(before)] != before:          # the template rewrites history: fall back to a prefix match
+                k = 0
+                while k < min(len(before), len(upto)) and before[k] == upto[k]:
+                    k += 1
+                before = upto[:k]
+            ids += upto[done:]
+            train += [False] * (len(before) - done) + [True] * (len(upto) - len(before))
+            done = len(upto)
+        if not ids:
+            raise ValueError("a 'messages' example needs at least one assistant turn")
+    elif "prompt" in example:
+        p = tokenizer.encode(example["prompt"], add_special_tokens=True)
+        r = tokenizer.encode(example.get("response", example.get("completion", "")), add_special_tokens=False) + eos
+        ids, train = p + r, [False] * len(p) + [True] * len(r)
+    elif "text" in example:
+        ids = tokenizer.encode(example["text"], add_special_tokens=True) + eos
+        train = [True] * len(ids)
+    else:
+        raise ValueError("an example needs 'text', 'prompt' + 'response', or 'messages'")
+    return ids[:max_length], train[:max_length]
+
+
+@dataclass
+class PackedBatch:
+    ids: torch.Tensor            # int32 [1, T]
+    targets: torch.Tensor        # int64 [1, T]; IGNORE where not trained
+    positions: torch.Tensor      # int32 [T]
+    spans: List[Tuple[int, int]]
+    trained_tokens: int
+
+
+def pack_batches(encoded: Sequence[Tuple[List[int], List[bool]]], batch_tokens: int, max_length: int,
+                 packing: bool = True) -> List[PackedBatch]:
+    """First-fit rows of at most ``max_length`` tokens, grouped into batches of at most ``batch_tokens``; every batch
+    is one packed row of sequences (``spans``), which is how the decoder takes them."""
+    rows: List[List[int]] = []          # indices of examples per row
+    room: List[int] = []
+    for i, (ids, _) in enumerate(encoded):
+        n = len(ids)
+        if n < 2:
+            continue
+        placed = False
+        if packing:
+            for r in range(len(rows)):
+                if room[r] >= n:
+                    rows[r].append(i)
+                    room[r] -= n
+                    placed = True
+                    break
+        if not placed:
+            rows.append([i])
+            room.append(max_length - n)
+    batches: List[List[int]] = []
+    cur: List[int] = []
+    cur_tokens = 0
+    for r, members in enumerate(rows):
+        used = max_length - room[r]
+        if cur and cur_tokens + used > batch_tokens:
+            batches.append(cur)
+            cur, cur_tokens = [], 0
+        cur += members
+        cur_tokens += used
+    if cur:
+        batches.append(cur)
+    out = []
+    for members in batches:
+        ids_all, tgt_all, pos_all, spans = [], [], [], []
+        trained = 0
+        for i in members:
+            ids, train = encoded[i]
+            lo = len(ids_all)
+            ids_all += ids
+            # next-token targets inside the sequence; its last token predicts nothing
+            tgt = [ids[j + 1] if train[j + 1] else IGNORE for j in range(len(ids) - 1)] + [IGNORE]
+            trained += sum(1 for t in tgt if t != IGNORE)
+            tgt_all += tgt
+            pos_all += list(range(len(ids)))
+            spans.append((lo, lo + len(ids)))
+        # kernels want the packed length to be a multiple of 8: pad with an untrained tail sequence
+        pad = (-len(ids_all)) % 8
+        if pad:
+            lo = len(ids_all)
+            ids_all += [0] * pad
+            tgt_all += [IGNORE] * pad
+            pos_all += list(range(pad))
+            spans.append((lo, lo + pad))
+        out.append(PackedBatch(torch.tensor([ids_all], dtype=torch.int32), torch.tensor([tgt_all], dtype=torch.int64),
+                               torch.tensor(pos_all, dtype=torch.int32), spans, trained))
+    return out
+
+
+def _lr_at(step: int, total: int, o: FineTuningOptions) -> float:
+    warm = max(int(total * o.warmup_fraction), 1)
+    if step < warm:
+        return o.learning_rate * (step + 1) / warm
+    if o.schedule == "constant" or total <= warm:
+        return o.learning_rate
+    t = (step - warm) / max(total - warm, 1)
+    if o.schedule == "linear":
+        return o.learning_rate * max(0.0, 1.0 - t)
+    return o.learning_rate * 0.5 * (1.0 + math.cos(math.pi * min(t, 1.0)))
+
+
+@contextlib.contextmanager
+def adapters_disabled(model):
+    """Run the frozen base alone (the reference policy of preference losses)."""
+    held = []
+    for mod in model.modules():
+        if getattr(mod, "adapters", None) is not None:
+            held.append((mod, mod.adapters))
+            mod.adapters = None
+    try:
+        yield
+    finally:
+        for mod, a in held:
+            mod.adapters = a
+
+
+def sequence_logprobs(model, batch: PackedBatch, device) -> torch.Tensor:
+    """Sum of the trained tokens' log-probabilities of every sequence of a packed batch ``[len(spans)]``."""
+    logits = model(batch.ids.to(device), batch.positions.to(device), spans=batch.spans)[0].float()
+    lp = torch.log_softmax(logits, -1)
+    tgt = batch.targets[0].to(device)
+    keep = tgt != IGNORE
+    tok = lp.gather(1, tgt.clamp(min=0)[:, None])[:, 0] * keep
+    return torch.stack([tok[lo:hi].sum() for lo, hi in batch.spans])
+
+
+class FineTuner:
+    """Drives the adapter training loop; ``FineTuner.train`` is the one-call form."""
+
+    def __init__(self, model, tokenizer, options: Optional[FineTuningOptions] = None, group=None):
+        self.model, self.tokenizer = model, tokenizer
+        self.o = options or FineTuningOptions()
+        self.group = group
+        self.device = next(model.parameters()).device
+        o = self.o
+        if o.base in ("int8", "int4") and self.device.type == "cuda":
+            from ..quant import quantize_model
+            quantize_model(model, o.base)
+        elif o.base not in ("bf16", "float32", "int8", "int4"):
+            raise ValueError(f"unknown base format '{o.base}' (bf16, int8, int4)")
+        if o.resume_from:          # the checkpoint's adapters come first: the optimizer is built over them
+            load_adapters(model, o.resume_from)
+        has = any(getattr(m, "adapters", None) is not None for m in model.modules())
+        self.params = adapter_parameters(model) if has else add_adapters(
+            model, o.rank, o.alpha, o.targets, dora=o.dora, rslora=o.rslora)
+        for p in self.params:
+            p.requires_grad_(True)
+        model.checkpoint_blocks = o.checkpoint_blocks
+        model.loss_chunk_rows = o.loss_chunk_rows
+        self.optimizer = FusedAdamW([{"params": self.params, "weight_decay": o.weight_decay}], lr=o.learning_rate,
+                                    weight_decay=o.weight_decay, max_grad_norm=o.clip)
+        self.template = ChatTemplate.for_tokenizer(tokenizer)
+        self.step = 0
+        self.result = FineTuningResult()
+
+    # ------------------------------------------------------------------ data
+    def batches(self, examples: Iterable[Dict[str, Any]]) -> List[PackedBatch]:
+        o = self.o
+        if o.loss == "dpo":
+            return self._preference_batches(examples)
+        enc = [encode_example(e, self.tokenizer, self.template, o.max_length) for e in examples]
+        return pack_batches(enc, o.batch_tokens, o.max_length, o.packing)
+
+    def _preference_batches(self, examples) -> List[PackedBatch]:
+        o, out = self.o, []
+        for e in examples:            # one batch per pair: [chosen, rejected] packed in one row
+            pair = [encode_example({"prompt": e["prompt"], "response": e[k]}, self.tokenizer, self.template, o.max_length)
+                    for k in ("chosen", "rejected")]
+            out += pack_batches(pair, 2 * o.max_length, o.max_length, packing=False)
+        return out
+
+    # ------------------------------------------------------------------ losses
+    def batch_loss(self, b: PackedBatch) -> torch.Tensor:
+        dev = self.device
+        if self.o.loss == "dpo":
+            policy = sequence_logprobs(self.model, b, dev)
+            with torch.no_grad(), adapters_disabled(self.model):
+                ref = sequence_logprobs(self.model, b, dev)
+            margin = (policy[0] - policy[1]) - (ref[0] - ref[1])
+            return -torch.nn.functional.logsigmoid(self.o.dpo_beta * margin)
+        return self.model.loss(b.ids.to(dev), b.targets.to(dev), b.positions.to(dev), ignore_index=IGNORE, spans=b.spans)
+
+    @torch.no_grad()
+    def evaluate(self, batches: Sequence[PackedBatch]) -> float:
+        self.model.eval()
+        total, count = 0.0, 0
+        for b in batches:
+            n = max(b.trained_tokens, 1)
+            total += float(self.batch_loss(b)) * n
+            count += n
+        self.model.train()
+        return total / max(count, 1)
+
+    # ------------------------------------------------------------------ the loop
+    def _reduce_grads(self) -> None:
+        if self.group is None and not (dist.is_initialized() and dist.get_world_size() > 1):
+            return
+        world = dist.get_world_size(self.group)
+        flat = torch.cat([p.grad.reshape(-1).float() for p in self.params if p.grad is not None])
+        dist.all_reduce(flat, group=self.group)
+        flat /= world
+        off = 0
+        for p in self.params:
+            if p.grad is not None:
+                p.grad.copy_(flat[off: off + p.numel()].view_as(p.grad))
+                off += p.numel()
+
+    def fit(self, train: Sequence[Dict[str, Any]], evaluation: Optional[Sequence[Dict[str, Any]]] = None,
+            out_dir: Optional[str] = None, progress: Optional[Callable[[int, float], None]] = None) -> FineTuningResult:
+        o, res = self.o, self.result
+        batches = self.batches(train)
+        if not batches:
+            raise ValueError("no trainable examples")
+        eval_batches = self.batches(evaluation) if evaluation else []
+        per_epoch = math.ceil(len(batches) / o.accumulation)
+        total = o.max_steps if o.max_steps > 0 else per_epoch * o.epochs
+        if o.resume_from:
+            self.load_checkpoint(o.resume_from)
+        rng = random.Random(o.seed)
+        order: List[int] = []
+        self.model.train()
+        bad_streak = 0
+        cursor = self.step * o.accumulation
+        while self.step < total:
+            while len(order) <= cursor + o.accumulation:       # the draw order is a pure function of the seed
+                epoch_order = list(range(len(batches)))
+                rng.shuffle(epoch_order)
+                order += epoch_order
+            group = [batches[order[cursor + k]] for k in range(o.accumulation)]
+            cursor += o.accumulation
+            tokens = sum(max(b.trained_tokens, 1) for b in group)
+            self.optimizer.zero_grad()
+            loss_value, finite = 0.0, True
+            for b in group:
+                w = max(b.trained_tokens, 1) / tokens              # token-weighted mean over the accumulated batches
+                loss = self.batch_loss(b)
+                value = float(loss.detach())                       # the one host read per batch
+                if not math.isfinite(value):
+                    finite = False
+                    break
+                (loss * w).backward()
+                loss_value += value * w
+            if not finite:
+                res.skipped_steps += 1
+                bad_streak += 1
+                if bad_streak >= o.non_finite_steps:
+                    raise FloatingPointError(f"{bad_streak} steps in a row had a non-finite loss")
+                continue
+            bad_streak = 0
+            self._reduce_grads()
+            self.optimizer.lr = _lr_at(self.step, total, o)
+            self.optimizer.step()
+            self.step += 1
+            res.steps, res.tokens = self.step, res.tokens + tokens
+            res.losses.append(loss_value)
+            if progress:
+                progress(self.step, loss_value)
+            if eval_batches and o.eval_every and self.step % o.eval_every == 0:
+                res.eval_losses.append((self.step, self.evaluate(eval_batches)))
+            if out_dir and o.save_every and self.step % o.save_every == 0:
+                self.save_checkpoint(os.path.join(out_dir, f"checkpoint-{self.step}"))
+        if eval_batches:
+            res.eval_losses.append((self.step, self.evaluate(eval_batches)))
+        if out_dir and self._is_writer():
+            os.makedirs(out_dir, exist_ok=True)
+            save_adapters(self.model, out_dir)
+            with open(os.path.join(out_dir, "finetuning.json"), "w") as f:
+                json.dump({"options": asdict(o), "steps": res.steps, "tokens": res.tokens,
+                           "final_loss": res.losses[-1] if res.losses else None, "eval": res.eval_losses}, f, indent=1)
+            res.adapter_folder = out_dir
+        return res
+
+    def _is_writer(self) -> bool:
+        return not dist.is_initialized() or dist.get_rank(self.group) == 0
+
+    # ------------------------------------------------------------------ checkpoints
+    def save_checkpoint(self, folder: str) -> None:
+        if not self._is_writer():
+            return
+        os.makedirs(folder, exist_ok=True)
+        save_adapters(self.model, folder)
+        from ..formats.safetensors import save_file
+        state = self.optimizer.state_dict()
+        save_file({k: v for k, v in state.items() if isinstance(v, torch.Tensor)},
+                  os.path.join(folder, "optimizer.safetensors"), metadata={"format": "idrak-optimizer", "optimizer": "AdamW"})
+        with open(os.path.join(folder, "train-state.json"), "w") as f:
+            json.dump({"step": self.step, "tokens": self.result.tokens, "losses": self.result.losses[-16:]}, f)
+
+    def load_checkpoint(self, folder: str) -> None:
+        """Optimizer moments and the step counter of a checkpoint whose adapters are already attached."""
+        from ..formats.safetensors import load_file
+        path = os.path.join(folder, "optimizer.safetensors")
+        if os.path.isfile(path):
+            self.optimizer.load_state_dict(load_file(path))
+        with open(os.path.join(folder, "train-state.json")) as f:
+            st = json.load(f)
+        self.step, self.result.tokens = int(st["step"]), int(st.get("tokens", 0))
+
+    # ------------------------------------------------------------------ one call
+    @staticmethod
+    def train(model, tokenizer, train: Sequence[Dict[str, Any]], evaluation=None,
+              options: Optional[FineTuningOptions] = None, out_dir: Optional[str] = None, progress=None,
+              group=None) -> FineTuningResult:
+        return FineTuner(model, tokenizer, options, group).fit(train, evaluation, out_dir, progress)

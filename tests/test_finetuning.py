@@ -1,0 +1,101 @@
+"""FineTuner on CPU: example encoding and loss masks, first-fit packing, a short LoRA run that lowers the loss and
+writes a PEFT folder that loads back, DPO, non-finite step handling and resume."""
+import json
+import math
+import os
+
+import pytest
+import torch
+
+from idrak_b200.adapters.lora import add_adapters, adapter_parameters
+from idrak_b200.adapters.peft import load_adapters
+from idrak_b200.models import DecoderSpec, build_decoder
+from idrak_b200.text import ByteTokenizer
+from idrak_b200.text.finetuning import (IGNORE, FineTuner, FineTuningOptions, _lr_at, encode_example, pack_batches)
+
+
+def _model(seed=1):
+    tok = ByteTokenizer()
+    spec = DecoderSpec.llama(layers=2, dim=64, heads=4, kv_heads=2, ff_dim=128, vocab=tok.vocab_size, max_positions=256)
+    model = build_decoder(spec, seed=seed).float()
+    model.head.data.mul_(20.0)       # the frozen head must be able to express confident predictions
+    return model, tok
+
+
+def test_encode_examples_and_masks():
+    _, tok = _model()
+    ids, train = encode_example({"prompt": "ab", "response": "cd"}, tok)
+    assert ids == [97, 98, 99, 100, tok.eos_token_ids[0]] and train == [False, False, True, True, True]
+    ids, train = encode_example({"text": "hey"}, tok)
+    assert all(train) and ids[-1] == tok.eos_token_ids[0]
+    msgs = {"messages": [{"role": "user", "content": "hi"}, {"role": "assistant", "content": "yo"},
+                         {"role": "user", "content": "more"}, {"role": "assistant", "content": "ok"}]}
+    ids, train = encode_example(msgs, tok)
+    text = tok.decode(ids)
+    trained = tok.decode([i for i, t in zip(ids, train) if t])
+    assert text.count("<|im_start|>") == 4 and trained == "yo<|im_end|>\nok<|im_end|>\n"
+    with pytest.raises(ValueError):
+        encode_example({"question": "?"}, tok)
+
+
+def test_packing_first_fit_spans_and_targets():
+    enc = [([1] * 10, [True] * 10), ([2] * 30, [False] * 15 + [True] * 15), ([3] * 25, [True] * 25), ([4] * 5, [True] * 5)]
+    batches = pack_batches(enc, batch_tokens=64, max_length=40, packing=True)
+    # rows: [10 + 30] and [25 + 5]; each row is 40 tokens, so two batches of one row... 64 holds only one 40-row
+    assert len(batches) == 2
+    b = batches[0]
+    assert b.spans[:2] == [(0, 10), (10, 40)] and b.ids.shape[1] % 8 == 0
+    assert b.positions[:10].tolist() == list(range(10)) and b.positions[10:40].tolist() == list(range(30))
+    assert b.targets[0, 9].item() == IGNORE                      # the last token of a sequence predicts nothing
+    assert (b.targets[0, 10:24] == IGNORE).all() and (b.targets[0, 24:39] == 2).all()
+    assert b.trained_tokens == 9 + 15
+    unpacked = pack_batches(enc, batch_tokens=64, max_length=40, packing=False)
+    assert sum(len(x.spans) for x in unpacked) >= 4 and len(unpacked) == 2       # 10 + 30 | 25 + 5 tokens
+    o = FineTuningOptions(learning_rate=1.0, warmup_fraction=0.1)
+    assert _lr_at(0, 100, o) == pytest.approx(0.1) and _lr_at(9, 100, o) == pytest.approx(1.0)
+    assert _lr_at(99, 100, o) < 0.01 and _lr_at(55, 100, o) == pytest.approx(0.5, abs=0.02)
+
+
+def test_lora_run_lowers_loss_saves_and_resumes(tmp_path):
+    model, tok = _model()
+    data = [{"prompt": f"say {w}: ", "response": w * 3} for w in ("ab", "cd", "ef", "gh")] * 3
+    o = FineTuningOptions(rank=4, alpha=8, learning_rate=3e-2, batch_tokens=128, max_length=64, epochs=20, base="bf16",
+                          save_every=4, eval_every=4, warmup_fraction=0.1)
+    seen = []
+    res = FineTuner.train(model, tok, data, evaluation=data[:4], options=o, out_dir=str(tmp_path / "out"),
+                          progress=lambda s, l: seen.append(s))
+    assert res.steps == len(seen) > 6 and res.losses[-1] < 0.7 * res.losses[0]
+    assert res.eval_losses and res.eval_losses[-1][1] < res.losses[0]
+    assert all(not p.requires_grad for n, p in model.named_parameters() if "adapters" not in n)
+    folder = tmp_path / "out"
+    cfg = json.loads((folder / "adapter_config.json").read_text())
+    assert cfg["r"] == 4 and cfg["peft_type"] == "LORA" and (folder / "adapter_model.safetensors").exists()
+    fresh, _ = _model()
+    add_adapters(fresh, 4, 8)
+    load_adapters(fresh, str(folder))
+    a = torch.cat([p.reshape(-1) for p in adapter_parameters(model)])
+    b = torch.cat([p.reshape(-1) for p in adapter_parameters(fresh)])
+    assert torch.allclose(a, b)
+    # resume from the step-4 checkpoint reproduces the rest of the run (same seeded order)
+    ck = folder / "checkpoint-4"
+    assert (ck / "optimizer.safetensors").exists() and json.loads((ck / "train-state.json").read_text())["step"] == 4
+    again, _ = _model()
+    o2 = FineTuningOptions(**{**o.__dict__, "resume_from": str(ck), "save_every": 0, "eval_every": 0})
+    res2 = FineTuner.train(again, tok, data, options=o2)
+    assert res2.steps == res.steps and res2.losses[-1] == pytest.approx(res.losses[-1], rel=1e-4)
+
+
+def test_dpo_prefers_chosen_and_non_finite_steps_stop():
+    model, tok = _model()
+    pairs = [{"prompt": "q: ", "chosen": "yes yes", "rejected": "no no"}] * 4
+    o = FineTuningOptions(rank=4, alpha=8, learning_rate=5e-2, loss="dpo", dpo_beta=0.5, max_length=32, max_steps=12,
+                          warmup_fraction=0.1)
+    res = FineTuner.train(model, tok, pairs, options=o)
+    assert res.losses[0] == pytest.approx(math.log(2), rel=1e-3)       # policy == reference at the start
+    assert res.losses[-1] < 0.5 * res.losses[0]
+    model2, _ = _model()
+    ft = FineTuner(model2, tok, FineTuningOptions(rank=2, non_finite_steps=3, max_length=32))
+    ft.batch_loss = lambda b: torch.tensor(float("nan"), requires_grad=True)
+    with pytest.raises(FloatingPointError, match="3 steps in a row"):
+        ft.fit([{"text": "abcdef"}] * 4)
+    assert ft.result.skipped_steps == 3 and ft.result.steps == 0
