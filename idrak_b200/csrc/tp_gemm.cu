@@ -58,6 +58,9 @@ struct TpParams {
   const __nv_bfloat16* rs_residual;   // [rows_per_rank, rs_ldr] or null
   int rs_ldr;
   const __nv_bfloat16* rs_bias;       // [N] or null
+  // NVSwitch multicast views of the same areas (null: plain peer stores / loads)
+  __nv_bfloat16* gather_mc;           // a store here lands in every rank's gather area
+  const __nv_bfloat16* stage_mc;      // a reducing load here sums every rank's staging area, laid out [M, N]
 };
 
 struct TpSmem {
@@ -100,13 +103,32 @@ __device__ __forceinline__ bool epi_any(bool pred) {
   return r != 0;
 }
 
+// 16-byte store through an NVSwitch multicast address: the switch writes it into every rank's copy.
+__device__ __forceinline__ void multimem_st16(void* mc, uint4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.bf16x2 [%0], {%1, %2, %3, %4};" ::"l"(mc), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+// 16-byte load through a multicast address that returns the sum over every rank's copy (8 bf16 values, summed
+// in fp32 inside the switch).
+__device__ __forceinline__ uint4 multimem_ld_reduce16(const void* mc) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc)
+               : "memory");
+  return v;
+}
+
 __device__ __forceinline__ void tp_unit_to_tile(const GemmParams& p, const TpParams& t, const CommCtx& c, int unit,
                                                 int& tm, int& tn, int& owner, int& chunk) {
   const int per_owner = t.chunks_per_rank * p.n_tiles;
   const int oi = unit / per_owner;
   const int r = unit - oi * per_owner;
-  chunk = r / p.n_tiles;
-  tn = r - chunk * p.n_tiles;
+  // inside an owner's block the row chunks vary fastest: the CTAs working side by side share one tile of W, which
+  // is then read from DRAM once per owner instead of once per chunk
+  tn = r / t.chunks_per_rank;
+  chunk = r - tn * t.chunks_per_rank;
   owner = (t.mode == 1) ? (c.rank - oi + c.world) % c.world : (c.rank + 1 + oi) % c.world;
   tm = owner * t.chunks_per_rank + chunk;
 }
@@ -122,9 +144,44 @@ __device__ void tp_push_rows(const GemmParams& p, const TpParams& t, const CommC
   }
   __syncthreads();
   if (!ok_flag) return;
-  const int items = c.world * t.chunks_per_rank;
   const int row_vecs = p.K / 8;                                  // 16-byte vectors per row
   const long long half_off = (long long)(q & 1u) * t.gather_half;
+  if (t.gather_mc != nullptr) {
+    // NVSwitch multicast: one store per 16 bytes reaches every rank's gather buffer (own copy included), so this
+    // rank's rows leave the GPU once instead of once per peer.
+    for (int chunk = blockIdx.x; chunk < t.chunks_per_rank; chunk += t.push_ctas) {
+      const __nv_bfloat16* src = t.x_local + size_t(chunk) * kBM * t.ldx;
+      __nv_bfloat16* dst = t.gather_mc + half_off + (size_t(c.rank) * t.rows_per_rank + size_t(chunk) * kBM) * p.K;
+      const int total = kBM * row_vecs;
+      constexpr int kUnroll = 8;
+      for (int i = threadIdx.x; i < total; i += kUnroll * blockDim.x) {
+        uint4 v[kUnroll];
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int j = i + u * blockDim.x;
+          if (j < total) {
+            const int r = j / row_vecs, cv = j - r * row_vecs;
+            v[u] = *reinterpret_cast<const uint4*>(src + size_t(r) * t.ldx + cv * 8);
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < kUnroll; ++u) {
+          const int j = i + u * blockDim.x;
+          if (j < total) {
+            const int r = j / row_vecs, cv = j - r * row_vecs;
+            multimem_st16(dst + size_t(r) * p.K + cv * 8, v[u]);
+          }
+        }
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) __threadfence_system();
+      __syncthreads();
+      if (threadIdx.x < c.world)
+        st_release_sys(c.flags[threadIdx.x] + (kTpChReady0 + chunk) * kMaxRanks + c.rank, q + 1u);
+    }
+    return;
+  }
+  const int items = c.world * t.chunks_per_rank;
   for (int item = blockIdx.x; item < items; item += t.push_ctas) {
     const int d = item / t.chunks_per_rank;                      // 0 = own buffer, 1 = rank + 1, ...
     const int chunk = item - d * t.chunks_per_rank;
@@ -132,10 +189,11 @@ __device__ void tp_push_rows(const GemmParams& p, const TpParams& t, const CommC
     const __nv_bfloat16* src = t.x_local + size_t(chunk) * kBM * t.ldx;
     __nv_bfloat16* dst = t.gather[peer] + half_off + (size_t(c.rank) * t.rows_per_rank + size_t(chunk) * kBM) * p.K;
     const int total = kBM * row_vecs;
-    for (int i = threadIdx.x; i < total; i += 4 * blockDim.x) {
-      uint4 v[4];
+    constexpr int kUnroll = 8;                 // 8 x 16 bytes per thread in flight: the loop is latency-bound
+    for (int i = threadIdx.x; i < total; i += kUnroll * blockDim.x) {
+      uint4 v[kUnroll];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < kUnroll; ++u) {
         const int j = i + u * blockDim.x;
         if (j < total) {
           const int r = j / row_vecs, cv = j - r * row_vecs;
@@ -143,7 +201,7 @@ __device__ void tp_push_rows(const GemmParams& p, const TpParams& t, const CommC
         }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < kUnroll; ++u) {
         const int j = i + u * blockDim.x;
         if (j < total) {
           const int r = j / row_vecs, cv = j - r * row_vecs;
@@ -151,8 +209,8 @@ __device__ void tp_push_rows(const GemmParams& p, const TpParams& t, const CommC
         }
       }
     }
-    __threadfence_system();
-    __syncthreads();
+    __syncthreads();                           // one fence by the signalling thread covers the CTA's stores
+    if (threadIdx.x == 0) __threadfence_system();
     if (threadIdx.x == 0) st_release_sys(c.flags[peer] + (kTpChReady0 + chunk) * kMaxRanks + c.rank, q + 1u);
   }
 }
@@ -181,14 +239,56 @@ __device__ void tp_reduce_rows(const GemmParams& p, const TpParams& t, const Com
       }
       ready_chunk = chunk;
     }
+    if (t.stage_mc != nullptr) {
+      // every rank wrote its partial rows at the same offset of its own staging area: one reducing load through
+      // the switch returns their sum. Several requests per thread are issued before the first result is used.
+      const __nv_bfloat16* mc_rows = t.stage_mc + (long long)(q & 1u) * t.stage_half +
+                                     size_t(c.rank) * t.rows_per_rank * p.N;
+      const int total = kRowsPerItem * vec_per_row;
+      constexpr int kPull = 8;                  // reducing loads in flight per thread
+      for (int i0 = tid128; i0 < total; i0 += kPull * 128) {
+        uint4 sum[kPull];
+#pragma unroll
+        for (int u = 0; u < kPull; ++u) {
+          const int i = i0 + u * 128;
+          if (i < total)
+            sum[u] = multimem_ld_reduce16(mc_rows + size_t(row0 + i / vec_per_row) * p.N + (i % vec_per_row) * 8);
+        }
+#pragma unroll
+        for (int u = 0; u < kPull; ++u) {
+          const int i = i0 + u * 128;
+          if (i < total) {
+            const int r = row0 + i / vec_per_row;
+            const int col = (i % vec_per_row) * 8;
+            float acc[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+            accum_bf16x8(acc, sum[u], 1.f);
+            if (t.rs_bias) accum_bf16x8(acc, __ldg(reinterpret_cast<const uint4*>(t.rs_bias + col)), 1.f);
+            if (t.rs_residual)
+              accum_bf16x8(acc, __ldg(reinterpret_cast<const uint4*>(t.rs_residual + size_t(r) * t.rs_ldr + col)), 1.f);
+            uint4 o;
+            o.x = pack_bf16x2(acc[0], acc[1]); o.y = pack_bf16x2(acc[2], acc[3]);
+            o.z = pack_bf16x2(acc[4], acc[5]); o.w = pack_bf16x2(acc[6], acc[7]);
+            *reinterpret_cast<uint4*>(t.out + size_t(r) * t.ldo + col) = o;
+          }
+        }
+      }
+      continue;
+    }
     for (int i = tid128; i < kRowsPerItem * vec_per_row; i += 128) {
       const int r = row0 + i / vec_per_row;
       const int col = (i % vec_per_row) * 8;
       float acc[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-      for (int s = 0; s < c.world; ++s)
-        accum_bf16x8(acc, __ldcg(reinterpret_cast<const uint4*>(base + s * slot + size_t(r) * p.N + col)), 1.f);
+      uint4 part[kMaxRanks];
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s)         // all loads first: eight 16-byte requests in flight per thread
+        if (s < c.world) part[s] = __ldcg(reinterpret_cast<const uint4*>(base + s * slot + size_t(r) * p.N + col));
+#pragma unroll
+      for (int s = 0; s < kMaxRanks; ++s)
+        if (s < c.world) accum_bf16x8(acc, part[s], 1.f);
       if (t.rs_bias) accum_bf16x8(acc, __ldg(reinterpret_cast<const uint4*>(t.rs_bias + col)), 1.f);
       if (t.rs_residual)
         accum_bf16x8(acc, __ldg(reinterpret_cast<const uint4*>(t.rs_residual + size_t(r) * t.rs_ldr + col)), 1.f);
@@ -381,9 +481,14 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         const int n0 = tn * BN;
         const bool gelu = (p.act == kActGelu);
         __nv_bfloat16* peer_rows = nullptr;
-        if (t.mode == 2)
-          peer_rows = t.stage[owner] + half_off +
-                      (size_t(c.rank) * t.rows_per_rank + size_t(chunk) * kBM + quarter * 32) * p.N;
+        if (t.mode == 2) {
+          // multicast pull: the partial tile stays in this rank's own staging area at its global row; otherwise
+          // it goes into the owner's slot of this rank
+          peer_rows = (t.stage_mc != nullptr)
+                          ? t.stage[c.rank] + half_off + (size_t(tm) * kBM + quarter * 32) * p.N
+                          : t.stage[owner] + half_off +
+                                (size_t(c.rank) * t.rows_per_rank + size_t(chunk) * kBM + quarter * 32) * p.N;
+        }
 #pragma unroll 1
         for (int s64 = 0; s64 < BN / 64; ++s64) {
           const int col0 = n0 + s64 * 64;
@@ -450,9 +555,11 @@ tp_gemm_kernel(const __grid_constant__ CUtensorMap tmA0, const __grid_constant__
         mbar_arrive(&tmem_empty[buf]);
         if (t.mode == 2) {
           // count the tile; the last tile of the 128-row chunk tells the owner that this rank's part is complete
-          __threadfence_system();
+          // (one system fence by the counting thread after the barrier covers the 128 threads' stores; a fence
+          //  per thread costs a system-wide drain each)
           epi_bar_sync();
           if (tid128 == 0) {
+            __threadfence_system();
             const uint32_t done = atomicAdd(t.counters + 1 + tm, 1u);
             if (done == uint32_t(p.n_tiles) - 1u) {
               t.counters[1 + tm] = 0;
@@ -556,11 +663,12 @@ IDRAK_API int idrak_tp_max_rows_per_rank() { return kTpMaxChunks * kBM; }
 //   gather_ptrs[p]  rank p's gather area, 2 * gather_half_elems bf16 (gather_half_elems >= M * K)
 //   W               [N, K] (w_mn = 0) or stored [K, N] (w_mn = 1), local shard
 //   seq, counters   device words shared by all fused ops of this rank (counters: idrak_tp_counter_words(M), zeroed)
+//   gather_multicast  NVSwitch multicast address of the gather areas (one store reaches all ranks), or null
 // Returns 0, a negative argument code, or a CUDA error.
 IDRAK_API int idrak_tp_ag_gemm(const void* ctx, const void* x_local, int ldx, void* const* gather_ptrs,
                                long long gather_half_elems, const void* W, int ldw, int w_mn, void* C, int ldc, int M,
                                int N, int K, const void* bias, int act, void* aux, int ld_aux, void* seq,
-                               void* counters, int push_ctas, int hold_done, void* stream_) {
+                               void* counters, int push_ctas, int hold_done, void* gather_multicast, void* stream_) {
   CommCtx c;
   memcpy(&c, ctx, sizeof(c));
   if (M <= 0 || N <= 0 || K <= 0 || M % (c.world * kBM) || K % 8 || (ldx & 7) || (ldw & 7) || (ldc & 7)) return -2;
@@ -592,6 +700,7 @@ IDRAK_API int idrak_tp_ag_gemm(const void* ctx, const void* x_local, int ldx, vo
   t.ldx = ldx;
   for (int i = 0; i < c.world; ++i) t.gather[i] = static_cast<__nv_bfloat16*>(gather_ptrs[i]);
   t.gather_half = gather_half_elems;
+  t.gather_mc = static_cast<__nv_bfloat16*>(gather_multicast);
 
   CUtensorMap a0, a1, b, cm, am;
   memset(&am, 0, sizeof(am));
@@ -635,7 +744,7 @@ IDRAK_API int idrak_tp_release(const void* ctx, const void* seq, void* stream_) 
 IDRAK_API int idrak_tp_gemm_rs(const void* ctx, const void* A, int lda, const void* W, int ldw, int w_mn,
                                void* const* stage_ptrs, long long stage_half_elems, void* out, int ldo, int M, int N,
                                int K, const void* bias, const void* residual, int ldr, void* seq, void* counters,
-                               void* stream_) {
+                               const void* stage_multicast, void* stream_) {
   CommCtx c;
   memcpy(&c, ctx, sizeof(c));
   if (M <= 0 || N <= 0 || K <= 0 || M % (c.world * kBM) || N % 64 || K % 8 || (lda & 7) || (ldw & 7) || (ldo & 7) ||
@@ -654,6 +763,7 @@ IDRAK_API int idrak_tp_gemm_rs(const void* ctx, const void* A, int lda, const vo
   t.counters = static_cast<uint32_t*>(counters);
   for (int i = 0; i < c.world; ++i) t.stage[i] = static_cast<__nv_bfloat16*>(stage_ptrs[i]);
   t.stage_half = stage_half_elems;
+  t.stage_mc = static_cast<const __nv_bfloat16*>(stage_multicast);
   t.out = static_cast<__nv_bfloat16*>(out);
   t.ldo = ldo;
   t.rs_residual = static_cast<const __nv_bfloat16*>(residual);

@@ -93,7 +93,7 @@ def main(argv=None) -> int:
         t_u = _time(unfused, a.warmup, a.iters, None)
         roof = max(flops / (GEMM_PEAK_TFLOPS * 1e12), link / (LINK_GBS * 1e9)) * 1e3
         if rank == 0:
-            print(json.dumps({"op": name, "world": world, "M": M, "N": N, "K": K, "fused_ms": round(t_f, 4),
+            print(json.dumps({"op": name, "world": world, "multicast": tp.gather_mc is not None, "M": M, "N": N, "K": K, "fused_ms": round(t_f, 4),
                               "nccl_plus_gemm_ms": round(t_u, 4), "speedup": round(t_u / t_f, 3),
                               "roofline_ms": round(roof, 4), "fused_frac_of_roofline": round(roof / t_f, 3),
                               "bound": "compute" if flops / (GEMM_PEAK_TFLOPS * 1e12) > link / (LINK_GBS * 1e9) else "link"}),

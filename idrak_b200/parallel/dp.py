@@ -265,6 +265,61 @@ class DataParallel:
     def zero_grad(self):
         self.flat.zero_grad()
 
+    # ------------------------------------------------------------------ optimizer state, independent of the world size
+    def _gather_shard(self, shard: torch.Tensor) -> torch.Tensor:
+        """The full flat fp32 vector whose slices the ranks hold (joined in rank order per bucket)."""
+        W = self.world
+        parts = [torch.empty_like(shard) for _ in range(W)]
+        dist.all_gather(parts, shard.contiguous(), group=self.group)
+        full = torch.zeros(self.flat.numel, dtype=torch.float32, device=shard.device)
+        for b, (s, e, _) in enumerate(self.buckets):
+            sl = (e - s) // W
+            for r in range(W):
+                full[s + r * sl: s + (r + 1) * sl] = parts[r][self.shard_offsets[b]: self.shard_offsets[b] + sl]
+        return full
+
+    def optimizer_state(self) -> dict:
+        """``step``, ``m.{i}``, ``v.{i}`` (and ``master.{i}``) by parameter index - the same entries a single-process
+        AdamW writes, so a run can resume at another world size (collective: every rank must call it)."""
+        if self.mode == "nccl":
+            return self.optimizer.state_dict()
+        opt = self.optimizer
+        out = {"step": torch.tensor(float(opt.step_count))}
+        for key, shard in (("m", opt.m), ("v", opt.v), ("master", opt.master)):
+            full = self._gather_shard(shard)
+            for pc in self.flat.pieces:
+                p = self.flat.params[pc.index]
+                out[f"{key}.{pc.index}"] = full[pc.offset: pc.offset + pc.numel].view(p.shape).cpu()
+        return out
+
+    def refresh_master_from_parameters(self) -> None:
+        """After the parameters were overwritten in place (a checkpoint load): rebuild this rank's fp32 master shard."""
+        if self.mode == "nccl":
+            if hasattr(self.optimizer, "refresh_master"):
+                self.optimizer.refresh_master()
+            return
+        W, r, opt = self.world, self.rank, self.optimizer
+        for b, (s, e, _) in enumerate(self.buckets):
+            sl = (e - s) // W
+            opt.master[self.shard_offsets[b]: self.shard_offsets[b] + sl].copy_(
+                self.flat.param[s + r * sl: s + (r + 1) * sl].float())
+
+    def load_optimizer_state(self, state: dict) -> None:
+        if self.mode == "nccl":
+            self.optimizer.load_state_dict(state)
+            return
+        opt, W, r = self.optimizer, self.world, self.rank
+        opt.step_count = int(float(state["step"]))
+        for key, shard in (("m", opt.m), ("v", opt.v), ("master", opt.master)):
+            if f"{key}.0" not in state:
+                continue                       # e.g. a file without master weights: keep the ones made from the parameters
+            full = torch.zeros(self.flat.numel, dtype=torch.float32, device=shard.device)
+            for pc in self.flat.pieces:
+                full[pc.offset: pc.offset + pc.numel] = state[f"{key}.{pc.index}"].reshape(-1).to(shard.device)
+            for b, (s, e, _) in enumerate(self.buckets):
+                sl = (e - s) // W
+                shard[self.shard_offsets[b]: self.shard_offsets[b] + sl] = full[s + r * sl: s + (r + 1) * sl]
+
     def close(self):
         for h in self._handles:
             h.remove()

@@ -41,8 +41,8 @@ def _bind():
     b = _native.bind
     b("idrak_tp_counter_words", i, [i])
     b("idrak_tp_max_rows_per_rank", i, [])
-    b("idrak_tp_ag_gemm", i, [vp, vp, i, pp, ll, vp, i, i, vp, i, i, i, i, vp, i, vp, i, vp, vp, i, i, vp])
-    b("idrak_tp_gemm_rs", i, [vp, vp, i, vp, i, i, pp, ll, vp, i, i, i, i, vp, vp, i, vp, vp, vp])
+    b("idrak_tp_ag_gemm", i, [vp, vp, i, pp, ll, vp, i, i, vp, i, i, i, i, vp, i, vp, i, vp, vp, i, i, vp, vp])
+    b("idrak_tp_gemm_rs", i, [vp, vp, i, vp, i, i, pp, ll, vp, i, i, i, i, vp, vp, i, vp, vp, vp, vp])
     b("idrak_tp_release", i, [vp, vp, vp])
     _BOUND = True
 
@@ -56,7 +56,7 @@ class TensorParallel:
     """
 
     def __init__(self, comm: Optional[Communicator] = None, max_rows: int = 0, max_in: int = 0, max_out: int = 0,
-                 mode: str = "fused", group=None, push_ctas: int = 16):
+                 mode: str = "fused", group=None, push_ctas: int = 16, multimem: bool = True):
         self.group = group
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -70,12 +70,47 @@ class TensorParallel:
             self.max_rows, self.max_in, self.max_out = max_rows, max_in, max_out
             self.gather_half = max_rows * max_in
             self.stage_half = max_rows * max_out
-            self.gather = comm.symmetric(2 * self.gather_half * 2)
-            self.stage = comm.symmetric(2 * self.stage_half * 2)
+            self.gather_mc = self.stage_mc = None
+            self._symm = []
+            import os
+            if multimem and self.world > 1 and os.environ.get("IDRAK_TP_MULTIMEM", "1") != "0":
+                self._try_multicast_buffers(comm.device)
+            if self.gather_mc is None:
+                self.gather = comm.symmetric(2 * self.gather_half * 2)
+                self.stage = comm.symmetric(2 * self.stage_half * 2)
+                self.gather_ptrs, self.stage_ptrs = self.gather.ptr_array, self.stage.ptr_array
             words = lib.idrak_tp_counter_words(max_rows)
             self.state = torch.zeros(1 + words, dtype=torch.int32, device=comm.device)   # [0] = seq, then counters
             dist.barrier(group=group)
             torch.cuda.synchronize()
+
+    def _try_multicast_buffers(self, device) -> None:
+        """Gather / staging areas from PyTorch's symmetric memory, which also binds them to an NVSwitch multicast
+        object: one ``multimem.st`` then reaches every rank and one ``multimem.ld_reduce`` sums every rank's copy.
+        Falls back to plain peer-mapped buffers when the machine or the build has no multicast support."""
+        try:
+            import torch.distributed._symmetric_memory as symm
+            group = self.group if self.group is not None else dist.group.WORLD
+            handles = []
+            for nbytes in (2 * self.gather_half * 2, 2 * self.stage_half * 2):
+                t = symm.empty(int(nbytes), dtype=torch.uint8, device=device)
+                h = symm.rendezvous(t, group)
+                handles.append((t, h))
+            ok = all(int(h.multicast_ptr) != 0 for _, h in handles)
+            flag = torch.tensor([1 if ok else 0], device=device)
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=self.group)
+            if int(flag.item()) == 0:
+                return
+            (gt, gh), (st, sh) = handles
+            gt.zero_()
+            st.zero_()
+            self._symm = handles
+            self.gather_ptrs = (C.c_void_p * self.world)(*[int(p) for p in gh.buffer_ptrs])
+            self.stage_ptrs = (C.c_void_p * self.world)(*[int(p) for p in sh.buffer_ptrs])
+            self.gather_mc, self.stage_mc = int(gh.multicast_ptr), int(sh.multicast_ptr)
+        except Exception as e:              # no multicast on this machine / build: the peer-store path still works
+            self.multicast_error = repr(e)
+            self.gather_mc = self.stage_mc = None
 
     # ------------------------------------------------------------------ helpers
     def fusable(self, rows_total: int, k: int, n: int, reduce: bool) -> bool:
@@ -130,10 +165,10 @@ class TensorParallel:
         y = torch.empty(M, N, dtype=torch.bfloat16, device=x_local.device)
         aux = torch.empty_like(y) if act == "gelu" else None
         rc = _native.lib().idrak_tp_ag_gemm(
-            self.comm.ctx, x_local.data_ptr(), x_local.stride(0), self.gather.ptr_array, self.gather_half,
+            self.comm.ctx, x_local.data_ptr(), x_local.stride(0), self.gather_ptrs, self.gather_half,
             w.data_ptr(), w.stride(0), int(w_mn), y.data_ptr(), y.stride(0), M, N, K, ptr(bias), _ACT[act], ptr(aux),
             aux.stride(0) if aux is not None else 0, self._seq_ptr(), self._counter_ptr(), self.push_ctas, 0,
-            stream_ptr())
+            self.gather_mc, stream_ptr())
         _native.check(rc, "idrak_tp_ag_gemm")
         return (y, aux) if act == "gelu" else y
 
@@ -154,8 +189,9 @@ class TensorParallel:
         assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and w.stride(1) == 1
         out = torch.empty(M // self.world, N, dtype=torch.bfloat16, device=x.device)
         rc = _native.lib().idrak_tp_gemm_rs(
-            self.comm.ctx, x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), int(w_mn), self.stage.ptr_array,
+            self.comm.ctx, x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), int(w_mn), self.stage_ptrs,
             self.stage_half, out.data_ptr(), out.stride(0), M, N, K, ptr(bias), ptr(residual),
-            residual.stride(0) if residual is not None else 0, self._seq_ptr(), self._counter_ptr(), stream_ptr())
+            residual.stride(0) if residual is not None else 0, self._seq_ptr(), self._counter_ptr(), self.stage_mc,
+            stream_ptr())
         _native.check(rc, "idrak_tp_gemm_rs")
         return out
