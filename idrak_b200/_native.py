@@ -112,8 +112,17 @@ def lib() -> C.CDLL:
         return _LIB
 
 
+_BOUND_NAMES = set()
+
+
+def exported_names():
+    """Names of the library's entry points this process knows: the signature table plus what modules bound."""
+    return sorted(set(_SIGNATURES) | _BOUND_NAMES)
+
+
 def bind(name: str, restype, argtypes):
     """Declare one more exported function (used by modules that own their part of the ABI)."""
+    _BOUND_NAMES.add(name)
     fn = getattr(lib(), name)
     fn.restype = restype
     fn.argtypes = argtypes

@@ -1,0 +1,132 @@
+"""Process-wide settings: one table of environment variables with types, defaults and meaning.
+
+``settings.get("IDRAK_TP_MULTIMEM")`` reads and validates a variable; ``describe()`` renders the table (the
+``idrak config`` command prints it). A value that does not parse is an error that names the variable, never a
+silent default.
+
+Reference: the environment table of the reference (src/Idrak.Abstraction/Configuration/EnvironmentSettings.cs) and
+``idrak config`` (src/Idrak.Cli.Commands/Commands/ConfigCommands.cs).
+"""
+from __future__ import annotations
+
+import os
+from dataclasses import dataclass
+from typing import Any, Callable, Dict, List, Optional
+
+
+def _bool(text: str) -> bool:
+    t = text.strip().lower()
+    if t in ("1", "true", "yes", "on"):
+        return True
+    if t in ("0", "false", "no", "off", ""):
+        return False
+    raise ValueError("expected 0/1, true/false, yes/no or on/off")
+
+
+def _size(text: str) -> int:
+    """Bytes with a power-of-1,024 unit: 512M, 2G, 64K, or a plain integer."""
+    t = text.strip().upper().rstrip("B")
+    units = {"K": 1 << 10, "M": 1 << 20, "G": 1 << 30, "T": 1 << 40}
+    if t and t[-1] in units:
+        return int(float(t[:-1]) * units[t[-1]])
+    return int(t)
+
+
+@dataclass(frozen=True)
+class Setting:
+    name: str
+    kind: str                    # bool | int | float | size | text | choice
+    default: Any
+    help: str
+    choices: tuple = ()
+
+    def parse(self, text: str) -> Any:
+        try:
+            if self.kind == "bool":
+                return _bool(text)
+            if self.kind == "int":
+                return int(text)
+            if self.kind == "float":
+                return float(text)
+            if self.kind == "size":
+                return _size(text)
+            if self.kind == "choice":
+                if text not in self.choices:
+                    raise ValueError(f"expected one of {', '.join(self.choices)}")
+                return text
+            return text
+        except ValueError as e:
+            raise ValueError(f"{self.name}={text!r}: {e}") from None
+
+
+TABLE: List[Setting] = [
+    Setting("IDRAK_BENCH_GRAPH", "bool", True, "bench.py: replay the training step as a CUDA graph"),
+    Setting("IDRAK_BENCH_DP", "choice", "fused", "bench.py: data-parallel path", ("fused", "nccl")),
+    Setting("IDRAK_TP_MULTIMEM", "bool", True, "tensor parallel: use NVSwitch multicast stores / reducing loads when "
+                                               "the machine offers them"),
+    Setting("IDRAK_TP_PUSH_CTAS", "int", 16, "tensor parallel: CTAs of the all-gather->GEMM kernel that move rows"),
+    Setting("IDRAK_PREFILL_CHUNK", "int", 8192, "serving: most prompt tokens computed in one prefill step"),
+    Setting("IDRAK_KV_FRACTION", "float", 0.8, "serving: share of the free device memory given to the KV cache"),
+    Setting("IDRAK_MAX_BATCH", "int", 64, "serving: most sequences decoded together"),
+    Setting("IDRAK_QUEUE_LIMIT", "int", 0, "serving: most requests waiting per model (0 = unbounded)"),
+    Setting("IDRAK_REQUEST_TIMEOUT", "float", 0.0, "serving: seconds a request may wait in the queue (0 = forever)"),
+    Setting("IDRAK_KEEP_ALIVE", "float", 300.0, "serving: seconds an idle model stays loaded (0 = forever)"),
+    Setting("IDRAK_WORKSPACE", "size", 256 << 20, "largest scratch buffer an op may keep between calls"),
+    Setting("IDRAK_TELEMETRY", "text", "", "telemetry levels to record, comma separated (step, kernel, comm, memory)"),
+    Setting("IDRAK_TELEMETRY_FILE", "text", "", "write telemetry events to this JSON-lines file"),
+    Setting("IDRAK_HOME", "text", os.path.join(os.path.expanduser("~"), ".idrak"), "models, runs and aliases live here"),
+    Setting("IDRAK_STOP_FILE", "text", "", "training stops cleanly at the next step when this file appears"),
+]
+_BY_NAME: Dict[str, Setting] = {s.name: s for s in TABLE}
+
+
+class Settings:
+    def __init__(self, environ: Optional[Dict[str, str]] = None):
+        self.environ = environ if environ is not None else os.environ
+        self._overrides: Dict[str, Any] = {}
+
+    def get(self, name: str) -> Any:
+        if name not in _BY_NAME:
+            raise KeyError(f"unknown setting {name}; known: {', '.join(sorted(_BY_NAME))}")
+        if name in self._overrides:
+            return self._overrides[name]
+        s = _BY_NAME[name]
+        raw = self.environ.get(name)
+        return s.default if raw is None else s.parse(raw)
+
+    def set(self, name: str, value: Any) -> None:
+        s = _BY_NAME[name] if name in _BY_NAME else None
+        if s is None:
+            raise KeyError(f"unknown setting {name}")
+        self._overrides[name] = s.parse(value) if isinstance(value, str) else value
+
+    def validate(self) -> List[str]:
+        """Problems with the current environment: unparsable values and unknown IDRAK_* names."""
+        problems = []
+        for key, raw in self.environ.items():
+            if not key.startswith("IDRAK_"):
+                continue
+            if key not in _BY_NAME:
+                problems.append(f"{key}: not a setting of this package")
+                continue
+            try:
+                _BY_NAME[key].parse(raw)
+            except ValueError as e:
+                problems.append(str(e))
+        return problems
+
+
+settings = Settings()
+
+
+def describe(current: Optional[Settings] = None) -> str:
+    cur = current or settings
+    rows = [("name", "type", "default", "now", "meaning")]
+    for s in TABLE:
+        try:
+            now = cur.get(s.name)
+        except ValueError as e:
+            now = f"invalid ({e})"
+        rows.append((s.name, s.kind if not s.choices else "|".join(s.choices), str(s.default), str(now), s.help))
+    widths = [max(len(r[i]) for r in rows) for i in range(4)]
+    return "\n".join("  ".join(r[i].ljust(widths[i]) for i in range(4)) + "  " + r[4] for r in rows)
