@@ -149,10 +149,17 @@ __device__ void tp_push_rows(const GemmParams& p, const TpParams& t, const CommC
   if (t.gather_mc != nullptr) {
     // NVSwitch multicast: one store per 16 bytes reaches every rank's gather buffer (own copy included), so this
     // rank's rows leave the GPU once instead of once per peer.
-    for (int chunk = blockIdx.x; chunk < t.chunks_per_rank; chunk += t.push_ctas) {
-      const __nv_bfloat16* src = t.x_local + size_t(chunk) * kBM * t.ldx;
-      __nv_bfloat16* dst = t.gather_mc + half_off + (size_t(c.rank) * t.rows_per_rank + size_t(chunk) * kBM) * p.K;
-      const int total = kBM * row_vecs;
+    // A chunk is cut into kParts row slabs so that every push CTA has work even with few chunks; the CTA that
+    // finishes a chunk's last slab publishes the chunk's flag.
+    constexpr int kParts = 4;
+    constexpr int kPartRows = kBM / kParts;
+    __shared__ int last_part;
+    for (int item = blockIdx.x; item < t.chunks_per_rank * kParts; item += t.push_ctas) {
+      const int chunk = item / kParts, part = item - chunk * kParts;
+      const size_t row0 = size_t(chunk) * kBM + size_t(part) * kPartRows;
+      const __nv_bfloat16* src = t.x_local + row0 * t.ldx;
+      __nv_bfloat16* dst = t.gather_mc + half_off + (size_t(c.rank) * t.rows_per_rank + row0) * p.K;
+      const int total = kPartRows * row_vecs;
       constexpr int kUnroll = 8;
       for (int i = threadIdx.x; i < total; i += kUnroll * blockDim.x) {
         uint4 v[kUnroll];
@@ -174,10 +181,19 @@ __device__ void tp_push_rows(const GemmParams& p, const TpParams& t, const CommC
         }
       }
       __syncthreads();
-      if (threadIdx.x == 0) __threadfence_system();
+      if (threadIdx.x == 0) {
+        __threadfence_system();
+        const uint32_t done = atomicAdd(t.counters + 1 + chunk, 1u);
+        last_part = (done == uint32_t(kParts) - 1u);
+        if (last_part) {
+          t.counters[1 + chunk] = 0;
+          __threadfence_system();
+        }
+      }
       __syncthreads();
-      if (threadIdx.x < c.world)
+      if (last_part && threadIdx.x < c.world)
         st_release_sys(c.flags[threadIdx.x] + (kTpChReady0 + chunk) * kMaxRanks + c.rank, q + 1u);
+      __syncthreads();
     }
     return;
   }
