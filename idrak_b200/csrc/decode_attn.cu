@@ -7,10 +7,11 @@
 //
 // paged_decode_kernel: grid (sequences, kv heads, splits). One CTA serves the G = heads / kv_heads query heads
 // that share a KV head over one contiguous share of the sequence's key blocks: each of its 4 warps stages
-// 32-key tiles of K and V in shared memory with 128-bit coalesced loads, lane l scores key l against the G
-// queries, the warp keeps an online softmax per query head, and lanes own slices of the head dimension for
-// the P·V accumulation. Splits write (max, sum, partial output) and decode_merge_kernel combines them in split
-// order. The kernel is bandwidth bound (each K / V byte is read once), which is why it runs on the FMA pipes.
+// 32-key tiles of K and V in shared memory with asynchronous 16-byte copies and runs Q·K^T and P·V as
+// m16n8k16 tensor-core MMAs with the G query heads as the (padded) 16 rows, keeping an online softmax per row
+// in registers. Splits write (max, sum, partial output) and decode_merge_kernel combines them in split
+// order. The kernel is bound by the bytes of K and V (each is read once); warp-level MMAs are enough to keep up
+// with them - a 16-row tile cannot feed tcgen05's 128-row instruction - while the FMA pipes are not.
 //
 // Reference counterparts: attention_decode_{f32,int8,bf16} (split over blocks, last block merges;
 // src/Idrak.Gpu/Cuda/PtxKernels.Rows.cs:2047-2060), kv_write_{f32,bf16} (PtxKernels.Decoding.cs:12),
@@ -37,131 +38,191 @@ struct DecodeParams {
   int window;                    // 0 = full; else attend to the last `window` positions only
 };
 
+// ---- warp-level tensor-core pieces (mma.sync m16n8k16, bf16 in, fp32 accumulate). Decode attention is bound by
+// the bytes of K and V; the tensor pipe only has to keep up with them, which these 16-row MMAs do with the G <= 16
+// query heads of a KV head as the rows - the FMA pipes cannot (2 multiply-adds per cache byte).
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(smem_row)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(smem_u32(smem_row)));
+}
+// 16-byte asynchronous copy global -> shared; `bytes` = 0 writes zeros instead (keys past the sequence's end)
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src, int bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 template <int D>
 __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const DecodeParams p) {
-  constexpr int kRow = D * 2 + 16;                       // padded shared-memory row (bytes)
-  constexpr int DPL = D / 32;                            // head-dim elements per lane in the P·V phase
+  constexpr int kRow = D * 2 + 16;                       // padded shared-memory row (bytes): conflict-free ldmatrix
+  constexpr int kChunks = D / 8;                         // 16-byte chunks per key row
+  constexpr int KS = D / 16;                             // k-steps of Q·K^T
+  constexpr int NT = D / 8;                              // n-tiles of P·V
   extern __shared__ uint8_t dsm[];
   const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
   const int G = p.H / p.Hkv;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  float* sq = reinterpret_cast<float*>(dsm);                                  // [G][D] queries, pre-scaled
-  uint8_t* sk = dsm + kDecMaxGroup * D * 4 + warp * (2 * kDecTile * kRow);     // this warp's K tile
+  uint8_t* sqb = dsm;                                                          // [16][kRow] queries (bf16), rows >= G zero
+  uint8_t* sk = dsm + 16 * kRow + warp * (2 * kDecTile * kRow);                // this warp's K tile
   uint8_t* sv = sk + kDecTile * kRow;                                          // and V tile
-  float* smerge = reinterpret_cast<float*>(dsm + kDecMaxGroup * D * 4 + kDecWarps * 2 * kDecTile * kRow);
+  float* smerge = reinterpret_cast<float*>(dsm + 16 * kRow + kDecWarps * 2 * kDecTile * kRow);
 
   const int len = p.seq_lens[seq];
   const int first_pos = (p.window > 0 && len > p.window) ? len - p.window : 0;
-  // this split's range of key tiles
   const int tiles = (len + kDecTile - 1) / kDecTile;
   const int first_tile = first_pos / kDecTile;
   const int span = tiles - first_tile;
   const int per = (span + p.splits - 1) / p.splits;
   const int t0 = first_tile + split * per, t1 = min(tiles, t0 + per);
 
-  for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
-    const int g = i / D, d = i - g * D;
-    sq[i] = __bfloat162float(p.q[(size_t(seq) * p.H + kvh * G + g) * D + d]) * p.scale_log2;
+  // queries of the G heads of this KV head -> shared (bf16, rows padded to 16 with zeros)
+  for (int i = threadIdx.x; i < 16 * kChunks; i += blockDim.x) {
+    const int g = i / kChunks, c = i - g * kChunks;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (g < G) v = *reinterpret_cast<const uint4*>(p.q + (size_t(seq) * p.H + kvh * G + g) * D + c * 8);
+    *reinterpret_cast<uint4*>(sqb + g * kRow + c * 16) = v;
   }
   __syncthreads();
+  // A fragments of Q for every k-step: ldmatrix.x4 gives (rows 0-7, k 0-7), (rows 8-15, k 0-7), (rows 0-7, k 8-15),
+  // (rows 8-15, k 8-15) = a0..a3
+  uint32_t qa[KS][4];
+#pragma unroll
+  for (int ks = 0; ks < KS; ++ks)
+    ldmatrix_x4(qa[ks], sqb + (lane & 15) * kRow + ks * 32 + (lane >> 4) * 16);
 
-  float m[kDecMaxGroup], l[kDecMaxGroup], acc[kDecMaxGroup][DPL];
+  float o[NT][4];
 #pragma unroll
-  for (int g = 0; g < kDecMaxGroup; ++g) {
-    m[g] = -INFINITY;
-    l[g] = 0.f;
-#pragma unroll
-    for (int j = 0; j < DPL; ++j) acc[g][j] = 0.f;
-  }
-  const size_t tok_stride = size_t(p.Hkv) * D;            // elements between tokens of a block
+  for (int n = 0; n < NT; ++n) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f; }
+  float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;      // rows lane / 4 and lane / 4 + 8
+  const size_t tok_stride = size_t(p.Hkv) * D;
   const int* table = p.block_table + size_t(seq) * p.max_blocks;
 
   for (int t = t0 + warp; t < t1; t += kDecWarps) {
     const int key0 = t * kDecTile;
-    // ---- stage 32 keys x D of K and V: chunk c of key r <- 16 bytes
-    constexpr int kChunks = D / 8;
+    // ---- stage 32 keys x D of K and V with asynchronous 16-byte copies (all in flight at once)
+#pragma unroll 4
     for (int i = lane; i < kDecTile * kChunks; i += 32) {
       const int r = i / kChunks, c = i - r * kChunks;
       const int pos = key0 + r;
-      uint4 kv4 = make_uint4(0, 0, 0, 0), vv4 = make_uint4(0, 0, 0, 0);
-      if (pos < len) {
+      const bool live = pos < len;
+      size_t off = 0;
+      if (live) {
         const int blk = table[pos / p.block_size];
-        const size_t off = (size_t(blk) * p.block_size + pos % p.block_size) * tok_stride + size_t(kvh) * D + c * 8;
-        kv4 = *reinterpret_cast<const uint4*>(p.k_cache + off);
-        vv4 = *reinterpret_cast<const uint4*>(p.v_cache + off);
+        off = (size_t(blk) * p.block_size + pos % p.block_size) * tok_stride + size_t(kvh) * D + c * 8;
       }
-      *reinterpret_cast<uint4*>(sk + r * kRow + c * 16) = kv4;
-      *reinterpret_cast<uint4*>(sv + r * kRow + c * 16) = vv4;
+      cp_async16(sk + r * kRow + c * 16, p.k_cache + off, live ? 16 : 0);
+      cp_async16(sv + r * kRow + c * 16, p.v_cache + off, live ? 16 : 0);
     }
+    cp_async_wait_all();
     __syncwarp();
-    // ---- scores: lane = key
-    const int pos = key0 + lane;
-    const bool valid = pos < len && pos >= first_pos;
-    float s[kDecMaxGroup];
+    // ---- S[16 x 32] = Q · K^T: 4 n-tiles of 8 keys
+    float s[4][4];
 #pragma unroll
-    for (int g = 0; g < kDecMaxGroup; ++g) s[g] = 0.f;
-    for (int c = 0; c < kChunks; ++c) {
-      const uint4 kk = *reinterpret_cast<const uint4*>(sk + lane * kRow + c * 16);
-      float kf[8];
-      float2 f;
-      f = unpack_bf16x2(kk.x); kf[0] = f.x; kf[1] = f.y;
-      f = unpack_bf16x2(kk.y); kf[2] = f.x; kf[3] = f.y;
-      f = unpack_bf16x2(kk.z); kf[4] = f.x; kf[5] = f.y;
-      f = unpack_bf16x2(kk.w); kf[6] = f.x; kf[7] = f.y;
+    for (int n = 0; n < 4; ++n) { s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f; }
 #pragma unroll
-      for (int g = 0; g < kDecMaxGroup; ++g) {
-        if (g < G) {
-          const float* qg = sq + g * D + c * 8;
+    for (int n = 0; n < 4; ++n) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) s[g] += qg[j] * kf[j];
-        }
+      for (int ks = 0; ks < KS; ks += 2) {
+        // matrices: (keys n*8.., d ks*16 + 0..7), (.., +8..15), (.., (ks+1)*16 + 0..7), (.., +8..15)
+        uint32_t kb[4];
+        ldmatrix_x4(kb, sk + (n * 8 + (lane & 7)) * kRow + ks * 32 + (lane >> 3) * 16);
+        mma_bf16_16816(s[n], qa[ks], kb[0], kb[1]);
+        mma_bf16_16816(s[n], qa[ks + 1], kb[2], kb[3]);
       }
     }
-    // ---- online softmax per query head, then P·V with lanes owning head-dim slices
+    // ---- mask, online softmax (log2 domain) for rows r0 = lane / 4 and r0 + 8
+    float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
-    for (int g = 0; g < kDecMaxGroup; ++g) {
-      if (g < G) {
-        const float sc = valid ? s[g] : -INFINITY;
-        const float mt = warp_max(sc);
-        const float mn = fmaxf(m[g], mt);
-        const float alpha = (m[g] == -INFINITY) ? 0.f : exp2f(m[g] - mn);
-        const float pr = (valid && mn != -INFINITY) ? exp2f(sc - mn) : 0.f;
-        l[g] = l[g] * alpha + warp_sum(pr);
-        m[g] = mn;
+    for (int n = 0; n < 4; ++n) {
 #pragma unroll
-        for (int j = 0; j < DPL; ++j) acc[g][j] *= alpha;
-        for (int r = 0; r < kDecTile; ++r) {
-          const float pw = __shfl_sync(0xffffffffu, pr, r);
-          if (pw != 0.f) {
-            const __nv_bfloat16* vr = reinterpret_cast<const __nv_bfloat16*>(sv + r * kRow) + lane * DPL;
+      for (int j = 0; j < 2; ++j) {
+        const int pos = key0 + n * 8 + 2 * (lane & 3) + j;
+        const bool valid = pos < len && pos >= first_pos;
+        s[n][j] = valid ? s[n][j] * p.scale_log2 : -INFINITY;
+        s[n][2 + j] = valid ? s[n][2 + j] * p.scale_log2 : -INFINITY;
+        mx0 = fmaxf(mx0, s[n][j]);
+        mx1 = fmaxf(mx1, s[n][2 + j]);
+      }
+    }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+    const float a0 = (m0 == -INFINITY) ? 0.f : exp2f(m0 - mn0);
+    const float a1 = (m1 == -INFINITY) ? 0.f : exp2f(m1 - mn1);
+    float sum0 = 0.f, sum1 = 0.f;
+    uint32_t pa[2][4];                                   // P as A fragments of the two 16-key k-steps
 #pragma unroll
-            for (int j = 0; j < DPL; ++j) acc[g][j] += pw * __bfloat162float(vr[j]);
-          }
-        }
+    for (int n = 0; n < 4; ++n) {
+      const float p00 = (mn0 == -INFINITY) ? 0.f : exp2f(s[n][0] - mn0);
+      const float p01 = (mn0 == -INFINITY) ? 0.f : exp2f(s[n][1] - mn0);
+      const float p10 = (mn1 == -INFINITY) ? 0.f : exp2f(s[n][2] - mn1);
+      const float p11 = (mn1 == -INFINITY) ? 0.f : exp2f(s[n][3] - mn1);
+      sum0 += p00 + p01;
+      sum1 += p10 + p11;
+      pa[n >> 1][(n & 1) * 2 + 0] = pack_bf16x2(p00, p01);
+      pa[n >> 1][(n & 1) * 2 + 1] = pack_bf16x2(p10, p11);
+    }
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 1);
+    sum0 += __shfl_xor_sync(0xffffffffu, sum0, 2);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 1);
+    sum1 += __shfl_xor_sync(0xffffffffu, sum1, 2);
+    l0 = l0 * a0 + sum0;
+    l1 = l1 * a1 + sum1;
+    m0 = mn0;
+    m1 = mn1;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
+    // ---- O[16 x D] += P[16 x 32] · V[32 x D]: V is [key][d], so its B fragments come through transposing loads
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+#pragma unroll
+      for (int n = 0; n < NT; n += 2) {
+        // matrices: (keys kk*16 + 0..7, d n*8..), (keys +8..15, d n*8..), (keys 0..7, d (n+1)*8..), (keys 8..15, ..)
+        uint32_t vb[4];
+        ldmatrix_x4_trans(vb, sv + (kk * 16 + (lane & 15)) * kRow + (n + (lane >> 4)) * 16);
+        mma_bf16_16816(o[n], pa[kk], vb[0], vb[1]);
+        mma_bf16_16816(o[n + 1], pa[kk], vb[2], vb[3]);
       }
     }
     __syncwarp();
   }
 
   // ---- combine the 4 warps of the CTA (in warp order), then write the split's partial or the final output
-  // smerge layout: [warp][g][D + 2]
+  // smerge layout: [warp][16][D + 2]
+  {
+    const int r0 = lane >> 2, c0 = 2 * (lane & 3);
+    float* d0 = smerge + (size_t(warp) * 16 + r0) * (D + 2);
+    float* d1 = smerge + (size_t(warp) * 16 + r0 + 8) * (D + 2);
 #pragma unroll
-  for (int g = 0; g < kDecMaxGroup; ++g) {
-    if (g < G) {
-      float* dst = smerge + (size_t(warp) * kDecMaxGroup + g) * (D + 2);
-#pragma unroll
-      for (int j = 0; j < DPL; ++j) dst[lane * DPL + j] = acc[g][j];
-      if (lane == 0) { dst[D] = m[g]; dst[D + 1] = l[g]; }
+    for (int n = 0; n < NT; ++n) {
+      d0[n * 8 + c0] = o[n][0]; d0[n * 8 + c0 + 1] = o[n][1];
+      d1[n * 8 + c0] = o[n][2]; d1[n * 8 + c0 + 1] = o[n][3];
     }
+    if ((lane & 3) == 0) { d0[D] = m0; d0[D + 1] = l0; d1[D] = m1; d1[D + 1] = l1; }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < G * D; i += blockDim.x) {
     const int g = i / D, d = i - g * D;
     float mm = -INFINITY;
-    for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, smerge[(size_t(w) * kDecMaxGroup + g) * (D + 2) + D]);
+    for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, smerge[(size_t(w) * 16 + g) * (D + 2) + D]);
     float ll = 0.f, oo = 0.f;
     for (int w = 0; w < kDecWarps; ++w) {
-      const float* src = smerge + (size_t(w) * kDecMaxGroup + g) * (D + 2);
+      const float* src = smerge + (size_t(w) * 16 + g) * (D + 2);
       const float a = (src[D] == -INFINITY) ? 0.f : exp2f(src[D] - mm);
       ll += src[D + 1] * a;
       oo += src[d] * a;
@@ -218,8 +279,8 @@ __global__ void kv_write_paged_kernel(const __nv_bfloat16* __restrict__ k_src, c
 
 template <int D>
 static size_t decode_smem() {
-  return size_t(kDecMaxGroup) * D * 4 + size_t(kDecWarps) * 2 * kDecTile * (D * 2 + 16) +
-         size_t(kDecWarps) * kDecMaxGroup * (D + 2) * 4;
+  return size_t(16) * (D * 2 + 16) + size_t(kDecWarps) * 2 * kDecTile * (D * 2 + 16) +
+         size_t(kDecWarps) * 16 * (D + 2) * 4;
 }
 
 }  // namespace idrak

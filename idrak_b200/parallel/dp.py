@@ -83,6 +83,35 @@ class _ShardedAdamW:
         self.v.copy_(state["v"])
 
 
+_HOOK_PROBE = None
+
+
+def _hook_fires_without_gradient() -> bool:
+    """Whether this PyTorch calls a parameter's post-accumulate-grad hook even when the backward function returned
+    ``None`` for it (newer versions do). Where it does, the hook alone says "this parameter's gradient is final" -
+    also for gradients a kernel wrote straight into ``.grad`` - and the direct-write notification must not be
+    counted on top of it."""
+    global _HOOK_PROBE
+    if _HOOK_PROBE is None:
+        class _Probe(torch.autograd.Function):
+            @staticmethod
+            def forward(ctx, x, w):
+                return x * 2
+
+            @staticmethod
+            def backward(ctx, g):
+                return g * 2, None
+
+        w = torch.nn.Parameter(torch.ones(1))
+        x = torch.ones(1, requires_grad=True)
+        fired = []
+        handle = w.register_post_accumulate_grad_hook(lambda _p: fired.append(1))
+        _Probe.apply(x, w).sum().backward()
+        handle.remove()
+        _HOOK_PROBE = bool(fired)
+    return _HOOK_PROBE
+
+
 class DataParallel:
     def __init__(self, model: torch.nn.Module, lr: float = 3e-4, betas=(0.9, 0.95), eps: float = 1e-8,
                  weight_decay: float = 0.1, max_grad_norm: float = 1.0, mode: str = "fused", group=None,
@@ -136,6 +165,7 @@ class DataParallel:
             for i in members:
                 self._bucket_of[i] = b
         self._remaining = [len(m) for _, _, m in self.buckets]
+        self._reported = {}
         self._launched = [False] * len(self.buckets)
 
     def _init_shard(self, decay_ids):
@@ -173,12 +203,24 @@ class DataParallel:
         for p in params:
             i = index_of[id(p)]
             self._handles.append(p.register_post_accumulate_grad_hook(lambda _p, i=i: self._grad_ready(i)))
-            p._idrak_ready = (lambda i=i: self._grad_ready(i))     # called by direct gradient writes
+            if not _hook_fires_without_gradient():
+                p._idrak_ready = (lambda i=i: self._grad_ready(i))     # called by direct gradient writes
 
     def _grad_ready(self, index: int):
         if not self._overlapping:
             return
         b = self._bucket_of[index]
+        if index in self._reported:
+            import os
+            first = self._reported[index] if os.environ.get("IDRAK_DP_DEBUG") else ""
+            raise RuntimeError(f"data parallel: parameter {index} reported its gradient ready twice in one backward "
+                               f"pass; its bucket would be reduced before the last write{first}")
+        import os
+        if os.environ.get("IDRAK_DP_DEBUG"):
+            import traceback
+            self._reported[index] = "\nfirst report from:\n" + "".join(traceback.format_stack(limit=8))
+        else:
+            self._reported[index] = True
         self._remaining[b] -= 1
         if self._remaining[b] == 0:
             self._launch_bucket(b)
@@ -189,6 +231,7 @@ class DataParallel:
     def overlap(self):
         """Wrap ``loss.backward()``: buckets are reduced on a side stream as their gradients complete."""
         self._remaining = [len(m) for _, _, m in self.buckets]
+        self._reported = {}
         self._launched = [False] * len(self.buckets)
         self._work = []
         if self.mode == "fused":

@@ -100,7 +100,7 @@ class LLMEngine:
     def __init__(self, model: Decoder, num_blocks: Optional[int] = None, block_size: int = 16, max_batch: int = 64,
                  max_prefill_tokens: int = 8192, queue_limit: int = 0, prefix_sharing: bool = True,
                  eos_token_ids: Sequence[int] = (), cache_bytes: Optional[int] = None,
-                 clock: Callable[[], float] = time.monotonic):
+                 clock: Callable[[], float] = time.monotonic, use_graph: bool = True):
         spec = model.spec
         p = next(model.parameters())
         if num_blocks is None:
@@ -125,6 +125,7 @@ class LLMEngine:
         self.tokens_generated = 0
         self.tokens_prefilled = 0
         self.steps = 0
+        self.use_graph = bool(use_graph) and self.device.type == "cuda"
         self.last_error: Optional[BaseException] = None
 
     # ------------------------------------------------------------------ requests
@@ -264,7 +265,10 @@ class LLMEngine:
             dev = self.device
             if dev.type == "cuda":
                 table, last, pos = (t.pin_memory().to(dev, non_blocking=True) for t in (table, last, pos))
-            logits = self.runner.decode(last, pos, table, max_len_hint=longest)
+            if self.use_graph:
+                logits = self.runner.decode_graphed(last, pos, table, longest)
+            else:
+                logits = self.runner.decode(last, pos, table, max_len_hint=longest)
         tokens, lps = self._sample(logits, reqs)
         now = self.clock()
         for i, r in enumerate(reqs):

@@ -42,10 +42,15 @@ class ModelRunner:
         self.block_size, self.num_blocks, self.max_batch = block_size, num_blocks, max_batch
         s = self.spec
         cd = cache_dtype or self.dtype
-        self.k_cache = [torch.zeros(num_blocks, block_size, s.kv_heads, s.head_dim, dtype=cd, device=self.device)
+        # one block more than the scheduler hands out: padding rows of a graph-replayed decode batch write there
+        self.k_cache = [torch.zeros(num_blocks + 1, block_size, s.kv_heads, s.head_dim, dtype=cd, device=self.device)
                         for _ in range(s.layers)]
         self.v_cache = [torch.zeros_like(k) for k in self.k_cache]
+        self.trash_block = num_blocks
         self.max_blocks_per_seq = (s.max_positions + block_size - 1) // block_size
+        self._graphs = {}
+        self._graph_pool = None
+        self.graph_replays = 0
 
     # ------------------------------------------------------------------ sizing
     @staticmethod
@@ -219,6 +224,56 @@ class ModelRunner:
         for blk in self.model.blocks:
             x = self._block(blk, x, attend)
         return self._logits(self.model.norm(x))
+
+    # ------------------------------------------------------------------ decode as a replayed CUDA graph
+    BATCH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+    @torch.no_grad()
+    def decode_graphed(self, tokens: torch.Tensor, positions: torch.Tensor, block_table: torch.Tensor,
+                       longest: int) -> torch.Tensor:
+        """``decode`` recorded once per (batch bucket, context bucket) as a CUDA graph and replayed: a decode step is
+        hundreds of small launches, and replaying them removes the host's share of the step. The batch is padded to
+        the bucket with rows that write to a spare cache block; the context bucket fixes the key split of the
+        attention kernel. Returns logits ``[n, padded vocabulary]`` (a view of the graph's output buffer)."""
+        n = tokens.shape[0]
+        bucket = next((b for b in self.BATCH_BUCKETS if b >= n), None)
+        if bucket is None or self.device.type != "cuda" or self.spec.attention_softcap is not None:
+            return self.decode(tokens, positions, block_table, max_len_hint=longest)
+        ctx = 256
+        while ctx < longest:
+            ctx *= 2
+        width = self.max_blocks_per_seq
+        key = (bucket, ctx)
+        entry = self._graphs.get(key)
+        if entry is None:
+            tok = torch.zeros(bucket, dtype=torch.int32, device=self.device)
+            pos = torch.zeros(bucket, dtype=torch.int32, device=self.device)
+            tab = torch.full((bucket, width), self.trash_block, dtype=torch.int32, device=self.device)
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):                   # warm-up: lazy buffers and kernel attributes get created
+                for _ in range(2):
+                    self.decode(tok, pos, tab, max_len_hint=ctx)
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, pool=self._graph_pool):
+                out = self.decode(tok, pos, tab, max_len_hint=ctx)
+            if self._graph_pool is None:
+                self._graph_pool = graph.pool()
+            entry = self._graphs[key] = (graph, tok, pos, tab, out)
+        graph, tok, pos, tab, out = entry
+        tok[:n].copy_(tokens, non_blocking=True)
+        pos[:n].copy_(positions, non_blocking=True)
+        if n < bucket:
+            tok[n:].zero_()
+            pos[n:].zero_()
+            tab[n:].fill_(self.trash_block)
+        w = block_table.shape[1]
+        tab[:n, :w].copy_(block_table, non_blocking=True)
+        graph.replay()
+        self.graph_replays += 1
+        return out[:n]
 
     def _decode_softcap(self, q, li, block_table, lens, scale, window):
         """Soft-capped scores (Gemma-2 style) composed from primitives, one sequence at a time."""
