@@ -151,6 +151,16 @@ class ModelRunner:
         tables = [torch.tensor(it.blocks, dtype=torch.long, device=dev) if it.start > 0 else None for it in items]
         x = self._embed(ids_t, pos_t)
         layer_index = {id(blk.attn): i for i, blk in enumerate(self.model.blocks)}
+        runs = []                                  # (first item, count, length) of >= 2 fresh prompts of equal length
+        i = 0
+        while i < len(items):
+            j = i
+            while (j + 1 < len(items) and items[j + 1].start == 0 and items[i].start == 0
+                   and len(items[j + 1].tokens) == len(items[i].tokens)):
+                j += 1
+            if j > i and len(items[i].tokens) % 8 == 0:
+                runs.append((i, j - i + 1, len(items[i].tokens)))
+            i = j + 1
 
         def attend(attn, h, residual):
             li = layer_index[id(attn)]
@@ -164,7 +174,18 @@ class ModelRunner:
             window = s.sliding_window if s.is_windowed(attn.layer) else None
             fast = window is None and s.attention_softcap is None
             out = torch.empty(qkv2.shape[0], H * D, dtype=qkv.dtype, device=dev)
+            done = set()
+            if fast:
+                # runs of fresh prompts of one length are contiguous in the pack: one batched attention launch
+                for first, count, length in runs:
+                    a, b = bounds[first], bounds[first + count]
+                    o = ops.attention(q[a:b].unflatten(0, (count, length)), k[a:b].unflatten(0, (count, length)),
+                                      v[a:b].unflatten(0, (count, length)), True, attn.scale)
+                    out[a:b] = o.reshape(b - a, H * D)
+                    done.update(range(first, first + count))
             for i, it in enumerate(items):
+                if i in done:
+                    continue
                 a, b = bounds[i], bounds[i + 1]
                 qi = q[a:b][None]
                 if it.start > 0:     # queries see the shared prefix too: read keys / values back from the cache
