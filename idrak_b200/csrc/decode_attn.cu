@@ -26,7 +26,8 @@ constexpr int kDecTile = 32;       // keys per warp tile
 constexpr int kDecMaxGroup = 16;   // query heads per KV head
 
 struct DecodeParams {
-  const __nv_bfloat16* q;        // [seqs, H, D]
+  const __nv_bfloat16* q;        // [seqs, H, D], sequences q_stride elements apart
+  long long q_stride;
   const __nv_bfloat16* k_cache;
   const __nv_bfloat16* v_cache;
   const int* block_table;        // [seqs, max_blocks]
@@ -92,7 +93,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
   for (int i = threadIdx.x; i < 16 * kChunks; i += blockDim.x) {
     const int g = i / kChunks, c = i - g * kChunks;
     uint4 v = make_uint4(0, 0, 0, 0);
-    if (g < G) v = *reinterpret_cast<const uint4*>(p.q + (size_t(seq) * p.H + kvh * G + g) * D + c * 8);
+    if (g < G) v = *reinterpret_cast<const uint4*>(p.q + size_t(seq) * p.q_stride + size_t(kvh * G + g) * D + c * 8);
     *reinterpret_cast<uint4*>(sqb + g * kRow + c * 16) = v;
   }
   __syncthreads();
@@ -291,7 +292,7 @@ IDRAK_API long long idrak_decode_partial_floats(int seqs, int H, int D, int spli
   return splits > 1 ? (long long)seqs * H * splits * (D + 2) : 0;
 }
 
-IDRAK_API int idrak_paged_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+IDRAK_API int idrak_paged_decode(const void* q, long long q_stride, const void* k_cache, const void* v_cache, const int* block_table,
                                  const int* seq_lens, void* out, float* partial, int seqs, int H, int Hkv, int D,
                                  int block_size, int max_blocks, int splits, float scale, int window, void* stream_) {
   if (D != 64 && D != 128) return -2;
@@ -300,6 +301,8 @@ IDRAK_API int idrak_paged_decode(const void* q, const void* k_cache, const void*
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   DecodeParams p;
   p.q = static_cast<const __nv_bfloat16*>(q);
+  p.q_stride = q_stride > 0 ? q_stride : (long long)H * D;
+  if ((p.q_stride % 8) || (reinterpret_cast<uintptr_t>(q) & 15)) return -5;
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
   p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
   p.block_table = block_table;

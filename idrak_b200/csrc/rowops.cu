@@ -105,6 +105,85 @@ __global__ void __launch_bounds__(128) norm_fwd_kernel(const __nv_bfloat16* __re
   }
 }
 
+// The same forward for a handful of long rows (a decode step): one 256-thread block per row, so a row's loads
+// are spread over eight warps instead of queueing behind one. C % 8 == 0, C <= 8 * 256 * 4.
+__device__ __forceinline__ float block_sum_256(float v, float* red) {
+  v = warp_sum(v);
+  __syncthreads();                       // red may still be read from the previous call
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float t = 0.f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) t += red[i];
+  return t;
+}
+
+__global__ void __launch_bounds__(256) norm_fwd_block_kernel(const __nv_bfloat16* __restrict__ x,
+                                                             const __nv_bfloat16* __restrict__ residual,
+                                                             const __nv_bfloat16* __restrict__ w,
+                                                             const __nv_bfloat16* __restrict__ b,
+                                                             __nv_bfloat16* __restrict__ out,
+                                                             __nv_bfloat16* __restrict__ sum_out,
+                                                             float* __restrict__ mean_out, float* __restrict__ rstd_out,
+                                                             int rows, int C, float eps, int rms) {
+  __shared__ float red[8];
+  const int row = blockIdx.x;
+  const size_t base = size_t(row) * C;
+  const int nvec = C >> 3;
+  float v[4][8], wv[4][8];
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      load8(x + base + vi * 8, v[i]);
+      load8(w + vi * 8, wv[i]);
+      if (residual) {
+        float r[8];
+        load8(residual + base + vi * 8, r);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] += r[j];
+        if (sum_out) {
+          store8(sum_out + base + vi * 8, v[i]);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[i][j] = __bfloat162float(__float2bfloat16(v[i][j]));
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += v[i][j];
+    }
+  }
+  float mean = 0.f;
+  if (!rms) mean = block_sum_256(s, red) / float(C);
+  float q = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    if (threadIdx.x + i * 256 < nvec) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float d = v[i][j] - mean;
+        q += d * d;
+      }
+    }
+  }
+  const float rstd = rsqrtf(block_sum_256(q, red) / float(C) + eps);
+  if (threadIdx.x == 0) {
+    if (mean_out) mean_out[row] = mean;
+    if (rstd_out) rstd_out[row] = rstd;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int vi = threadIdx.x + i * 256;
+    if (vi < nvec) {
+      float bv[8], o[8];
+      if (b) load8(b + vi * 8, bv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * wv[i][j] + (b ? bv[j] : 0.f);
+      store8(out + base + vi * 8, o);
+    }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // LayerNorm / RMSNorm backward. One warp per row for dx; each block also accumulates the rows it owns
 // into per-block partial sums of dw / db ([gridDim.x, C] fp32) which `colsum_final_kernel` folds in
@@ -647,6 +726,12 @@ IDRAK_API int idrak_norm_fwd(const void* x, const void* residual, const void* w,
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   const int blocks = (rows + 3) / 4;
   const int nvec = C / 8;
+  if (rows <= 2 * sm_count() && nvec >= 128) {      // few long rows: a block per row
+    norm_fwd_block_kernel<<<rows, 256, 0, s>>>(CBF(x), CBF(residual), CBF(w), CBF(b), BF(out), BF(sum_out), mean, rstd,
+                                               rows, C, eps, rms);
+    note_launches(1);
+    return int(cudaGetLastError());
+  }
 #define NF(V) norm_fwd_kernel<V><<<blocks, 128, 0, s>>>(CBF(x), CBF(residual), CBF(w), CBF(b), BF(out), BF(sum_out), mean, rstd, rows, C, eps, rms)
   if (nvec <= 32 * 1) NF(1);
   else if (nvec <= 32 * 2) NF(2);

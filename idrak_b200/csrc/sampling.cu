@@ -38,7 +38,25 @@ __global__ void __launch_bounds__(kSampleThreads) argmax_rows_kernel(const void*
   const int row = blockIdx.x;
   float best = -INFINITY;
   int bi = 0x7fffffff;
-  for (int j = threadIdx.x; j < vocab; j += blockDim.x) {
+  int tail_from = 0;
+  if (!fp32 && (ld & 7) == 0 && (reinterpret_cast<uintptr_t>(logits) & 15) == 0) {
+    // bf16 rows that start on 16 bytes: eight logits per load
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(logits) + size_t(row) * ld);
+    const int nvec = vocab >> 3;
+    for (int c = threadIdx.x; c < nvec; c += blockDim.x) {
+      const uint4 u = src[c];
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {
+        const float lo = __uint_as_float(w[h] << 16), hi = __uint_as_float(w[h] & 0xffff0000u);
+        const int j = c * 8 + h * 2;
+        if (lo > best || (lo == best && j < bi)) { best = lo; bi = j; }
+        if (hi > best || (hi == best && j + 1 < bi)) { best = hi; bi = j + 1; }
+      }
+    }
+    tail_from = nvec << 3;
+  }
+  for (int j = tail_from + threadIdx.x; j < vocab; j += blockDim.x) {
     const float v = load_logit(logits, fp32, size_t(row) * ld + j);
     if (v > best || (v == best && j < bi)) { best = v; bi = j; }
   }

@@ -41,6 +41,48 @@ def _timed(fn: Callable[[], None], warmup: int, iters: int, flush: bool) -> floa
     return total / iters
 
 
+def _timed_graph(fn: Callable[[], None], warmup: int, iters: int, flush: bool, reps: int) -> float:
+    """Device time of one ``fn`` with the host's launch cost taken out: ``reps`` copies of (L2 flush, fn) are captured
+    into one CUDA graph, a second graph holds the flushes alone, and the difference of their replay times is
+    divided by ``reps``. For kernels of a few microseconds, where the plain loop measures the host."""
+    dev = torch.device("cuda")
+    junk = torch.empty(160 << 20, dtype=torch.uint8, device=dev) if flush else None
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for _ in range(max(warmup, 1)):
+            fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+
+    def capture(with_fn: bool):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                if junk is not None:
+                    junk.fill_(1)
+                if with_fn:
+                    fn()
+        return g
+
+    def replay_ms(g) -> float:
+        g.replay()
+        torch.cuda.synchronize()
+        total = 0.0
+        for _ in range(iters):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            total += a.elapsed_time(b)
+        return total / iters
+
+    full = replay_ms(capture(True))
+    base = replay_ms(capture(False)) if junk is not None else 0.0
+    return (full - base) / reps
+
+
 def case_gemm(a) -> Tuple[Callable, float, float]:
     from ..ops.gemm import gemm
     x = torch.randn(a.m, a.k, device="cuda", dtype=torch.bfloat16)
@@ -149,13 +191,16 @@ def main(argv=None) -> int:
         ap.add_argument(f"--{name}", type=int, default=default)
     ap.add_argument("--kind", default="int4", choices=["int4", "int8"])
     ap.add_argument("--flush-l2", action="store_true")
+    ap.add_argument("--graph", type=int, default=0, metavar="REPS",
+                    help="time REPS captured copies per replay of a CUDA graph (takes the host's launch cost out)")
     a = ap.parse_args(argv)
     if a.case == "list":
         print("\n".join(sorted(CASES)))
         return 0
     torch.cuda.set_device(0)
     fn, flops, nbytes = CASES[a.case](a)
-    ms = _timed(fn, a.warmup, a.iters, a.flush_l2)
+    ms = (_timed_graph(fn, a.warmup, a.iters, a.flush_l2, a.graph) if a.graph > 0
+          else _timed(fn, a.warmup, a.iters, a.flush_l2))
     from .. import _native
     _native.check_status()
     out = {"case": a.case, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1) if flops else None,

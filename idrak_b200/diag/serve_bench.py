@@ -54,6 +54,9 @@ def main(argv=None) -> int:
     eng.generate(prompts[: min(a.max_batch, a.requests)], GenerationOptions.greedy_options(4))
     torch.cuda.synchronize()
     steps0, gen0, pre0 = eng.steps, eng.tokens_generated, eng.tokens_prefilled
+    for d in (eng.phase_seconds, eng.phase_steps):
+        for k in d:
+            d[k] = 0
     t0 = time.perf_counter()
     records = eng.generate(prompts, opts)
     torch.cuda.synchronize()
@@ -68,7 +71,10 @@ def main(argv=None) -> int:
            "mean_ttft_s": round(sum(ttft) / max(len(ttft), 1), 3), "graph_replays": eng.runner.graph_replays,
            "parameters": params, "quant": a.quant, "dtype": "bf16",
            "model": f"llama-like {a.layers}L d{a.dim} h{a.heads}/{a.kv_heads} ff{a.ff} v{a.vocab}",
-           "preemptions": eng.stats()["preemptions"]}
+           "preemptions": eng.stats()["preemptions"],
+           "prefill_seconds": round(eng.phase_seconds["prefill"], 3), "prefill_steps": eng.phase_steps["prefill"],
+           "decode_seconds": round(eng.phase_seconds["decode"], 3), "decode_steps": eng.phase_steps["decode"],
+           "ms_per_decode_step": round(eng.phase_seconds["decode"] / max(eng.phase_steps["decode"], 1) * 1e3, 3)}
     print(json.dumps(out))
     return 0
 

@@ -26,7 +26,7 @@ def _bind():
         return
     vp, i, f, ll = C.c_void_p, C.c_int, C.c_float, C.c_longlong
     _native.bind("idrak_decode_partial_floats", ll, [i, i, i, i])
-    _native.bind("idrak_paged_decode", i, [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, i, vp])
+    _native.bind("idrak_paged_decode", i, [vp, C.c_longlong, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, i, vp])
     _native.bind("idrak_kv_write_paged", i, [vp, vp, ll, vp, vp, vp, i, i, vp])
     _native.bind("idrak_argmax_rows", i, [vp, i, i, i, ll, vp, vp])
     _native.bind("idrak_sample_rows", i, [vp, i, i, i, ll, vp, vp, vp, vp, vp, vp, vp, i, vp, vp, vp, vp, C.c_uint, vp])
@@ -91,12 +91,14 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
         ctas = seqs * Hkv
         longest = max_len_hint if max_len_hint is not None else block_table.shape[1] * bs
         splits = max(1, min(lib.idrak_sm_count() * 2 // max(ctas, 1), (longest + 255) // 256, 32))
-    out = torch.empty_like(q)
+    out = torch.empty(seqs, H, D, dtype=q.dtype, device=q.device)
     part = None
     if splits > 1:
         part = scratch("decode_partial", lib.idrak_decode_partial_floats(seqs, H, D, splits), torch.float32, q.device)
-    assert q.is_contiguous() and block_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
-    rc = lib.idrak_paged_decode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
+    if q.stride(2) != 1 or q.stride(1) != D or q.stride(0) % 8 or q.data_ptr() % 16:
+        q = q.contiguous()                     # heads must be packed; sequences may be a strided view
+    assert block_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
+    rc = lib.idrak_paged_decode(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
                                 seq_lens.data_ptr(), out.data_ptr(), ptr(part), seqs, H, Hkv, D, bs,
                                 block_table.shape[1], splits, float(scale), int(window), stream_ptr())
     _native.check(rc, "idrak_paged_decode")

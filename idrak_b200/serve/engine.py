@@ -125,6 +125,8 @@ class LLMEngine:
         self.tokens_generated = 0
         self.tokens_prefilled = 0
         self.steps = 0
+        self.phase_seconds = {"prefill": 0.0, "decode": 0.0}
+        self.phase_steps = {"prefill": 0, "decode": 0}
         self.use_graph = bool(use_graph) and self.device.type == "cuda"
         self.last_error: Optional[BaseException] = None
 
@@ -238,6 +240,7 @@ class LLMEngine:
             self._notify(outs)
             return outs
         self.steps += 1
+        started = time.perf_counter()
         reqs = [self.requests[i] for i in ids]
         bs = self.block_size
         if kind == PREFILL:
@@ -269,7 +272,10 @@ class LLMEngine:
                 logits = self.runner.decode_graphed(last, pos, table, longest)
             else:
                 logits = self.runner.decode(last, pos, table, max_len_hint=longest)
-        tokens, lps = self._sample(logits, reqs)
+        tokens, lps = self._sample(logits, reqs)       # reads the tokens back: the step's device work is done here
+        phase = "prefill" if kind == PREFILL else "decode"
+        self.phase_seconds[phase] += time.perf_counter() - started
+        self.phase_steps[phase] += 1
         now = self.clock()
         for i, r in enumerate(reqs):
             tok = int(tokens[i])
@@ -313,5 +319,7 @@ class LLMEngine:
 
     def stats(self) -> dict:
         s = self.sched.stats()
-        s.update(tokens_generated=self.tokens_generated, tokens_prefilled=self.tokens_prefilled, steps=self.steps)
+        s.update(tokens_generated=self.tokens_generated, tokens_prefilled=self.tokens_prefilled, steps=self.steps,
+                 prefill_seconds=self.phase_seconds["prefill"], decode_seconds=self.phase_seconds["decode"],
+                 prefill_steps=self.phase_steps["prefill"], decode_steps=self.phase_steps["decode"])
         return s

@@ -236,7 +236,7 @@ class ModelRunner:
             dops.kv_write_paged(k, v, slots, self.k_cache[li], self.v_cache[li])
             window = s.sliding_window if s.is_windowed(attn.layer) else 0
             if s.attention_softcap is None:
-                o = dops.paged_decode(q.contiguous(), self.k_cache[li], self.v_cache[li], block_table, lens,
+                o = dops.paged_decode(q, self.k_cache[li], self.v_cache[li], block_table, lens,
                                       attn.scale, window or 0, max_len_hint=max_len_hint)
             else:
                 o = self._decode_softcap(q, li, block_table, lens, attn.scale, window or None)
