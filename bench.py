@@ -7,6 +7,7 @@ synthetic uniform token ids, random-init weights. Metric: train tokens/s over al
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
     python bench.py --impl reference        # the reference's own build (needs the .NET SDK)
+    python bench.py --impl torch            # comparison arm: the same step on library kernels + DDP only
 
 Rank 0 prints one JSON line. ``value`` is timed on the device (CUDA events, max over ranks) over
 exactly ``--steps`` optimizer steps with the inputs resident on the GPU; ``e2e`` times the same steps
@@ -32,7 +33,7 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--impl", default="idrak_b200", choices=["idrak_b200", "reference"])
+    ap.add_argument("--impl", default="idrak_b200", choices=["idrak_b200", "reference", "torch"])
     ap.add_argument("--layers", type=int, default=12)
     ap.add_argument("--dim", type=int, default=768)
     ap.add_argument("--heads", type=int, default=12)
@@ -125,18 +126,28 @@ def main():
     from idrak_b200.training import TrainStep
 
     lib = _native.lib()
+    is_torch = args.impl == "torch"
     spec = DecoderSpec.gpt2(layers=args.layers, dim=args.dim, heads=args.heads, vocab=args.vocab,
                             max_positions=args.seq)
-    model = build_decoder(spec, seed=1234).to(dev, torch.bfloat16)
     sync = None
-    if world > 1:
+    if is_torch:
+        # the comparison arm: library kernels and DistributedDataParallel only (baseline/torch_gpt2.py)
+        from baseline.torch_gpt2 import TorchStep
+        step = TorchStep(args.layers, args.dim, args.heads, args.vocab, args.seq, dev, world)
+        step.replays, step.graph_kernels = 0, 0
+    else:
+        model = build_decoder(spec, seed=1234).to(dev, torch.bfloat16)
+    if is_torch:
+        pass
+    elif world > 1:
         from idrak_b200.parallel.dp import DataParallel
         sync = DataParallel(model, lr=6e-4, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0,
                             mode=args.dp)
         opt = sync.optimizer
     else:
         opt = FusedAdamW(model.decay_groups(0.1), lr=6e-4, betas=(0.9, 0.95), weight_decay=0.1, max_grad_norm=1.0)
-    step = TrainStep(model, opt, sync=sync, use_graph=bool(args.graph), ignore_index=None)
+    if not is_torch:
+        step = TrainStep(model, opt, sync=sync, use_graph=bool(args.graph), ignore_index=None)
 
     B, S = args.micro_batch, args.seq
     gen = torch.Generator().manual_seed(1000 + rank)
@@ -195,7 +206,7 @@ def main():
     ms, e2e_ms = float(t[0]), float(t[1])
     tokens = B * S * world * args.steps
     if rank == 0:
-        graph_on = bool(args.graph)
+        graph_on = bool(args.graph) and not is_torch
         value = tokens / (ms / 1e3)
         out = {
             "metric": "train tokens/s (GPT-2-small DP bf16)", "value": value, "unit": "tokens/s",
@@ -203,11 +214,13 @@ def main():
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": (value / PUBLISHED_BASELINE) if PUBLISHED_BASELINE else None,
             "dtype": "bf16", "data": "synthetic uniform token ids, random-init weights",
-            "impl": "idrak_b200",
+            "impl": args.impl,
             "config": {"model": "gpt2-small (12L, d768, 12 heads, ff 3072 GELU, vocab 50257)"
                        if (args.layers, args.dim) == (12, 768) else f"gpt2 {args.layers}L d{args.dim}",
                        "global_batch": B * world, "seq_len": S, "parallelism": f"dp{world}",
                        "optimizer": "AdamW b0.9/0.95 wd0.1 clip1.0, fp32 master + moments",
+                       "numerics": ("fp32 parameters under bf16 autocast; library kernels and DDP only" if is_torch
+                                    else "bf16 parameters and activations, fp32 master copy in the optimizer"),
                        "cuda_graph": graph_on, "dp_mode": args.dp if world > 1 else None,
                        "l2_policy": "working set per step (>10 GB of activations and weights) far exceeds the "
                                     "126 MB L2; 8 distinct input batches cycled",

@@ -1,0 +1,119 @@
+"""Scopes that change how work inside them runs: product precision, activation memory policy, tensor lifetime, and a
+captured compute graph.
+
+* ``mixed_precision("bfloat16")`` - products inside run with operands rounded to that type (autocast for library
+  modules; this package's own layers follow their parameters' dtype). ``IDRAK_MATMUL`` sets the process default.
+* ``activation_memory(model, "checkpoint_blocks" | "held")`` - switches a decoder between keeping block activations
+  and recomputing them in backward.
+* ``TensorScope`` - frees what was allocated inside on exit (the caching allocator makes this a no-op except for an
+  optional cache trim).
+* ``ComputeGraph`` - capture a function over static inputs as a CUDA graph, replay it with new input values.
+
+Reference: MixedPrecision.Use (src/Idrak.Abstraction/Tensors/MixedPrecision.cs:54), ActivationMemory.CheckpointBlocks /
+Recompute / CompressToBFloat16 (ActivationMemory.cs), TensorScope.cs, ComputeGraph.Capture / Replay (ComputeGraph.cs).
+"""
+from __future__ import annotations
+
+import contextlib
+import os
+from typing import Callable, Optional, Sequence
+
+import torch
+
+_KINDS = {"float32": None, "f32": None, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.float16,
+          "f16": torch.float16, "float8": torch.bfloat16, "f8": torch.bfloat16}
+_current = [os.environ.get("IDRAK_MATMUL", "float32").lower()]
+
+
+def product_precision() -> str:
+    """The precision products run at in the current scope."""
+    return _current[-1]
+
+
+@contextlib.contextmanager
+def mixed_precision(kind: str):
+    k = kind.lower()
+    if k not in _KINDS:
+        raise ValueError(f"unknown precision '{kind}'; known: {', '.join(sorted(set(_KINDS)))}")
+    _current.append(k)
+    dtype = _KINDS[k]
+    try:
+        if dtype is None:
+            with torch.autocast("cuda", enabled=False), torch.autocast("cpu", enabled=False):
+                yield
+        else:
+            with torch.autocast("cuda", dtype=dtype), torch.autocast("cpu", dtype=torch.bfloat16):
+                yield
+    finally:
+        _current.pop()
+
+
+@contextlib.contextmanager
+def activation_memory(model: torch.nn.Module, policy: str):
+    """``held`` keeps every block's activations; ``checkpoint_blocks`` keeps block inputs only and re-runs each block
+    in backward. Applies to modules that expose ``checkpoint_blocks`` (the decoder and its parallel variants)."""
+    if policy not in ("held", "checkpoint_blocks"):
+        raise ValueError("policy must be 'held' or 'checkpoint_blocks'")
+    touched = [(m, m.checkpoint_blocks) for m in model.modules() if hasattr(m, "checkpoint_blocks")]
+    for m, _ in touched:
+        m.checkpoint_blocks = policy == "checkpoint_blocks"
+    try:
+        yield
+    finally:
+        for m, old in touched:
+            m.checkpoint_blocks = old
+
+
+class TensorScope:
+    """``with TensorScope(): ...`` - tensors made inside die with their last reference as usual; on exit the scope can
+    hand cached blocks back to the driver (``trim=True``), which the reference's arena disposal amounts to."""
+
+    def __init__(self, trim: bool = False):
+        self.trim = trim
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        if self.trim and torch.cuda.is_available():
+            torch.cuda.empty_cache()
+        return False
+
+
+class ComputeGraph:
+    """A function over fixed-shape device inputs, recorded once and replayed.
+
+        g = ComputeGraph.capture(fn, example_a, example_b)
+        out = g.replay(new_a, new_b)          # copies the new values into the recorded inputs, launches the graph
+    """
+
+    def __init__(self, graph, inputs: Sequence[torch.Tensor], outputs):
+        self.graph, self.inputs, self.outputs = graph, list(inputs), outputs
+        self.replays = 0
+
+    @classmethod
+    def capture(cls, fn: Callable, *inputs: torch.Tensor, warmup: int = 2) -> "ComputeGraph":
+        if not inputs or not all(t.is_cuda for t in inputs):
+            raise ValueError("capture takes CUDA tensors")
+        static = [t.clone() for t in inputs]
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(max(warmup, 1)):          # lazy initialisation (kernel attributes, workspaces) happens here
+                fn(*static)
+        torch.cuda.current_stream().wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            outputs = fn(*static)
+        return cls(graph, static, outputs)
+
+    def replay(self, *inputs: torch.Tensor):
+        if len(inputs) != len(self.inputs):
+            raise ValueError(f"the graph was recorded with {len(self.inputs)} inputs")
+        for dst, src in zip(self.inputs, inputs):
+            if dst.shape != src.shape or dst.dtype != src.dtype:
+                raise ValueError("replay inputs must match the recorded shapes and types")
+            dst.copy_(src, non_blocking=True)
+        self.graph.replay()
+        self.replays += 1
+        return self.outputs

@@ -23,23 +23,29 @@
 namespace idrak {
 
 
-template <int BN>
+// AROWS < 128 is the few-row (decode) layout: only AROWS rows of the A tile are copied and kept per stage, the
+// output goes straight from registers to global memory (no staging slabs), and the shared memory saved buys more
+// stages, i.e. more weight bytes in flight per SM. The MMA still spans 128 rows; rows AROWS..127 of the A operand
+// read whatever follows in the stage (the B tile - finite numbers) and land in accumulator rows that are never
+// stored.
+template <int BN, int AROWS = kBM>
 struct GemmSmem {
-  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kABytes = AROWS * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kStagingBytes = 4 * 2 * 4096;   // per epilogue warp: two 32-row x 128-byte slabs
+  static constexpr int kStages = AROWS == 32 ? 6 : (AROWS == 64 ? 5 : ((BN == 256) ? 4 : 6));
+  static constexpr int kStagingBytes = AROWS < kBM ? 0 : 4 * 2 * 4096;   // per epilogue warp: two 32-row x 128-byte slabs
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
-template <int BN, int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN, int AROWS = kBM>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
-  using L = GemmSmem<BN>;
+  using L = GemmSmem<BN, AROWS>;
   constexpr int kStages = L::kStages;
+  static_assert(AROWS == kBM || (!A_MN && !B_MN), "the few-row layout is for K-major operands");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + kStages * L::kStageBytes;        // 1024-byte aligned (stages are 16 KB multiples)
@@ -330,11 +336,12 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) 
 // ---------------------------------------------------------------------------
 // host launcher
 // ---------------------------------------------------------------------------
-template <int BN, int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN, int AROWS = kBM>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                        const CUtensorMap& tmAux, const GemmParams& p, int grid, cudaStream_t stream) {
-  using L = GemmSmem<BN>;
-  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  using L = GemmSmem<BN, AROWS>;
+  static_assert(L::kTotal <= 232448, "shared memory per CTA");
+  auto kern = gemm_kernel<BN, A_MN, B_MN, AROWS>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
@@ -430,8 +437,10 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
   p.st = status_device_ptr();
   p.col_scale = nullptr;
 
+  // few rows, K-major operands, wide N: the decode layout (fewer A rows per stage, more stages)
+  const int a_rows = (!a_mn && !b_mn && bn == 256 && M <= 64) ? (M <= 32 ? 32 : 64) : kBM;
   CUtensorMap tmA, tmB;
-  int e = make_operand_map(&tmA, A, M, K, lda, a_mn, kBM, fp16);
+  int e = make_operand_map(&tmA, A, M, K, lda, a_mn, a_rows, fp16);
   if (e) return -10 - (e > 0 ? 0 : 1);
   e = make_operand_map(&tmB, B, N, K, ldb, b_mn, bn, fp16);
   if (e) return -12;
@@ -441,7 +450,7 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
   memset(&tmC, 0, sizeof(tmC));
   memset(&tmAux, 0, sizeof(tmAux));
   p.tma_store = 0;
-  if (!c_fp32 && !beta && p.splits == 1 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+  if (a_rows == kBM && !c_fp32 && !beta && p.splits == 1 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
       (act != kActGelu || ((ld_aux % 8) == 0 && (reinterpret_cast<uintptr_t>(aux) & 15) == 0))) {
     uint64_t dims[2] = {uint64_t(N), uint64_t(M)};
     uint32_t box[2] = {64, 32};
@@ -460,7 +469,9 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
   const int grid = min(units, sm_count());
   int rc;
 #define IDRAK_GEMM_CASE(BN_, AM_, BM_) rc = launch_gemm<BN_, AM_, BM_>(tmA, tmB, tmC, tmAux, p, grid, stream)
-  if (bn == 256) {
+  if (a_rows == 32) rc = launch_gemm<256, 0, 0, 32>(tmA, tmB, tmC, tmAux, p, grid, stream);
+  else if (a_rows == 64) rc = launch_gemm<256, 0, 0, 64>(tmA, tmB, tmC, tmAux, p, grid, stream);
+  else if (bn == 256) {
     if (!a_mn && !b_mn) IDRAK_GEMM_CASE(256, 0, 0);
     else if (!a_mn && b_mn) IDRAK_GEMM_CASE(256, 0, 1);
     else if (a_mn && !b_mn) IDRAK_GEMM_CASE(256, 1, 0);

@@ -46,6 +46,25 @@ def test_gemm_splitk_matches_and_is_deterministic(splits):
     assert torch.equal(o1, o2)
 
 
+@pytest.mark.parametrize("M", [1, 7, 16, 32, 33, 48, 64])
+@pytest.mark.parametrize("N,K,splits", [(512, 256, 1), (6144, 4096, None), (4096, 1024, 4), (1000, 520, 1)])
+def test_gemm_few_rows(M, N, K, splits):
+    """Decode-sized products take the few-row layout (part of the A tile per stage, more stages): every epilogue the
+    serving path uses, with and without split-K, and N / K that are not tile multiples."""
+    a, b = _rand((M, K), 1.0, 11), _rand((N, K), 0.05, 12)
+    bias, res = _rand((N,), 1.0, 13), _rand((M, N), 1.0, 14)
+    _check(gemm(a, b, splits=splits), gemm_reference(a, b, out_dtype=torch.float32))
+    _check(gemm(a, b, bias=bias, residual=res, splits=splits),
+           gemm_reference(a, b, bias=bias, residual=res, out_dtype=torch.float32))
+    out, pre = gemm(a, b, bias=bias, act="gelu", splits=splits)
+    ref, ref_pre = gemm_reference(a, b, bias=bias, act="gelu", out_dtype=torch.float32)
+    _check(pre, ref_pre)
+    _check(out, ref)
+    o32 = gemm(a, b, splits=splits, out_dtype=torch.float32)
+    assert torch.equal(o32, gemm(a, b, splits=splits, out_dtype=torch.float32))
+    _check(o32, gemm_reference(a, b, out_dtype=torch.float32), 5e-3)
+
+
 def test_gemm_epilogues():
     M, N, K = 512, 1024, 256
     a, b = _rand((M, K), 1.0, 5), _rand((N, K), 0.1, 6)
