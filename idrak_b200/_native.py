@@ -42,7 +42,7 @@ _SIGNATURES = {
     "idrak_gemm_pick_splits": (c_int, [c_int, c_int, c_int, c_int]),
     "idrak_gemm_bf16": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                                 c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int,
-                                c_int, c_float, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p]),
+                                c_int, c_float, c_int, c_void_p, c_int, c_void_p]),
     "idrak_norm_fwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_float, c_int, c_void_p]),
     "idrak_norm_bwd_blocks": (c_int, [c_int]),
     "idrak_norm_bwd": (c_int, [c_void_p] * 11 + [c_int, c_int, c_int, c_int, c_int, c_void_p]),

@@ -31,8 +31,6 @@ struct GemmParams {
   int m_tiles, n_tiles;
   int tma_store;                  // 1: bf16 C (and aux) leave through shared-memory staging + TMA stores
   const __half* col_scale;        // [N] per-column factor applied to the accumulator first (int8 weights), or null
-  unsigned* tile_sync;            // [tiles][2] arrive / depart counters (all zero between launches): the CTAs of a
-                                  // tile's splits sum the partials themselves; null: a second kernel does
   Status* st;
 };
 

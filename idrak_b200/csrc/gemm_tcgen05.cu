@@ -23,29 +23,23 @@
 namespace idrak {
 
 
-// AROWS < 128 is the few-row (decode) layout: only AROWS rows of the A tile are copied and kept per stage, the
-// output goes straight from registers to global memory (no staging slabs), and the shared memory saved buys more
-// stages, i.e. more weight bytes in flight per SM. The MMA still spans 128 rows; rows AROWS..127 of the A operand
-// read whatever follows in the stage (the B tile - finite numbers) and land in accumulator rows that are never
-// stored.
-template <int BN, int AROWS = kBM>
+template <int BN>
 struct GemmSmem {
-  static constexpr int kABytes = AROWS * kBK * 2;
+  static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = AROWS == 32 ? 6 : (AROWS == 64 ? 5 : ((BN == 256) ? 4 : 6));
-  static constexpr int kStagingBytes = AROWS < kBM ? 0 : 4 * 2 * 4096;   // per epilogue warp: two 32-row x 128-byte slabs
+  static constexpr int kStages = (BN == 256) ? 4 : 6;
+  static constexpr int kStagingBytes = 4 * 2 * 4096;   // per epilogue warp: two 32-row x 128-byte slabs
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
-template <int BN, int A_MN, int B_MN, int AROWS = kBM>
+template <int BN, int A_MN, int B_MN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
-  using L = GemmSmem<BN, AROWS>;
+  using L = GemmSmem<BN>;
   constexpr int kStages = L::kStages;
-  static_assert(AROWS == kBM || (!A_MN && !B_MN), "the few-row layout is for K-major operands");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* staging = smem + kStages * L::kStageBytes;        // 1024-byte aligned (stages are 16 KB multiples)
@@ -56,7 +50,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint64_t* tmem_empty = tmem_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
   volatile uint32_t* abort_flag = tmem_slot + 1;
-  volatile uint32_t* reduce_go = tmem_slot + 2;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -294,76 +287,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       }
       tc_fence_before();
       mbar_arrive(&tmem_empty[buf]);
-      if (p.splits > 1 && p.tile_sync) {
-        // ---- split-K finished inside the kernel: every split CTA of this tile is resident (the host enables this only
-        // when there are no more units than CTAs), so once all of them have stored their partials each one sums
-        // 1/splits of the tile over the partials in split order - the same sums as the separate reduction kernel.
-        unsigned* arrive = p.tile_sync + 2 * (tm * p.n_tiles + tn);
-        unsigned* depart = arrive + 1;
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (row_in_tile == 0) {
-          atomicAdd(arrive, 1u);
-          uint64_t t0 = 0;
-          uint32_t polls = 0, good = 1u;
-          while (*reinterpret_cast<volatile unsigned*>(arrive) < unsigned(p.splits)) {
-            if ((++polls & 63u) == 0u) {
-              const uint64_t now = global_timer_ns();
-              if (t0 == 0) t0 = now;
-              if (*abort_flag || now - t0 > IDRAK_WAIT_BUDGET_NS) {
-                *abort_flag = 1u;
-                report(p.st, kTimeoutGeneric, (1u << 16) | 0x5bu, unsigned(split));
-                good = 0u;
-                break;
-              }
-            }
-          }
-          __threadfence();
-          *reduce_go = good;
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (*reduce_go) {
-          const int rows_valid = min(kBM, p.M - tm * kBM);
-          const int cols_valid = min(BN, p.N - n0);
-          const int groups = (cols_valid + 7) >> 3;
-          const int items = rows_valid * groups;
-          const int per = (items + p.splits - 1) / p.splits;
-          const int hi = min(items, (split + 1) * per);
-          for (int it = split * per + row_in_tile; it < hi; it += 128) {
-            const int r = it / groups, g = it - r * groups;
-            const int grow = tm * kBM + r, gcol = n0 + g * 8;
-            const int nvalid = min(8, p.N - gcol);
-            float v[8];
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = 0.f;
-            const float* w = p.workspace + size_t(grow) * p.N + gcol;
-            const size_t plane = size_t(p.M) * p.N;
-            if (nvalid == 8 && ((reinterpret_cast<uintptr_t>(w) & 15) == 0) && ((plane & 3) == 0)) {
-#pragma unroll 4
-              for (int sp = 0; sp < p.splits; ++sp) {
-                const float4 a = __ldcg(reinterpret_cast<const float4*>(w + sp * plane));
-                const float4 b = __ldcg(reinterpret_cast<const float4*>(w + sp * plane) + 1);
-                v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
-                v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
-              }
-            } else {
-              for (int sp = 0; sp < p.splits; ++sp)
-                for (int j = 0; j < nvalid; ++j) v[j] += __ldcg(w + sp * plane + j);
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] *= p.alpha;
-            epilogue8(p, grow, gcol, v, nvalid);
-          }
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (row_in_tile == 0 && *reduce_go) {
-          __threadfence();
-          if (atomicAdd(depart, 1u) == unsigned(p.splits - 1)) {   // the last one out clears the counters for the next launch
-            atomicExch(arrive, 0u);
-            atomicExch(depart, 0u);
-          }
-        }
-      }
     }
     if (p.tma_store && lane == 0) tma_store_wait<0>();   // staged slabs are read out before shared memory goes away
   }
@@ -407,12 +330,11 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) 
 // ---------------------------------------------------------------------------
 // host launcher
 // ---------------------------------------------------------------------------
-template <int BN, int A_MN, int B_MN, int AROWS = kBM>
+template <int BN, int A_MN, int B_MN>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                        const CUtensorMap& tmAux, const GemmParams& p, int grid, cudaStream_t stream) {
-  using L = GemmSmem<BN, AROWS>;
-  static_assert(L::kTotal <= 232448, "shared memory per CTA");
-  auto kern = gemm_kernel<BN, A_MN, B_MN, AROWS>;
+  using L = GemmSmem<BN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
@@ -476,7 +398,7 @@ IDRAK_API int idrak_gemm_pick_splits(int M, int N, int K, int bn) {
 IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, void* C, int ldc,
                               int c_fp32, int M, int N, int K, const void* bias, const void* residual, int ldr,
                               int act, void* aux, int ld_aux, int beta, float alpha, int splits, float* workspace,
-                              int fp16, unsigned* tile_sync, int tile_sync_words, void* stream_) {
+                              int fp16, void* stream_) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((lda & 7) || (ldb & 7)) return -2;
   if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
@@ -507,16 +429,9 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
   p.n_tiles = (N + bn - 1) / bn;
   p.st = status_device_ptr();
   p.col_scale = nullptr;
-  // split-K summed inside the kernel needs every unit resident at once and a counter pair per tile
-  p.tile_sync = nullptr;
-  if (p.splits > 1 && tile_sync && p.m_tiles * p.n_tiles * p.splits <= sm_count() &&
-      2 * p.m_tiles * p.n_tiles <= tile_sync_words)
-    p.tile_sync = tile_sync;
 
-  // few rows, K-major operands, wide N: the decode layout (fewer A rows per stage, more stages)
-  const int a_rows = (!a_mn && !b_mn && bn == 256 && M <= 64) ? (M <= 32 ? 32 : 64) : kBM;
   CUtensorMap tmA, tmB;
-  int e = make_operand_map(&tmA, A, M, K, lda, a_mn, a_rows, fp16);
+  int e = make_operand_map(&tmA, A, M, K, lda, a_mn, kBM, fp16);
   if (e) return -10 - (e > 0 ? 0 : 1);
   e = make_operand_map(&tmB, B, N, K, ldb, b_mn, bn, fp16);
   if (e) return -12;
@@ -526,7 +441,7 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
   memset(&tmC, 0, sizeof(tmC));
   memset(&tmAux, 0, sizeof(tmAux));
   p.tma_store = 0;
-  if (a_rows == kBM && !c_fp32 && !beta && p.splits == 1 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
+  if (!c_fp32 && !beta && p.splits == 1 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
       (act != kActGelu || ((ld_aux % 8) == 0 && (reinterpret_cast<uintptr_t>(aux) & 15) == 0))) {
     uint64_t dims[2] = {uint64_t(N), uint64_t(M)};
     uint32_t box[2] = {64, 32};
@@ -545,9 +460,7 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
   const int grid = min(units, sm_count());
   int rc;
 #define IDRAK_GEMM_CASE(BN_, AM_, BM_) rc = launch_gemm<BN_, AM_, BM_>(tmA, tmB, tmC, tmAux, p, grid, stream)
-  if (a_rows == 32) rc = launch_gemm<256, 0, 0, 32>(tmA, tmB, tmC, tmAux, p, grid, stream);
-  else if (a_rows == 64) rc = launch_gemm<256, 0, 0, 64>(tmA, tmB, tmC, tmAux, p, grid, stream);
-  else if (bn == 256) {
+  if (bn == 256) {
     if (!a_mn && !b_mn) IDRAK_GEMM_CASE(256, 0, 0);
     else if (!a_mn && b_mn) IDRAK_GEMM_CASE(256, 0, 1);
     else if (a_mn && !b_mn) IDRAK_GEMM_CASE(256, 1, 0);
@@ -560,7 +473,7 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
   }
 #undef IDRAK_GEMM_CASE
   if (rc) return rc;
-  if (p.splits > 1 && !p.tile_sync) {
+  if (p.splits > 1) {
     const long long groups = (long long)M * ((N + 7) / 8);
     long long want = (groups + 255) / 256, cap = (long long)sm_count() * 8;
     int blocks = int(want < cap ? want : cap);

@@ -44,17 +44,6 @@ def scratch(name: str, numel: int, dtype: torch.dtype, device: torch.device) -> 
     return buf
 
 
-def zeroed_words(name: str, numel: int, device: torch.device) -> torch.Tensor:
-    """A persistent int32 buffer per (name, device, stream) that starts as zeros and that kernels hand back as
-    zeros (counters that the last user clears). Made once; never resized."""
-    key = (name, "zeroed", device.index, torch.cuda.current_stream().cuda_stream)
-    buf = _SCRATCH.get(key)
-    if buf is None:
-        buf = torch.zeros(numel, dtype=torch.int32, device=device)
-        _SCRATCH[key] = buf
-    return buf
-
-
 def release_scratch() -> None:
     _SCRATCH.clear()
 

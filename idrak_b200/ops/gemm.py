@@ -16,9 +16,7 @@ from __future__ import annotations
 import torch
 
 from .. import _native
-from ._util import ptr, scratch, stream_ptr, zeroed_words
-
-_TILE_SYNC_WORDS = 2 * 1024       # an arrive / depart counter pair per output tile of a split-K product
+from ._util import ptr, scratch, stream_ptr
 
 ACT_NONE, ACT_GELU, ACT_GELU_GRAD = 0, 1, 2
 _ACT_IDS = {None: ACT_NONE, "none": ACT_NONE, "gelu": ACT_GELU, "gelu_grad": ACT_GELU_GRAD}
@@ -106,10 +104,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     bn = 128 if N <= 128 else 256
     if splits is None:
         splits = lib.idrak_gemm_pick_splits(M, N, K, bn)
-    ws = sync = None
+    ws = None
     if splits > 1:
         ws = scratch("gemm_splitk", splits * M * N, torch.float32, a.device)
-        sync = zeroed_words("gemm_tile_sync", _TILE_SYNC_WORDS, a.device)
     if bias is not None:
         assert bias.dtype == torch.bfloat16 and bias.numel() == N
     if residual is not None:
@@ -119,8 +116,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         out.data_ptr(), out.stride(0), c_fp32, M, N, K,
         ptr(bias), ptr(residual), residual.stride(0) if residual is not None else 0,
         act_id, ptr(aux_t), aux_t.stride(0) if aux_t is not None else 0,
-        int(beta), float(alpha), int(splits), ptr(ws), 1 if a.dtype == torch.float16 else 0,
-        ptr(sync), _TILE_SYNC_WORDS if sync is not None else 0, stream_ptr())
+        int(beta), float(alpha), int(splits), ptr(ws), 1 if a.dtype == torch.float16 else 0, stream_ptr())
     _native.check(rc, "idrak_gemm_bf16")
     return (out, aux_t) if act_id == ACT_GELU else out
 
