@@ -135,3 +135,6 @@ def augment(question: str, hits: Sequence[Hit], instruction: str = DEFAULT_INSTR
     context = "\n\n".join(parts) if parts else "(no passages found)"
     return [{"role": "system", "content": instruction},
             {"role": "user", "content": f"Passages:\n{context}\n\nQuestion: {question}"}]
+
+
+from .bm25 import Bm25Index, reciprocal_rank_fusion, rerank  # noqa: E402
