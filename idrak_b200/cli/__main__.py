@@ -456,6 +456,20 @@ def cmd_config(a) -> int:
     return 1 if problems else 0
 
 
+def cmd_tuning(a) -> int:
+    """Show (or forget) the measured decisions kept for this GPU."""
+    from ..runtime.tuning import tuner
+    t = tuner()
+    if a.forget is not None:
+        print(f"forgot {t.forget(a.forget)} decisions")
+        return 0
+    print(f"file   {t.path}\ndevice {t.key}\ntuning {'on' if t.enabled else 'off (set IDRAK_AUTOTUNE=1 to measure)'}")
+    for name, e in sorted(t.entries().items()):
+        ratios = ", ".join(f"{k}: {v:.3f}" for k, v in e.get("ratios", {}).items())
+        print(f"  {name}  ->  {e['choice']}  (default {e['default']} {e.get('default_ms', 0):.4f} ms; ratios {ratios})")
+    return 0
+
+
 # ------------------------------------------------------------------ parser
 def _sampling(p):
     p.add_argument("--max-tokens", type=int, default=256)
@@ -487,6 +501,8 @@ def build_parser() -> argparse.ArgumentParser:
         return p
 
     add("devices", cmd_devices, "list CUDA devices")
+    p = add("tuning", cmd_tuning, "show the measured per-device decisions (split-K factors, ...)")
+    p.add_argument("--forget", nargs="?", const="", metavar="PREFIX", help="drop decisions whose name starts with PREFIX (all without one)")
     add("check", cmd_check, "run one tiny training step and one decode").add_argument("--device")
     add("doctor", cmd_doctor, "report what is installed and what is missing")
     add("kernels", cmd_kernels, "list the native library's entry points")

@@ -76,6 +76,10 @@ TABLE: List[Setting] = [
     Setting("IDRAK_TELEMETRY_FILE", "text", "", "write telemetry events to this JSON-lines file"),
     Setting("IDRAK_HOME", "text", os.path.join(os.path.expanduser("~"), ".idrak"), "models, runs and aliases live here"),
     Setting("IDRAK_STOP_FILE", "text", "", "training stops cleanly at the next step when this file appears"),
+    Setting("IDRAK_AUTOTUNE", "bool", False, "time the candidates the first time a shape class needs a choice and keep the winner"),
+    Setting("IDRAK_TUNING_CACHE", "text", "", "file of measured decisions (default: tuning.json under IDRAK_HOME)"),
+    Setting("IDRAK_MATMUL", "choice", "float32", "precision of products in library modules outside a mixed_precision scope",
+            ("float32", "bfloat16", "float16", "float8")),
 ]
 _BY_NAME: Dict[str, Setting] = {s.name: s for s in TABLE}
 
@@ -117,6 +121,11 @@ class Settings:
 
 
 settings = Settings()
+
+
+def get(name: str) -> Any:
+    """The current value of a setting (environment, or an override made with ``settings.set``)."""
+    return settings.get(name)
 
 
 def describe(current: Optional[Settings] = None) -> str:

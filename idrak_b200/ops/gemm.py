@@ -60,6 +60,24 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, residual=None, ac
     return (res, aux_out) if _ACT_IDS[act] == ACT_GELU else res
 
 
+def _tuned_splits(a, b, a_mn, b_mn, M, N, K, default, out) -> int:
+    """The measured split-K factor for few-row products of this shape class (decode-sized work is where the built-in
+    rule is least sure): read from the tuning cache, measured once with a cold L2 when tuning is on."""
+    from ..runtime.tuning import size_class, tuner
+    t = tuner()
+    shape = (size_class(M), N, K, int(a_mn), int(b_mn))
+    known = t.lookup("gemm.splits", shape)
+    if known is not None:
+        return int(known)
+    if not t.enabled or torch.cuda.is_current_stream_capturing():
+        return default
+    kblocks = (K + 63) // 64
+    options = sorted({default, 1, 2, 4, 8} & set(range(1, kblocks + 1)) | {default})
+    scratch_out = torch.empty_like(out)
+    cands = {str(s): (lambda s=s: gemm(a, b, a_mn=a_mn, b_mn=b_mn, out=scratch_out, splits=s)) for s in options}
+    return int(t.choose("gemm.splits", shape, cands, default=str(default), cold_l2=True))
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = False,
          bias: torch.Tensor | None = None, residual: torch.Tensor | None = None, act: str | None = None,
          aux: torch.Tensor | None = None, out: torch.Tensor | None = None, beta: bool = False,
@@ -104,6 +122,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     bn = 128 if N <= 128 else 256
     if splits is None:
         splits = lib.idrak_gemm_pick_splits(M, N, K, bn)
+        if M <= 256 and not (beta or act_id):
+            splits = _tuned_splits(a, b, a_mn, b_mn, M, N, K, splits, out)
     ws = None
     if splits > 1:
         ws = scratch("gemm_splitk", splits * M * N, torch.float32, a.device)

@@ -96,3 +96,25 @@ def test_linear_autograd_matches_torch():
     _check(x.grad, xr.grad)
     _check(w.grad, wr.grad)
     _check(b.grad, br.grad)
+
+
+def test_autotune_measures_once_and_keeps_results_equal(tmp_path):
+    from idrak_b200 import config
+    from idrak_b200.runtime import reset_tuner, tuner
+    config.settings.set("IDRAK_AUTOTUNE", True)
+    config.settings.set("IDRAK_TUNING_CACHE", str(tmp_path / "tuning.json"))
+    reset_tuner()
+    try:
+        a, b = _rand((48, 2048), 1.0, 21), _rand((1536, 2048), 0.05, 22)
+        first = gemm(a, b)
+        t = tuner()
+        assert t.measured == 1 and any(k.startswith("gemm.splits:64x1536x2048") for k in t.entries())
+        second = gemm(a, b)
+        assert t.measured == 1
+        ref = gemm_reference(a, b, out_dtype=torch.float32)
+        _check(first, ref)
+        _check(second, ref)
+    finally:
+        config.settings._overrides.pop("IDRAK_AUTOTUNE", None)
+        config.settings._overrides.pop("IDRAK_TUNING_CACHE", None)
+        reset_tuner()
