@@ -91,3 +91,39 @@ def test_tune_and_package_commands(model_dir, tmp_path, capsys):
     listing = capsys.readouterr().out
     assert "Tokenizer" in listing and "Weights" in listing
     assert main(["config"]) in (0, 1)
+
+
+def test_data_retrieval_onnx_and_page_commands(tmp_path, capsys):
+    import json as _json
+    from idrak_b200.cli.__main__ import main as run
+    rows = tmp_path / "rows.jsonl"
+    rows.write_text("\n".join(_json.dumps({"text": t}) for t in
+                              ["the cat sat on the mat", "the cat sat on the mat", "dogs run in the park every day", "qubits power quantum computers"]))
+    assert run(["data", "dedupe", str(rows), "-o", str(tmp_path / "u.jsonl")]) == 0
+    assert _json.loads(capsys.readouterr().out)["kept"] == 3
+    assert run(["data", "split", str(tmp_path / "u.jsonl"), "-o", str(tmp_path / "part.jsonl"), "--fraction", "0.67"]) == 0
+    assert _json.loads(capsys.readouterr().out) == {"first": 2, "rest": 1}
+    assert run(["index", str(tmp_path / "u.jsonl"), "-o", str(tmp_path / "idx")]) == 0
+    capsys.readouterr()
+    assert run(["search", str(tmp_path / "idx"), "quantum qubits", "-k", "1"]) == 0
+    assert "qubits" in _json.loads(capsys.readouterr().out.splitlines()[0])["text"]
+    from idrak_b200.nn import Network
+    (tmp_path / "net.json").write_text(_json.dumps(Network.input(4).linear(3).relu().linear(2).to_json()))
+    assert run(["onnx", "export", str(tmp_path / "net.json"), "-o", str(tmp_path / "net.onnx")]) == 0
+    capsys.readouterr()
+    assert run(["onnx", "inspect", str(tmp_path / "net.onnx")]) == 0
+    info = _json.loads(capsys.readouterr().out)
+    assert info["operators"]["Gemm"] == 2 and info["unsupported"] == [] and info["parameters"] >= 4 * 3 + 3 + 3 * 2 + 2
+    import numpy as np
+    np.save(tmp_path / "x.npy", np.ones((5, 4), np.float32))
+    assert run(["onnx", "run", str(tmp_path / "net.onnx"), "--input", str(tmp_path / "x.npy")]) == 0
+    assert _json.loads(capsys.readouterr().out)["shape"] == [5, 2]
+    pytest.importorskip("PIL")
+    assert run(["page", "a short page of text for the test", "-o", str(tmp_path / "p.png"), "--width", "300", "--height", "120",
+                "--size", "16", "--margin", "10", "--effects", "gaussian_noise,rotate_small"]) == 0
+    out = _json.loads(capsys.readouterr().out)
+    assert out["words"] == 8 and (tmp_path / "p.words.jsonl").exists()
+    from idrak_b200.imaging import decode
+    assert decode((tmp_path / "p.png").read_bytes()).shape == (120, 300, 3)
+    assert run(["image", "resize", str(tmp_path / "p.png"), "-o", str(tmp_path / "small.png"), "--width", "60", "--height", "24"]) == 0
+    assert _json.loads(capsys.readouterr().out)["shape"] == [24, 60, 3]
