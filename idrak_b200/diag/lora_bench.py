@@ -47,8 +47,10 @@ def main(argv=None) -> int:
     spec = DecoderSpec.llama(layers=a.layers, dim=a.dim, heads=a.heads, kv_heads=a.kv_heads, ff_dim=a.ff, vocab=a.vocab,
                              max_positions=a.seq)
     torch.set_default_dtype(torch.bfloat16)
+    torch.manual_seed(1234)                                 # the same base on every rank
+    torch.cuda.manual_seed(1234)
     with torch.device(dev):
-        model = build_decoder(spec, seed=1234)              # the same base on every rank
+        model = build_decoder(spec)
     torch.set_default_dtype(torch.float32)
     model = model.to(dev, torch.bfloat16)
     if a.base != "bf16":

@@ -175,6 +175,9 @@ def quantize_weight(w_in_out: torch.Tensor, kind: str):
 
 
 # --------------------------------------------------------------------------- the op
+DENSE_ROWS = 512        # from this many activation rows on, the weight is unpacked to bf16 first and multiplied densely
+
+
 def qgemm(x2: torch.Tensor, w, transposed: bool = False, bias=None, residual=None, act: Optional[str] = None,
           out: Optional[torch.Tensor] = None, splits: Optional[int] = None):
     """``x2 @ W`` (or ``x2 @ W^T``) with the fused epilogue of the dense GEMM."""
@@ -195,6 +198,11 @@ def qgemm(x2: torch.Tensor, w, transposed: bool = False, bias=None, residual=Non
             y = y + residual.float()
         y = y.to(x2.dtype)
         return (y, aux) if aux is not None else y
+    if M >= DENSE_ROWS and x2.dtype == torch.bfloat16 and w.cols % 8 == 0 and x2.stride(0) % 8 == 0:
+        # many rows: unpacking the weight once (a bandwidth-bound pass over it) and running the dense tensor-core GEMM
+        # beats unpacking inside the GEMM's producer warps, which is sized for decode-like row counts
+        from ..ops.gemm import gemm
+        return gemm(x2, dequantize_bf16(w), b_mn=not transposed, bias=bias, residual=residual, act=act, out=out)
     _bind()
     lib = _native.lib()
     fn = lib.idrak_qgemm

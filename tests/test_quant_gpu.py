@@ -42,3 +42,16 @@ def test_qlinear_autograd_and_epilogue():
     yr.backward(dy.float())
     assert (y.float() - yr).abs().max().item() < 2e-2 * yr.abs().max().item()
     assert (x.grad.float() - xr.grad).abs().max().item() < 2e-2 * xr.grad.abs().max().item()
+
+
+def test_many_rows_take_the_dense_path_and_agree_with_the_fused_kernel(monkeypatch):
+    from idrak_b200.quant import weights
+    qw = Int4Weight.quantize(_rand((1024, 768), 0.05, 1).float())
+    x, bias = _rand((2048, 1024), 1.0, 2), _rand((768,), 0.1, 3)
+    dense = qgemm(x, qw, bias=bias)
+    monkeypatch.setattr(weights, "DENSE_ROWS", 1 << 30)
+    fused = qgemm(x, qw, bias=bias)
+    ref = x.float() @ qw.dequantize() + bias.float()
+    for y in (dense, fused):
+        assert (y.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
+    assert (dense.float() - fused.float()).abs().max().item() < 2e-2 * ref.abs().max().item()
