@@ -3,6 +3,7 @@ filters, seeded scan / paper effects, page layout and file codecs - on CPU tenso
 plain device buffers."""
 from .codecs import ImageFormatError, decode, decode_bmp, decode_png, decode_pnm, encode, encode_bmp, encode_png, encode_pnm
 from .effects import EFFECTS, PixelPass, apply, pixel_pass, random_pipeline
+from .jpeg import decode_jpeg
 from .font import FontError, TrueTypeFont, render_text
 from .layout import Page, WordBox, compose_page, wrap
 from .raster import Path, coverage_reference, ellipse, rasterize, rect, supersample_reference

@@ -5,8 +5,8 @@ arrays ``[H, W]`` or ``[H, W, C]`` of uint8.
     pixels = decode(open("page.png", "rb").read())
     open("out.png", "wb").write(encode_png(pixels))
 
-Reference: the reference's codecs (src/Idrak.Imaging/Codecs: PNG, JPEG, BMP, Netpbm readers and writers). JPEG is not
-read here.
+Reference: the reference's codecs (src/Idrak.Imaging/Codecs: PNG, JPEG, BMP, Netpbm readers and writers). Baseline JPEG
+is read by ``imaging/jpeg.py`` (``decode`` dispatches to it); JPEG is not written.
 """
 from __future__ import annotations
 
@@ -266,7 +266,10 @@ def decode(data: bytes) -> np.ndarray:
         return decode_bmp(data)
     if data[:1] == b"P" and data[1:2] in b"2356":
         return decode_pnm(data)
-    raise ImageFormatError("unknown image format (PNG, BMP and Netpbm are read)")
+    if data[:2] == b"\xFF\xD8":
+        from .jpeg import decode_jpeg
+        return decode_jpeg(data)
+    raise ImageFormatError("unknown image format (PNG, JPEG, BMP and Netpbm are read)")
 
 
 def encode(pixels: np.ndarray, format: str) -> bytes:

@@ -206,3 +206,29 @@ def test_effects_are_seeded_and_change_the_page():
     assert abs(n.mean().item() - 128) < 0.5 and abs(n.std().item() - 0.05 * 255) < 0.6
     sp = im.pixel_pass(flat, im.PixelPass(salt=0.02, pepper=0.03, seed=9))
     assert abs((sp == 255).float().mean().item() - 0.02) < 0.005 and abs((sp == 0).float().mean().item() - 0.03) < 0.005
+
+
+def test_baseline_jpeg_decoder_against_libjpeg():
+    yy, xx = np.mgrid[0:67, 0:93]
+    img = np.stack([(np.sin(xx / 9) + 1) * 120, (np.cos(yy / 7) + 1) * 110, (xx + yy) % 256], -1).astype(np.uint8)
+
+    def both(array, **save):
+        buf = io.BytesIO()
+        Image.fromarray(array).save(buf, "JPEG", **save)
+        mine = im.decode(buf.getvalue()).astype(int)
+        ref = Image.open(io.BytesIO(buf.getvalue()))
+        return mine, np.asarray(ref if array.ndim == 2 else ref.convert("RGB")).astype(int)
+
+    mine, ref = both(img[..., 0], quality=75)
+    assert np.array_equal(mine, ref)                                     # grey: the inverse DCT alone
+    mine, ref = both(img, quality=90, subsampling=0)
+    assert mine.shape == (67, 93, 3) and np.abs(mine - ref).max() <= 2    # colour conversion rounding
+    mine, ref = both(img, quality=85, subsampling=0, restart_marker_blocks=3)
+    assert np.abs(mine - ref).max() <= 2
+    for sub in (1, 2):                                                    # chroma replicated here, interpolated there
+        mine, ref = both(img, quality=90, subsampling=sub)
+        assert np.abs(mine - ref).mean() < 4.0
+    buf = io.BytesIO()
+    Image.fromarray(img).save(buf, "JPEG", progressive=True)
+    with pytest.raises(im.ImageFormatError, match="progressive"):
+        im.decode(buf.getvalue())
