@@ -161,4 +161,8 @@ __device__ __forceinline__ void unit_to_tile(const GemmParams& p, int unit, int&
   tm = first_m + (r % gsz);
   tn = r / gsz;
 }
+// The CTA-pair kernel (gemm2_tcgen05.cu): whether a product should use it, and its launcher.
+bool gemm_pair_wanted(int M, int N, int K, int splits);
+int gemm_pair_launch(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, const CUtensorMap& tmC,
+                     const CUtensorMap& tmAux, GemmParams p, int fp16, cudaStream_t stream);
 }  // namespace idrak

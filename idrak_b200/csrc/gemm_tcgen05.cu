@@ -456,6 +456,10 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
     p.tma_store = ok ? 1 : 0;
   }
 
+  // large one-pass products go to CTA pairs (256 x 256 tiles, cta_group::2)
+  if (bn == 256 && gemm_pair_wanted(M, N, K, p.splits))
+    return gemm_pair_launch(A, lda, a_mn, B, ldb, b_mn, tmC, tmAux, p, fp16, stream);
+
   const int units = p.m_tiles * p.n_tiles * p.splits;
   const int grid = min(units, sm_count());
   int rc;

@@ -225,6 +225,41 @@ class Bandit(Environment):
 
 
 # ---------------------------------------------------------------------------------------------------------------------
+# rollouts across ranks
+# ---------------------------------------------------------------------------------------------------------------------
+def exchange_rollouts(episodes: Sequence[torch.Tensor], group=None) -> List[torch.Tensor]:
+    """All ranks' episodes on every rank. Each episode is a 1-D tensor (token ids, or flattened transitions) of any
+    length; ranks may hold different numbers of episodes. Two collectives: the counts and longest length, then the
+    episodes padded to that length. The result is ordered by rank, then by the rank's own order."""
+    import torch.distributed as dist
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return [e.clone() for e in episodes]
+    world = dist.get_world_size(group)
+    dtype = episodes[0].dtype if episodes else torch.int64
+    device = episodes[0].device if episodes else torch.device("cpu")
+    mine = torch.tensor([len(episodes), max((len(e) for e in episodes), default=0),
+                         int(bool(episodes) and dtype.is_floating_point)], dtype=torch.int64, device=device)
+    counts = [torch.zeros_like(mine) for _ in range(world)]
+    dist.all_gather(counts, mine, group=group)
+    most, longest = max(int(c[0]) for c in counts), max(int(c[1]) for c in counts)
+    floating = any(int(c[2]) for c in counts)             # a rank without episodes does not know the type: agree on it
+    if not episodes:
+        dtype = torch.float32 if floating else torch.int64
+    block = torch.zeros(most, longest + 1, dtype=torch.float64 if floating else torch.int64, device=device)
+    for i, e in enumerate(episodes):
+        block[i, 0] = len(e)
+        block[i, 1: 1 + len(e)] = e.to(block.dtype)
+    blocks = [torch.zeros_like(block) for _ in range(world)]
+    dist.all_gather(blocks, block, group=group)
+    out = []
+    for r in range(world):
+        for i in range(int(counts[r][0])):
+            n = int(blocks[r][i, 0])
+            out.append(blocks[r][i, 1: 1 + n].to(dtype))
+    return out
+
+
+# ---------------------------------------------------------------------------------------------------------------------
 # on-policy trainer (PPO with a separate value network; discrete actions)
 # ---------------------------------------------------------------------------------------------------------------------
 @dataclass

@@ -118,3 +118,34 @@ def test_autotune_measures_once_and_keeps_results_equal(tmp_path):
         config.settings._overrides.pop("IDRAK_AUTOTUNE", None)
         config.settings._overrides.pop("IDRAK_TUNING_CACHE", None)
         reset_tuner()
+
+
+def _pair_case(M, N, K, a_mn, b_mn):
+    a = _rand((K, M) if a_mn else (M, K), 1.0, 31)
+    b = _rand((K, N) if b_mn else (N, K), 0.05, 32)
+    ref = gemm_reference(a, b, a_mn=a_mn, b_mn=b_mn, out_dtype=torch.float32)
+    out = gemm(a, b, a_mn=a_mn, b_mn=b_mn, splits=1)
+    _check(out, ref)
+    assert torch.equal(out, gemm(a, b, a_mn=a_mn, b_mn=b_mn, splits=1))
+    if not a_mn and not b_mn:
+        bias, res = _rand((N,), 1.0, 33), _rand((M, N), 1.0, 34)
+        _check(gemm(a, b, bias=bias, residual=res, splits=1), gemm_reference(a, b, bias=bias, residual=res, out_dtype=torch.float32))
+        o, pre = gemm(a, b, bias=bias, act="gelu", splits=1)
+        r, r_pre = gemm_reference(a, b, bias=bias, act="gelu", out_dtype=torch.float32)
+        _check(pre, r_pre)
+        _check(o, r)
+        _check(gemm(a, b, act="gelu_grad", aux=pre, splits=1), gemm_reference(a, b, act="gelu_grad", aux=pre, out_dtype=torch.float32))
+        acc = torch.ones((M, N), dtype=torch.float32, device="cuda")
+        gemm(a, b, out=acc, beta=True, alpha=0.5, splits=1)
+        _check(acc, gemm_reference(a, b, alpha=0.5, out_dtype=torch.float32) + 1.0)
+
+
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
+@pytest.mark.parametrize("M,N,K", [(2048, 2304, 768), (4096, 768, 3072), (1504, 1000, 520), (16384, 768, 768)])
+def test_gemm_large_products(M, N, K, a_mn, b_mn):
+    """Products large enough for the CTA-pair kernel (256 x 256 tiles on two SMs, when it is switched on with
+    IDRAK_GEMM_PAIR=1; the single-CTA kernel otherwise): all operand layouts, sizes that are not tile multiples, every
+    epilogue."""
+    _pair_case(M, N, K, a_mn, b_mn)
+    from idrak_b200 import _native
+    _native.check_status("large products")

@@ -83,3 +83,23 @@ def test_ppo_learns_cartpole():
     history = trainer.train(12)
     first, best = history[0]["mean_return"], max(h["mean_return"] for h in history)
     assert best > 2.5 * first and best > 80, (first, best)
+
+
+def test_rollouts_are_exchanged_across_ranks(tmp_path):
+    import os
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    sys.path.insert(0, here)
+    from rollout_worker import episodes_of
+    out = tmp_path / "r.pt"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=3", "--master-addr", "127.0.0.1",
+           "--master-port", "29771", os.path.join(here, "rollout_worker.py"), str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-3000:]
+    got = torch.load(out)
+    want = [e for rank in range(3) for e in episodes_of(rank)]
+    assert len(got["all"]) == len(want) == 6 and all(torch.equal(a, b) for a, b in zip(got["all"], want))
+    assert [e.tolist() for e in got["empty"]] == [[1.5, 2.5], [1.5, 2.5]]
+    solo = rl.exchange_rollouts([torch.tensor([1, 2, 3])])
+    assert solo[0].tolist() == [1, 2, 3]
