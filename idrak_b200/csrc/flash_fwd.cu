@@ -3,9 +3,11 @@
 //
 // One CTA owns 128 query rows of one (batch, head) and walks the key/value sequence in blocks of 128:
 //   warp 0      TMA producer: Q once, then K and V blocks through two-stage rings (128B swizzle)
-//   warp 1      MMA issuer:   S = Q K^T into TMEM (tcgen05.mma, K-major x K-major), then O += P V
-//                             (P from shared memory, V as an MN-major operand, accumulator kept in TMEM)
-//   warps 2..5  softmax:      one thread per query row reads its row of S with tcgen05.ld (no shuffles),
+//   warp 1      MMA issuer:   S = Q K^T into one of TWO score buffers in TMEM (tcgen05.mma, K-major x K-major), issued
+//                             one block ahead so the scores of block j+1 are being computed while block j is in the
+//                             softmax; then O += P V (P from shared memory, V as an MN-major operand, accumulator in TMEM)
+//   warps 2..5  softmax:      one thread per query row pulls its whole row of S into registers with four tcgen05.ld in
+//                             flight and one wait, hands the score buffer back at once, then takes the
 //                             online max / sum in the log2 domain, writes P as bf16 into the swizzled
 //                             operand layout, rescales the TMEM accumulator only when the running max
 //                             moved by more than 2^8 (warp-uniform decision), and finally normalises
@@ -32,7 +34,7 @@ struct FwdSmem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, (D == 64) ? 2 : 1)
+__global__ void __launch_bounds__(192, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
   using L = FwdSmem<D>;
@@ -44,10 +46,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint64_t* v_full = bars + 3;    // [2]
   uint64_t* k_empty = bars + 5;   // [2]
   uint64_t* v_empty = bars + 7;   // [2]
-  uint64_t* s_full = bars + 9;
-  uint64_t* p_ready = bars + 10;
-  uint64_t* o_done = bars + 11;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* s_full = bars + 9;    // [2]
+  uint64_t* s_empty = bars + 11;  // [2]
+  uint64_t* p_ready = bars + 13;
+  uint64_t* o_done = bars + 14;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -69,13 +72,16 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(&k_empty[s], 1);
       mbar_init(&v_empty[s], 1);
     }
-    mbar_init(s_full, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(&s_full[b], 1);
+      mbar_init(&s_empty[b], 128);
+    }
     mbar_init(p_ready, 128);
     mbar_init(o_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
   }
-  constexpr uint32_t kTmemCols = 256;   // S: columns [0,128), O: [128, 128+D)
+  constexpr uint32_t kTmemCols = 512;   // S: two buffers at columns [0,128) and [128,256), O: [256, 256+D)
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
@@ -84,7 +90,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128;
+  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256;
 
   if (warp == 0) {
     if (lane == 0 && nkv > 0) {
@@ -128,20 +134,30 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       bool ok = mbar_wait(q_full, 0, abort_flag, p.st, kTimeoutSmemFull, (2u << 16) | 8);
       const uint32_t sq = smem_u32(smem + L::kQ);
       const uint32_t sp = smem_u32(smem + L::kPOff);
-      for (int j = 0; j < nkv && ok; ++j) {
+      // scores of block j go to buffer j & 1; they are issued one block ahead of the P V product
+      auto issue_scores = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (2u << 16) | st)) { ok = false; break; }
+        if (!mbar_wait(&k_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (2u << 16) | st)) return false;
+        // the buffer's previous use (block j - 2) has been read out by the softmax warps
+        if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutTmemEmpty, (2u << 16) | (12 + st))) return false;
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + L::kK + st * L::kTile);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t o = (kk >> 2) * 16384 + (kk & 3) * 32;
-          tc_mma_f16_ss(tmem_S, make_smem_desc_sw128(sq + o, 16, 1024), make_smem_desc_sw128(sk + o, 16, 1024),
+          tc_mma_f16_ss(tmem_S + st * 128, make_smem_desc_sw128(sq + o, 16, 1024), make_smem_desc_sw128(sk + o, 16, 1024),
                         idesc_s, kk > 0 ? 1u : 0u);
         }
-        tc_commit(s_full);
+        tc_commit(&s_full[st]);
         tc_commit(&k_empty[st]);
+        return true;
+      };
+      if (ok) ok = issue_scores(0);
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (j + 1 < nkv && !issue_scores(j + 1)) { ok = false; break; }
         if (!mbar_wait(p_ready, j & 1, abort_flag, p.st, kTimeoutGeneric, (2u << 16) | 9)) { ok = false; break; }
         if (!mbar_wait(&v_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (2u << 16) | (2 + st))) { ok = false; break; }
         tc_fence_after();
@@ -167,7 +183,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float l = 0.f;
     bool ok = nkv > 0;
     for (int j = 0; j < nkv && ok; ++j) {
-      if (!mbar_wait(s_full, j & 1, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 10)) { ok = false; break; }
+      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 10)) { ok = false; break; }
       tc_fence_after();
       const int k0 = j * 128;
       // keys visible to this row in this block: columns [0, lim)
@@ -175,22 +191,33 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (p.causal) lim = min(lim, row + off - k0 + 1);
       lim = max(0, min(128, lim));
       const bool need_mask = lim < 128;
-      // pass 1: row max
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        tmem_ld_32x32b_x32(tmem_S + lane_addr + c * 32, s);
-        tmem_ld_wait();
-        if (!need_mask) {
+      // the whole row of scores into registers: four loads in flight, one wait; then the buffer goes back to the MMA warp
+      uint32_t s[4][32];
+      const uint32_t s_addr = tmem_S + uint32_t(j & 1) * 128 + lane_addr;
+      tmem_ld_32x32b_x32(s_addr + 0, s[0]);
+      tmem_ld_32x32b_x32(s_addr + 32, s[1]);
+      tmem_ld_32x32b_x32(s_addr + 64, s[2]);
+      tmem_ld_32x32b_x32(s_addr + 96, s[3]);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(&s_empty[j & 1]);
+      // four independent chains (one per 32-column chunk) keep the dependent latency short
+      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      if (!need_mask) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(s[i]));
-        } else {
+        for (int i = 0; i < 32; ++i) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i)
-            if (c * 32 + i < lim) mx = fmaxf(mx, __uint_as_float(s[i]));
+          for (int c = 0; c < 4; ++c) m4[c] = fmaxf(m4[c], __uint_as_float(s[c][i]));
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            if (c * 32 + i < lim) m4[c] = fmaxf(m4[c], __uint_as_float(s[c][i]));
         }
       }
+      float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
       mx *= p.scale_log2;
       const float m_new = fmaxf(m_used, mx);
       // the accumulator is rescaled only when some row of this warp moved its max by more than 2^8
@@ -219,20 +246,19 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         tmem_st_wait();
       }
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
-      // pass 2: probabilities -> bf16 operand tile (K-major, 128B swizzle: chunk ^= row % 8)
-#pragma unroll 1
+      // probabilities -> bf16 operand tile (K-major, 128B swizzle: chunk ^= row % 8), from the registers
+#pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint32_t s[32];
-        tmem_ld_32x32b_x32(tmem_S + lane_addr + c * 32, s);
-        tmem_ld_wait();
         float pv[32];
+        float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = exp2f(__uint_as_float(s[i]) * p.scale_log2 - m_sub);
+          float e = exp2f(__uint_as_float(s[c][i]) * p.scale_log2 - m_sub);
           if (need_mask && (c * 32 + i >= lim)) e = 0.f;
           pv[i] = e;
-          l += e;
+          l4[i & 3] += e;
         }
+        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
         uint8_t* atom = sP + (c >> 1) * 16384 + r * 128;
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
