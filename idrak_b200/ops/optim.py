@@ -181,24 +181,29 @@ class FusedAdamW(FusedOptimizerBase):
 
     def _step_cpu(self, bc1, bc2, extra_sumsq=None):
         b1, b2 = self.betas
-        grads = [p.grad.float() * self.grad_scale if p.grad is not None else None for p in self.params]
-        scale = 1.0
-        sq = sum(float(g.pow(2).sum()) for g in grads if g is not None)
+        live = [i for i, p in enumerate(self.params) if p.grad is not None]
+        grads = [self.params[i].grad.float() for i in live]
+        if self.grad_scale != 1.0:
+            grads = [g * self.grad_scale for g in grads]
+        sq = float(torch.stack(torch._foreach_norm(grads)).pow(2).sum()) if grads else 0.0
         if extra_sumsq is not None:
             sq += float(extra_sumsq.sum())
         norm = math.sqrt(sq)
         self._last_norm = norm
         if self.max_grad_norm > 0 and norm > self.max_grad_norm:
-            scale = self.max_grad_norm / (norm + 1e-6)
-        for i, p in enumerate(self.params):
-            if grads[i] is None:
-                continue
-            g = grads[i] * scale
-            self.m[i].mul_(b1).add_(g, alpha=1 - b1)
-            self.v[i].mul_(b2).addcmul_(g, g, value=1 - b2)
-            w = self.master[i]
-            w.mul_(1 - self.lr * self._wd[i])
-            w.addcdiv_(self.m[i], self.v[i].sqrt() / math.sqrt(bc2) + self.eps, value=-self.lr / bc1)
+            grads = torch._foreach_mul(grads, self.max_grad_norm / (norm + 1e-6))
+        ms, vs, ws = [self.m[i] for i in live], [self.v[i] for i in live], [self.master[i] for i in live]
+        torch._foreach_mul_(ms, b1)
+        torch._foreach_add_(ms, grads, alpha=1 - b1)
+        torch._foreach_mul_(vs, b2)
+        torch._foreach_addcmul_(vs, grads, grads, value=1 - b2)
+        torch._foreach_mul_(ws, [1 - self.lr * self._wd[i] for i in live])
+        denom = torch._foreach_sqrt(vs)
+        torch._foreach_div_(denom, math.sqrt(bc2))
+        torch._foreach_add_(denom, self.eps)
+        torch._foreach_addcdiv_(ws, ms, denom, value=-self.lr / bc1)
+        for i in live:
+            p, w = self.params[i], self.master[i]
             if w.data_ptr() != p.data_ptr():
                 p.copy_(w.to(p.dtype))
             if self.zero_grad_in_step:
