@@ -8,3 +8,4 @@ from .tool_calls import (ChatDelta, MarkedToolCallParser, ToolCall, create_parse
 __all__ = ["ChatTemplate", "render_chat", "ByteTokenizer", "HfTokenizer", "SentencePieceTokenizer", "StreamingDecoder",
            "Tokenizer", "load_tokenizer", "tokenizer_from_gguf", "train_tokenizer", "ChatDelta", "MarkedToolCallParser",
            "ToolCall", "create_parser", "detect_format", "register_tool_call_format"]
+from .conversation import Conversation, Tool  # noqa: E402,F401
