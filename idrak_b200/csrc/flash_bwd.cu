@@ -110,7 +110,8 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* sdp_full = bars + 5;
   uint64_t* ds_ready = bars + 6;
   uint64_t* dq_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* sdp_taken = bars + 8;   // the element-wise warps hold S and dP of the block in registers: TMEM may be rewritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -132,6 +133,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(sdp_full, 1);
     mbar_init(ds_ready, 128);
     mbar_init(dq_done, 1);
+    mbar_init(sdp_taken, 128);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -177,10 +179,13 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       constexpr uint32_t idesc_dq = make_idesc_f16(128, D, 0, 1, 1);
       bool ok = mbar_wait(qdo_full, 0, abort_flag, p.st, kTimeoutSmemFull, (3u << 16) | 8);
       const uint32_t sq = smem_u32(smem + L::kQ), sdo = smem_u32(smem + L::kDO), sds = smem_u32(smem + L::kDS);
-      for (int j = 0; j < nkv && ok; ++j) {
+      // S and dP of block j; with two K/V stages they are issued one block ahead, as soon as the element-wise warps
+      // have taken the previous block's S and dP into registers
+      auto issue_scores = [&](int j) -> bool {
         const int st = j % NS;
         const uint32_t ph = (j / NS) & 1;
-        if (!mbar_wait(&kv_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (3u << 16) | st)) break;
+        if (!mbar_wait(&kv_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (3u << 16) | st)) return false;
+        if (j > 0 && !mbar_wait(sdp_taken, (j - 1) & 1, abort_flag, p.st, kTimeoutTmemEmpty, (3u << 16) | 13)) return false;
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + L::kK + st * L::kTile), sv = smem_u32(smem + L::kV + st * L::kTile);
 #pragma unroll
@@ -190,8 +195,20 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int kk = 0; kk < D / 16; ++kk)
           tc_mma_f16_ss(tmem_dP, kmajor_desc(sdo, kk), kmajor_desc(sv, kk), idesc_s, kk > 0 ? 1u : 0u);
         tc_commit(sdp_full);
+        return true;
+      };
+      constexpr bool kAhead = NS >= 2;      // one stage: the next K / V cannot land before this block's dQ product is done
+      if (ok && kAhead) ok = issue_scores(0);
+      for (int j = 0; j < nkv && ok; ++j) {
+        const int st = j % NS;
+        if (kAhead) {
+          if (j + 1 < nkv && !issue_scores(j + 1)) break;
+        } else if (!issue_scores(j)) {
+          break;
+        }
         if (!mbar_wait(ds_ready, j & 1, abort_flag, p.st, kTimeoutGeneric, (3u << 16) | 9)) break;
         tc_fence_after();
+        const uint32_t sk = smem_u32(smem + L::kK + st * L::kTile);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           tc_mma_f16_ss(tmem_dQ, kmajor_desc(sds, kk), mnmajor_desc(sk, kk), idesc_dq, (j > 0 || kk > 0) ? 1u : 0u);
@@ -216,29 +233,42 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int j = 0; j < nkv && ok; ++j) {
       if (!mbar_wait(sdp_full, j & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 10)) { ok = false; break; }
       tc_fence_after();
-      if (j > 0) {
-        // the previous dQ product still reads the dS tile until dq_done completes
-        if (!mbar_wait(dq_done, (j - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 11)) { ok = false; break; }
-      }
       const int k0 = j * 128;
       int lim = p.Skv - k0;
       if (p.causal) lim = min(lim, row + off - k0 + 1);
       lim = max(0, min(128, lim));
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32], dp[32];
-        tmem_ld_32x32b_x32(tmem_S + lane_addr + c * 32, s);
-        tmem_ld_32x32b_x32(tmem_dP + lane_addr + c * 32, dp);
-        tmem_ld_wait();
-        float ds[32];
+      // two halves of 64 columns: four loads in flight and one wait each; after the second half is in registers the
+      // MMA warp may overwrite S and dP with the next block's
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float pr = exp2f(__uint_as_float(s[i]) * p.scale_log2 - lse2);
-          float v = pr * (__uint_as_float(dp[i]) - dlt) * p.scale;
-          ds[i] = (c * 32 + i < lim) ? v : 0.f;
+      for (int h = 0; h < 2; ++h) {
+        uint32_t s[2][32], dp[2][32];
+        tmem_ld_32x32b_x32(tmem_S + lane_addr + h * 64, s[0]);
+        tmem_ld_32x32b_x32(tmem_S + lane_addr + h * 64 + 32, s[1]);
+        tmem_ld_32x32b_x32(tmem_dP + lane_addr + h * 64, dp[0]);
+        tmem_ld_32x32b_x32(tmem_dP + lane_addr + h * 64 + 32, dp[1]);
+        tmem_ld_wait();
+        if (h == 1) {
+          tc_fence_before();
+          mbar_arrive(sdp_taken);
         }
-        store_operand_chunk(sDS, r, c, ds);
+        if (h == 0 && j > 0) {
+          // the previous dQ product still reads the dS tile until dq_done completes
+          if (!mbar_wait(dq_done, (j - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 11)) { ok = false; }
+        }
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = h * 2 + cc;
+          float ds[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float pr = exp2f(__uint_as_float(s[cc][i]) * p.scale_log2 - lse2);
+            float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * p.scale;
+            ds[i] = (c * 32 + i < lim) ? v : 0.f;
+          }
+          if (ok) store_operand_chunk(sDS, r, c, ds);
+        }
       }
+      if (!ok) break;
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(ds_ready);
@@ -315,7 +345,8 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* sdp_full = bars + 5;
   uint64_t* pds_ready = bars + 6;
   uint64_t* acc_done = bars + 7;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 8);
+  uint64_t* sdp_taken = bars + 8;   // S^T and dP^T of the block are in registers: TMEM may be rewritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   float* s_lse2 = reinterpret_cast<float*>(smem + L::kStat);
   float* s_delta = s_lse2 + 128;
@@ -340,6 +371,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(sdp_full, 1);
     mbar_init(pds_ready, 128);
     mbar_init(acc_done, 1);
+    mbar_init(sdp_taken, 128);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -389,10 +421,13 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       bool ok = mbar_wait(kv_full, 0, abort_flag, p.st, kTimeoutSmemFull, (4u << 16) | 8);
       const uint32_t sk = smem_u32(smem + L::kK), sv = smem_u32(smem + L::kV);
       const uint32_t spt = smem_u32(smem + L::kPT), sdst = smem_u32(smem + L::kDST);
-      for (int it = 0; it < iters && ok; ++it) {
+      // S^T and dP^T of iteration `it`; with two Q / dO stages they are issued one iteration ahead, as soon as the
+      // element-wise warps hold the previous iteration's scores in registers
+      auto issue_scores = [&](int it) -> bool {
         const int st = it % NS;
         const uint32_t ph = (it / NS) & 1;
-        if (!mbar_wait(&qdo_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (4u << 16) | st)) break;
+        if (!mbar_wait(&qdo_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (4u << 16) | st)) return false;
+        if (it > 0 && !mbar_wait(sdp_taken, (it - 1) & 1, abort_flag, p.st, kTimeoutTmemEmpty, (4u << 16) | 13)) return false;
         tc_fence_after();
         const uint32_t sq = smem_u32(smem + L::kQ + st * L::kTile), sdo = smem_u32(smem + L::kDO + st * L::kTile);
 #pragma unroll
@@ -402,8 +437,20 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int kk = 0; kk < D / 16; ++kk)
           tc_mma_f16_ss(tmem_dPT, kmajor_desc(sv, kk), kmajor_desc(sdo, kk), idesc_s, kk > 0 ? 1u : 0u);
         tc_commit(sdp_full);
+        return true;
+      };
+      constexpr bool kAhead = NS >= 2;
+      if (ok && kAhead) ok = issue_scores(0);
+      for (int it = 0; it < iters && ok; ++it) {
+        const int st = it % NS;
+        if (kAhead) {
+          if (it + 1 < iters && !issue_scores(it + 1)) break;
+        } else if (!issue_scores(it)) {
+          break;
+        }
         if (!mbar_wait(pds_ready, it & 1, abort_flag, p.st, kTimeoutGeneric, (4u << 16) | 9)) break;
         tc_fence_after();
+        const uint32_t sq = smem_u32(smem + L::kQ + st * L::kTile), sdo = smem_u32(smem + L::kDO + st * L::kTile);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
           tc_mma_f16_ss(tmem_dV, kmajor_desc(spt, kk), mnmajor_desc(sdo, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
@@ -443,29 +490,45 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       softmax_bar_sync();
       if (!mbar_wait(sdp_full, it & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 10)) { ok = false; break; }
       tc_fence_after();
-      if (it > 0) {
-        if (!mbar_wait(acc_done, (it - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 11)) { ok = false; break; }
-      }
       // query q (column) sees this key iff key <= q + off  <=>  q >= key - off
       const int first_q = p.causal ? (key - off - qrow0) : 0;    // columns below this are masked
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t s[32], dp[32];
-        tmem_ld_32x32b_x32(tmem_ST + lane_addr + c * 32, s);
-        tmem_ld_32x32b_x32(tmem_dPT + lane_addr + c * 32, dp);
-        tmem_ld_wait();
-        float pt[32], dst[32];
+      // two halves of 64 columns: four loads in flight and one wait each; the MMA warp may rewrite S^T and dP^T once
+      // the second half is in registers
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int col = c * 32 + i;
-          float pr = exp2f(__uint_as_float(s[i]) * p.scale_log2 - s_lse2[col]);
-          if (col < first_q) pr = 0.f;
-          pt[i] = pr;
-          dst[i] = pr * (__uint_as_float(dp[i]) - s_delta[col]) * p.scale;
+      for (int h = 0; h < 2; ++h) {
+        uint32_t s[2][32], dp[2][32];
+        tmem_ld_32x32b_x32(tmem_ST + lane_addr + h * 64, s[0]);
+        tmem_ld_32x32b_x32(tmem_ST + lane_addr + h * 64 + 32, s[1]);
+        tmem_ld_32x32b_x32(tmem_dPT + lane_addr + h * 64, dp[0]);
+        tmem_ld_32x32b_x32(tmem_dPT + lane_addr + h * 64 + 32, dp[1]);
+        tmem_ld_wait();
+        if (h == 1) {
+          tc_fence_before();
+          mbar_arrive(sdp_taken);
         }
-        store_operand_chunk(sPT, r, c, pt);
-        store_operand_chunk(sDST, r, c, dst);
+        if (h == 0 && it > 0) {
+          // the previous accumulation still reads the P^T and dS^T tiles until acc_done completes
+          if (!mbar_wait(acc_done, (it - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 11)) ok = false;
+        }
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          const int c = h * 2 + cc;
+          float pt[32], dst[32];
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            float pr = exp2f(__uint_as_float(s[cc][i]) * p.scale_log2 - s_lse2[col]);
+            if (col < first_q) pr = 0.f;
+            pt[i] = pr;
+            dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * p.scale;
+          }
+          if (ok) {
+            store_operand_chunk(sPT, r, c, pt);
+            store_operand_chunk(sDST, r, c, dst);
+          }
+        }
       }
+      if (!ok) break;
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(pds_ready);
