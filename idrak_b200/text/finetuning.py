@@ -55,6 +55,7 @@ class FineTuningOptions:
     loss_chunk_rows: int = 512
     non_finite_steps: int = 8            # give up after this many skipped steps in a row
     checkpoint_blocks: bool = False      # recompute block activations in backward
+    activation_ladder: bool = True       # estimate activation memory before the first step, step down on out-of-memory
     loss: str = "sft"                    # sft | dpo
     dpo_beta: float = 0.1
     save_every: int = 0                  # steps; 0 = only at the end
@@ -71,6 +72,7 @@ class FineTuningResult:
     eval_losses: List[Tuple[int, float]] = field(default_factory=list)
     skipped_steps: int = 0
     adapter_folder: Optional[str] = None
+    activation_policy: str = "held"
 
 
 # ------------------------------------------------------------------ examples -> token rows
@@ -246,6 +248,34 @@ class FineTuner:
         self.template = ChatTemplate.for_tokenizer(tokenizer)
         self.step = 0
         self.result = FineTuningResult()
+        self.activation_policy = "checkpoint_blocks" if o.checkpoint_blocks else "held"
+
+    # ------------------------------------------------------------------ activation memory
+    def plan_activation_memory(self, tokens: int) -> str:
+        """Pick the first rung of the ladder that fits the free memory for steps of ``tokens`` tokens."""
+        from . import activation_memory as am
+        if not self.o.activation_ladder:
+            return self.activation_policy
+        est = am.choose_policy(self.model.spec, tokens, am.free_device_bytes(self.device), adapter_rank=self.o.rank,
+                               start=self.activation_policy)
+        self.activation_policy = est.policy
+        am.apply_policy(self.model, est.policy)
+        self.result.activation_policy = est.policy
+        return est.policy
+
+    def _step_down(self) -> bool:
+        """After an out-of-memory step: move to the next rung (False when there is none)."""
+        from . import activation_memory as am
+        nxt = am.next_rung(self.activation_policy) if self.o.activation_ladder else None
+        if nxt is None:
+            return False
+        self.activation_policy = nxt
+        am.apply_policy(self.model, nxt)
+        self.result.activation_policy = nxt
+        self.optimizer.zero_grad()
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+        return True
 
     # ------------------------------------------------------------------ data
     def batches(self, examples: Iterable[Dict[str, Any]]) -> List[PackedBatch]:
@@ -313,6 +343,7 @@ class FineTuner:
         rng = random.Random(o.seed)
         order: List[int] = []
         self.model.train()
+        self.plan_activation_memory(max(b.ids.numel() for b in batches))
         bad_streak = 0
         cursor = self.step * o.accumulation
         while self.step < total:
@@ -325,15 +356,22 @@ class FineTuner:
             tokens = sum(max(b.trained_tokens, 1) for b in group)
             self.optimizer.zero_grad()
             loss_value, finite = 0.0, True
-            for b in group:
-                w = max(b.trained_tokens, 1) / tokens              # token-weighted mean over the accumulated batches
-                loss = self.batch_loss(b)
-                value = float(loss.detach())                       # the one host read per batch
-                if not math.isfinite(value):
-                    finite = False
-                    break
-                (loss * w).backward()
-                loss_value += value * w
+            try:
+                for b in group:
+                    w = max(b.trained_tokens, 1) / tokens          # token-weighted mean over the accumulated batches
+                    loss = self.batch_loss(b)
+                    value = float(loss.detach())                   # the one host read per batch
+                    if not math.isfinite(value):
+                        finite = False
+                        break
+                    (loss * w).backward()
+                    loss_value += value * w
+            except torch.OutOfMemoryError:
+                loss = None
+                if not self._step_down():
+                    raise
+                cursor -= o.accumulation                           # the same batches again on the next rung
+                continue
             if not finite:
                 res.skipped_steps += 1
                 bad_streak += 1

@@ -99,3 +99,45 @@ def test_dpo_prefers_chosen_and_non_finite_steps_stop():
     with pytest.raises(FloatingPointError, match="3 steps in a row"):
         ft.fit([{"text": "abcdef"}] * 4)
     assert ft.result.skipped_steps == 3 and ft.result.steps == 0
+
+
+def test_activation_estimate_and_ladder():
+    from idrak_b200.models import DecoderSpec
+    from idrak_b200.text import activation_memory as am
+    spec = DecoderSpec.llama(layers=32, dim=4096, heads=32, kv_heads=8, ff_dim=14336, vocab=128256, max_positions=4096)
+    held = am.estimate(spec, 8192, "held", adapter_rank=16)
+    ckpt = am.estimate(spec, 8192, "checkpoint_blocks", adapter_rank=16)
+    assert 25 < held.gib < 60                          # the measured LoRA step holds ~ 36 GiB above the weights at 8192 tokens
+    assert ckpt.total_bytes < held.total_bytes / 6
+    assert am.choose_policy(spec, 8192, 200 << 30).policy == "held"
+    assert am.choose_policy(spec, 8192, 20 << 30).policy == "checkpoint_blocks"
+    assert am.choose_policy(spec, 8192, 1 << 20).policy == "checkpoint_blocks"      # the last rung even when nothing fits
+    assert am.next_rung("held") == "checkpoint_blocks" and am.next_rung("checkpoint_blocks") is None
+
+
+def test_fine_tuner_steps_down_the_ladder_on_out_of_memory(monkeypatch):
+    torch.manual_seed(0)
+    tok = _tokenizer() if "_tokenizer" in globals() else None
+    if tok is None:
+        from idrak_b200.text import ByteTokenizer
+        tok = ByteTokenizer()
+    from idrak_b200.models import DecoderSpec, build_decoder
+    from idrak_b200.text.finetuning import FineTuner, FineTuningOptions
+    model = build_decoder(DecoderSpec.llama(layers=2, dim=32, heads=2, kv_heads=2, ff_dim=64, vocab=tok.vocab_size, max_positions=128), seed=0)
+    ft = FineTuner(model, tok, FineTuningOptions(rank=4, alpha=8.0, max_steps=3, batch_tokens=64, max_length=64))
+    calls = {"n": 0}
+    real = ft.batch_loss
+
+    def flaky(b):
+        calls["n"] += 1
+        if calls["n"] == 1:
+            raise torch.OutOfMemoryError("simulated")
+        return real(b)
+    monkeypatch.setattr(ft, "batch_loss", flaky)
+    res = ft.fit([{"prompt": "hello ", "completion": "world " * 3} for _ in range(6)])
+    assert res.steps == 3 and res.activation_policy == "checkpoint_blocks" and model.checkpoint_blocks is True
+    monkeypatch.setattr(ft, "batch_loss", lambda b: (_ for _ in ()).throw(torch.OutOfMemoryError("again")))
+    ft.o.max_steps = 5
+    import pytest as _pytest
+    with _pytest.raises(torch.OutOfMemoryError):
+        ft.fit([{"prompt": "hello ", "completion": "world"}])
