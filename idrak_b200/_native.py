@@ -133,8 +133,29 @@ class NativeError(RuntimeError):
     pass
 
 
+_DEBUG_SYNC = None
+
+
+def _debug_sync() -> bool:
+    """``IDRAK_CUDA_DEBUG=1``: synchronise after every native launch and name the call whose kernel failed or gave up a
+    bounded wait - what an asynchronous error would otherwise pin on some later call."""
+    global _DEBUG_SYNC
+    if _DEBUG_SYNC is None:
+        import os
+        _DEBUG_SYNC = os.environ.get("IDRAK_CUDA_DEBUG", "0") not in ("", "0", "false", "off")
+    return _DEBUG_SYNC
+
+
 def check(rc: int, what: str) -> None:
     if rc == 0:
+        if _debug_sync():
+            import torch
+            if torch.cuda.is_available() and not torch.cuda.is_current_stream_capturing():
+                try:
+                    torch.cuda.synchronize()
+                except RuntimeError as e:
+                    raise NativeError(f"{what}: {e}") from None
+                check_status(what)
         return
     if rc > 0:
         try:

@@ -167,7 +167,40 @@ def cmd_audio(a) -> int:
     return 0
 
 
+def cmd_profile(a) -> int:
+    """Profile a small training step of the tiny decoder (or of a model folder) cold and warm, with the kernel table."""
+    import torch
+    from ..diag.profiler import Profiler
+    from ..models import DecoderSpec, build_decoder
+    from ..ops import FusedAdamW
+    dev = torch.device(a.device or ("cuda" if torch.cuda.is_available() else "cpu"))
+    spec = DecoderSpec.gpt2(layers=a.layers, dim=a.dim, heads=max(a.dim // 64, 1), vocab=a.vocab, max_positions=a.seq)
+    model = build_decoder(spec, seed=0).to(dev, torch.bfloat16 if dev.type == "cuda" else torch.float32)
+    opt = FusedAdamW(model.parameters(), lr=1e-4)
+    ids = torch.randint(0, a.vocab, (a.batch, a.seq + 1), device=dev, dtype=torch.int32)
+
+    def step():
+        loss = model.loss(ids[:, :-1].contiguous(), ids[:, 1:].contiguous())
+        loss.backward()
+        opt.step()
+        opt.zero_grad()
+        return loss
+
+    rep = Profiler.run(f"train step {a.layers}L d{a.dim} {a.batch}x{a.seq}", step, warm=a.warm)
+    print({"table": rep.table, "markdown": rep.to_markdown, "csv": rep.to_csv, "json": rep.to_json}[a.format]())
+    return 0
+
+
 def register(add) -> None:
+    p = add("profile", cmd_profile, "profile a training step: cold / warm time, memory, device time per kernel")
+    p.add_argument("--layers", type=int, default=4)
+    p.add_argument("--dim", type=int, default=256)
+    p.add_argument("--vocab", type=int, default=1024)
+    p.add_argument("--batch", type=int, default=4)
+    p.add_argument("--seq", type=int, default=128)
+    p.add_argument("--warm", type=int, default=5)
+    p.add_argument("--device")
+    p.add_argument("--format", choices=["table", "markdown", "csv", "json"], default="table")
     p = add("data", cmd_data, "convert / dedupe / split / mix / count record files (JSONL, JSON, CSV, TSV, text, Parquet)")
     p.add_argument("action", choices=["convert", "dedupe", "split", "mix", "count"])
     p.add_argument("inputs", nargs="+")
