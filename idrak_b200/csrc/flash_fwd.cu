@@ -34,7 +34,7 @@ struct FwdSmem {
 };
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(192, (D == 64) ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
   using L = FwdSmem<D>;
@@ -81,7 +81,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     *abort_flag = 0;
     fence_barrier_init();
   }
-  constexpr uint32_t kTmemCols = 512;   // S: two buffers at columns [0,128) and [128,256), O: [256, 256+D)
+  // D = 64: one score buffer [0,128) and O at [128,192) in 256 columns, so two CTAs share an SM (one CTA's prologue and
+  // epilogue hide behind the other's main loop); the buffer is handed back as soon as the row sits in registers, which
+  // lets the next block's scores be computed during this block's softmax all the same.
+  // D = 128: two score buffers at [0,128) and [128,256), O at [256,384), one CTA per SM.
+  constexpr int kSBufs = (D == 64) ? 1 : 2;
+  constexpr uint32_t kTmemCols = (D == 64) ? 256 : 512;
   if (warp == 1) {
     tmem_alloc(tmem_slot, kTmemCols);
     tmem_relinquish();
@@ -90,7 +95,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 256;
+  const uint32_t tmem_S = tmem_base, tmem_O = tmem_base + 128 * kSBufs;
 
   if (warp == 0) {
     if (lane == 0 && nkv > 0) {
@@ -140,16 +145,18 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const uint32_t ph = (j >> 1) & 1;
         if (!mbar_wait(&k_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (2u << 16) | st)) return false;
         // the buffer's previous use (block j - 2) has been read out by the softmax warps
-        if (!mbar_wait(&s_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutTmemEmpty, (2u << 16) | (12 + st))) return false;
+        const int sb = (kSBufs == 2) ? st : 0;
+        const uint32_t sph = (kSBufs == 2) ? (ph ^ 1) : uint32_t((j + 1) & 1);     // the buffer's previous use: block j - kSBufs
+        if (!mbar_wait(&s_empty[sb], sph, abort_flag, p.st, kTimeoutTmemEmpty, (2u << 16) | (12 + sb))) return false;
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + L::kK + st * L::kTile);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t o = (kk >> 2) * 16384 + (kk & 3) * 32;
-          tc_mma_f16_ss(tmem_S + st * 128, make_smem_desc_sw128(sq + o, 16, 1024), make_smem_desc_sw128(sk + o, 16, 1024),
+          tc_mma_f16_ss(tmem_S + sb * 128, make_smem_desc_sw128(sq + o, 16, 1024), make_smem_desc_sw128(sk + o, 16, 1024),
                         idesc_s, kk > 0 ? 1u : 0u);
         }
-        tc_commit(&s_full[st]);
+        tc_commit(&s_full[sb]);
         tc_commit(&k_empty[st]);
         return true;
       };
@@ -183,7 +190,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float l = 0.f;
     bool ok = nkv > 0;
     for (int j = 0; j < nkv && ok; ++j) {
-      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 10)) { ok = false; break; }
+      const int sb = (kSBufs == 2) ? (j & 1) : 0;
+      const uint32_t sph = (kSBufs == 2) ? uint32_t((j >> 1) & 1) : uint32_t(j & 1);
+      if (!mbar_wait(&s_full[sb], sph, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 10)) { ok = false; break; }
       tc_fence_after();
       const int k0 = j * 128;
       // keys visible to this row in this block: columns [0, lim)
@@ -193,14 +202,14 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const bool need_mask = lim < 128;
       // the whole row of scores into registers: four loads in flight, one wait; then the buffer goes back to the MMA warp
       uint32_t s[4][32];
-      const uint32_t s_addr = tmem_S + uint32_t(j & 1) * 128 + lane_addr;
+      const uint32_t s_addr = tmem_S + uint32_t(sb) * 128 + lane_addr;
       tmem_ld_32x32b_x32(s_addr + 0, s[0]);
       tmem_ld_32x32b_x32(s_addr + 32, s[1]);
       tmem_ld_32x32b_x32(s_addr + 64, s[2]);
       tmem_ld_32x32b_x32(s_addr + 96, s[3]);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(&s_empty[j & 1]);
+      mbar_arrive(&s_empty[sb]);
       // four independent chains (one per 32-column chunk) keep the dependent latency short
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (!need_mask) {
