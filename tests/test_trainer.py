@@ -131,3 +131,16 @@ def test_checkpoint_keep_and_optimizer_state_names(tmp_path):
         assert "step" in names and "m.0" in names and "v.0" in names
         assert r.metadata["format"] == "idrak-optimizer"
         assert float(r.read("step")) == 8.0
+
+
+def test_training_run_is_the_trainer_as_one_object():
+    import dataclasses
+    from idrak_b200.training import TrainingRun
+    run = TrainingRun(model=_mlp(), loss=torch.nn.functional.binary_cross_entropy,
+                      optimizer=lambda p: FusedAdamW(p, lr=5e-2, weight_decay=0.0), train=_xor_data(), epochs=30,
+                      validation=_xor_data(), metrics=[Metrics.accuracy], max_gradient_norm=1.0)
+    history = run.fit()
+    assert run.trainer is not None and history.epochs[-1].metrics["accuracy"] == 1.0
+    variant = dataclasses.replace(run, model=_mlp(1), epochs=2, max_gradient_norm=0.5)
+    assert variant.epochs == 2 and run.epochs == 30
+    assert len(variant.fit().epochs) == 2 and variant.trainer.max_gradient_norm == 0.5
