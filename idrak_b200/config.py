@@ -77,7 +77,8 @@ TABLE: List[Setting] = [
     Setting("IDRAK_HOME", "text", os.path.join(os.path.expanduser("~"), ".idrak"), "models, runs and aliases live here"),
     Setting("IDRAK_STOP_FILE", "text", "", "training stops cleanly at the next step when this file appears"),
     Setting("IDRAK_CUDA_DEBUG", "bool", False, "synchronise after every native launch and name the call that failed"),
-    Setting("IDRAK_GEMM_PAIR", "bool", False, "large one-pass GEMMs on CTA pairs (256 x 256 tiles, cta_group::2)"),
+    Setting("IDRAK_GEMM_PAIR", "choice", "1", "large one-pass GEMMs on CTA pairs (256 x 256 tiles, cta_group::2): 0 never, "
+            "1 where it measured faster, 2 wherever it can run", ("0", "1", "2")),
     Setting("IDRAK_DP_DEBUG", "bool", False, "data parallel: record where a duplicate gradient-ready signal came from"),
     Setting("IDRAK_AUTOTUNE", "bool", False, "time the candidates the first time a shape class needs a choice and keep the winner"),
     Setting("IDRAK_TUNING_CACHE", "text", "", "file of measured decisions (default: tuning.json under IDRAK_HOME)"),

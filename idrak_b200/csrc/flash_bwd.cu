@@ -261,7 +261,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
           float ds[32];
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            float pr = exp2f(__uint_as_float(s[cc][i]) * p.scale_log2 - lse2);
+            float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - lse2);
             float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * p.scale;
             ds[i] = (c * 32 + i < lim) ? v : 0.f;
           }
@@ -517,7 +517,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = c * 32 + i;
-            float pr = exp2f(__uint_as_float(s[cc][i]) * p.scale_log2 - s_lse2[col]);
+            float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - s_lse2[col]);
             if (col < first_q) pr = 0.f;
             pt[i] = pr;
             dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * p.scale;

@@ -262,7 +262,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = exp2f(__uint_as_float(s[c][i]) * p.scale_log2 - m_sub);
+          float e = fast_exp2(__uint_as_float(s[c][i]) * p.scale_log2 - m_sub);
           if (need_mask && (c * 32 + i >= lim)) e = 0.f;
           pv[i] = e;
           l4[i & 3] += e;

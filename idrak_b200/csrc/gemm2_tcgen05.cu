@@ -380,11 +380,14 @@ bool gemm_pair_wanted(int M, int N, int K, int splits) {
   static int enabled = -1;
   if (enabled < 0) {
     const char* e = getenv("IDRAK_GEMM_PAIR");
-    enabled = (e != nullptr && e[0] == '1') ? 1 : 0;       // opt-in
+    enabled = (e == nullptr) ? 1 : (e[0] == '0' ? 0 : (e[0] == '2' ? 2 : 1));     // 0 off, 1 where it measured faster, 2 wherever it can run
   }
   if (!enabled || splits > 1 || M < 1024 || N < 256 || K < 128) return false;
   const long long tiles = (long long)((M + 255) / 256) * ((N + 255) / 256);
-  return tiles >= sm_count() / 4;
+  if (tiles < sm_count() / 4) return false;
+  // measured against the single-CTA kernel (cold L2, CUDA-graph replays): pairs win from K = 3072 (+13 %) and on very wide
+  // outputs (+2..4 %), and lose ~5 % on K = 768 with modest N, where the tile's fixed costs dominate
+  return enabled == 2 || K >= 2048 || N >= 16384;
 }
 
 // Same contract as the single-CTA launcher; `p` arrives filled except for the tile counts. tmC / tmAux are the store maps

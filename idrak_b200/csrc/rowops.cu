@@ -370,7 +370,7 @@ __global__ void __launch_bounds__(256) colsum_part_scalar_kernel(const __nv_bflo
 // warps per block walking the block's rows; per-lane dw / db sums are folded across the warps of a block in
 // warp order through shared memory, so the per-block partials have a fixed summation order.
 template <int VPL>
-__global__ void __launch_bounds__(256) norm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy,
+__global__ void __launch_bounds__(256, 2) norm_bwd_warp_kernel(const __nv_bfloat16* __restrict__ dy,
                                                             const __nv_bfloat16* __restrict__ x,
                                                             const __nv_bfloat16* __restrict__ w,
                                                             const float* __restrict__ mean_in,

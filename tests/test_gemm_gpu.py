@@ -143,9 +143,9 @@ def _pair_case(M, N, K, a_mn, b_mn):
 @pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, False), (True, True)])
 @pytest.mark.parametrize("M,N,K", [(2048, 2304, 768), (4096, 768, 3072), (1504, 1000, 520), (16384, 768, 768)])
 def test_gemm_large_products(M, N, K, a_mn, b_mn):
-    """Products large enough for the CTA-pair kernel (256 x 256 tiles on two SMs, when it is switched on with
-    IDRAK_GEMM_PAIR=1; the single-CTA kernel otherwise): all operand layouts, sizes that are not tile multiples, every
-    epilogue."""
+    """Products large enough for the CTA-pair kernel (256 x 256 tiles on two SMs; IDRAK_GEMM_PAIR=2 sends every such
+    product there, the default only the shapes where it measured faster, 0 none): all operand layouts, sizes that are
+    not tile multiples, every epilogue."""
     _pair_case(M, N, K, a_mn, b_mn)
     from idrak_b200 import _native
     _native.check_status("large products")
