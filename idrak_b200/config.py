@@ -84,6 +84,8 @@ TABLE: List[Setting] = [
     Setting("IDRAK_TUNING_CACHE", "text", "", "file of measured decisions (default: tuning.json under IDRAK_HOME)"),
     Setting("IDRAK_MATMUL", "choice", "float32", "precision of products in library modules outside a mixed_precision scope",
             ("float32", "bfloat16", "float16", "float8")),
+    Setting("IDRAK_TOKENIZER", "choice", "library", "runtime for tokenizer.json files: the tokenizers library, or this package's "
+            "own BPE / WordPiece / Unigram runtime (native merge engine)", ("library", "own")),
 ]
 _BY_NAME: Dict[str, Setting] = {s.name: s for s in TABLE}
 

@@ -34,6 +34,14 @@ def load_tokenizer(folder: str) -> Tokenizer:
                 break
     tj = os.path.join(folder, "tokenizer.json")
     if os.path.isfile(tj):
+        from .. import config as settings
+        if settings.get("IDRAK_TOKENIZER") == "own":
+            from .tokenizers_native import load_tokenizer_json
+            t = load_tokenizer_json(tj, config)
+            g = gen.get("eos_token_id")
+            if g is not None:
+                t.eos_token_ids = tuple(dict.fromkeys(list(t.eos_token_ids) + ([g] if isinstance(g, int) else list(g))))
+            return t
         return HfTokenizer.from_file(tj, config, gen)
     tm = os.path.join(folder, "tokenizer.model")
     if os.path.isfile(tm):
