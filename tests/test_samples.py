@@ -1,0 +1,48 @@
+"""The sample programs run end to end at small sizes."""
+import importlib.util
+import os
+
+import pytest
+import torch
+
+ROOT = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "samples")
+
+
+def _load(name):
+    spec = importlib.util.spec_from_file_location(f"sample_{name}", os.path.join(ROOT, f"{name}.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_gpt_training_sample_learns(tmp_path):
+    out = _load("gpt_training").main(["--steps", "30", "--device", "cpu", "--eval-every", "30", "--quiet",
+                                      "--save", str(tmp_path / "m.ikw")])
+    assert out["final_loss"] < out["first_loss"] - 1.0
+    assert out["held_out_loss"] < 5.0 and len(out["sample"]) == 84
+    assert (tmp_path / "m.ikw").stat().st_size > 3_000_000
+
+
+def test_xor_sample():
+    out = _load("xor").main(quiet=True)
+    p = out["predictions"]
+    assert p[0] < 0.1 and p[1] > 0.9 and p[2] > 0.9 and p[3] < 0.1 and out["rebuilt_matches"]
+
+
+def test_rag_sample():
+    out = _load("rag").main(quiet=True)
+    assert out["sources"][0] == "dp.txt"
+    assert "reduce-scatter" in out["messages"][-1]["content"]
+
+
+def test_house_prices_api_sample():
+    pytest.importorskip("fastapi")
+    out = _load("house_prices_api").main([])
+    assert out["mae"] < 8.0
+    assert 250 < out["one"]["output"][0] < 420 and len(out["many"]["outputs"]) == 2
+
+
+@pytest.mark.gpu
+def test_quantization_sample():
+    out = _load("quantization").main(["--kind", "int4", "--layers", "2", "--dim", "512"])
+    assert out["relative_error"] < 0.25 and out["reload_identical"]
