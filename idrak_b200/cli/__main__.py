@@ -504,8 +504,9 @@ def build_parser() -> argparse.ArgumentParser:
     p = add("tuning", cmd_tuning, "show the measured per-device decisions (split-K factors, ...)")
     p.add_argument("--forget", nargs="?", const="", metavar="PREFIX", help="drop decisions whose name starts with PREFIX (all without one)")
     add("check", cmd_check, "run one tiny training step and one decode").add_argument("--device")
-    from . import extra
+    from . import extra, more
     extra.register(add)
+    more.register(add)
     add("doctor", cmd_doctor, "report what is installed and what is missing")
     add("kernels", cmd_kernels, "list the native library's entry points")
     add("memory", cmd_memory, "device memory in use")
