@@ -157,14 +157,21 @@ def cmd_cluster(a) -> int:
         print(f"world {topo.world}; inside a node: {topo.link_type(names[0], names[0])}"
               + (f"; between nodes: {topo.link_type(names[0], names[1])}" if len(names) > 1 else ""))
         if a.bytes:
-            # ring all-reduce: 2 (W - 1) / W of the bytes over the slowest link + 2 (W - 1) latencies
-            bw = {"nvlink": 770e9, "pcie-host": 50e9, "shared-memory": 20e9, "rdma": 45e9, "direct-link": 10e9, "tcp": 3e9}
-            lat = {"nvlink": 3e-6, "pcie-host": 8e-6, "shared-memory": 2e-6, "rdma": 4e-6, "direct-link": 30e-6, "tcp": 60e-6}
-            kinds = {topo.link_type(x, y) for x in names for y in names} if len(names) > 1 else {topo.intra_node}
-            slow = min(kinds, key=lambda k: bw.get(k, 1e9))
-            w = topo.world
-            t = 2 * (w - 1) / w * a.bytes / bw.get(slow, 1e9) + 2 * (w - 1) * lat.get(slow, 50e-6)
-            print(f"predicted ring all-reduce of {a.bytes} bytes over {slow}: {t * 1e3:.3f} ms")
+            from ..cluster.links import ClusterCache, predict_all_reduce
+            measured = ClusterCache(os.path.join(_home(), "cluster.json")).load()
+            for algorithm in ("naive", "ring", "hierarchical"):
+                t = predict_all_reduce(topo, a.bytes, algorithm, measured)
+                print(f"predicted {algorithm:12s} all-reduce of {a.bytes} bytes: {t * 1e3:.3f} ms")
+        return 0
+    if a.action == "calibrate":
+        # path: CSV of "bytes,seconds" rows measured on the link (the link bench prints them); stored under --link
+        from ..cluster.links import ClusterCache, LinkCalibration
+        with open(a.path, "r", encoding="utf-8") as f:
+            rows = [line.strip().split(",") for line in f if line.strip() and line[0].isdigit()]
+        cal = LinkCalibration.fit([(float(r[0]), float(r[1])) for r in rows])
+        ClusterCache(os.path.join(_home(), "cluster.json")).store(a.link, cal)
+        print(f"{a.link}: latency {cal.link.latency * 1e6:.2f} us, bandwidth {cal.link.bandwidth / 1e9:.2f} GB/s, "
+              f"r2 {cal.r2:.5f} over {cal.samples} samples")
         return 0
     if a.action in ("sim", "replay"):
         import numpy as np
@@ -405,13 +412,14 @@ def register(add) -> None:
     p = add("runs", cmd_runs, "list run folders")
     p.add_argument("folder", nargs="?", default=".")
     p.add_argument("--json", action="store_true")
-    p = add("cluster", cmd_cluster, "topology files and the in-process cluster simulator: init / inspect / sim / replay")
-    p.add_argument("action", choices=["init", "inspect", "sim", "replay"])
+    p = add("cluster", cmd_cluster, "topology files and the in-process cluster simulator: init / inspect / sim / replay / calibrate")
+    p.add_argument("action", choices=["init", "inspect", "sim", "replay", "calibrate"])
     p.add_argument("path", nargs="?")
     p.add_argument("--nodes", type=int, default=1)
     p.add_argument("--gpus", type=int, default=8)
     p.add_argument("--memory", default="180GiB")
     p.add_argument("--inter-node", default="tcp")
+    p.add_argument("--link", default="tcp", help="calibrate: the link type the measurements belong to")
     p.add_argument("--bytes", type=int, default=0)
     p.add_argument("--world", type=int, default=4)
     p.add_argument("--steps", type=int, default=10)

@@ -30,12 +30,19 @@ def test_train_predict_runs(tmp_path, capsys):
     assert rc == 0 and "tensors" in text
 
 
-def test_cluster_commands(tmp_path, capsys):
+def test_cluster_commands(tmp_path, capsys, monkeypatch):
+    monkeypatch.setenv("IDRAK_HOME", str(tmp_path / "home"))
     topo = tmp_path / "t.json"
     rc, _ = run(capsys, "cluster", "init", str(topo), "--nodes", "2", "--gpus", "4")
     assert rc == 0 and json.loads(topo.read_text())["format"] == "idrak-topology/1"
     rc, text = run(capsys, "cluster", "inspect", str(topo), "--bytes", str(1 << 26))
-    assert "world 8" in text and "predicted ring all-reduce" in text
+    assert "world 8" in text and "predicted ring" in text and "predicted hierarchical" in text
+    csv = tmp_path / "m.csv"
+    csv.write_text("bytes,seconds\n" + "\n".join(f"{n},{5e-5 + n / 5e9}" for n in (1024, 1 << 20, 1 << 26)) + "\n")
+    rc, cal = run(capsys, "cluster", "calibrate", str(csv), "--link", "tcp")
+    assert rc == 0 and "bandwidth 5.00 GB/s" in cal
+    rc, again = run(capsys, "cluster", "inspect", str(topo), "--bytes", str(1 << 26))
+    assert again != text                                       # the calibrated link changes the prediction
     log = tmp_path / "run.evlog"
     rc, text = run(capsys, "cluster", "sim", "--world", "3", "--steps", "6", "--failures", "slow-worker", "--rate", "0.9",
                    "--values", "1024", "--log", str(log), "--seed", "3")
