@@ -634,3 +634,84 @@ def train_bpe(texts: Iterable[str], vocab_size: int, special_tokens: Sequence[st
                 config[key] = n
                 break
     return BpeTokenizer(spec, config)
+
+
+# --------------------------------------------------------------------------------------------- WordPiece trainer
+def train_wordpiece(texts: Iterable[str], vocab_size: int, special_tokens: Sequence[str] = ("[UNK]", "[CLS]", "[SEP]", "[PAD]", "[MASK]"),
+                    min_frequency: int = 2, lowercase: bool = False, prefix: str = "##") -> WordPieceTokenizer:
+    """WordPiece vocabulary by pair merging: words are split into a first character and ``##`` continuations, and the
+    pair with the largest count(ab) / (count(a) · count(b)) among those seen ``min_frequency`` times is merged
+    (ties: the smaller pair), until the vocabulary is full. Writes the BertNormalizer / BertPreTokenizer layout."""
+    specials = list(special_tokens)
+    if "[UNK]" not in specials:
+        specials = ["[UNK]"] + specials
+    norm_spec = {"type": "BertNormalizer", "clean_text": True, "handle_chinese_chars": True, "strip_accents": None,
+                 "lowercase": lowercase}
+    normalize = build_normalizer(norm_spec)
+    split, _ = build_pre_tokenizer({"type": "BertPreTokenizer"})
+    counts: Counter = Counter()
+    for t in texts:
+        counts.update(split([normalize(t)]))
+    vocab: Dict[str, int] = {}
+    for s in specials:
+        vocab.setdefault(s, len(vocab))
+    words = [[w[0]] + [prefix + c for c in w[1:]] for w in counts]
+    freqs = [counts[w] for w in counts]
+    for sym in sorted({s for w in words for s in w}):
+        vocab.setdefault(sym, len(vocab))
+    unit: Counter = Counter()
+    pairs: Counter = Counter()
+    where: Dict[Tuple[str, str], set] = defaultdict(set)
+    for k, (w, f) in enumerate(zip(words, freqs)):
+        for s in w:
+            unit[s] += f
+        for a, b in zip(w, w[1:]):
+            pairs[(a, b)] += f
+            where[(a, b)].add(k)
+    while len(vocab) < vocab_size:
+        best, best_score = None, 0.0
+        for (a, b), c in pairs.items():
+            if c < min_frequency:
+                continue
+            score = c / (unit[a] * unit[b])
+            if score > best_score or (score == best_score and best is not None and (a, b) < best):
+                best, best_score = (a, b), score
+        if best is None:
+            break
+        a, b = best
+        merged = a + b[len(prefix):]
+        vocab.setdefault(merged, len(vocab))
+        for k in list(where.pop((a, b), ())):
+            w, f = words[k], freqs[k]
+            for s in w:
+                unit[s] -= f
+            for x, y in zip(w, w[1:]):
+                pairs[(x, y)] -= f
+                if pairs[(x, y)] <= 0:
+                    del pairs[(x, y)]
+            out, i = [], 0
+            while i < len(w):
+                if i + 1 < len(w) and w[i] == a and w[i + 1] == b:
+                    out.append(merged)
+                    i += 2
+                else:
+                    out.append(w[i])
+                    i += 1
+            words[k] = out
+            for s in out:
+                unit[s] += f
+            for x, y in zip(out, out[1:]):
+                pairs[(x, y)] += f
+                where[(x, y)].add(k)
+        pairs.pop((a, b), None)
+    spec = {
+        "version": "1.0", "truncation": None, "padding": None,
+        "added_tokens": [{"id": vocab[s], "content": s, "single_word": False, "lstrip": False, "rstrip": False,
+                          "normalized": False, "special": True} for s in specials],
+        "normalizer": norm_spec, "pre_tokenizer": {"type": "BertPreTokenizer"}, "post_processor": None,
+        "decoder": {"type": "WordPiece", "prefix": prefix, "cleanup": True},
+        "model": {"type": "WordPiece", "unk_token": "[UNK]", "continuing_subword_prefix": prefix,
+                  "max_input_chars_per_word": 100, "vocab": vocab},
+    }
+    config = {k: v for k, v in (("pad_token", "[PAD]"), ("bos_token", "[CLS]"), ("eos_token", "[SEP]")) if v in specials}
+    return WordPieceTokenizer(spec, config)

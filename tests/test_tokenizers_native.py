@@ -112,3 +112,19 @@ def test_unsupported_parts_are_refused_by_name(tmp_path):
     json.dump(spec, open(p, "w"))
     with pytest.raises(ValueError, match="CharDelimiterSplit"):
         load_tokenizer_json(p)
+
+
+def test_wordpiece_trainer_round_trip(tmp_path):
+    from idrak_b200.text.tokenizers_native import train_wordpiece
+    tok = train_wordpiece(CORPUS, 300, min_frequency=2, lowercase=True)
+    assert 100 < tok.vocab_size <= 300 and tok.pad_token_id == tok.vocab["[PAD]"]
+    text = "the quick brown fox jumps over the lazy dog."
+    ids = tok.encode(text)
+    assert tok.unk_id not in ids and tok.decode(ids) == text
+    assert len(ids) < len(text.replace(" ", ""))                     # pieces longer than single characters were learned
+    assert any(t.startswith("##") and len(t) > 3 for t in tok.vocab)
+    path = os.path.join(tmp_path, "wp.json")
+    tok.save(path)
+    lib = tokenizers.Tokenizer.from_file(path)
+    assert lib.encode(text, add_special_tokens=False).ids == ids      # the library reads the file and agrees
+    assert tok.encode("zzzq ☃") .count(tok.unk_id) >= 1             # a symbol never seen is unknown
