@@ -47,10 +47,15 @@ def test_fused_dp_matches_nccl_and_single_process(tmp_path):
     single_w, single_losses = _single(4)
     # same data, same init: first-step loss of rank 0 differs from the global-batch loss only by batch split
     assert abs(fused["losses"][0] - nccl["losses"][0]) < 1e-3
-    dw = (fused["weights"] - nccl["weights"]).abs().max().item()
-    assert dw < 5e-3, dw
-    ds = (fused["weights"] - single_w).abs().max().item()
-    assert ds < 5e-3, ds
+    # the two paths add the ranks' gradients in different orders, so a bf16 weight may round the other way: at most one
+    # bf16 unit in the last place of a weight in [1, 2) (2^-7), and only for a few weights
+    ulp = 2.0 ** -7 + 1e-6
+    d = (fused["weights"] - nccl["weights"]).abs()
+    assert d.max().item() <= ulp, d.max().item()
+    assert (d > 5e-3).float().mean().item() < 1e-3
+    d = (fused["weights"] - single_w).abs()
+    assert d.max().item() <= ulp, d.max().item()
+    assert (d > 5e-3).float().mean().item() < 1e-3
     assert abs(fused["grad_norm"] - nccl["grad_norm"]) < 0.05 * nccl["grad_norm"] + 1e-3
 
 
