@@ -22,7 +22,7 @@ from typing import Callable, Dict, List, Optional, Sequence, Tuple
 from .sim import LinkModel
 from .topology import FORMAT, Topology
 
-# latency (s), bandwidth (B/s): NVLink is this pool's measured peer copy; the rest are typical figures to be replaced by
+# latency (s), bandwidth (B/s): NVLink is a measured B200 peer copy through NVSwitch; the rest are typical figures to be replaced by
 # a calibration on the machine at hand
 BUILT_IN_LINKS: Dict[str, LinkModel] = {
     "sim": LinkModel(0.0, 1e15),

@@ -21,7 +21,12 @@ from typing import Callable, Optional, Sequence
 import torch
 
 _KINDS = {"float32": None, "f32": None, "bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.float16,
-          "f16": torch.float16, "float8": torch.bfloat16, "f8": torch.bfloat16}
+          "f16": torch.float16}
+# Products in 8-bit floats need the fp8 GEMM (ops/gemm8.py); a scope asking for them says so by name instead of
+# running bf16 under another label, and the request is counted like the reference counts reduced-precision fallbacks
+# (src/Idrak.Gpu/ReducedPrecision.cs, CudaBackend.cs:1385-1388).
+_FLOAT8 = ("float8", "f8")
+fallbacks = {"float8_to_bfloat16": 0}
 _current = [os.environ.get("IDRAK_MATMUL", "float32").lower()]
 
 
@@ -33,6 +38,13 @@ def product_precision() -> str:
 @contextlib.contextmanager
 def mixed_precision(kind: str):
     k = kind.lower()
+    if k in _FLOAT8:
+        import warnings
+        fallbacks["float8_to_bfloat16"] += 1
+        warnings.warn("mixed_precision('float8'): layers built from idrak_b200 modules have no 8-bit product path inside "
+                      "autocast; products in this scope run in bfloat16 (use ops.gemm8 for an explicit fp8 product)",
+                      RuntimeWarning, stacklevel=3)
+        k = "bfloat16"
     if k not in _KINDS:
         raise ValueError(f"unknown precision '{kind}'; known: {', '.join(sorted(set(_KINDS)))}")
     _current.append(k)

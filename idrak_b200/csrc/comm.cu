@@ -144,10 +144,15 @@ __global__ void __launch_bounds__(512) reduce_scatter_kernel(CommCtx c, PeerPtrs
   }
 }
 
-// every rank's slice `rank` of `in` (local, n_slice elements of elem_bytes) is stored into all peers' bufs
+// every rank's slice `rank` of `in` (local, slice_bytes) is stored into all peers' bufs; uses channel and channel + 1
 __global__ void __launch_bounds__(512) all_gather_kernel(CommCtx c, PeerPtrs bufs, const void* __restrict__ in,
                                                          long long slice_bytes, int channel) {
   const uint32_t e = *c.epoch;
+  // Nobody stores into a peer's buffer before that peer says it is done with the previous contents: a rank
+  // publishes "my buffer is free" on channel + 1 when this kernel starts (stream order puts that after its last
+  // consumer of the earlier result) and every block waits for all peers' word before its first store.
+  if (blockIdx.x == 0) signal_peers(c, channel + 1, e);
+  if (!wait_peers(c, channel + 1, e, 33)) return;
   const long long nv = slice_bytes / 16;
   const uint4* src = static_cast<const uint4*>(in);
   for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
@@ -221,7 +226,11 @@ __global__ void __launch_bounds__(512) allreduce_twoshot_kernel(CommCtx c, PeerP
 __global__ void __launch_bounds__(512) broadcast_kernel(CommCtx c, PeerPtrs bufs, long long bytes, int root,
                                                         int channel) {
   const uint32_t e = *c.epoch;
+  // receivers publish "my buffer is free" (channel + 1) in stream order after their last reader of the old contents;
+  // the root stores nothing before it has every receiver's word
+  if (c.rank != root && blockIdx.x == 0) signal_peers(c, channel + 1, e);
   if (c.rank == root) {
+    if (!wait_peers(c, channel + 1, e, 34, root)) return;
     const long long nv = bytes / 16;
     const uint4* src = static_cast<const uint4*>(bufs.p[root]);
     for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
@@ -451,6 +460,10 @@ IDRAK_API void idrak_comm_ctx_init(void* ctx_out, int rank, int world, void* con
   memcpy(ctx_out, &c, sizeof(c));
 }
 
+// A kernel signals on `channel` and, for its second phase, on the channel after it: both rows must lie inside the
+// flag area of kFlagChannels rows that every rank allocated.
+static inline bool bad_channel(int channel) { return channel < 0 || channel + 1 >= kFlagChannels; }
+
 static inline CommCtx load_ctx(const void* ctx) {
   CommCtx c;
   memcpy(&c, ctx, sizeof(c));
@@ -469,17 +482,20 @@ IDRAK_API int idrak_comm_bump_epoch(const void* ctx, void* stream_) {
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_comm_barrier(const void* ctx, int channel, void* stream_) {
+  if (bad_channel(channel)) return -3;
   comm_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(load_ctx(ctx), channel);
   note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_comm_wait(const void* ctx, int channel, unsigned add, void* stream_) {
+  if (bad_channel(channel)) return -3;
   comm_wait_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream_)>>>(load_ctx(ctx), channel, add);
   note_launches(1);
   return int(cudaGetLastError());
 }
 IDRAK_API int idrak_allreduce_oneshot(const void* ctx, const float* in, float* out, int n, int op_max, int channel,
                                       void* stream_) {
+  if (bad_channel(channel)) return -3;
   CommCtx c = load_ctx(ctx);
   if (n > c.slot_floats) return -2;
   allreduce_oneshot_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream_)>>>(c, in, out, n, op_max, channel);
@@ -488,6 +504,7 @@ IDRAK_API int idrak_allreduce_oneshot(const void* ctx, const float* in, float* o
 }
 IDRAK_API int idrak_reduce_scatter(const void* ctx, void* const* bufs, void* out, long long n, int bf16,
                                    int out_fp32, float scale, int channel, int max_blocks, void* stream_) {
+  if (bad_channel(channel)) return -3;
   CommCtx c = load_ctx(ctx);
   const int V = bf16 ? 8 : 4;
   if (n % (c.world * V)) return -2;
@@ -502,6 +519,7 @@ IDRAK_API int idrak_reduce_scatter(const void* ctx, void* const* bufs, void* out
 }
 IDRAK_API int idrak_all_gather(const void* ctx, void* const* bufs, const void* in, long long slice_bytes,
                                int channel, int max_blocks, void* stream_) {
+  if (bad_channel(channel)) return -3;
   CommCtx c = load_ctx(ctx);
   if (slice_bytes % 16) return -2;
   PeerPtrs p = load_ptrs(bufs, c.world);
@@ -512,6 +530,7 @@ IDRAK_API int idrak_all_gather(const void* ctx, void* const* bufs, const void* i
 }
 IDRAK_API int idrak_allreduce_twoshot(const void* ctx, void* const* bufs, long long n, int bf16, float scale,
                                       int channel, int max_blocks, void* stream_) {
+  if (bad_channel(channel)) return -3;
   CommCtx c = load_ctx(ctx);
   const int V = bf16 ? 8 : 4;
   if (n % (c.world * V)) return -2;
@@ -526,6 +545,7 @@ IDRAK_API int idrak_allreduce_twoshot(const void* ctx, void* const* bufs, long l
 }
 IDRAK_API int idrak_broadcast(const void* ctx, void* const* bufs, long long bytes, int root, int channel,
                               int max_blocks, void* stream_) {
+  if (bad_channel(channel)) return -3;
   CommCtx c = load_ctx(ctx);
   if (bytes % 16) return -2;
   PeerPtrs p = load_ptrs(bufs, c.world);
@@ -538,6 +558,7 @@ IDRAK_API int idrak_broadcast(const void* ctx, void* const* bufs, long long byte
 IDRAK_API int idrak_dp_reduce_scatter(const void* ctx, void* const* grads, long long start, long long len,
                                       long long shard_off, float* shard_grad, float* sumsq_partial,
                                       const float* rank_weights, int channel, int blocks, void* stream_) {
+  if (bad_channel(channel)) return -3;
   CommCtx c = load_ctx(ctx);
   if (len % (c.world * 8)) return -2;
   PeerPtrs p = load_ptrs(grads, c.world);
@@ -550,6 +571,7 @@ IDRAK_API int idrak_dp_reduce_scatter(const void* ctx, void* const* grads, long 
 }
 IDRAK_API int idrak_dp_norm_exchange(const void* ctx, const float* partials, int n_partials, float* hyper,
                                      int channel, void* stream_) {
+  if (bad_channel(channel)) return -3;
   dp_norm_exchange_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream_)>>>(load_ctx(ctx), partials, n_partials,
                                                                             hyper, channel);
   note_launches(1);
@@ -559,6 +581,7 @@ IDRAK_API int idrak_dp_adamw_allgather(const void* ctx, void* const* params, lon
                                        long long shard_off, const float* shard_grad, float* master, float* m,
                                        float* v, const void* decay_flags, const float* hyper, float weight_decay,
                                        int channel, int signal_done, int blocks, void* stream_) {
+  if (bad_channel(channel)) return -3;
   CommCtx c = load_ctx(ctx);
   if (len % (c.world * 8)) return -2;
   PeerPtrs p = load_ptrs(params, c.world);

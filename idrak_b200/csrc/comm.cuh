@@ -35,12 +35,13 @@ __device__ __forceinline__ void signal_peers(const CommCtx& c, int channel, uint
   }
 }
 
-// Every thread returns true once all peers published >= value on `channel` (bounded).
-__device__ __forceinline__ bool wait_peers(const CommCtx& c, int channel, uint32_t value, uint32_t kernel_id) {
+// Every thread returns true once all peers (except `skip`, if given) published >= value on `channel` (bounded).
+__device__ __forceinline__ bool wait_peers(const CommCtx& c, int channel, uint32_t value, uint32_t kernel_id,
+                                           int skip = -1) {
   __shared__ int ok_flag;
   if (threadIdx.x == 0) ok_flag = 1;
   __syncthreads();
-  if (threadIdx.x < c.world) {
+  if (threadIdx.x < c.world && int(threadIdx.x) != skip) {
     const uint32_t* f = c.flags[c.rank] + channel * kMaxRanks + threadIdx.x;
     uint64_t t0 = 0;
     uint32_t polls = 0;

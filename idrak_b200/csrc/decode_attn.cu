@@ -314,12 +314,15 @@ IDRAK_API int idrak_paged_decode(const void* q, long long q_stride, const void* 
   p.scale_log2 = scale * 1.4426950408889634f;
   p.window = window;
   dim3 grid(seqs, Hkv, p.splits);
-  static bool configured = false;
-  if (!configured) {
-    cudaFuncSetAttribute(paged_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(decode_smem<64>()));
-    cudaFuncSetAttribute(paged_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, int(decode_smem<128>()));
-    configured = true;
-  }
+  static DeviceOnce configured;
+  if (int e = configured.run([&] {
+        cudaError_t e1 = cudaFuncSetAttribute(paged_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              int(decode_smem<64>()));
+        if (e1 != cudaSuccess) return int(e1);
+        return int(cudaFuncSetAttribute(paged_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        int(decode_smem<128>())));
+      }))
+    return e;
   if (D == 64) paged_decode_kernel<64><<<grid, kDecWarps * 32, decode_smem<64>(), s>>>(p);
   else paged_decode_kernel<128><<<grid, kDecWarps * 32, decode_smem<128>(), s>>>(p);
   note_launches(1);

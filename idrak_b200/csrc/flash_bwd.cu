@@ -582,14 +582,13 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
                       const FlashParams& p, cudaStream_t stream) {
   auto kq = flash_bwd_q_kernel<D>;
   auto kkv = flash_bwd_kv_kernel<D>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdQSmem<D>::kTotal);
-    if (e != cudaSuccess) return int(e);
-    e = cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdKVSmem<D>::kTotal);
-    if (e != cudaSuccess) return int(e);
-    configured = true;
-  }
+  static DeviceOnce configured;
+  if (int e = configured.run([&] {
+        cudaError_t e1 = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdQSmem<D>::kTotal);
+        if (e1 != cudaSuccess) return int(e1);
+        return int(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdKVSmem<D>::kTotal));
+      }))
+    return e;
   dim3 gq((p.Sq + 127) / 128, p.H, p.B);
   kq<<<gq, 192, BwdQSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
   note_launches(1);

@@ -336,12 +336,11 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
                       cudaStream_t stream) {
   using L = FwdSmem<D>;
   auto kern = flash_fwd_kernel<D>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
-    if (e != cudaSuccess) return int(e);
-    configured = true;
-  }
+  static DeviceOnce configured;
+  if (int e = configured.run([&] {
+        return int(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      }))
+    return e;
   dim3 grid((p.Sq + 127) / 128, p.H, p.B);
   kern<<<grid, 192, L::kTotal, stream>>>(tq, tk, tv, p);
   note_launches(1);

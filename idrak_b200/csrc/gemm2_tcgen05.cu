@@ -2,7 +2,7 @@
 //
 // A cluster of two CTAs is the unit of work. Each CTA loads its own 128 rows of A and its own 128 of the 256 B rows
 // (columns of C) per K block - 32 KB per stage instead of the 48 KB a lone CTA needs for a 128 x 256 tile, so the same
-// shared memory holds six stages and every byte fetched from L2 feeds 1.5x the FLOPs. The even CTA of the pair (the
+// shared memory holds five stages and two output staging buffers per epilogue group and every byte fetched from L2 feeds 1.5x the FLOPs. The even CTA of the pair (the
 // leader) issues the MMAs; the instruction reads both CTAs' shared memory and writes each CTA's half of the
 // accumulator (its 128 rows x 256 columns) into that CTA's TMEM. Each CTA drains its own half through the same fused
 // epilogue as the single-CTA kernel.
@@ -13,7 +13,7 @@
 //            shared::cluster barrier address). No load here uses cluster multicast.
 //   empty  - in both CTAs, count 1: tcgen05.commit.cta_group::2 with multicast to both CTAs releases the stage in each.
 //   tmem_full[2]  - in both CTAs, count 1: multicast commit after the last K block of a tile.
-//   tmem_empty[2] - in the leader, count 256: the 128 epilogue threads of each CTA arrive (the peer's remotely).
+//   tmem_empty[2] - in the leader, count 512: the 256 epilogue threads of each CTA arrive (the peer's remotely).
 // Every wait is bounded (two seconds of %globaltimer); a CTA that gives up reports through the status word, waits
 // for the copies it issued and still meets its peer at the closing cluster barrier, so neither CTA leaves while the
 // other can still touch its shared memory or barriers.
@@ -34,8 +34,8 @@ struct PairSmem {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = kHalfBN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;       // 32 KB
-  static constexpr int kStages = 6;
-  static constexpr int kStagingBytes = 4 * 2 * 4096;
+  static constexpr int kStages = 5;
+  static constexpr int kStagingBytes = 2 * kDenseStagingBytes;   // two buffers per epilogue group
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;
 };
@@ -101,7 +101,7 @@ __device__ __forceinline__ void tc_mma_pair_f16_ss(uint32_t d_tmem, uint64_t a_d
 // the kernel: grid = 2 x pairs, cluster (2, 1, 1); warp roles as in the single-CTA kernel
 // ---------------------------------------------------------------------------------------------------------------
 template <int A_MN, int B_MN>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kDenseThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
   using L = PairSmem;
@@ -135,7 +135,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], 256);
+      mbar_init(&tmem_empty[b], 2 * 32 * kEpiWarps);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -204,21 +204,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
+      unsigned long long t_acc = 0, t_ops = 0;
+      const long long t_begin = p.prof ? clock64() : 0;
       for (int unit = pair; unit < units && ok; unit += pairs, ++local) {
         const int buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
+        const long long c0 = p.prof ? clock64() : 0;
         if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1, abort_flag, p.st, kTimeoutTmemEmpty, (2u << 16) | buf)) {
           ok = false;
           break;
         }
         tc_fence_after();
+        if (p.prof) t_acc += (unsigned long long)(clock64() - c0);
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = 0; kb < k_blocks; ++kb) {
+          const long long c2 = p.prof ? clock64() : 0;
           if (!mbar_wait(&full[stage], phase, abort_flag, p.st, kTimeoutSmemFull, (2u << 16) | stage)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          if (p.prof) t_ops += (unsigned long long)(clock64() - c2);
           const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
           const uint32_t sb = sa + L::kABytes;
 #pragma unroll
@@ -234,104 +240,57 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         }
         if (ok) tc_commit_pair(&tmem_full[buf], 0x3);
       }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 0] = (unsigned long long)(clock64() - t_begin);
+        p.prof[blockIdx.x * 8 + 1] = t_acc;
+        p.prof[blockIdx.x * 8 + 2] = t_ops;
+      }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps, this CTA's 128 rows)
-    const int quarter = warp & 3;
-    const int row_in_tile = quarter * 32 + lane;
+    // ------------------------------------------------------------------ epilogue (8 warps, this CTA's 128 rows)
+    const int ewarp = warp - 2;
     const uint32_t empty_bar_leader0 = map_shared_to_cta(smem_u32(&tmem_empty[0]), 0);
     const uint32_t empty_bar_leader1 = map_shared_to_cta(smem_u32(&tmem_empty[1]), 0);
     int local = 0;
-    int ring = 0;
+    unsigned long long t_wait = 0, t_busy = 0;
+    SideAhead ahead;
+    ahead.ready = false;
+    ahead.ring = 0;
     for (int unit = pair; unit < units; unit += pairs, ++local) {
       int tm, tn, split;
       unit_to_tile(p, unit, tm, tn, split);
+      NextTile next{false, 0, 0};
+      if (unit + pairs < units) {
+        int nm, nn, ns;
+        unit_to_tile(p, unit + pairs, nm, nn, ns);
+        next = NextTile{true, nm * 2 * kBM + int(rank) * kBM, nn * BN};
+      }
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
+      const long long c0 = p.prof ? clock64() : 0;
       if (!mbar_wait(&tmem_full[buf], acc_phase, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | buf)) break;
       tc_fence_after();
-      const int row_base = tm * 2 * kBM + int(rank) * kBM;
-      const int row = row_base + row_in_tile;
-      const int n0 = tn * BN;
-      if (p.tma_store) {
-        // registers -> swizzled shared slab (32 rows x 64 columns) -> TMA store
-        const int row0 = row_base + quarter * 32;
-        const bool gelu = (p.act == kActGelu);
-        uint8_t* my_stage = staging + quarter * 2 * 4096;
-#pragma unroll 1
-        for (int s64 = 0; s64 < BN / 64; ++s64) {
-          const int col0 = n0 + s64 * 64;
-          if (col0 >= p.N || row0 >= p.M) break;                      // warp-uniform
-          uint8_t* cbuf = my_stage + (gelu ? 0 : (ring & 1)) * 4096;
-          uint8_t* abuf = my_stage + 4096;
-          if (lane == 0) {
-            if (gelu) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
-          }
-          __syncwarp();
-#pragma unroll 1
-          for (int h = 0; h < 2; ++h) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + s64 * 64 + h * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int col = col0 + h * 32 + g * 8;
-              float v[8], pre[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) { v[i] = __uint_as_float(r[g * 8 + i]) * p.alpha; pre[i] = 0.f; }
-              if (row < p.M && col < p.N) epilogue_math8(p, row, col, v, min(8, p.N - col), false, pre);
-              const int chunk = ((h * 4 + g) ^ (lane & 7)) << 4;
-              uint4 o;
-              o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-              o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-              *reinterpret_cast<uint4*>(cbuf + lane * 128 + chunk) = o;
-              if (gelu) {
-                uint4 a;
-                a.x = pack_bf16x2(pre[0], pre[1]); a.y = pack_bf16x2(pre[2], pre[3]);
-                a.z = pack_bf16x2(pre[4], pre[5]); a.w = pack_bf16x2(pre[6], pre[7]);
-                *reinterpret_cast<uint4*>(abuf + lane * 128 + chunk) = a;
-              }
-            }
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&tmC, cbuf, col0, row0);
-            tma_store_commit();
-            if (gelu) {
-              tma_store_2d(&tmAux, abuf, col0, row0);
-              tma_store_commit();
-            }
-          }
-          ++ring;
-        }
-      } else {
-#pragma unroll 1
-        for (int c = 0; c < BN / 32; ++c) {
-          uint32_t r[32];
-          tmem_ld_32x32b_x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + c * 32, r);
-          tmem_ld_wait();
-          const int col0 = n0 + c * 32;
-          if (row < p.M && col0 < p.N) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int col = col0 + g * 8;
-              if (col < p.N) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * p.alpha;
-                epilogue8(p, row, col, v, min(8, p.N - col));
-              }
-            }
-          }
-        }
+      const long long c1 = p.prof ? clock64() : 0;
+      uint64_t* done_local = &tmem_empty[buf];
+      const uint32_t done_remote = buf ? empty_bar_leader1 : empty_bar_leader0;
+      // this CTA's half of the accumulator is free once read: tell the leader's MMA warp
+      drain_accumulator<BN, 2>(p, &tmC, &tmAux, tmem_base + buf * BN, ewarp, lane, tm * 2 * kBM + int(rank) * kBM, tn * BN,
+                            0, true, staging, ahead, next, [=]() {
+                              tc_fence_before();
+                              if (leader) mbar_arrive(done_local);
+                              else mbar_arrive_cluster(done_remote);
+                            });
+      if (p.prof) {
+        t_wait += (unsigned long long)(c1 - c0);
+        t_busy += (unsigned long long)(clock64() - c1);
       }
-      tc_fence_before();
-      // this CTA's half of the accumulator is free: tell the leader's MMA warp
-      if (leader) mbar_arrive(&tmem_empty[buf]);
-      else mbar_arrive_cluster(buf ? empty_bar_leader1 : empty_bar_leader0);
     }
-    if (p.tma_store && lane == 0) tma_store_wait<0>();
+    if (p.tma_store && (ewarp & 3) == 2 && lane == 0) tma_store_wait<0>();
+    if (p.prof && ewarp == 0 && lane == 0) {
+      p.prof[blockIdx.x * 8 + 4] = t_wait;
+      p.prof[blockIdx.x * 8 + 5] = t_busy;
+      p.prof[blockIdx.x * 8 + 6] = (unsigned long long)local;
+    }
   }
 
   tc_fence_before();
@@ -349,13 +308,12 @@ template <int A_MN, int B_MN>
 static int launch_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC, const CUtensorMap& tmAux,
                        const GemmParams& p, int grid, cudaStream_t stream) {
   auto kern = gemm_pair_kernel<A_MN, B_MN>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kTotal);
-    if (e != cudaSuccess) return int(e);
-    configured = true;
-  }
-  kern<<<grid, kGemmThreads, PairSmem::kTotal, stream>>>(tmA, tmB, tmC, tmAux, p);
+  static DeviceOnce configured;
+  if (int e = configured.run([&] {
+        return int(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::kTotal));
+      }))
+    return e;
+  kern<<<grid, kDenseThreads, PairSmem::kTotal, stream>>>(tmA, tmB, tmC, tmAux, p);
   note_launches(1);
   return int(cudaGetLastError());
 }
@@ -391,7 +349,7 @@ bool gemm_pair_wanted(int M, int N, int K, int splits) {
 }
 
 // Same contract as the single-CTA launcher; `p` arrives filled except for the tile counts. tmC / tmAux are the store maps
-// (box 64 x 32) made by the caller.
+// (box 64 x 128) made by the caller.
 int gemm_pair_launch(const void* A, int lda, int a_mn, const void* B, int ldb, int b_mn, const CUtensorMap& tmC,
                      const CUtensorMap& tmAux, GemmParams p, int fp16, cudaStream_t stream) {
   CUtensorMap tmA, tmB;

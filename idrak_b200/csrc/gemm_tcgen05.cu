@@ -3,8 +3,9 @@
 // One persistent CTA per SM, warp-specialised:
 //   warp 0      TMA producer   (cp.async.bulk.tensor into a 128B-swizzled shared-memory ring)
 //   warp 1      MMA issuer     (one thread issues tcgen05.mma; owns the TMEM allocation)
-//   warps 2..5  epilogue       (tcgen05.ld the fp32 accumulator, fuse bias / GELU / GELU' / residual /
-//                               accumulate, write bf16 or fp32)
+//   warps 2..9  epilogue       (tcgen05.ld the fp32 accumulator, fuse bias / GELU / GELU' / residual /
+//                               accumulate, write bf16 or fp32; two groups of four warps, each group owning
+//                               half of the tile's columns - see drain_accumulator in gemm_epilogue.cuh)
 // The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i overlaps the
 // main loop of tile i+1. Both operands may be K-major or MN-major in memory, which gives the four
 // BLAS transposition cases without a transposed copy:
@@ -29,13 +30,13 @@ struct GemmSmem {
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kStages = (BN == 256) ? 4 : 6;
-  static constexpr int kStagingBytes = 4 * 2 * 4096;   // per epilogue warp: two 32-row x 128-byte slabs
+  static constexpr int kStagingBytes = kDenseStagingBytes;   // per epilogue group: one 128-row x 128-byte slab
   static constexpr int kBarrierBytes = 256;
   static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
 template <int BN, int A_MN, int B_MN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kDenseThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
   using L = GemmSmem<BN>;
@@ -64,7 +65,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&tmem_full[b], 1);
-      mbar_init(&tmem_empty[b], 128);
+      mbar_init(&tmem_empty[b], 32 * kEpiWarps);
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -136,6 +137,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
+      unsigned long long t_acc = 0, t_ops = 0;
+      const long long t_begin = p.prof ? clock64() : 0;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++local) {
         int tm, tn, split;
         unit_to_tile(p, unit, tm, tn, split);
@@ -143,18 +146,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int kb1 = min(k_blocks_total, kb0 + kb_per_split);
         const int buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
+        const long long c0 = p.prof ? clock64() : 0;
         if (!mbar_wait(&tmem_empty[buf], acc_phase ^ 1, abort_flag, p.st, kTimeoutTmemEmpty, (1u << 16) | buf)) {
           ok = false;
           break;
         }
         tc_fence_after();
+        if (p.prof) t_acc += (unsigned long long)(clock64() - c0);
         const uint32_t d_tmem = tmem_base + buf * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
+          const long long c2 = p.prof ? clock64() : 0;
           if (!mbar_wait(&full[stage], phase, abort_flag, p.st, kTimeoutSmemFull, (1u << 16) | stage)) {
             ok = false;
             break;
           }
           tc_fence_after();
+          if (p.prof) t_ops += (unsigned long long)(clock64() - c2);
           const uint32_t sa = smem_u32(smem + stage * L::kStageBytes);
           const uint32_t sb = sa + L::kABytes;
 #pragma unroll
@@ -170,125 +177,58 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         if (ok) tc_commit(&tmem_full[buf]);
       }
+      if (p.prof) {
+        p.prof[blockIdx.x * 8 + 0] = (unsigned long long)(clock64() - t_begin);   // MMA warp's whole loop
+        p.prof[blockIdx.x * 8 + 1] = t_acc;                                        // ... waiting for a free accumulator
+        p.prof[blockIdx.x * 8 + 2] = t_ops;                                        // ... waiting for operand stages
+      }
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (4 warps, 128 rows)
-    const int quarter = warp & 3;            // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
-    const int row_in_tile = quarter * 32 + lane;
+    // ------------------------------------------------------------------ epilogue (8 warps, 128 rows)
+    const int ewarp = warp - 2;
     int local = 0;
-    int ring = 0;
     bool ok = true;
+    unsigned long long t_wait = 0, t_busy = 0;
+    SideAhead ahead;
+    ahead.ready = false;
+    ahead.ring = 0;
     for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++local) {
       int tm, tn, split;
       unit_to_tile(p, unit, tm, tn, split);
+      NextTile next{false, 0, 0};
+      if (unit + int(gridDim.x) < units) {
+        int nm, nn, ns;
+        unit_to_tile(p, unit + gridDim.x, nm, nn, ns);
+        next = NextTile{true, nm * kBM, nn * BN};
+      }
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
       const int kb0 = split * kb_per_split;
       const bool has_k = kb0 < k_blocks_total;   // a split past the end of K contributes zeros
+      const long long c0 = p.prof ? clock64() : 0;
       if (!mbar_wait(&tmem_full[buf], acc_phase, abort_flag, p.st, kTimeoutTmemFull, (1u << 16) | buf)) {
         ok = false;
         break;
       }
       tc_fence_after();
-      const int row = tm * kBM + row_in_tile;
-      const int n0 = tn * BN;
-      if (p.tma_store && p.splits == 1) {
-        // ---- staged path: registers -> swizzled shared slab (32 rows x 64 columns) -> TMA store
-        const int row0 = tm * kBM + quarter * 32;
-        const bool gelu = (p.act == kActGelu);
-        uint8_t* my_stage = staging + quarter * 2 * 4096;
-#pragma unroll 1
-        for (int s64 = 0; s64 < BN / 64; ++s64) {
-          const int col0 = n0 + s64 * 64;
-          if (col0 >= p.N || row0 >= p.M) break;                      // warp-uniform
-          uint8_t* cbuf = my_stage + (gelu ? 0 : (ring & 1)) * 4096;
-          uint8_t* abuf = my_stage + 4096;
-          if (lane == 0) {
-            if (gelu) tma_store_wait_read<0>(); else tma_store_wait_read<1>();
-          }
-          __syncwarp();
-#pragma unroll 1
-          for (int h = 0; h < 2; ++h) {
-            uint32_t r[32];
-            tmem_ld_32x32b_x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + s64 * 64 + h * 32, r);
-            tmem_ld_wait();
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int col = col0 + h * 32 + g * 8;
-              float v[8], pre[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) { v[i] = __uint_as_float(r[g * 8 + i]) * p.alpha; pre[i] = 0.f; }
-              if (row < p.M && col < p.N) epilogue_math8(p, row, col, v, min(8, p.N - col), false, pre);
-              const int chunk = ((h * 4 + g) ^ (lane & 7)) << 4;
-              uint4 o;
-              o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-              o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
-              *reinterpret_cast<uint4*>(cbuf + lane * 128 + chunk) = o;
-              if (gelu) {
-                uint4 a;
-                a.x = pack_bf16x2(pre[0], pre[1]); a.y = pack_bf16x2(pre[2], pre[3]);
-                a.z = pack_bf16x2(pre[4], pre[5]); a.w = pack_bf16x2(pre[6], pre[7]);
-                *reinterpret_cast<uint4*>(abuf + lane * 128 + chunk) = a;
-              }
-            }
-          }
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            tma_store_2d(&tmC, cbuf, col0, row0);
-            tma_store_commit();
-            if (gelu) {
-              tma_store_2d(&tmAux, abuf, col0, row0);
-              tma_store_commit();
-            }
-          }
-          ++ring;
-        }
-        tc_fence_before();
-        mbar_arrive(&tmem_empty[buf]);
-        continue;
+      const long long c1 = p.prof ? clock64() : 0;
+      uint64_t* done = &tmem_empty[buf];
+      drain_accumulator<BN, 1>(p, &tmC, &tmAux, tmem_base + buf * BN, ewarp, lane, tm * kBM, tn * BN, split, has_k,
+                            staging, ahead, next, [done]() {
+                              tc_fence_before();
+                              mbar_arrive(done);
+                            });
+      if (p.prof) {
+        t_wait += (unsigned long long)(c1 - c0);
+        t_busy += (unsigned long long)(clock64() - c1);
       }
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        uint32_t r[32];
-        if (has_k) {
-          tmem_ld_32x32b_x32(tmem_base + (uint32_t(quarter * 32) << 16) + buf * BN + c * 32, r);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) r[i] = 0u;
-        }
-        const int col0 = n0 + c * 32;
-        if (row < p.M && col0 < p.N) {
-          if (p.splits > 1) {
-            float* w = p.workspace + (size_t(split) * p.M + row) * p.N + col0;
-            if (col0 + 32 <= p.N && ((reinterpret_cast<uintptr_t>(w) & 15) == 0)) {
-#pragma unroll
-              for (int i = 0; i < 8; ++i)
-                reinterpret_cast<float4*>(w)[i] =
-                    make_float4(__uint_as_float(r[4 * i]), __uint_as_float(r[4 * i + 1]),
-                                __uint_as_float(r[4 * i + 2]), __uint_as_float(r[4 * i + 3]));
-            } else {
-              for (int i = 0; i < 32 && col0 + i < p.N; ++i) w[i] = __uint_as_float(r[i]);
-            }
-          } else {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              const int col = col0 + g * 8;
-              if (col < p.N) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]) * p.alpha;
-                epilogue8(p, row, col, v, min(8, p.N - col));
-              }
-            }
-          }
-        }
-      }
-      tc_fence_before();
-      mbar_arrive(&tmem_empty[buf]);
     }
-    if (p.tma_store && lane == 0) tma_store_wait<0>();   // staged slabs are read out before shared memory goes away
+    if (p.tma_store && (ewarp & 3) == 2 && lane == 0) tma_store_wait<0>();   // the groups' leaders (lane quarter 0)
+    if (p.prof && ewarp == 0 && lane == 0) {
+      p.prof[blockIdx.x * 8 + 4] = t_wait;
+      p.prof[blockIdx.x * 8 + 5] = t_busy;
+      p.prof[blockIdx.x * 8 + 6] = (unsigned long long)local;
+    }
   }
 
   tc_fence_before();
@@ -335,16 +275,34 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
                        const CUtensorMap& tmAux, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = GemmSmem<BN>;
   auto kern = gemm_kernel<BN, A_MN, B_MN>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
-    if (e != cudaSuccess) return int(e);
-    configured = true;
-  }
-  kern<<<grid, kGemmThreads, L::kTotal, stream>>>(tmA, tmB, tmC, tmAux, p);
+  static DeviceOnce configured;
+  if (int e = configured.run([&] {
+        return int(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      }))
+    return e;
+  kern<<<grid, kDenseThreads, L::kTotal, stream>>>(tmA, tmB, tmC, tmAux, p);
   note_launches(1);
   return int(cudaGetLastError());
 }
+
+int pick_epi_mode(const GemmParams& p) {
+  auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+  if (!p.tma_store || p.col_scale) return kEpiGeneric;
+  if (p.bias && !aligned(p.bias)) return kEpiGeneric;
+  if (p.residual && (!aligned(p.residual) || (p.ldr & 7))) return kEpiGeneric;
+  const bool b = p.bias != nullptr, r = p.residual != nullptr;
+  if (p.act == kActNone) return b ? (r ? kEpiBiasRes : kEpiBias) : (r ? kEpiRes : kEpiPlain);
+  if (p.act == kActGelu && !r) return b ? kEpiBiasGelu : kEpiGelu;
+  if (p.act == kActGeluGrad && !b && !r && aligned(p.aux) && (p.ld_aux & 7) == 0) return kEpiGeluGrad;
+  return kEpiGeneric;
+}
+
+// Role timers: with a buffer set, every dense GEMM CTA writes eight cycle counts at [blockIdx.x * 8]:
+//   0 MMA warp, whole tile loop   1 of that, waiting for a drained accumulator   2 of that, waiting for operands
+//   4 first epilogue warp waiting for a finished accumulator   5 the same warp draining   6 tiles this CTA ran
+// (3 and 7 unused). They say which of the three roles bounds a shape. The buffer must hold 8 words per SM.
+static std::atomic<unsigned long long*> g_role_timers{nullptr};
+unsigned long long* role_timer_buffer() { return g_role_timers.load(std::memory_order_relaxed); }
 
 static int make_operand_map(CUtensorMap* tm, const void* ptr, int mn_extent, int k_extent, int ld, int mn_major,
                             int box_mn, int fp16) {
@@ -371,6 +329,11 @@ static int make_operand_map(CUtensorMap* tm, const void* ptr, int mn_extent, int
 }  // namespace idrak
 
 using namespace idrak;
+
+// Switch the role timers on (a device buffer of 8 * SM-count 64-bit words) or off (null).
+IDRAK_API void idrak_gemm_role_timers(void* device_buffer) {
+  g_role_timers.store(static_cast<unsigned long long*>(device_buffer), std::memory_order_relaxed);
+}
 
 // Number of fp32 workspace elements a call with these sizes needs (0 when it will not split K).
 IDRAK_API long long idrak_gemm_workspace_elems(int M, int N, int K, int splits) {
@@ -405,7 +368,7 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
   if (act != kActNone && aux == nullptr) return -4;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int bn = (N <= 128) ? 128 : 256;
-  GemmParams p;
+  GemmParams p{};
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -444,7 +407,7 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
   if (!c_fp32 && !beta && p.splits == 1 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
       (act != kActGelu || ((ld_aux % 8) == 0 && (reinterpret_cast<uintptr_t>(aux) & 15) == 0))) {
     uint64_t dims[2] = {uint64_t(N), uint64_t(M)};
-    uint32_t box[2] = {64, 32};
+    uint32_t box[2] = {64, 128};
     uint64_t str_c[1] = {uint64_t(ldc) * 2};
     int ok = encode_tensor_map(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, dims, str_c, box,
                                CU_TENSOR_MAP_SWIZZLE_128B) == 0;
@@ -455,6 +418,8 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
     }
     p.tma_store = ok ? 1 : 0;
   }
+  p.epi_mode = pick_epi_mode(p);
+  p.prof = role_timer_buffer();
 
   // large one-pass products go to CTA pairs (256 x 256 tiles, cta_group::2)
   if (bn == 256 && gemm_pair_wanted(M, N, K, p.splits))

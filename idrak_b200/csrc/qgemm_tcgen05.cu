@@ -380,12 +380,11 @@ static int launch_q(const CUtensorMap& tmA, const CUtensorMap& tmC, const CUtens
                     const QWeight& w, int grid, cudaStream_t stream) {
   using L = QSmem<BN>;
   auto kern = qgemm_kernel<BN, kTrans>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal);
-    if (e != cudaSuccess) return int(e);
-    configured = true;
-  }
+  static DeviceOnce configured;
+  if (int e = configured.run([&] {
+        return int(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+      }))
+    return e;
   kern<<<grid, kQThreads, L::kTotal, stream>>>(tmA, tmC, tmAux, p, w);
   note_launches(1);
   return int(cudaGetLastError());
@@ -423,7 +422,7 @@ IDRAK_API int idrak_qgemm(const void* x, int ldx, const void* codes, const void*
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const int bn = (N <= 128) ? 128 : 256;
-  GemmParams p;
+  GemmParams p{};
   memset(&p, 0, sizeof(p));
   p.M = M; p.N = N; p.K = K;
   p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;

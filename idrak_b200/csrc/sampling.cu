@@ -113,6 +113,7 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const Sampl
   __shared__ float cand_v[kCandidates * 2];
   __shared__ int cand_i[kCandidates * 2];
   __shared__ int n_cand;
+  __shared__ int tie_warp[32];
   const int row = blockIdx.x;
   const float temp = fmaxf(p.temperature ? p.temperature[row] : 1.f, 1e-6f);
   int k = p.top_k ? p.top_k[row] : kCandidates;
@@ -145,15 +146,49 @@ __global__ void __launch_bounds__(kSampleThreads) sample_rows_kernel(const Sampl
     __syncthreads();
   }
   const uint32_t kth = s_prefix;
-  // ---- gather candidates: everything strictly above the k-th value, then ties by ascending id
+  // ---- gather candidates: everything strictly above the k-th value (fewer than k of them, in any order: they are
+  // sorted below), then as many entries equal to it as the k places still need, by ascending id. Ties can never
+  // crowd a larger logit out of the slots, and which tied ids are kept does not depend on thread timing.
   if (threadIdx.x == 0) n_cand = 0;
   __syncthreads();
   for (int j = threadIdx.x; j < p.vocab; j += blockDim.x) {
     const float v = penalised(p, row, j, load_logit(p.logits, p.fp32, size_t(row) * p.ld + j)) / temp;
-    if (ordered_bits(v) >= kth) {
+    if (ordered_bits(v) > kth) {
       const int slot = atomicAdd(&n_cand, 1);
       if (slot < kCandidates * 2) { cand_v[slot] = v; cand_i[slot] = j; }
     }
+  }
+  __syncthreads();
+  {
+    const int n_greater = min(n_cand, kCandidates * 2);
+    const int need = min(k - n_greater, kCandidates * 2 - n_greater);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    int tie_base = 0;
+    for (int base = 0; base < p.vocab && tie_base < need; base += blockDim.x) {
+      const int j = base + threadIdx.x;
+      float v = 0.f;
+      bool tie = false;
+      if (j < p.vocab) {
+        v = penalised(p, row, j, load_logit(p.logits, p.fp32, size_t(row) * p.ld + j)) / temp;
+        tie = ordered_bits(v) == kth;
+      }
+      const unsigned ballot = __ballot_sync(0xffffffffu, tie);
+      if (lane == 0) tie_warp[warp] = __popc(ballot);
+      __syncthreads();
+      int before = 0, total = 0;
+      for (int w = 0; w < warps; ++w) {
+        const int c = tie_warp[w];
+        if (w < warp) before += c;
+        total += c;
+      }
+      if (tie) {
+        const int pos = tie_base + before + __popc(ballot & ((1u << lane) - 1u));
+        if (pos < need) { cand_v[n_greater + pos] = v; cand_i[n_greater + pos] = j; }
+      }
+      tie_base += total;
+      __syncthreads();
+    }
+    if (threadIdx.x == 0) n_cand = n_greater + max(0, min(tie_base, need));
   }
   __syncthreads();
   if (threadIdx.x == 0) {

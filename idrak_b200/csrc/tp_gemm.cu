@@ -647,12 +647,11 @@ static int tp_launch(const CUtensorMap& a0, const CUtensorMap& a1, const CUtenso
                      const CUtensorMap& aux, const GemmParams& p, const TpParams& t, const CommCtx& c, int grid,
                      cudaStream_t stream) {
   auto kern = tp_gemm_kernel<B_MN>;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TpSmem::kTotal);
-    if (e != cudaSuccess) return int(e);
-    configured = true;
-  }
+  static DeviceOnce configured;
+  if (int e = configured.run([&] {
+        return int(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, TpSmem::kTotal));
+      }))
+    return e;
   kern<<<grid, kGemmThreads, TpSmem::kTotal, stream>>>(a0, a1, b, cm, aux, p, t, c);
   note_launches(1);
   return int(cudaGetLastError());
@@ -692,7 +691,7 @@ IDRAK_API int idrak_tp_ag_gemm(const void* ctx, const void* x_local, int ldx, vo
   if (rows / kBM > kTpMaxChunks || gather_half_elems < (long long)M * K) return -3;
   if (act != kActNone && act != kActGelu) return -4;
   if (act == kActGelu && (aux == nullptr || (ld_aux & 7))) return -4;
-  GemmParams p;
+  GemmParams p{};
   tp_base_params(p, M, N, K);
   p.C = C; p.ldc = ldc;
   p.bias = static_cast<const __nv_bfloat16*>(bias);
@@ -768,7 +767,7 @@ IDRAK_API int idrak_tp_gemm_rs(const void* ctx, const void* A, int lda, const vo
     return -2;
   const int rows = M / c.world;
   if (rows / kBM > kTpMaxChunks || stage_half_elems < (long long)M * N) return -3;
-  GemmParams p;
+  GemmParams p{};
   tp_base_params(p, M, N, K);
   TpParams t;
   memset(&t, 0, sizeof(t));

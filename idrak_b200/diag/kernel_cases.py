@@ -84,11 +84,26 @@ def _timed_graph(fn: Callable[[], None], warmup: int, iters: int, flush: bool, r
 
 
 def case_gemm(a) -> Tuple[Callable, float, float]:
+    """``--epi`` picks the fused epilogue: plain, bias, bias_res, bias_gelu (saves the pre-activation), gelu_grad
+    (input gradient through a saved pre-activation; the weight operand is read MN-major like a backward pass)."""
     from ..ops.gemm import gemm
     x = torch.randn(a.m, a.k, device="cuda", dtype=torch.bfloat16)
-    w = torch.randn(a.n, a.k, device="cuda", dtype=torch.bfloat16)
     out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
-    return (lambda: gemm(x, w, out=out)), 2.0 * a.m * a.n * a.k, 2.0 * (a.m * a.k + a.n * a.k + a.m * a.n)
+    flops, nbytes = 2.0 * a.m * a.n * a.k, 2.0 * (a.m * a.k + a.n * a.k + a.m * a.n)
+    epi = getattr(a, "epi", "plain")
+    if epi == "gelu_grad":
+        w = torch.randn(a.k, a.n, device="cuda", dtype=torch.bfloat16)          # [out, in] of the layer: B stored [K, N]
+        aux = torch.randn(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+        return (lambda: gemm(x, w, b_mn=True, act="gelu_grad", aux=aux, out=out)), flops, nbytes + 2.0 * a.m * a.n
+    w = torch.randn(a.n, a.k, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(a.n, device="cuda", dtype=torch.bfloat16) if epi != "plain" else None
+    if epi == "bias_res":
+        res = torch.randn(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+        return (lambda: gemm(x, w, bias=bias, residual=res, out=out)), flops, nbytes + 2.0 * a.m * a.n
+    if epi == "bias_gelu":
+        aux = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+        return (lambda: gemm(x, w, bias=bias, act="gelu", aux=aux, out=out)), flops, nbytes + 2.0 * a.m * a.n
+    return (lambda: gemm(x, w, bias=bias, out=out)), flops, nbytes
 
 
 def case_gemm_wgrad(a):
@@ -176,6 +191,30 @@ def case_qgemm(a):
     return (lambda: qgemm(x, w)), 2.0 * a.m * a.n * a.k, a.k * a.n * bits / 8 + 2.0 * a.m * (a.k + a.n)
 
 
+def _role_timers(fn: Callable[[], None]) -> dict:
+    """One launch with the dense GEMM's role timers on: mean cycles per tile, over the CTAs that ran tiles."""
+    import ctypes as C
+    from .. import _native
+    lib = _native.lib()
+    sms = lib.idrak_sm_count()
+    buf = torch.zeros(sms * 8, device="cuda", dtype=torch.int64)
+    setter = _native.bind("idrak_gemm_role_timers", None, [C.c_void_p])
+    setter(buf.data_ptr())
+    try:
+        fn()
+        torch.cuda.synchronize()
+    finally:
+        setter(None)
+    t = buf.view(sms, 8).cpu().double()
+    ran = t[:, 6] > 0
+    t = t[ran]
+    tiles = t[:, 6].clamp(min=1)
+    mean = lambda c: round(float((t[:, c] / tiles).mean()), 1)
+    return {"ctas": int(ran.sum()), "tiles_per_cta": round(float(tiles.mean()), 2),
+            "mma_loop_cycles_per_tile": mean(0), "mma_wait_accumulator": mean(1), "mma_wait_operands": mean(2),
+            "epilogue_wait_accumulator": mean(4), "epilogue_drain": mean(5)}
+
+
 CASES: Dict[str, Callable] = {
     "gemm": case_gemm, "gemm_wgrad": case_gemm_wgrad, "cublas": case_cublas, "flash_fwd": case_flash_fwd,
     "flash_bwd": case_flash_bwd, "xent": case_xent, "norm": case_norm, "adamw": case_adamw,
@@ -190,6 +229,10 @@ def main(argv=None) -> int:
                           ("seq", 1024), ("dim", 64), ("warmup", 3), ("iters", 10)):
         ap.add_argument(f"--{name}", type=int, default=default)
     ap.add_argument("--kind", default="int4", choices=["int4", "int8"])
+    ap.add_argument("--epi", default="plain", choices=["plain", "bias", "bias_res", "bias_gelu", "gelu_grad"])
+    ap.add_argument("--role-timers", action="store_true",
+                    help="gemm cases: after timing, run one more launch with the kernel's role timers on and print "
+                         "the mean cycles per tile each warp role spent waiting")
     ap.add_argument("--flush-l2", action="store_true")
     ap.add_argument("--graph", type=int, default=0, metavar="REPS",
                     help="time REPS captured copies per replay of a CUDA graph (takes the host's launch cost out)")
@@ -203,8 +246,11 @@ def main(argv=None) -> int:
           else _timed(fn, a.warmup, a.iters, a.flush_l2))
     from .. import _native
     _native.check_status()
+    roles = _role_timers(fn) if a.role_timers else None
     out = {"case": a.case, "ms": round(ms, 4), "tflops": round(flops / ms / 1e9, 1) if flops else None,
            "gbs": round(nbytes / ms / 1e6, 1), "args": {k: v for k, v in vars(a).items() if k != "case"}}
+    if roles:
+        out["roles"] = roles
     print(json.dumps(out))
     return 0
 

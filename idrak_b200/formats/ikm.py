@@ -18,6 +18,7 @@ import datetime as _dt
 import io
 import json
 import os
+import struct
 import zipfile
 from dataclasses import dataclass
 from typing import Callable, List, Optional, Tuple
@@ -49,6 +50,52 @@ def file_name(e: PackageEntry) -> str:
     }.get(e.kind, f"text/{e.name}.txt")
 
 
+TRAINABLE_MAGIC = 0x31504B49        # "IKP1": selected parameters with their positions
+
+
+def trainable_to_bytes(module: torch.nn.Module) -> bytes:
+    """The parameters that still take gradients, each with its index among ``module.parameters()``:
+    u32 magic ``IKP1``, i32 count, then per tensor i32 index, i32 rank, i32 dims, float32 values (little endian).
+    Reference: ModuleExtensions.SaveTrainable (src/Idrak/Layers/ModuleExtensions.cs:18,59-83)."""
+    chosen = [(i, p) for i, p in enumerate(module.parameters()) if p.requires_grad]
+    out = [struct.pack("<Ii", TRAINABLE_MAGIC, len(chosen))]
+    for i, p in chosen:
+        out.append(struct.pack(f"<ii{p.dim()}i", i, p.dim(), *p.shape))
+        out.append(p.detach().to(torch.float32).contiguous().cpu().numpy().astype("<f4", copy=False).tobytes())
+    return b"".join(out)
+
+
+def load_trainable_bytes(module: torch.nn.Module, data: bytes) -> int:
+    """Read what ``trainable_to_bytes`` wrote into the same positions; the index and the shape of every tensor are
+    checked against the model. Returns how many tensors were loaded."""
+    import numpy as np
+    params = list(module.parameters())
+    if len(data) < 8 or struct.unpack_from("<I", data, 0)[0] != TRAINABLE_MAGIC:
+        raise ValueError("Not a trainable-parameters file (magic IKP1 expected).")
+    count = struct.unpack_from("<i", data, 4)[0]
+    at = 8
+    with torch.no_grad():
+        for _ in range(count):
+            index, rank = struct.unpack_from("<ii", data, at)
+            at += 8
+            if index < 0 or index >= len(params):
+                raise ValueError(f"The file refers to parameter {index}, but the model has {len(params)}.")
+            if rank < 0 or rank > 8:
+                raise ValueError(f"Parameter {index}: rank {rank} is not plausible; the file is damaged.")
+            shape = struct.unpack_from(f"<{rank}i", data, at)
+            at += 4 * rank
+            p = params[index]
+            if tuple(shape) != tuple(p.shape):
+                raise ValueError(f"Parameter {index}: file has {list(shape)}, model has {list(p.shape)}.")
+            n = p.numel()
+            if at + 4 * n > len(data):
+                raise ValueError(f"Parameter {index}: the file ends inside its values.")
+            values = np.frombuffer(data, dtype="<f4", count=n, offset=at)
+            at += 4 * n
+            p.copy_(torch.from_numpy(values.copy()).reshape(p.shape).to(p.dtype))
+    return count
+
+
 class ModelPackageWriter:
     def __init__(self, path: str | os.PathLike):
         self.path = str(path)
@@ -57,8 +104,11 @@ class ModelPackageWriter:
     def _add(self, kind: str, name: str, producer: Callable[[], bytes]) -> "ModelPackageWriter":
         if kind not in KINDS:
             raise ValueError(f"unknown entry kind '{kind}'")
+        if "/" in name or "\\" in name:
+            raise ValueError("Entry names cannot contain '/' or '\\'.")
         entry = PackageEntry(kind, name)
-        if any(e == entry for e, _ in self._entries):
+        # two entries may not share a path inside the zip (a StandardScaler and a MinMaxScaler of one name would)
+        if any(file_name(e) == file_name(entry) for e, _ in self._entries):
             raise ValueError(f"The package already has a {kind} entry named '{name}'.")
         self._entries.append((entry, producer))
         return self
@@ -71,10 +121,7 @@ class ModelPackageWriter:
         return self._add("Weights", name, produce)
 
     def trainable_weights(self, module: torch.nn.Module, name: str = DEFAULT_MODEL_NAME):
-        def produce():
-            tensors = [p.detach() for p in module.parameters() if p.requires_grad]
-            return ikw.to_bytes(tensors)
-        return self._add("TrainableWeights", name, produce)
+        return self._add("TrainableWeights", name, lambda: trainable_to_bytes(module))
 
     def architecture(self, description: dict | str, name: str = DEFAULT_MODEL_NAME):
         text = description if isinstance(description, str) else json.dumps(description, indent=2)
@@ -141,13 +188,7 @@ class ModelPackageReader:
         ikw.load_module(module, io.BytesIO(self._read("Weights", name)))
 
     def load_trainable(self, module: torch.nn.Module, name: str = DEFAULT_MODEL_NAME) -> None:
-        contents = ikw.read(io.BytesIO(self._read("TrainableWeights", name)))
-        params = [p for p in module.parameters() if p.requires_grad]
-        if len(params) != len(contents.tensors):
-            raise ValueError(f"The file has {len(contents.tensors)} trainable tensors but the model has {len(params)}.")
-        with torch.no_grad():
-            for p, t in zip(params, contents.tensors):
-                p.copy_(t.reshape(p.shape))
+        load_trainable_bytes(module, self._read("TrainableWeights", name))
 
     def architecture(self, name: str = DEFAULT_MODEL_NAME) -> dict:
         return json.loads(self._read("Architecture", name))

@@ -25,7 +25,7 @@ import torch.distributed as dist
 from .. import _native
 
 # channel map of the flag area (two consecutive channels where a collective needs a second phase)
-CH_BARRIER, CH_NORM, CH_STEP_DONE, CH_ONESHOT, CH_RS, CH_AG, CH_AR, CH_BCAST, CH_BUCKET0 = 0, 4, 6, 8, 10, 12, 13, 15, 16
+CH_BARRIER, CH_NORM, CH_STEP_DONE, CH_ONESHOT, CH_RS, CH_AG, CH_AR, CH_BCAST, CH_BUCKET0 = 0, 4, 6, 8, 10, 12, 14, 16, 20
 
 _c_void_p, _c_int, _c_ll, _c_float = C.c_void_p, C.c_int, C.c_longlong, C.c_float
 _PP = C.POINTER(C.c_void_p)
@@ -221,7 +221,9 @@ class Communicator:
 
     def all_gather(self, buf: SymmetricBuffer, local_slice: torch.Tensor, algorithm: str = "peer",
                    max_blocks: int = 64):
-        """Store ``local_slice`` as slice ``rank`` of every rank's ``buf``; on return ``buf`` holds all slices."""
+        """Store ``local_slice`` as slice ``rank`` of every rank's ``buf``; on return ``buf`` holds all slices.
+        A rank's stores wait until every peer has entered its own call (in stream order after whatever still read
+        the buffer's earlier contents), so back-to-back gathers into one buffer need no barrier between them."""
         nbytes = local_slice.numel() * local_slice.element_size()
         if algorithm == "nccl":
             t = buf.tensor(local_slice.dtype, local_slice.numel() * self.world)

@@ -83,6 +83,11 @@ class _ShardedAdamW:
         self.v.copy_(state["v"])
 
 
+def bucket_channels_fit(n_buckets: int, flag_channels: int) -> bool:
+    """Whether ``n_buckets`` gradient buckets can each have their own flag channel (plus the one after it)."""
+    return CH_BUCKET0 + n_buckets + 1 <= flag_channels
+
+
 _HOOK_PROBE = None
 
 
@@ -160,6 +165,13 @@ class DataParallel:
     # ------------------------------------------------------------------ layout
     def _make_buckets(self, bucket_elems: int):
         self.buckets = self.flat.buckets(bucket_elems)          # (start, end, [param indices])
+        if self.mode == "fused":
+            # bucket b signals on flag channel CH_BUCKET0 + b (and the kernels use the channel after it for their
+            # second phase): a layout with more buckets than channels would index past the peers' flag areas
+            channels = _native.lib().idrak_comm_flag_channels()
+            while not bucket_channels_fit(len(self.buckets), channels):
+                bucket_elems *= 2
+                self.buckets = self.flat.buckets(bucket_elems)
         self._bucket_of = {}
         for b, (_, _, members) in enumerate(self.buckets):
             for i in members:

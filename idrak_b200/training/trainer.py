@@ -78,6 +78,32 @@ class TrainingHistory:
 
 
 # --------------------------------------------------------------------------- callbacks
+TRAIN_STATE_FORMAT = "idrak-train-state/2"
+
+
+def _dropout_layers(model: torch.nn.Module):
+    return [m for m in model.modules() if isinstance(m, (torch.nn.Dropout, torch.nn.Dropout1d, torch.nn.Dropout2d))
+            or hasattr(m, "draws")]
+
+
+def dropout_draws(model: torch.nn.Module) -> list:
+    """How many masks each dropout layer has drawn (layers that count them expose ``draws``; PyTorch's own dropout
+    draws from the global generator, whose state is checkpointed beside the json, and reports 0)."""
+    return [int(getattr(m, "draws", 0)) for m in _dropout_layers(model)]
+
+
+def restore_dropout_draws(model: torch.nn.Module, draws, where) -> None:
+    layers = _dropout_layers(model)
+    if len(draws) != len(layers):
+        raise ValueError(f"{where} was written for a model with {len(draws)} dropout layers; this one has "
+                         f"{len(layers)}: resume the run with its own model")
+    for m, d in zip(layers, draws):
+        if hasattr(m, "advance"):
+            m.advance(max(0, int(d) - int(getattr(m, "draws", 0))))
+        elif hasattr(m, "draws"):
+            m.draws = int(d)
+
+
 class TrainerCallback:
     def on_train_begin(self, trainer: "Trainer"): ...
     def on_batch_end(self, trainer: "Trainer", event: BatchCompleted): ...
@@ -269,11 +295,24 @@ class Trainer:
     def fit(self, train: Iterable, epochs: int, validation: Optional[Iterable] = None) -> TrainingHistory:
         history = TrainingHistory()
         start_epoch, skip_steps = 0, 0
-        if self.resume_from is not None:
-            state = self.load_checkpoint(self.resume_from)
-            start_epoch, skip_steps = state["epoch"], state["step_in_epoch"]
         best_state = None
         bad_epochs = 0
+        if self.resume_from is not None:
+            state = self.load_checkpoint(self.resume_from)
+            if "epoch" in state:
+                start_epoch, skip_steps = int(state["epoch"]), int(state.get("step_in_epoch", 0))
+            else:
+                # a checkpoint that only counts steps (the reference's layout): place it by the length of an epoch
+                per_epoch = len(train) if hasattr(train, "__len__") else 0
+                if per_epoch <= 0 and self.global_step > 0:
+                    raise ValueError("this checkpoint records steps only; resuming it needs a training source with a length")
+                start_epoch, skip_steps = (divmod(self.global_step, per_epoch) if per_epoch else (0, 0))
+            if state.get("best_loss") is not None:
+                history.best_loss = float(state["best_loss"])
+            history.best_epoch = int(state.get("best_epoch", -1))
+            bad_epochs = int(state.get("since_best", 0))
+            best_state = state.get("_best_weights")
+        self._early = (history, bad_epochs, best_state)
         for cb in self.callbacks:
             cb.on_train_begin(self)
         self.model.train()
@@ -335,6 +374,7 @@ class Trainer:
                     best_state = {k: v.detach().clone() for k, v in self.model.state_dict().items()}
             else:
                 bad_epochs += 1
+            self._early = (history, bad_epochs, best_state)
             if self.checkpoint_folder is not None and (epoch + 1) % self.checkpoint_every_epochs == 0:
                 self.save_checkpoint(self.checkpoint_folder, epoch + 1, 0)
             if self.early_stopping_patience is not None and bad_epochs >= self.early_stopping_patience:
@@ -399,9 +439,22 @@ class Trainer:
                           metadata={"format": "idrak-optimizer", "optimizer": type(self.optimizer).__name__})
             else:
                 torch.save(state, tmp / "optimizer.pt")
-        (tmp / "train-state.json").write_text(json.dumps({
-            "global_step": self.global_step, "epoch": epoch, "step_in_epoch": step_in_epoch,
-            "lr": float(getattr(self.optimizer, "lr", 0.0) or 0.0), "stop_reason": self._stop_reason}, indent=2))
+        history, since_best, best_state = getattr(self, "_early", (None, 0, None))
+        state = {"format": TRAIN_STATE_FORMAT, "step": self.global_step,
+                 "best_epoch": history.best_epoch if history is not None else -1, "since_best": int(since_best),
+                 "dropout_draws": dropout_draws(self.model),
+                 # beyond the reference's keys: where in the epoch the run stood, and how it was stopped
+                 "epoch": epoch, "step_in_epoch": step_in_epoch,
+                 "lr": float(getattr(self.optimizer, "lr", 0.0) or 0.0), "stop_reason": self._stop_reason}
+        if history is not None and math.isfinite(history.best_loss):
+            state["best_loss"] = history.best_loss
+        if best_state is not None:
+            # the weights of the best epoch so far, one flat fp32 entry per parameter / buffer, named by position
+            save_file({str(i): v.detach().float().reshape(-1).contiguous().cpu() for i, v in enumerate(best_state.values())},
+                      tmp / "best-weights.safetensors", metadata={"format": "idrak-best-weights"})
+        torch.save({"cpu": torch.get_rng_state(),
+                    "cuda": torch.cuda.get_rng_state_all() if torch.cuda.is_available() else []}, tmp / "rng-state.pt")
+        (tmp / "train-state.json").write_text(json.dumps(state, indent=2) + "\n")
         if target.exists():
             shutil.rmtree(target)
         os.replace(tmp, target)
@@ -428,5 +481,30 @@ class Trainer:
         if hasattr(self.optimizer, "sync_master_from_params"):
             self.optimizer.sync_master_from_params()
         state = json.loads((folder / "train-state.json").read_text())
-        self.global_step = int(state["global_step"])
+        fmt = state.get("format")
+        if fmt is not None and not str(fmt).startswith("idrak-train-state/"):
+            raise ValueError(f"{folder / 'train-state.json'}: format '{fmt}' is not a trainer state")
+        if "step" not in state and "global_step" not in state:
+            raise ValueError(f"{folder / 'train-state.json'} names no step")
+        self.global_step = int(state["step"] if "step" in state else state["global_step"])
+        draws = state.get("dropout_draws") or []
+        if draws:
+            restore_dropout_draws(self.model, draws, folder)
+        if (folder / "rng-state.pt").exists():
+            rng = torch.load(folder / "rng-state.pt", weights_only=True)
+            torch.set_rng_state(rng["cpu"])
+            if torch.cuda.is_available() and len(rng["cuda"]) == torch.cuda.device_count():
+                torch.cuda.set_rng_state_all(rng["cuda"])
+        if (folder / "best-weights.safetensors").exists():
+            with SafeTensorsReader.open(folder / "best-weights.safetensors") as r:
+                current = self.model.state_dict()
+                if len(r.tensors) != len(current):
+                    raise ValueError(f"{folder}: best weights hold {len(r.tensors)} tensors, the model {len(current)}")
+                best = {}
+                for i, (k, v) in enumerate(current.items()):
+                    flat = r.read(str(i))
+                    if flat.numel() != v.numel():
+                        raise ValueError(f"{folder}: best weights entry {i} has {flat.numel()} values, '{k}' has {v.numel()}")
+                    best[k] = flat.reshape(v.shape).to(v.dtype).to(v.device)
+                state["_best_weights"] = best
         return state

@@ -3,7 +3,16 @@ import sys
 
 import pytest
 
-sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+_REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, _REPO)
+
+# Fixtures written by the reference project's own tools (its tests/Idrak.Tests/data folder) are read through
+# IDRAK_REFERENCE_DATA. When the variable is unset, a checkout of the reference beside this repository is used if
+# there is one; tests that need the files skip otherwise.
+if not os.environ.get("IDRAK_REFERENCE_DATA"):
+    _beside = os.path.join(os.path.dirname(_REPO), "reference", "tests", "Idrak.Tests", "data")
+    if os.path.isdir(_beside):
+        os.environ["IDRAK_REFERENCE_DATA"] = _beside
 
 
 def pytest_configure(config):

@@ -84,3 +84,28 @@ def test_argmax_and_sampler():
                         torch.zeros(rows, device=dev), seeds, 0, history=hist,
                         repeat_penalty=torch.full((rows,), 50.0, device=dev))
     assert not torch.equal(pen, ids)
+
+
+def test_sampler_ties_do_not_crowd_out_larger_logits():
+    """All-equal logits with a few larger ones (a masked vocabulary looks like this): the larger ones must all be
+    candidates, the tied places go to the lowest ids, and the draw repeats."""
+    rows, V = 4, 4096
+    dev = "cuda"
+    logits = torch.zeros(rows, V, device=dev, dtype=torch.float32)
+    big = [4000, 4010, 4095]
+    for j, b in enumerate(big):
+        logits[:, b] = 5.0 + j
+    t = torch.ones(rows, device=dev)
+    ones, zeros = torch.ones(rows, device=dev), torch.zeros(rows, device=dev)
+    seeds = torch.arange(rows, dtype=torch.int64, device=dev)
+    greedy = D.sample_rows(logits, V, t, torch.ones(rows, dtype=torch.int32, device=dev), ones, zeros, seeds, 0)
+    assert greedy.tolist() == [4095] * rows
+    k = torch.full((rows,), 8, dtype=torch.int32, device=dev)
+    allowed = set(big) | {0, 1, 2, 3, 4}              # three larger logits, then five ties by ascending id
+    seen = set()
+    for step in range(200):
+        a = D.sample_rows(logits, V, t, k, ones, zeros, seeds, step)
+        b = D.sample_rows(logits, V, t, k, ones, zeros, seeds, step)
+        assert torch.equal(a, b)
+        seen |= set(a.tolist())
+    assert seen <= allowed and set(big) <= seen, sorted(seen)

@@ -63,3 +63,17 @@ def test_fused_dp_is_deterministic(tmp_path):
     a = _run("fused", tmp_path / "a.pt", port=29643)
     b = _run("fused", tmp_path / "b.pt", port=29644)
     assert torch.equal(a["weights"], b["weights"])
+
+
+def test_peer_memory_collectives_match_nccl_and_back_to_back_gathers_do_not_overwrite(tmp_path):
+    """Every collective of the communicator on 2 ranks against NCCL; two all-gathers (and two broadcasts) in a row
+    into one symmetric buffer with one rank slow to read the first result: the second must not land early."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    out = tmp_path / "comm.pt"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29644", os.path.join(HERE, "comm_worker.py"), str(out)]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    for rank, ok in enumerate(torch.load(out)):
+        bad = [k for k, v in ok.items() if not v]
+        assert not bad, f"rank {rank}: {bad}"

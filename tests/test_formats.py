@@ -17,8 +17,9 @@ from idrak_b200.formats.safetensors import SafeTensorsReader, load_file, save_fi
 from idrak_b200.models import DecoderSpec, build_decoder
 from idrak_b200.models.checkpoint import (from_hf_tensors, idrak_tensors, load_idrak_tensors, to_hf_tensors)
 
-REF = "/root/reference/tests/Idrak.Tests/data"
-needs_ref = pytest.mark.skipif(not os.path.isdir(REF), reason="reference fixtures not mounted")
+# folder of the reference project's test data (its tests/Idrak.Tests/data); tests that read it skip when it is not given
+REF = os.environ.get("IDRAK_REFERENCE_DATA", "")
+needs_ref = pytest.mark.skipif(not os.path.isdir(REF), reason="IDRAK_REFERENCE_DATA does not name the fixture folder")
 
 
 def test_safetensors_round_trip_all_float_types(tmp_path):
@@ -150,6 +151,48 @@ def test_ikm_package_round_trip(tmp_path):
         m2 = r.build_model()
     ids = torch.randint(0, 256, (1, 16))
     assert torch.equal(m(ids), m2(ids))
+
+
+def test_ikm_trainable_entry_is_the_indexed_parameter_file(tmp_path):
+    """``trainable/NAME.nsp``: u32 'IKP1', i32 count, then per tensor its index among the parameters, rank, dims and
+    float32 values - checked on load against the model's index range and shapes."""
+    import struct
+    import zipfile
+    lin = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.Linear(3, 2))
+    for q in lin[0].parameters():
+        q.requires_grad_(False)
+    path = tmp_path / "t.ikm"
+    ikm.create(path).trainable_weights(lin, "head").save()
+    with zipfile.ZipFile(path) as z:
+        raw = z.read("trainable/head.nsp")
+    magic, count = struct.unpack_from("<Ii", raw, 0)
+    assert magic == 0x31504B49 and count == 2
+    index, rank, d0, d1 = struct.unpack_from("<iiii", raw, 8)
+    assert (index, rank, d0, d1) == (2, 2, 2, 3)
+    first = struct.unpack_from("<6f", raw, 24)
+    assert list(first) == [float(x) for x in lin[1].weight.detach().reshape(-1)]
+    other = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.Linear(3, 2))
+    with ikm.open_package(path) as r:
+        r.load_trainable(other, "head")                      # requires_grad of the target plays no part
+    assert torch.equal(other[1].weight, lin[1].weight) and torch.equal(other[1].bias, lin[1].bias)
+    assert not torch.equal(other[0].weight, lin[0].weight)
+    wrong = torch.nn.Sequential(torch.nn.Linear(4, 3), torch.nn.Linear(3, 5))
+    with ikm.open_package(path) as r, pytest.raises(ValueError, match="Parameter 2: file has"):
+        r.load_trainable(wrong, "head")
+    small = torch.nn.Sequential(torch.nn.Linear(4, 3))
+    with ikm.open_package(path) as r, pytest.raises(ValueError, match="refers to parameter 2"):
+        r.load_trainable(small, "head")
+    with pytest.raises(ValueError, match="magic IKP1"):
+        ikm.load_trainable_bytes(lin, b"IKW3" + raw[4:])
+
+
+def test_ikm_entry_names_and_paths_are_unique(tmp_path):
+    w = ikm.create(tmp_path / "p.ikm").scaler("StandardScaler", "0 1", "x")
+    with pytest.raises(ValueError, match="already has"):
+        w.scaler("MinMaxScaler", "0 1", "x")                 # both would be scalers/x.txt
+    for bad in ("a/b", "a\\b"):
+        with pytest.raises(ValueError, match="cannot contain"):
+            w.text("t", bad)
 
 
 def test_token_file_record_and_windows(tmp_path):

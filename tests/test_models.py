@@ -12,8 +12,8 @@ from idrak_b200.models import DecoderSpec, build_decoder
 from idrak_b200.models.families import architectures, spec_from_hf_config
 from idrak_b200.models.pretrained import load_pretrained, save_huggingface, save_idrak
 
-REF = "/root/reference/tests/Idrak.Tests/data/gguf"
-needs_ref = pytest.mark.skipif(not os.path.isdir(REF), reason="reference fixtures not mounted")
+REF = os.path.join(os.environ.get("IDRAK_REFERENCE_DATA", ""), "gguf")
+needs_ref = pytest.mark.skipif(not os.path.isdir(REF), reason="IDRAK_REFERENCE_DATA does not name the fixture folder")
 
 
 @needs_ref

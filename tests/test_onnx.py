@@ -9,7 +9,7 @@ from idrak_b200 import onnx as ox
 from idrak_b200.nn import Network
 from idrak_b200.onnx import proto as P
 
-REF = "/root/reference/tests/Idrak.Tests/data"
+REF = os.environ.get("IDRAK_REFERENCE_DATA", "")
 
 
 def test_protobuf_round_trip_of_every_message_kind():

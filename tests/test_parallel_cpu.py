@@ -117,3 +117,15 @@ def test_gradient_compression_kinds(kind, ratio, error, tmp_path):
     from idrak_b200.parallel.compression import Compressor
     with pytest.raises(KeyError, match="not registered"):
         Compressor("zip")
+
+
+def test_fused_dp_bucket_count_is_bounded_by_the_flag_channels():
+    """Bucket b signals on flag channel CH_BUCKET0 + b and the one after it; a layout with more buckets than the flag
+    area has rows must be refused (the layout code then doubles the bucket size until it fits)."""
+    from idrak_b200.parallel.comm import CH_BUCKET0
+    from idrak_b200.parallel.dp import bucket_channels_fit
+    channels = 512
+    assert bucket_channels_fit(1, channels)
+    assert bucket_channels_fit(channels - CH_BUCKET0 - 1, channels)
+    assert not bucket_channels_fit(channels - CH_BUCKET0, channels)
+    assert not bucket_channels_fit(10_000, channels)

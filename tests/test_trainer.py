@@ -110,7 +110,11 @@ def test_stop_file_checkpoint_and_resume_is_bit_exact(tmp_path):
     assert hist.stopped_by_request and a.global_step == 4
     state = json.loads((ck / "checkpoint-4" / "train-state.json").read_text())
     assert state["epoch"] == 0 and state["step_in_epoch"] == 4
-    assert {p.name for p in (ck / "checkpoint-4").iterdir()} == {"model.ikw", "optimizer.safetensors", "train-state.json"}
+    # the reference's keys (Trainer.cs WriteState): format, step, best_epoch, since_best, dropout_draws
+    assert state["format"] == "idrak-train-state/2" and state["step"] == 4
+    assert {"best_epoch", "since_best", "dropout_draws"} <= set(state)
+    assert {p.name for p in (ck / "checkpoint-4").iterdir()} == {"model.ikw", "optimizer.safetensors", "train-state.json",
+                                                                 "rng-state.pt"}
     os.remove(ck / "stop")
 
     b = _lm_trainer(resume=str(ck))
@@ -144,3 +148,49 @@ def test_training_run_is_the_trainer_as_one_object():
     variant = dataclasses.replace(run, model=_mlp(1), epochs=2, max_gradient_norm=0.5)
     assert variant.epochs == 2 and run.epochs == 30
     assert len(variant.fit().epochs) == 2 and variant.trainer.max_gradient_norm == 0.5
+
+
+def test_resume_from_a_reference_style_checkpoint_folder(tmp_path):
+    """A folder laid out the way the reference's trainer writes it: train-state.json with format / step / best_loss /
+    best_epoch / since_best / dropout_draws only, model.ikw, optimizer.safetensors, best-weights.safetensors with one
+    flat entry per tensor named by position. The step count places the resume inside the epoch."""
+    from idrak_b200.formats import ikw
+    from idrak_b200.formats.safetensors import save_file
+    src = _lm_trainer()
+    src.fit(_lm_batches(0), epochs=1)
+    ck = tmp_path / "checkpoint-6"
+    ck.mkdir()
+    ikw.save_module(src.model, ck / "model.ikw")
+    save_file({k: v.float().contiguous() for k, v in src.optimizer.state_dict().items()}, ck / "optimizer.safetensors",
+              metadata={"format": "idrak-optimizer", "optimizer": "AdamW"})
+    best = {str(i): torch.full((v.numel(),), float(i)) for i, v in enumerate(src.model.state_dict().values())}
+    save_file(best, ck / "best-weights.safetensors", metadata={"format": "idrak-best-weights"})
+    (ck / "train-state.json").write_text(json.dumps(
+        {"format": "idrak-train-state/2", "step": 6, "best_epoch": 0, "since_best": 1, "dropout_draws": [],
+         "best_loss": 1.25}) + "\n")
+    t = _lm_trainer(resume=str(ck))
+    state = t.load_checkpoint(ck)
+    assert t.global_step == 6 and state["best_loss"] == 1.25 and state["since_best"] == 1
+    first = next(iter(state["_best_weights"].values()))
+    assert float(first.float().mean()) == 0.0 and len(state["_best_weights"]) == len(best)
+    hist = t.fit(_lm_batches(0), epochs=2)          # 6 steps per epoch: resumes at the start of the second epoch
+    assert t.global_step == 12 and len(hist.epochs) == 1 and hist.epochs[0].epoch == 1
+
+    bad = tmp_path / "checkpoint-7"
+    bad.mkdir()
+    (bad / "train-state.json").write_text(json.dumps({"format": "idrak-train-state/2", "best_epoch": 0}))
+    ikw.save_module(src.model, bad / "model.ikw")
+    with pytest.raises(ValueError, match="names no step"):
+        _lm_trainer().load_checkpoint(bad)
+
+
+def test_early_stopping_state_survives_a_checkpoint(tmp_path):
+    t = _lm_trainer(folder=str(tmp_path))
+    t.early_stopping_patience, t.restore_best_weights = 50, True
+    t.fit(_lm_batches(2, n=2), epochs=3)
+    newest = sorted(tmp_path.glob("checkpoint-*"), key=lambda p: int(p.name.split("-")[1]))[-1]
+    state = json.loads((newest / "train-state.json").read_text())
+    assert "best_loss" in state and state["best_epoch"] >= 0 and (newest / "best-weights.safetensors").exists()
+    r = _lm_trainer(resume=str(newest))
+    loaded = r.load_checkpoint(newest)
+    assert loaded["best_loss"] == state["best_loss"] and "_best_weights" in loaded
