@@ -4,8 +4,9 @@ library kernels only (cuBLAS matmuls, the library's fused attention, fused AdamW
 hand-written kernels" number measured on the same GPU, with the same model, batch, optimizer settings and timing
 as the main arm.
 
-Numerics follow the common recipe: fp32 master parameters, bf16 autocast for the forward and backward passes,
-gradient clipping at 1.0, AdamW (0.9, 0.95), weight decay 0.1 on matrices only.
+Numerics match the main arm: bf16 parameters and activations, fp32 master weights and moments in the optimizer,
+gradient clipping at 1.0, AdamW (0.9, 0.95), weight decay 0.1 on matrices only; on one GPU the step is replayed from
+a CUDA graph like the main arm's.
 """
 from __future__ import annotations
 
@@ -61,29 +62,70 @@ class GPT2(nn.Module):
 
 
 class TorchStep:
-    """forward + backward + clip + AdamW, under DDP when there is more than one rank."""
+    """forward + backward + clip + AdamW the way a tuned PyTorch script does it: bf16 parameters and activations,
+    fp32 master weights and moments stepped by the fused (capturable) AdamW, and - on one GPU - the whole step
+    captured in a CUDA graph so the host's launch cost is off the clock. Under more than one rank the model runs
+    in DistributedDataParallel (NCCL all-reduce overlapped with backward) without the graph."""
 
-    def __init__(self, layers, dim, heads, vocab, seq, device, world):
+    def __init__(self, layers, dim, heads, vocab, seq, device, world, use_graph: bool = True):
         torch.manual_seed(1234)
-        self.model = GPT2(layers, dim, heads, vocab, seq).to(device)
-        decay = [p for p in self.model.parameters() if p.dim() >= 2]
-        plain = [p for p in self.model.parameters() if p.dim() < 2]
+        self.device = device
+        self.model = GPT2(layers, dim, heads, vocab, seq).to(device).to(torch.bfloat16)
+        self.params = [p for p in self.model.parameters()]
+        self.master = [p.detach().float().clone() for p in self.params]
+        for m in self.master:
+            m.grad = torch.zeros_like(m)
+        decay = [m for m, p in zip(self.master, self.params) if p.dim() >= 2]
+        plain = [m for m, p in zip(self.master, self.params) if p.dim() < 2]
         self.opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": plain, "weight_decay": 0.0}],
-                                     lr=6e-4, betas=(0.9, 0.95), fused=True)
+                                     lr=6e-4, betas=(0.9, 0.95), fused=True, capturable=True)
         self.net = self.model
         if world > 1:
             from torch.nn.parallel import DistributedDataParallel
             self.net = DistributedDataParallel(self.model, device_ids=[device.index], gradient_as_bucket_view=True)
-        self.device = device
+        self.graph = None
+        self.use_graph = use_graph and world == 1
+        self.static_ids = self.static_tgt = self.static_loss = None
+
+    def _body(self, ids, targets):
+        loss = self.net(ids.long(), targets.long())
+        loss.backward()
+        with torch.no_grad():
+            torch._foreach_copy_([m.grad for m in self.master], [p.grad for p in self.params])
+            torch.nn.utils.clip_grad_norm_(self.master, 1.0, foreach=True)
+            self.opt.step()
+            torch._foreach_copy_(self.params, self.master)
+            torch._foreach_zero_([p.grad for p in self.params])
+        return loss.detach()
+
+    def _capture(self, ids, targets):
+        self.static_ids, self.static_tgt = ids.clone(), targets.clone()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(3):                       # warm-up outside the graph: allocations, optimizer state
+                self._body(self.static_ids, self.static_tgt)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            self.static_loss = self._body(self.static_ids, self.static_tgt)
+        self.graph = g
 
     def __call__(self, ids, targets):
-        with torch.autocast("cuda", dtype=torch.bfloat16):
-            loss = self.net(ids.long(), targets.long())
-        loss.backward()
-        torch.nn.utils.clip_grad_norm_(self.model.parameters(), 1.0)
-        self.opt.step()
-        self.opt.zero_grad(set_to_none=True)
-        return loss.detach()
+        if not self.use_graph:
+            return self._body(ids, targets)
+        if self.graph is None:
+            try:
+                self._capture(ids, targets)
+            except Exception:                        # a PyTorch build that cannot capture this step: run it eagerly
+                self.use_graph = False
+                torch.cuda.synchronize()
+                return self._body(ids, targets)
+        self.static_ids.copy_(ids, non_blocking=True)
+        self.static_tgt.copy_(targets, non_blocking=True)
+        self.graph.replay()
+        return self.static_loss
 
     def step_from_host(self, host_ids, host_targets):
         ids = host_ids.to(self.device, non_blocking=True)

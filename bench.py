@@ -43,7 +43,15 @@ def parse():
     ap.add_argument("--graph", type=int, default=int(os.environ.get("IDRAK_BENCH_GRAPH", "1")))
     ap.add_argument("--dp", default=os.environ.get("IDRAK_BENCH_DP", "fused"), choices=["fused", "nccl"])
     ap.add_argument("--no-e2e", action="store_true")
-    return ap.parse_args()
+    ap.add_argument("--config", default="gpt2-dp", choices=["gpt2-dp"] + sorted(OTHER_CONFIGS),
+                    help="gpt2-dp is the headline step; the others run the benchmark module of that BASELINE config "
+                         "(arguments after -- go to it)")
+    ap.add_argument("--torch-arm", default="auto", choices=["auto", "on", "off"],
+                    help="also time baseline/torch_gpt2.py in the same process and report vs_torch_arm "
+                         "(auto: on one GPU only)")
+    args, rest = ap.parse_known_args()
+    args.rest = [r for r in rest if r != "--"]
+    return args
 
 
 class ClockSampler:
@@ -93,16 +101,44 @@ class ClockSampler:
 
 
 def reference_arm(args):
-    print(json.dumps({"impl": "reference", "unavailable":
-                      "the reference is a C#/.NET 10 solution; no dotnet SDK exists on this image and "
-                      "`pip install /root/reference` finds neither setup.py nor pyproject.toml"}))
+    """The reference is a C# / .NET 10 solution without a Python package: it can only run where a .NET SDK is
+    installed. Look for one, and for an installed copy under baseline/_ref, and say what was found."""
+    import shutil
+    here = os.path.dirname(os.path.abspath(__file__))
+    dotnet = shutil.which("dotnet") or shutil.which("mono")
+    installed = os.path.isdir(os.path.join(here, "baseline", "_ref")) and bool(os.listdir(os.path.join(here, "baseline", "_ref")))
+    if dotnet is None:
+        why = ("the reference is a C#/.NET 10 solution and no dotnet (or mono) executable is on PATH; "
+               + ("baseline/_ref holds no installed copy either" if not installed else "baseline/_ref cannot run without it")
+               + "; pip finds neither setup.py nor pyproject.toml in it")
+    else:
+        why = (f"a .NET host was found at {dotnet}, but the reference's bench program (benches/Idrak.Benches) has no "
+               "GPT-2-small data-parallel case and its solution is not restored offline here: nothing was run")
+    print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
+
+
+OTHER_CONFIGS = {
+    # BASELINE.json configs 3-5 behind the same entry point: each module prints its own JSON line(s)
+    "tp8-train": ("idrak_b200.diag.tp_train_bench", ["--mode", "fused"]),
+    "lora-int4": ("idrak_b200.diag.lora_bench", ["--base", "int4"]),
+    "serve-tp8": ("idrak_b200.diag.serve_bench", ["--tp", "8"]),
+}
+
+
+def other_config(name: str, extra) -> int:
+    import importlib
+    module, argv = OTHER_CONFIGS[name]
+    mod = importlib.import_module(module)
+    return int(mod.main(argv + list(extra)) or 0)
 
 
 def main():
     args = parse()
     if args.impl == "reference":
         return reference_arm(args)
+    if args.config != "gpt2-dp":
+        return other_config(args.config, args.rest)
 
     import torch
     import torch.distributed as dist
@@ -200,6 +236,28 @@ def main():
         barrier()
         e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
 
+    # ---------------------------------------------------------------- the PyTorch arm, same process and GPU
+    torch_arm = None
+    want_arm = (args.torch_arm == "on") or (args.torch_arm == "auto" and world == 1)
+    if want_arm and not is_torch:
+        try:
+            from baseline.torch_gpt2 import TorchStep
+            del step
+            torch.cuda.empty_cache()
+            tstep = TorchStep(args.layers, args.dim, args.heads, args.vocab, args.seq, dev, world)
+            for i in range(max(args.warmup, 3)):
+                tstep(dev_ids[i % n_batches], dev_tgt[i % n_batches])
+            barrier()
+            t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0.record()
+            for i in range(args.steps):
+                tstep(dev_ids[i % n_batches], dev_tgt[i % n_batches])
+            t1.record()
+            barrier()
+            torch_arm = {"ms_per_step": t0.elapsed_time(t1) / args.steps, "cuda_graph": bool(tstep.graph is not None)}
+        except Exception as e:       # the comparison must never cost the main number
+            torch_arm = {"error": f"{type(e).__name__}: {e}"[:200]}
+
     t = torch.tensor([ms, e2e_ms or 0.0], device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -230,6 +288,13 @@ def main():
             "gpu_launches_note": ("kernels of this library launched in the timed region: counted by the library "
                                   "at launch; for graph replays, replays x kernels recorded in the graph"),
         }
+        if torch_arm is not None:
+            if "ms_per_step" in torch_arm:
+                torch_arm["tokens_per_s"] = B * S * world / (torch_arm["ms_per_step"] / 1e3)
+                out["vs_torch_arm"] = value / torch_arm["tokens_per_s"]
+            torch_arm["what"] = ("baseline/torch_gpt2.py: the same step on library kernels only (cuBLAS, fused "
+                                 "attention, fused AdamW), bf16 parameters + fp32 master, CUDA graph on one GPU")
+            out["torch_arm"] = torch_arm
         if e2e_ms:
             out["e2e"] = {"value": tokens / (e2e_ms / 1e3), "unit": "tokens/s", "ms_per_step": e2e_ms / args.steps,
                           "h2d_bytes_per_step": int(2 * B * S * 4), "d2h_bytes_per_step": 4}

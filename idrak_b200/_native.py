@@ -46,6 +46,8 @@ _SIGNATURES = {
     "idrak_norm_fwd": (c_int, [c_void_p] * 8 + [c_int, c_int, c_float, c_int, c_void_p]),
     "idrak_norm_bwd_blocks": (c_int, [c_int]),
     "idrak_norm_bwd": (c_int, [c_void_p] * 11 + [c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "idrak_norm_bwd_fused": (c_int, [c_void_p] * 11 + [c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "idrak_norm_bwd_sums_dx": (c_int, [c_int, c_int]),
     "idrak_colsum_blocks": (c_int, [c_int]),
     "idrak_colsum": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "idrak_gelu_fwd": (c_int, [c_void_p, c_void_p, c_ll, c_void_p]),
@@ -72,6 +74,10 @@ _SIGNATURES = {
     "idrak_opt_sgd": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_void_p]),
     "idrak_flash_fwd": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 7 + [c_float, c_int, c_void_p]),
     "idrak_flash_bwd": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 9 + [c_float, c_int, c_void_p]),
+    "idrak_flash_fwd_ex": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 7 + [c_float, c_int, c_int, c_void_p, c_float,
+                                                                              c_void_p]),
+    "idrak_flash_bwd_ex": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 9 + [c_float, c_int, c_int, c_void_p,
+                                                                               c_float, c_void_p]),
 }
 
 

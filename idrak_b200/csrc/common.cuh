@@ -212,6 +212,19 @@ __device__ __forceinline__ void tc_mma_f16_ss(uint32_t d_tmem, uint64_t a_desc, 
       : "memory");
 }
 
+// The same for 8-bit floating-point operands (kind::f8f6f4; the operand formats come from the instruction descriptor).
+__device__ __forceinline__ void tc_mma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n" ::"r"(d_tmem),
+      "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // D[tmem] (+)= A[tmem] * B[smem]
 __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
                                               uint32_t accumulate) {
@@ -230,6 +243,11 @@ __device__ __forceinline__ void tc_mma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, 
 __host__ __device__ constexpr uint32_t make_idesc_f16(int M, int N, int a_mn, int b_mn, int fmt = 1) {
   return (1u << 4) | (uint32_t(fmt) << 7) | (uint32_t(fmt) << 10) | (uint32_t(a_mn) << 15) |
          (uint32_t(b_mn) << 16) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
+}
+
+// Instruction descriptor for kind::f8f6f4 with both operands e4m3 (format code 0), K-major, fp32 accumulator.
+__host__ __device__ constexpr uint32_t make_idesc_e4m3(int M, int N) {
+  return (1u << 4) | (uint32_t(N >> 3) << 17) | (uint32_t(M >> 4) << 24);
 }
 
 // Shared-memory matrix descriptor, 128-byte swizzle, sm_100 version field = 1.
@@ -330,6 +348,16 @@ __device__ __forceinline__ float gelu_tanh_grad(float x) {
   const float du = k0 * fmaf(3.0f * k1, x2, 1.0f);
   const float hx = 0.5f * x;
   return fmaf(hx * du, fmaf(-t, t, 1.0f), fmaf(0.5f, t, 0.5f));
+}
+// GELU and its derivative from one tanh: g = gelu(x), d = gelu'(x).
+__device__ __forceinline__ void gelu_tanh_both(float x, float& g, float& d) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  const float x2 = x * x;
+  const float t = tanh_fast(k0 * x * fmaf(k1, x2, 1.0f));
+  const float du = k0 * fmaf(3.0f * k1, x2, 1.0f);
+  const float hx = 0.5f * x;
+  g = fmaf(hx, t, hx);
+  d = fmaf(hx * du, fmaf(-t, t, 1.0f), fmaf(0.5f, t, 0.5f));
 }
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

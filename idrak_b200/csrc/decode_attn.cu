@@ -28,8 +28,10 @@ constexpr int kDecMaxGroup = 16;   // query heads per KV head
 struct DecodeParams {
   const __nv_bfloat16* q;        // [seqs, H, D], sequences q_stride elements apart
   long long q_stride;
-  const __nv_bfloat16* k_cache;
+  const __nv_bfloat16* k_cache;  // bf16 cache; with an int8 cache these point at int8 codes [blocks, block_size, Hkv, D]
   const __nv_bfloat16* v_cache;
+  const float* k_scale;          // int8 cache: one scale per (slot, kv head), [blocks * block_size, Hkv]
+  const float* v_scale;
   const int* block_table;        // [seqs, max_blocks]
   const int* seq_lens;           // [seqs]
   __nv_bfloat16* out;            // [seqs, H, D]
@@ -66,7 +68,26 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src,
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
-template <int D>
+// 16 int8 codes times a scale -> 16 bf16 values (two 16-byte words)
+__device__ __forceinline__ void dequant16(const uint4& raw, float scale, uint4& lo, uint4& hi) {
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+  uint32_t o[8];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float a = float(int8_t(w[i] & 0xff)) * scale, b = float(int8_t((w[i] >> 8) & 0xff)) * scale;
+    const float c = float(int8_t((w[i] >> 16) & 0xff)) * scale, d = float(int8_t(w[i] >> 24)) * scale;
+    o[2 * i] = pack_bf16x2(a, b);
+    o[2 * i + 1] = pack_bf16x2(c, d);
+  }
+  lo = make_uint4(o[0], o[1], o[2], o[3]);
+  hi = make_uint4(o[4], o[5], o[6], o[7]);
+}
+
+// KV8 = 1: the cache holds int8 codes with one scale per (slot, kv head) (norm_rope_kv's int8 mode). A tile's codes
+// are staged into the upper half of each shared-memory row and expanded to bf16 in place - lane r owns row r and
+// walks it front to back, and the bf16 written for chunk c never reaches the codes of a chunk not yet read - so the
+// tensor-core part below is unchanged and the cache costs half the bytes.
+template <int D, int KV8>
 __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const DecodeParams p) {
   constexpr int kRow = D * 2 + 16;                       // padded shared-memory row (bytes): conflict-free ldmatrix
   constexpr int kChunks = D / 8;                         // 16-byte chunks per key row
@@ -114,21 +135,67 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
   for (int t = t0 + warp; t < t1; t += kDecWarps) {
     const int key0 = t * kDecTile;
     // ---- stage 32 keys x D of K and V with asynchronous 16-byte copies (all in flight at once)
+    if (!KV8) {
 #pragma unroll 4
-    for (int i = lane; i < kDecTile * kChunks; i += 32) {
-      const int r = i / kChunks, c = i - r * kChunks;
-      const int pos = key0 + r;
-      const bool live = pos < len;
-      size_t off = 0;
-      if (live) {
-        const int blk = table[pos / p.block_size];
-        off = (size_t(blk) * p.block_size + pos % p.block_size) * tok_stride + size_t(kvh) * D + c * 8;
+      for (int i = lane; i < kDecTile * kChunks; i += 32) {
+        const int r = i / kChunks, c = i - r * kChunks;
+        const int pos = key0 + r;
+        const bool live = pos < len;
+        size_t off = 0;
+        if (live) {
+          const int blk = table[pos / p.block_size];
+          off = (size_t(blk) * p.block_size + pos % p.block_size) * tok_stride + size_t(kvh) * D + c * 8;
+        }
+        cp_async16(sk + r * kRow + c * 16, p.k_cache + off, live ? 16 : 0);
+        cp_async16(sv + r * kRow + c * 16, p.v_cache + off, live ? 16 : 0);
       }
-      cp_async16(sk + r * kRow + c * 16, p.k_cache + off, live ? 16 : 0);
-      cp_async16(sv + r * kRow + c * 16, p.v_cache + off, live ? 16 : 0);
+      cp_async_wait_all();
+      __syncwarp();
+    } else {
+      constexpr int kByteChunks = D / 16;                  // 16-byte chunks of int8 codes per key row
+      const int8_t* kc = reinterpret_cast<const int8_t*>(p.k_cache);
+      const int8_t* vc = reinterpret_cast<const int8_t*>(p.v_cache);
+#pragma unroll 4
+      for (int i = lane; i < kDecTile * kByteChunks; i += 32) {
+        const int r = i / kByteChunks, c = i - r * kByteChunks;
+        const int pos = key0 + r;
+        const bool live = pos < len;
+        size_t off = 0;
+        if (live) {
+          const int blk = table[pos / p.block_size];
+          off = (size_t(blk) * p.block_size + pos % p.block_size) * tok_stride + size_t(kvh) * D + c * 16;
+        }
+        cp_async16(sk + r * kRow + D + c * 16, kc + off, live ? 16 : 0);
+        cp_async16(sv + r * kRow + D + c * 16, vc + off, live ? 16 : 0);
+      }
+      // this lane's row: its slot's scales (0 for a key past the end: the codes are zeros there anyway)
+      float ks = 0.f, vs = 0.f;
+      {
+        const int pos = key0 + lane;
+        if (pos < len) {
+          const size_t slot = size_t(table[pos / p.block_size]) * p.block_size + pos % p.block_size;
+          ks = p.k_scale[slot * p.Hkv + kvh];
+          vs = p.v_scale[slot * p.Hkv + kvh];
+        }
+      }
+      cp_async_wait_all();
+      __syncwarp();
+      uint8_t* rk = sk + lane * kRow;
+      uint8_t* rv = sv + lane * kRow;
+#pragma unroll
+      for (int c = 0; c < kByteChunks; ++c) {
+        const uint4 ck = *reinterpret_cast<const uint4*>(rk + D + c * 16);
+        const uint4 cv = *reinterpret_cast<const uint4*>(rv + D + c * 16);
+        uint4 lo, hi;
+        dequant16(ck, ks, lo, hi);
+        *reinterpret_cast<uint4*>(rk + c * 32) = lo;
+        *reinterpret_cast<uint4*>(rk + c * 32 + 16) = hi;
+        dequant16(cv, vs, lo, hi);
+        *reinterpret_cast<uint4*>(rv + c * 32) = lo;
+        *reinterpret_cast<uint4*>(rv + c * 32 + 16) = hi;
+      }
+      __syncwarp();
     }
-    cp_async_wait_all();
-    __syncwarp();
     // ---- S[16 x 32] = Q · K^T: 4 n-tiles of 8 keys
     float s[4][4];
 #pragma unroll
@@ -292,10 +359,14 @@ IDRAK_API long long idrak_decode_partial_floats(int seqs, int H, int D, int spli
   return splits > 1 ? (long long)seqs * H * splits * (D + 2) : 0;
 }
 
-IDRAK_API int idrak_paged_decode(const void* q, long long q_stride, const void* k_cache, const void* v_cache, const int* block_table,
-                                 const int* seq_lens, void* out, float* partial, int seqs, int H, int Hkv, int D,
-                                 int block_size, int max_blocks, int splits, float scale, int window, void* stream_) {
+// The same over an int8 cache when k_scale / v_scale are given (one fp32 scale per (slot, kv head)).
+IDRAK_API int idrak_paged_decode_kv(const void* q, long long q_stride, const void* k_cache, const void* v_cache,
+                                    const float* k_scale, const float* v_scale, const int* block_table,
+                                    const int* seq_lens, void* out, float* partial, int seqs, int H, int Hkv, int D,
+                                    int block_size, int max_blocks, int splits, float scale, int window, void* stream_) {
   if (D != 64 && D != 128) return -2;
+  const bool kv8 = k_scale != nullptr;
+  if (kv8 && !v_scale) return -6;
   if (H % Hkv || H / Hkv > kDecMaxGroup) return -3;
   if (splits > 1 && !partial) return -4;
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
@@ -305,6 +376,8 @@ IDRAK_API int idrak_paged_decode(const void* q, long long q_stride, const void* 
   if ((p.q_stride % 8) || (reinterpret_cast<uintptr_t>(q) & 15)) return -5;
   p.k_cache = static_cast<const __nv_bfloat16*>(k_cache);
   p.v_cache = static_cast<const __nv_bfloat16*>(v_cache);
+  p.k_scale = k_scale;
+  p.v_scale = v_scale;
   p.block_table = block_table;
   p.seq_lens = seq_lens;
   p.out = static_cast<__nv_bfloat16*>(out);
@@ -316,15 +389,27 @@ IDRAK_API int idrak_paged_decode(const void* q, long long q_stride, const void* 
   dim3 grid(seqs, Hkv, p.splits);
   static DeviceOnce configured;
   if (int e = configured.run([&] {
-        cudaError_t e1 = cudaFuncSetAttribute(paged_decode_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        cudaError_t e1 = cudaFuncSetAttribute(paged_decode_kernel<64, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               int(decode_smem<64>()));
-        if (e1 != cudaSuccess) return int(e1);
-        return int(cudaFuncSetAttribute(paged_decode_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        int(decode_smem<128>())));
+        if (e1 == cudaSuccess)
+          e1 = cudaFuncSetAttribute(paged_decode_kernel<64, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    int(decode_smem<64>()));
+        if (e1 == cudaSuccess)
+          e1 = cudaFuncSetAttribute(paged_decode_kernel<128, 0>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    int(decode_smem<128>()));
+        if (e1 == cudaSuccess)
+          e1 = cudaFuncSetAttribute(paged_decode_kernel<128, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    int(decode_smem<128>()));
+        return int(e1);
       }))
     return e;
-  if (D == 64) paged_decode_kernel<64><<<grid, kDecWarps * 32, decode_smem<64>(), s>>>(p);
-  else paged_decode_kernel<128><<<grid, kDecWarps * 32, decode_smem<128>(), s>>>(p);
+  if (D == 64) {
+    if (kv8) paged_decode_kernel<64, 1><<<grid, kDecWarps * 32, decode_smem<64>(), s>>>(p);
+    else paged_decode_kernel<64, 0><<<grid, kDecWarps * 32, decode_smem<64>(), s>>>(p);
+  } else {
+    if (kv8) paged_decode_kernel<128, 1><<<grid, kDecWarps * 32, decode_smem<128>(), s>>>(p);
+    else paged_decode_kernel<128, 0><<<grid, kDecWarps * 32, decode_smem<128>(), s>>>(p);
+  }
   note_launches(1);
   int rc = int(cudaGetLastError());
   if (rc) return rc;
@@ -334,6 +419,13 @@ IDRAK_API int idrak_paged_decode(const void* q, long long q_stride, const void* 
     rc = int(cudaGetLastError());
   }
   return rc;
+}
+
+IDRAK_API int idrak_paged_decode(const void* q, long long q_stride, const void* k_cache, const void* v_cache, const int* block_table,
+                                 const int* seq_lens, void* out, float* partial, int seqs, int H, int Hkv, int D,
+                                 int block_size, int max_blocks, int splits, float scale, int window, void* stream_) {
+  return idrak_paged_decode_kv(q, q_stride, k_cache, v_cache, nullptr, nullptr, block_table, seq_lens, out, partial, seqs,
+                               H, Hkv, D, block_size, max_blocks, splits, scale, window, stream_);
 }
 
 IDRAK_API int idrak_kv_write_paged(const void* k_src, const void* v_src, long long src_stride, const int* slots,

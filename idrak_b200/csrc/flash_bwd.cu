@@ -94,7 +94,7 @@ struct BwdQSmem {
   static constexpr int kTotal = kBar + 256 + 1024;
 };
 
-template <int D>
+template <int D, bool MODES>
 __global__ void __launch_bounds__(192, 1)
 flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -120,9 +120,13 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const int kv_head = head / (p.H / p.Hkv);
   const int q0 = qb * 128;
   const int off = p.Skv - p.Sq;
-  int nkv = (p.Skv + 127) / 128;
-  if (p.causal) nkv = min(nkv, (q0 + 127 + off) / 128 + 1);
-  if (nkv < 0) nkv = 0;
+  int nkv_end = (p.Skv + 127) / 128;
+  if (p.causal) nkv_end = min(nkv_end, (q0 + 127 + off) / 128 + 1);
+  if (nkv_end < 0) nkv_end = 0;
+  // key blocks wholly below what the tile's first row may see are skipped (window / packed-sequence bounds)
+  const bool bounded = MODES && p.causal && (p.window > 0 || p.row_start != nullptr);
+  const int jlo = bounded ? min(nkv_end, max(0, flash_row_lo(p, batch, min(q0, p.Sq - 1), off)) / 128) : 0;
+  const int nkv = nkv_end - jlo;      // key block of iteration j is jlo + j
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
@@ -167,8 +171,8 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         mbar_expect_tx(&kv_full[st], 2 * L::kTile);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
-          tma_load_4d(smem + L::kK + st * L::kTile + c * 16384, &tmK, &kv_full[st], c * 64, j * 128, kv_head, batch);
-          tma_load_4d(smem + L::kV + st * L::kTile + c * 16384, &tmV, &kv_full[st], c * 64, j * 128, kv_head, batch);
+          tma_load_4d(smem + L::kK + st * L::kTile + c * 16384, &tmK, &kv_full[st], c * 64, (jlo + j) * 128, kv_head, batch);
+          tma_load_4d(smem + L::kV + st * L::kTile + c * 16384, &tmV, &kv_full[st], c * 64, (jlo + j) * 128, kv_head, batch);
         }
       }
       if (*abort_flag) __nanosleep(50000);
@@ -230,13 +234,19 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       dlt = p.delta[idx];
     }
     bool ok = nkv > 0;
+    const int row_lo = bounded ? flash_row_lo(p, batch, row, off) : 0;
+    const bool capped = MODES && p.softcap > 0.f;
+    const bool special = bounded || capped;
+    const float cap_in = capped ? p.scale / p.softcap : 0.f;
+    const float cap_l2 = p.softcap * kLog2e;
     for (int j = 0; j < nkv && ok; ++j) {
       if (!mbar_wait(sdp_full, j & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 10)) { ok = false; break; }
       tc_fence_after();
-      const int k0 = j * 128;
+      const int k0 = (jlo + j) * 128;
       int lim = p.Skv - k0;
       if (p.causal) lim = min(lim, row + off - k0 + 1);
       lim = max(0, min(128, lim));
+      const int lo = max(0, min(128, row_lo - k0));          // keys below the row's window / sequence start
       // two halves of 64 columns: four loads in flight and one wait each; after the second half is in registers the
       // MMA warp may overwrite S and dP with the next block's
 #pragma unroll
@@ -259,11 +269,29 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         for (int cc = 0; cc < 2; ++cc) {
           const int c = h * 2 + cc;
           float ds[32];
+          if (!special) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - lse2);
-            float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * p.scale;
-            ds[i] = (c * 32 + i < lim) ? v : 0.f;
+            for (int i = 0; i < 32; ++i) {
+              float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - lse2);
+              float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * p.scale;
+              ds[i] = (c * 32 + i < lim) ? v : 0.f;
+            }
+          } else {
+            // lower key bound and / or soft-capped scores: u = cap * tanh(s * scale / cap), du/ds = scale * (1 - tanh^2)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float sc = __uint_as_float(s[cc][i]), g = p.scale;
+              if (capped) {
+                const float t = tanh_fast(sc * cap_in);
+                sc = t * cap_l2;
+                g *= 1.f - t * t;
+              } else {
+                sc *= p.scale_log2;
+              }
+              float pr = fast_exp2(sc - lse2);
+              float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * g;
+              ds[i] = (c * 32 + i < lim && c * 32 + i >= lo) ? v : 0.f;
+            }
           }
           if (ok) store_operand_chunk(sDS, r, c, ds);
         }
@@ -277,7 +305,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       if (!mbar_wait(dq_done, (nkv - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 12)) ok = false;
     }
     tc_fence_after();
-    if (ok || nkv == 0) {     // warp-uniform: every thread of the warp waited on the same barriers
+    if (ok || nkv <= 0) {     // warp-uniform: every thread of the warp waited on the same barriers
       __nv_bfloat16* drow = p.dQ + (size_t(batch) * p.Sq + row) * p.dq_row_stride + size_t(head) * D;
 #pragma unroll 1
       for (int c = 0; c < D / 32; ++c) {
@@ -324,12 +352,12 @@ struct BwdKVSmem {
   static constexpr int kDO = kQ + kStages * kTile;
   static constexpr int kPT = kDO + kStages * kTile;
   static constexpr int kDST = kPT + 32768;
-  static constexpr int kStat = kDST + 32768;       // lse2[128], delta[128]
-  static constexpr int kBar = kStat + 1024;
+  static constexpr int kStat = kDST + 32768;       // lse2[128], delta[128], lo[128]
+  static constexpr int kBar = kStat + 1536;
   static constexpr int kTotal = kBar + 256 + 1024;
 };
 
-template <int D>
+template <int D, bool MODES>
 __global__ void __launch_bounds__(192, 1)
 flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
@@ -350,6 +378,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   volatile uint32_t* abort_flag = tmem_slot + 1;
   float* s_lse2 = reinterpret_cast<float*>(smem + L::kStat);
   float* s_delta = s_lse2 + 128;
+  int* s_lo = reinterpret_cast<int*>(s_delta + 128);      // first key each query of the block may see
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kb = blockIdx.x, kv_head = blockIdx.y, batch = blockIdx.z;
@@ -359,7 +388,20 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const int nq = (p.Sq + 127) / 128;
   int i_min = 0;
   if (p.causal) i_min = max(0, (k0 - off) / 128);
-  const int per_head = max(0, nq - i_min);
+  // query blocks past the last one that can see these keys are skipped too: a sliding window bounds them directly,
+  // packed sequences by the first block whose first row already starts beyond this key block
+  const bool bounded = MODES && p.causal && (p.window > 0 || p.row_start != nullptr);
+  int i_end = nq;
+  if (bounded) {
+    if (p.window > 0) i_end = min(i_end, (k0 + 127 + p.window - 1 - off) / 128 + 1);
+    if (p.row_start) {
+      int i = i_min;
+      while (i < i_end && p.row_start[size_t(batch) * p.Sq + min(i * 128, p.Sq - 1)] <= k0 + 127) ++i;
+      i_end = i;
+    }
+    i_end = max(i_end, i_min);
+  }
+  const int per_head = max(0, i_end - i_min);
   const int iters = per_head * group;
 
   if (threadIdx.x == 0) {
@@ -469,6 +511,10 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     uint8_t* sPT = smem + L::kPT;
     uint8_t* sDST = smem + L::kDST;
     bool ok = true;
+    const bool capped = MODES && p.softcap > 0.f;
+    const bool special = bounded || capped;
+    const float cap_in = capped ? p.scale / p.softcap : 0.f;
+    const float cap_l2 = p.softcap * kLog2e;
     for (int it = 0; it < iters && ok; ++it) {
       const int head = kv_head * group + it / per_head;
       const int qi = i_min + it % per_head;
@@ -486,6 +532,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         }
         s_lse2[r] = l2;
         s_delta[r] = dl;
+        s_lo[r] = bounded ? flash_row_lo(p, batch, qr, off) : 0;
       }
       softmax_bar_sync();
       if (!mbar_wait(sdp_full, it & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 10)) { ok = false; break; }
@@ -514,13 +561,32 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         for (int cc = 0; cc < 2; ++cc) {
           const int c = h * 2 + cc;
           float pt[32], dst[32];
+          if (!special) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = c * 32 + i;
-            float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - s_lse2[col]);
-            if (col < first_q) pr = 0.f;
-            pt[i] = pr;
-            dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * p.scale;
+            for (int i = 0; i < 32; ++i) {
+              const int col = c * 32 + i;
+              float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - s_lse2[col]);
+              if (col < first_q) pr = 0.f;
+              pt[i] = pr;
+              dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * p.scale;
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              const int col = c * 32 + i;
+              float sc = __uint_as_float(s[cc][i]), g = p.scale;
+              if (capped) {
+                const float t = tanh_fast(sc * cap_in);
+                sc = t * cap_l2;
+                g *= 1.f - t * t;
+              } else {
+                sc *= p.scale_log2;
+              }
+              float pr = fast_exp2(sc - s_lse2[col]);
+              if (col < first_q || key < s_lo[col]) pr = 0.f;
+              pt[i] = pr;
+              dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * g;
+            }
           }
           if (ok) {
             store_operand_chunk(sPT, r, c, pt);
@@ -577,11 +643,11 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   }
 }
 
-template <int D>
+template <int D, bool MODES>
 static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& tdo,
                       const FlashParams& p, cudaStream_t stream) {
-  auto kq = flash_bwd_q_kernel<D>;
-  auto kkv = flash_bwd_kv_kernel<D>;
+  auto kq = flash_bwd_q_kernel<D, MODES>;
+  auto kkv = flash_bwd_kv_kernel<D, MODES>;
   static DeviceOnce configured;
   if (int e = configured.run([&] {
         cudaError_t e1 = cudaFuncSetAttribute(kq, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdQSmem<D>::kTotal);
@@ -607,14 +673,18 @@ using namespace idrak;
 // out / dout: contiguous [B, Sq, H, D]; lse, delta [B,H,Sq]. dq / dk / dv rows hold heads packed [heads, D] with
 // the given row strides in elements (0 = contiguous), so they may be slices of one fused d(QKV) buffer;
 // their batch stride is rows * row stride.
-IDRAK_API int idrak_flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
-                              const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int H, int Hkv,
-                              int Sq, int Skv, int D, long long q_row_stride, long long k_row_stride,
-                              long long v_row_stride, long long q_batch_stride, long long k_batch_stride,
-                              long long v_batch_stride, long long dq_row_stride, long long dk_row_stride,
-                              long long dv_row_stride, float scale, int causal, void* stream_) {
+// window > 0 and row_start (one int per query row, [B, Sq]) restrict the keys a query sees exactly as in the forward
+// entry point; both need `causal`. `softcap` > 0 differentiates through the tanh cap of the forward.
+IDRAK_API int idrak_flash_bwd_ex(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                                 const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int H, int Hkv,
+                                 int Sq, int Skv, int D, long long q_row_stride, long long k_row_stride,
+                                 long long v_row_stride, long long q_batch_stride, long long k_batch_stride,
+                                 long long v_batch_stride, long long dq_row_stride, long long dk_row_stride,
+                                 long long dv_row_stride, float scale, int causal, int window, const int* row_start,
+                                 float softcap, void* stream_) {
   if (D != 64 && D != 128) return -2;
   if (H % Hkv) return -3;
+  if ((window > 0 || row_start) && !causal) return -4;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   {
     const long long rows = (long long)B * Sq * H;
@@ -636,6 +706,9 @@ IDRAK_API int idrak_flash_bwd(const void* q, const void* k, const void* v, const
   p.scale = scale;
   p.scale_log2 = scale * kLog2e;
   p.causal = causal;
+  p.window = window > 0 ? window : 0;
+  p.row_start = row_start;
+  p.softcap = softcap > 0.f ? softcap : 0.f;
   p.st = status_device_ptr();
   p.dQ = static_cast<__nv_bfloat16*>(dq);
   p.dK = static_cast<__nv_bfloat16*>(dk);
@@ -648,5 +721,18 @@ IDRAK_API int idrak_flash_bwd(const void* q, const void* k, const void* v, const
   if (make_head_map(&tk, k, D, Skv, Hkv, B, k_row_stride, k_batch_stride)) return -11;
   if (make_head_map(&tv, v, D, Skv, Hkv, B, v_row_stride, v_batch_stride)) return -12;
   if (make_head_map(&tdo, dout, D, Sq, H, B, (long long)H * D, (long long)Sq * H * D)) return -13;
-  return D == 64 ? launch_bwd<64>(tq, tk, tv, tdo, p, stream) : launch_bwd<128>(tq, tk, tv, tdo, p, stream);
+  if (p.window > 0 || p.row_start || p.softcap > 0.f)
+    return D == 64 ? launch_bwd<64, true>(tq, tk, tv, tdo, p, stream) : launch_bwd<128, true>(tq, tk, tv, tdo, p, stream);
+  return D == 64 ? launch_bwd<64, false>(tq, tk, tv, tdo, p, stream) : launch_bwd<128, false>(tq, tk, tv, tdo, p, stream);
+}
+
+IDRAK_API int idrak_flash_bwd(const void* q, const void* k, const void* v, const void* out, const void* dout,
+                              const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int H, int Hkv,
+                              int Sq, int Skv, int D, long long q_row_stride, long long k_row_stride,
+                              long long v_row_stride, long long q_batch_stride, long long k_batch_stride,
+                              long long v_batch_stride, long long dq_row_stride, long long dk_row_stride,
+                              long long dv_row_stride, float scale, int causal, void* stream_) {
+  return idrak_flash_bwd_ex(q, k, v, out, dout, lse, delta, dq, dk, dv, B, H, Hkv, Sq, Skv, D, q_row_stride,
+                            k_row_stride, v_row_stride, q_batch_stride, k_batch_stride, v_batch_stride, dq_row_stride,
+                            dk_row_stride, dv_row_stride, scale, causal, 0, nullptr, 0.f, stream_);
 }

@@ -11,6 +11,14 @@ struct FlashParams {
   int B, H, Hkv, Sq, Skv;
   float scale, scale_log2;
   int causal;
+  // Optional lower bounds on the keys a query may see (both need `causal`):
+  //   window     > 0: query at position r sees keys (r + off - window, r + off] only (sliding-window attention)
+  //   row_start  per query row [B * Sq]: the first key index it may see - the start of its own sequence when several
+  //              sequences are packed into one row of the batch. Must not decrease along a row of the batch.
+  int window;
+  const int* row_start;
+  // logit soft-capping: scores become softcap * tanh(scale * s / softcap) before the softmax (0 = off; forward only)
+  float softcap;
   Status* st;
   // backward only
   const float* delta;  // [B, H, Sq] rowsum(dO * O)
@@ -27,6 +35,14 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+
+// First key index query `row` (position in its batch entry) may see; off = Skv - Sq.
+__device__ __forceinline__ int flash_row_lo(const FlashParams& p, int batch, int row, int off) {
+  int lo = 0;
+  if (p.window > 0) lo = max(lo, row + off - p.window + 1);
+  if (p.row_start && row < p.Sq) lo = max(lo, p.row_start[size_t(batch) * p.Sq + row]);
+  return lo;
 }
 
 // 4-D map (d, position, head, batch) over a buffer whose rows hold heads packed as [heads, D].

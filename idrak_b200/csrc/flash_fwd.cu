@@ -33,7 +33,8 @@ struct FwdSmem {
   static constexpr int kTotal = kBar + 256 + 1024;
 };
 
-template <int D>
+// MODES = false compiles the window / packed-sequence / soft-cap code out: the plain causal kernel is unchanged by them
+template <int D, bool MODES>
 __global__ void __launch_bounds__(192, (D == 64) ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
@@ -60,9 +61,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   const int kv_head = head / (p.H / p.Hkv);
   const int q0 = qb * 128;
   const int off = p.Skv - p.Sq;   // causal: query row r sees keys <= r + off
-  int nkv = (p.Skv + 127) / 128;
-  if (p.causal) nkv = min(nkv, (q0 + 127 + off) / 128 + 1);
-  if (nkv < 0) nkv = 0;
+  int nkv_end = (p.Skv + 127) / 128;
+  if (p.causal) nkv_end = min(nkv_end, (q0 + 127 + off) / 128 + 1);
+  if (nkv_end < 0) nkv_end = 0;
+  // key blocks wholly below what the tile's first row may see are skipped (the bounds do not decrease along rows)
+  const bool bounded = MODES && p.causal && (p.window > 0 || p.row_start != nullptr);
+  const int jlo = bounded ? min(nkv_end, max(0, flash_row_lo(p, batch, min(q0, p.Sq - 1), off)) / 128) : 0;
+  const int nkv = nkv_end - jlo;      // blocks this CTA walks: key block of iteration j is jlo + j
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -114,13 +119,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         mbar_expect_tx(&k_full[st], L::kTile);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem + L::kK + st * L::kTile + c * 16384, &tmK, &k_full[st], c * 64, j * 128, kv_head, batch);
+          tma_load_4d(smem + L::kK + st * L::kTile + c * 16384, &tmK, &k_full[st], c * 64, (jlo + j) * 128, kv_head, batch);
         inflight |= 1u << st;
         if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (2u << 16) | (2 + st))) { ok = false; break; }
         mbar_expect_tx(&v_full[st], L::kTile);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem + L::kV + st * L::kTile + c * 16384, &tmV, &v_full[st], c * 64, j * 128, kv_head, batch);
+          tma_load_4d(smem + L::kV + st * L::kTile + c * 16384, &tmV, &v_full[st], c * 64, (jlo + j) * 128, kv_head, batch);
         inflight |= 4u << st;
       }
       if (!ok || *abort_flag) {
@@ -189,17 +194,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     float m_used = -INFINITY;                    // max the accumulator and the running sum are scaled by
     float l = 0.f;
     bool ok = nkv > 0;
+    const int row_lo = bounded ? flash_row_lo(p, batch, row, off) : 0;     // first key this row may see
+    const bool capped = MODES && p.softcap > 0.f;
+    const float cap_in = capped ? p.scale / p.softcap : 0.f;               // s -> softcap * tanh(s * scale / softcap)
+    const float sl2 = capped ? p.softcap * 1.4426950408889634f : p.scale_log2;   // factor into the log2 domain
     for (int j = 0; j < nkv && ok; ++j) {
       const int sb = (kSBufs == 2) ? (j & 1) : 0;
       const uint32_t sph = (kSBufs == 2) ? uint32_t((j >> 1) & 1) : uint32_t(j & 1);
       if (!mbar_wait(&s_full[sb], sph, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 10)) { ok = false; break; }
       tc_fence_after();
-      const int k0 = j * 128;
-      // keys visible to this row in this block: columns [0, lim)
+      const int k0 = (jlo + j) * 128;
+      // keys visible to this row in this block: columns [lo, lim)
       int lim = p.Skv - k0;
       if (p.causal) lim = min(lim, row + off - k0 + 1);
       lim = max(0, min(128, lim));
-      const bool need_mask = lim < 128;
+      const int lo = max(0, min(128, row_lo - k0));
+      const bool need_mask = lim < 128 || lo > 0;
       // the whole row of scores into registers: four loads in flight, one wait; then the buffer goes back to the MMA warp
       uint32_t s[4][32];
       const uint32_t s_addr = tmem_S + uint32_t(sb) * 128 + lane_addr;
@@ -210,6 +220,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       tmem_ld_wait();
       tc_fence_before();
       mbar_arrive(&s_empty[sb]);
+      if (capped) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) s[c][i] = __float_as_uint(tanh_fast(__uint_as_float(s[c][i]) * cap_in));
+      }
       // four independent chains (one per 32-column chunk) keep the dependent latency short
       float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (!need_mask) {
@@ -223,11 +239,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         for (int i = 0; i < 32; ++i) {
 #pragma unroll
           for (int c = 0; c < 4; ++c)
-            if (c * 32 + i < lim) m4[c] = fmaxf(m4[c], __uint_as_float(s[c][i]));
+            if (c * 32 + i < lim && c * 32 + i >= lo) m4[c] = fmaxf(m4[c], __uint_as_float(s[c][i]));
         }
       }
       float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-      mx *= p.scale_log2;
+      mx *= sl2;
       const float m_new = fmaxf(m_used, mx);
       // the accumulator is rescaled only when some row of this warp moved its max by more than 2^8
       const bool need = (j > 0) && (m_new - m_used > 8.0f);
@@ -262,8 +278,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         float l4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-          float e = fast_exp2(__uint_as_float(s[c][i]) * p.scale_log2 - m_sub);
-          if (need_mask && (c * 32 + i >= lim)) e = 0.f;
+          float e = fast_exp2(__uint_as_float(s[c][i]) * sl2 - m_sub);
+          if (need_mask && (c * 32 + i >= lim || c * 32 + i < lo)) e = 0.f;
           pv[i] = e;
           l4[i & 3] += e;
         }
@@ -288,7 +304,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       if (!mbar_wait(o_done, (nkv - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 12)) ok = false;
     }
     tc_fence_after();
-    if (nkv == 0) {
+    if (nkv <= 0) {
       // no visible key: output zeros, lse = -inf
       if (row < p.Sq) {
         __nv_bfloat16* orow = p.O + (size_t(batch) * p.Sq + row) * p.o_row_stride + size_t(head) * D;
@@ -331,11 +347,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   }
 }
 
-template <int D>
+template <int D, bool MODES>
 static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtensorMap& tv, const FlashParams& p,
                       cudaStream_t stream) {
   using L = FwdSmem<D>;
-  auto kern = flash_fwd_kernel<D>;
+  auto kern = flash_fwd_kernel<D, MODES>;
   static DeviceOnce configured;
   if (int e = configured.run([&] {
         return int(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
@@ -354,13 +370,18 @@ using namespace idrak;
 // q: rows of (batch, position) with `q_row_stride` elements between positions and heads packed as
 // [H, D] inside a row; likewise k, v with Hkv heads. o: [B*Sq, o_row_stride] with heads packed [H, D].
 // lse: [B, H, Sq] fp32 (may be null). Pointers 16-byte aligned, strides multiples of 8 elements.
-IDRAK_API int idrak_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
-                              int Hkv, int Sq, int Skv, int D, long long q_row_stride, long long k_row_stride,
-                              long long v_row_stride, long long o_row_stride, long long q_batch_stride,
-                              long long k_batch_stride, long long v_batch_stride, float scale, int causal,
-                              void* stream_) {
+// `window` > 0 (sliding window), `row_start` ([B * Sq] int32: the first key each query row may see, for sequences packed
+// into one batch row) and `softcap` > 0 (tanh soft-capping of the scaled scores) are the optional modes; the first
+// two need `causal`. Reference: window and soft-cap of attention_flash_* (src/Idrak.Gpu/Cuda/PtxKernels.Rows.cs:779),
+// per-row key ranges of the span kernels (PtxKernels.SpansTiled.cs).
+IDRAK_API int idrak_flash_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
+                                 int Hkv, int Sq, int Skv, int D, long long q_row_stride, long long k_row_stride,
+                                 long long v_row_stride, long long o_row_stride, long long q_batch_stride,
+                                 long long k_batch_stride, long long v_batch_stride, float scale, int causal,
+                                 int window, const int* row_start, float softcap, void* stream_) {
   if (D != 64 && D != 128) return -2;
   if (H % Hkv) return -3;
+  if ((window > 0 || row_start) && !causal) return -4;
   FlashParams p;
   p.O = static_cast<__nv_bfloat16*>(o);
   p.o_row_stride = o_row_stride;
@@ -369,11 +390,26 @@ IDRAK_API int idrak_flash_fwd(const void* q, const void* k, const void* v, void*
   p.scale = scale;
   p.scale_log2 = scale * 1.4426950408889634f;
   p.causal = causal;
+  p.window = window > 0 ? window : 0;
+  p.row_start = row_start;
+  p.softcap = softcap > 0.f ? softcap : 0.f;
   p.st = status_device_ptr();
   CUtensorMap tq, tk, tv;
   if (make_head_map(&tq, q, D, Sq, H, B, q_row_stride, q_batch_stride)) return -10;
   if (make_head_map(&tk, k, D, Skv, Hkv, B, k_row_stride, k_batch_stride)) return -11;
   if (make_head_map(&tv, v, D, Skv, Hkv, B, v_row_stride, v_batch_stride)) return -12;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  return D == 64 ? launch_fwd<64>(tq, tk, tv, p, stream) : launch_fwd<128>(tq, tk, tv, p, stream);
+  if (p.window > 0 || p.row_start || p.softcap > 0.f)
+    return D == 64 ? launch_fwd<64, true>(tq, tk, tv, p, stream) : launch_fwd<128, true>(tq, tk, tv, p, stream);
+  return D == 64 ? launch_fwd<64, false>(tq, tk, tv, p, stream) : launch_fwd<128, false>(tq, tk, tv, p, stream);
+}
+
+IDRAK_API int idrak_flash_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
+                              int Hkv, int Sq, int Skv, int D, long long q_row_stride, long long k_row_stride,
+                              long long v_row_stride, long long o_row_stride, long long q_batch_stride,
+                              long long k_batch_stride, long long v_batch_stride, float scale, int causal,
+                              void* stream_) {
+  return idrak_flash_fwd_ex(q, k, v, o, lse, B, H, Hkv, Sq, Skv, D, q_row_stride, k_row_stride, v_row_stride,
+                            o_row_stride, q_batch_stride, k_batch_stride, v_batch_stride, scale, causal, 0, nullptr, 0.f,
+                            stream_);
 }

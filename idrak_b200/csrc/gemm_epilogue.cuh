@@ -11,7 +11,10 @@ constexpr int kUmmaK = 16;
 constexpr int kGemmThreads = 192;
 constexpr int kGroupM = 16;      // raster: 16 row-tiles share the resident column tiles in L2
 
-enum GemmAct : int { kActNone = 0, kActGelu = 1, kActGeluGrad = 2 };
+// kActGelu / kActGeluGrad: C = gelu(v) with the pre-activation saved in aux / C = v * gelu'(aux).
+// kActGeluD / kActMulAux: the same layer with the derivative taken in the forward pass, where the tanh is at hand
+// anyway: C = gelu(v) and aux = gelu'(v) / C = v * aux. The backward epilogue is then one multiply.
+enum GemmAct : int { kActNone = 0, kActGelu = 1, kActGeluGrad = 2, kActGeluD = 3, kActMulAux = 4 };
 
 struct GemmParams {
   int M, N, K;
@@ -22,7 +25,8 @@ struct GemmParams {
   const __nv_bfloat16* residual;  // [M, ldr] or null
   int ldr;
   int act;                        // GemmAct
-  __nv_bfloat16* aux;             // kActGelu: pre-activation out; kActGeluGrad: pre-activation in. [M, ld_aux]
+  __nv_bfloat16* aux;             // kActGelu: pre-activation out; kActGeluGrad: pre-activation in; kActGeluD:
+                                  // derivative out; kActMulAux: factor in. [M, ld_aux]
   int ld_aux;
   int beta;                       // 1: add the old contents of C
   float alpha;                    // scale on the accumulator
@@ -31,6 +35,8 @@ struct GemmParams {
   int m_tiles, n_tiles;
   int tma_store;                  // 1: bf16 C (and aux) leave through shared-memory staging + TMA stores
   const __half* col_scale;        // [N] per-column factor applied to the accumulator first (int8 weights), or null
+  const float* row_scale_f;       // [M] and
+  const float* col_scale_f;       // [N] fp32 factors on the accumulator (8-bit operands quantised per row), or null
   unsigned long long* prof;       // role timers [grid][8] (cycles), or null: see idrak_gemm_role_timers
   int epi_mode;                   // EpiMode: which compile-time variant of the staged epilogue fits this product
   Status* st;
@@ -44,6 +50,10 @@ __device__ __forceinline__ void epilogue_math8(const GemmParams& p, int row, int
   const bool vec = (nvalid == 8);
   if (p.col_scale) {
     for (int i = 0; i < nvalid; ++i) v[i] *= __half2float(p.col_scale[col + i]);
+  }
+  if (p.row_scale_f) {
+    const float rs = p.row_scale_f[row];
+    for (int i = 0; i < nvalid; ++i) v[i] *= rs * p.col_scale_f[col + i];
   }
   if (p.bias) {
     if (vec && ((reinterpret_cast<uintptr_t>(p.bias + col) & 15) == 0)) {
@@ -60,22 +70,34 @@ __device__ __forceinline__ void epilogue_math8(const GemmParams& p, int row, int
   if (p.act != kActNone) {
     __nv_bfloat16* ax = p.aux + size_t(row) * p.ld_aux + col;
     const bool axvec = vec && ((reinterpret_cast<uintptr_t>(ax) & 15) == 0);
-    if (p.act == kActGelu) {
+    if (p.act == kActGelu || p.act == kActGeluD) {
+      if (p.act == kActGeluD) {
+        // value and derivative from the unrounded pre-activation; `pre` carries the derivative
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float g, d;
+          gelu_tanh_both(v[i], g, d);
+          v[i] = g;
+          pre[i] = d;
+        }
+      } else {
+        // the activation sees the value as it is stored (bf16), so forward and backward agree
+#pragma unroll
+        for (int i = 0; i < 8; ++i) pre[i] = __bfloat162float(__float2bfloat16(v[i]));
+      }
       if (store_aux) {
         if (axvec) {
           uint4 o;
-          o.x = pack_bf16x2(v[0], v[1]); o.y = pack_bf16x2(v[2], v[3]);
-          o.z = pack_bf16x2(v[4], v[5]); o.w = pack_bf16x2(v[6], v[7]);
+          o.x = pack_bf16x2(pre[0], pre[1]); o.y = pack_bf16x2(pre[2], pre[3]);
+          o.z = pack_bf16x2(pre[4], pre[5]); o.w = pack_bf16x2(pre[6], pre[7]);
           *reinterpret_cast<uint4*>(ax) = o;
         } else {
-          for (int i = 0; i < nvalid; ++i) ax[i] = __float2bfloat16(v[i]);
+          for (int i = 0; i < nvalid; ++i) ax[i] = __float2bfloat16(pre[i]);
         }
       }
-      // the activation sees the value as it was stored (bf16), so forward and backward agree
+      if (p.act == kActGelu) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        pre[i] = __bfloat162float(__float2bfloat16(v[i]));
-        v[i] = gelu_tanh(pre[i]);
+        for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(pre[i]);
       }
     } else {
       float x[8];
@@ -89,8 +111,13 @@ __device__ __forceinline__ void epilogue_math8(const GemmParams& p, int row, int
       } else {
         for (int i = 0; i < 8; ++i) x[i] = i < nvalid ? __bfloat162float(ax[i]) : 0.f;
       }
+      if (p.act == kActMulAux) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] *= gelu_tanh_grad(x[i]);
+        for (int i = 0; i < 8; ++i) v[i] *= x[i];
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] *= gelu_tanh_grad(x[i]);
+      }
     }
   }
   if (p.residual) {
@@ -182,7 +209,8 @@ constexpr int kDenseStagingBytes = 2 * 16384;        // per staging buffer of ea
 
 // Which compile-time variant of the slab arithmetic a product takes (GemmParams::epi_mode); 0 keeps every test at
 // run time (column scales, odd alignments, ragged column edges).
-enum EpiMode : int { kEpiGeneric = 0, kEpiPlain, kEpiBias, kEpiBiasRes, kEpiRes, kEpiBiasGelu, kEpiGelu, kEpiGeluGrad };
+enum EpiMode : int { kEpiGeneric = 0, kEpiPlain, kEpiBias, kEpiBiasRes, kEpiRes, kEpiBiasGelu, kEpiGelu, kEpiGeluGrad,
+                     kEpiBiasGeluD, kEpiGeluD, kEpiMulAux };
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
@@ -203,12 +231,12 @@ __device__ __forceinline__ void side_fetch(const __nv_bfloat16* base, int ld, in
 // caller applies gelu_of_packed after it has been stored.
 template <bool BIAS, int ACT, bool RES>
 __device__ __forceinline__ void half_math(const GemmParams& p, int col0, int half, const uint32_t (&acc)[32],
-                                          const uint4 (&sidev)[4], uint32_t (&out)[16]) {
+                                          const uint4 (&sidev)[4], uint32_t (&out)[16], uint32_t (&second)[16]) {
 #pragma unroll
   for (int g = 0; g < 4; ++g) {
     float v[8];
     uint32_t side[4];
-    if (RES || ACT == kActGeluGrad) {
+    if (RES || ACT == kActGeluGrad || ACT == kActMulAux) {
       side[0] = sidev[g].x; side[1] = sidev[g].y; side[2] = sidev[g].z; side[3] = sidev[g].w;
     }
 #pragma unroll
@@ -227,6 +255,24 @@ __device__ __forceinline__ void half_math(const GemmParams& p, int col0, int hal
         const float2 x = unpack_bf16x2(side[i]);
         v[2 * i] *= gelu_tanh_grad(x.x);
         v[2 * i + 1] *= gelu_tanh_grad(x.y);
+      }
+    } else if (ACT == kActMulAux) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 x = unpack_bf16x2(side[i]);
+        v[2 * i] *= x.x;
+        v[2 * i + 1] *= x.y;
+      }
+    } else if (ACT == kActGeluD) {
+      // value and derivative from the one tanh; `second` takes the derivative
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float g0, d0, g1, d1;
+        gelu_tanh_both(v[2 * i], g0, d0);
+        gelu_tanh_both(v[2 * i + 1], g1, d1);
+        v[2 * i] = g0;
+        v[2 * i + 1] = g1;
+        second[g * 4 + i] = pack_bf16x2(d0, d1);
       }
     }
     if (RES) {
@@ -281,8 +327,9 @@ __device__ __forceinline__ void half_to_smem(uint8_t* buf, int r, int half, cons
 }
 
 __device__ __forceinline__ bool mode_has_side(int mode) {
-  return mode == kEpiBiasRes || mode == kEpiRes || mode == kEpiGeluGrad;
+  return mode == kEpiBiasRes || mode == kEpiRes || mode == kEpiGeluGrad || mode == kEpiMulAux;
 }
+__device__ __forceinline__ bool mode_side_is_aux(int mode) { return mode == kEpiGeluGrad || mode == kEpiMulAux; }
 
 // The side input a thread fetched ahead of the half-slab it will drain next (16 registers carried across halves,
 // slabs and tiles), so the global-memory latency of the residual / saved pre-activation is off the critical path.
@@ -321,6 +368,7 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
   const bool staged = p.tma_store && p.splits == 1;
   const bool leader = (quarter == 0) && (lane == 0);  // issues and waits for this group's TMA stores
   const bool gelu = (p.act == kActGelu);
+  const bool two_outputs = gelu || (p.act == kActGeluD);
   bool released = false;
 
 #pragma unroll 1
@@ -332,10 +380,10 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
     if (staged) {
       const int mode = (col0 + 64 <= p.N) ? p.epi_mode : kEpiGeneric;      // uniform over the warp
       const bool has_side = mode_has_side(mode);
-      const __nv_bfloat16* side_base = (mode == kEpiGeluGrad) ? p.aux : p.residual;
-      const int side_ld = (mode == kEpiGeluGrad) ? p.ld_aux : p.ldr;
-      uint32_t out[32];                               // the slab's packed output (or pre-activation)
-      uint32_t pre_generic[32];                       // generic GELU only
+      const __nv_bfloat16* side_base = mode_side_is_aux(mode) ? p.aux : p.residual;
+      const int side_ld = mode_side_is_aux(mode) ? p.ld_aux : p.ldr;
+      uint32_t out[32];                               // the slab's packed output (kActGelu: its pre-activation)
+      uint32_t second[32];                            // what goes to aux: generic GELU's pre-activation, kActGeluD's derivative
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         uint32_t acc[32];
@@ -370,19 +418,19 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
         if (have_acc) tmem_ld_wait();
         if (h == 1 && last_slab) { release(); released = true; }
         uint32_t(&o)[16] = *reinterpret_cast<uint32_t(*)[16]>(&out[h * 16]);
+        uint32_t(&o2)[16] = *reinterpret_cast<uint32_t(*)[16]>(&second[h * 16]);
         switch (mode) {
-          case kEpiPlain:    half_math<false, kActNone, false>(p, col0, h, acc, cur, o); break;
-          case kEpiBias:     half_math<true, kActNone, false>(p, col0, h, acc, cur, o); break;
-          case kEpiBiasRes:  half_math<true, kActNone, true>(p, col0, h, acc, cur, o); break;
-          case kEpiRes:      half_math<false, kActNone, true>(p, col0, h, acc, cur, o); break;
-          case kEpiBiasGelu: half_math<true, kActGelu, false>(p, col0, h, acc, cur, o); break;
-          case kEpiGelu:     half_math<false, kActGelu, false>(p, col0, h, acc, cur, o); break;
-          case kEpiGeluGrad: half_math<false, kActGeluGrad, false>(p, col0, h, acc, cur, o); break;
-          default: {
-            uint32_t(&pg)[16] = *reinterpret_cast<uint32_t(*)[16]>(&pre_generic[h * 16]);
-            half_math_generic(p, row, col0, h, acc, o, pg);
-            break;
-          }
+          case kEpiPlain:     half_math<false, kActNone, false>(p, col0, h, acc, cur, o, o2); break;
+          case kEpiBias:      half_math<true, kActNone, false>(p, col0, h, acc, cur, o, o2); break;
+          case kEpiBiasRes:   half_math<true, kActNone, true>(p, col0, h, acc, cur, o, o2); break;
+          case kEpiRes:       half_math<false, kActNone, true>(p, col0, h, acc, cur, o, o2); break;
+          case kEpiBiasGelu:  half_math<true, kActGelu, false>(p, col0, h, acc, cur, o, o2); break;
+          case kEpiGelu:      half_math<false, kActGelu, false>(p, col0, h, acc, cur, o, o2); break;
+          case kEpiGeluGrad:  half_math<false, kActGeluGrad, false>(p, col0, h, acc, cur, o, o2); break;
+          case kEpiBiasGeluD: half_math<true, kActGeluD, false>(p, col0, h, acc, cur, o, o2); break;
+          case kEpiGeluD:     half_math<false, kActGeluD, false>(p, col0, h, acc, cur, o, o2); break;
+          case kEpiMulAux:    half_math<false, kActMulAux, false>(p, col0, h, acc, cur, o, o2); break;
+          default:            half_math_generic(p, row, col0, h, acc, o, o2); break;
         }
       }
       // registers -> this group's next staging buffer -> one TMA store of the 128 x 64 slab
@@ -400,10 +448,12 @@ __device__ __forceinline__ void drain_accumulator(const GemmParams& p, const CUt
         }
         ahead.ring = (ahead.ring + 1) % kBufs;
       };
-      if (gelu) {
-        // the saved pre-activation leaves first; the activation is evaluated while its store reads the buffer
-        stage_and_store(tmAux, (mode == kEpiGeneric) ? pre_generic : out);
-        if (mode != kEpiGeneric) gelu_of_packed(out);
+      if (two_outputs) {
+        // what is saved for the backward pass leaves first. kActGelu: the pre-activation, and the activation is
+        // evaluated while that store reads the buffer; kActGeluD and the generic path hold both outputs already
+        const bool pre_in_out = gelu && mode != kEpiGeneric;
+        stage_and_store(tmAux, pre_in_out ? out : second);
+        if (pre_in_out) gelu_of_packed(out);
       }
       stage_and_store(tmC, out);
     } else {

@@ -35,7 +35,9 @@ struct GemmSmem {
   static constexpr int kTotal = kStages * kStageBytes + kStagingBytes + kBarrierBytes + 1024;  // + alignment slack
 };
 
-template <int BN, int A_MN, int B_MN>
+// F8 = 1: both operands are e4m3 bytes, K-major; a 128-byte swizzle row then holds 128 elements of K, the MMA is
+// kind::f8f6f4 (K = 32 per instruction, the same 32 bytes per step), everything else is unchanged.
+template <int BN, int A_MN, int B_MN, int F8 = 0>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
@@ -54,7 +56,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int k_blocks_total = (p.K + kBK - 1) / kBK;
+  constexpr int kKB = F8 ? 2 * kBK : kBK;          // elements of K per shared-memory stage
+  const int k_blocks_total = (p.K + kKB - 1) / kKB;
   const int kb_per_split = (k_blocks_total + p.splits - 1) / p.splits;
   const int units = p.m_tiles * p.n_tiles * p.splits;
 
@@ -103,15 +106,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           mbar_expect_tx(&full[stage], L::kStageBytes);
           if (A_MN) {
 #pragma unroll
-            for (int j = 0; j < kBM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full[stage], tm * kBM + j * 64, kb * kBK);
+            for (int j = 0; j < kBM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full[stage], tm * kBM + j * 64, kb * kKB);
           } else {
-            tma_load_2d(sa, &tmA, &full[stage], kb * kBK, tm * kBM);
+            tma_load_2d(sa, &tmA, &full[stage], kb * kKB, tm * kBM);
           }
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[stage], tn * BN + j * 64, kb * kBK);
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[stage], tn * BN + j * 64, kb * kKB);
           } else {
-            tma_load_2d(sb, &tmB, &full[stage], kb * kBK, tn * BN);
+            tma_load_2d(sb, &tmB, &full[stage], kb * kKB, tn * BN);
           }
           issued_mask |= 1u << stage;
           issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
@@ -132,7 +135,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(kBM, BN, A_MN, B_MN, 1);
+      constexpr uint32_t idesc = F8 ? make_idesc_e4m3(kBM, BN) : make_idesc_f16(kBM, BN, A_MN, B_MN, 1);
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -170,7 +173,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                      : make_smem_desc_sw128(sa + kk * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc_sw128(sb + kk * 2048, 8192, 1024)
                                      : make_smem_desc_sw128(sb + kk * 32, 16, 1024);
-            tc_mma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+            if (F8) tc_mma_f8_ss(d_tmem, da, db, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
+            else tc_mma_f16_ss(d_tmem, da, db, idesc, (kb > kb0 || kk > 0) ? 1u : 0u);
           }
           tc_commit(&empty[stage]);   // releases the stage once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -270,11 +274,11 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) 
 // ---------------------------------------------------------------------------
 // host launcher
 // ---------------------------------------------------------------------------
-template <int BN, int A_MN, int B_MN>
+template <int BN, int A_MN, int B_MN, int F8 = 0>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                        const CUtensorMap& tmAux, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = GemmSmem<BN>;
-  auto kern = gemm_kernel<BN, A_MN, B_MN>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, F8>;
   static DeviceOnce configured;
   if (int e = configured.run([&] {
         return int(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
@@ -287,13 +291,15 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
 
 int pick_epi_mode(const GemmParams& p) {
   auto aligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
-  if (!p.tma_store || p.col_scale) return kEpiGeneric;
+  if (!p.tma_store || p.col_scale || p.row_scale_f) return kEpiGeneric;
   if (p.bias && !aligned(p.bias)) return kEpiGeneric;
   if (p.residual && (!aligned(p.residual) || (p.ldr & 7))) return kEpiGeneric;
   const bool b = p.bias != nullptr, r = p.residual != nullptr;
   if (p.act == kActNone) return b ? (r ? kEpiBiasRes : kEpiBias) : (r ? kEpiRes : kEpiPlain);
   if (p.act == kActGelu && !r) return b ? kEpiBiasGelu : kEpiGelu;
   if (p.act == kActGeluGrad && !b && !r && aligned(p.aux) && (p.ld_aux & 7) == 0) return kEpiGeluGrad;
+  if (p.act == kActGeluD && !r) return b ? kEpiBiasGeluD : kEpiGeluD;
+  if (p.act == kActMulAux && !b && !r && aligned(p.aux) && (p.ld_aux & 7) == 0) return kEpiMulAux;
   return kEpiGeneric;
 }
 
@@ -405,13 +411,13 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
   memset(&tmAux, 0, sizeof(tmAux));
   p.tma_store = 0;
   if (!c_fp32 && !beta && p.splits == 1 && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0 &&
-      (act != kActGelu || ((ld_aux % 8) == 0 && (reinterpret_cast<uintptr_t>(aux) & 15) == 0))) {
+      ((act != kActGelu && act != kActGeluD) || ((ld_aux % 8) == 0 && (reinterpret_cast<uintptr_t>(aux) & 15) == 0))) {
     uint64_t dims[2] = {uint64_t(N), uint64_t(M)};
     uint32_t box[2] = {64, 128};
     uint64_t str_c[1] = {uint64_t(ldc) * 2};
     int ok = encode_tensor_map(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, dims, str_c, box,
                                CU_TENSOR_MAP_SWIZZLE_128B) == 0;
-    if (ok && act == kActGelu) {
+    if (ok && (act == kActGelu || act == kActGeluD)) {
       uint64_t str_a[1] = {uint64_t(ld_aux) * 2};
       ok = encode_tensor_map(&tmAux, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, aux, dims, str_a, box,
                              CU_TENSOR_MAP_SWIZZLE_128B) == 0;
@@ -451,4 +457,56 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
     rc = int(cudaGetLastError());
   }
   return rc;
+}
+
+// C[M, N] (bf16) = (A B^T) * row_scale[m] * col_scale[n] (+ bias) with A [M, K] and B [N, K] e4m3 bytes, K-major
+// (lda, ldb in bytes, multiples of 16; K a multiple of 16). fp32 accumulation on the kind::f8f6f4 tensor path.
+// Covers the reference's gemm8_e4m3_f32 with per-row A scales and per-column B scales applied in the epilogue
+// (src/Idrak.Gpu/Cuda/PtxKernels.EightBit.cs:17-23).
+IDRAK_API int idrak_gemm_fp8(const void* A, int lda, const void* B, int ldb, void* C, int ldc, int M, int N, int K,
+                             const float* row_scale, const float* col_scale, const void* bias, void* stream_) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 15) || (ldb & 15) || (K & 15)) return -2;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -3;
+  if (!row_scale || !col_scale) return -4;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int bn = (N <= 128) ? 128 : 256;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.c_fp32 = 0;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.act = kActNone;
+  p.alpha = 1.f;
+  p.splits = 1;
+  p.m_tiles = (M + kBM - 1) / kBM;
+  p.n_tiles = (N + bn - 1) / bn;
+  p.st = status_device_ptr();
+  p.row_scale_f = row_scale;
+  p.col_scale_f = col_scale;
+  auto byte_map = [](CUtensorMap* tm, const void* ptr, int rows, int k, int ld, int box_rows) {
+    uint64_t dims[2] = {uint64_t(k), uint64_t(rows)};
+    uint64_t strides[1] = {uint64_t(ld)};
+    uint32_t box[2] = {128, uint32_t(box_rows)};
+    return encode_tensor_map(tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims, strides, box,
+                             CU_TENSOR_MAP_SWIZZLE_128B);
+  };
+  CUtensorMap tmA, tmB, tmC, tmAux;
+  if (byte_map(&tmA, A, M, K, lda, kBM)) return -11;
+  if (byte_map(&tmB, B, N, K, ldb, bn)) return -12;
+  memset(&tmC, 0, sizeof(tmC));
+  memset(&tmAux, 0, sizeof(tmAux));
+  p.tma_store = 0;
+  if ((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
+    uint64_t dims[2] = {uint64_t(N), uint64_t(M)};
+    uint32_t box[2] = {64, 128};
+    uint64_t str_c[1] = {uint64_t(ldc) * 2};
+    p.tma_store = encode_tensor_map(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, dims, str_c, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B) == 0;
+  }
+  p.epi_mode = kEpiGeneric;
+  p.prof = nullptr;
+  const int units = p.m_tiles * p.n_tiles;
+  const int grid = min(units, sm_count());
+  if (bn == 256) return launch_gemm<256, 0, 0, 1>(tmA, tmB, tmC, tmAux, p, grid, stream);
+  return launch_gemm<128, 0, 0, 1>(tmA, tmB, tmC, tmAux, p, grid, stream);
 }

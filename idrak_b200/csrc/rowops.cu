@@ -9,6 +9,8 @@
 // layernorm_bwd_params_f32 / bias_gelu_f32 (PtxKernels.Decoding.cs:12), gather / scatter and
 // sum_cols_strided (PtxKernels.Advanced.cs:12, PtxKernels.Rows.cs:13).
 #include "common.cuh"
+#include "norm_bulk.h"
+#include <cstdlib>
 
 namespace idrak {
 
@@ -744,39 +746,93 @@ IDRAK_API int idrak_norm_fwd(const void* x, const void* residual, const void* w,
   return int(cudaGetLastError());
 }
 
-// Number of row blocks the backward pass uses; dw_part/db_part must hold [that, C] floats.
+IDRAK_API int idrak_colsum(const void* x, int rows, int C, int ld, float* part, void* out, int out_fp32,
+                           int accumulate, void* stream_);
+
+// Number of row blocks the backward pass uses at most; its scratch holds 3 x [that, C] floats.
 IDRAK_API int idrak_norm_bwd_blocks(int rows) {
   int b = sm_count() * 2;
   return rows < b ? rows : b;
 }
 
+// Backward of LayerNorm / RMSNorm. dx = norm backward of dy (+ dres_in); dw / db are written (or accumulated into)
+// in fp32 or bf16. `part` holds 3 * idrak_norm_bwd_blocks(rows) * C floats. `dx_colsum` (fp32 [C], optional) receives
+// the column sums of dx: the bias gradient of the linear layer whose output this norm read. Rows of up to 1024
+// elements take the bulk-copy pipeline of norm_bulk.cu, which produces that sum for free; wider rows take the
+// register kernels and, when the sum is asked for, a column-sum pass over dx.
+IDRAK_API int idrak_norm_bwd_fused(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
+                                   const void* dres_in, void* dx, float* part, void* dw, void* db, float* dx_colsum,
+                                   int grads_fp32, int accumulate, int rows, int C, int rms, void* stream_) {
+  if (C % 8 || C > 8192 || rows <= 0) return -2;
+  cudaStream_t s = static_cast<cudaStream_t>(stream_);
+  int blocks = norm_bwd_bulk_blocks(rows, C);
+  static int use_bulk = -1;
+  if (use_bulk < 0) {
+    const char* e = getenv("IDRAK_NORM_BULK");
+    use_bulk = (e && e[0] == '0') ? 0 : 1;
+  }
+  if (!use_bulk) blocks = 0;
+  float* dw_part = part;
+  float* db_part;
+  float* dxs_part;
+  int rc;
+  if (blocks > 0) {
+    db_part = part + size_t(blocks) * C;
+    dxs_part = part + size_t(2) * blocks * C;
+    NormBulkParams q{};
+    q.dy = CBF(dy); q.x = CBF(x); q.w = CBF(w); q.mean = mean; q.rstd = rstd; q.dres = CBF(dres_in);
+    q.dx = BF(dx); q.dw_part = dw_part; q.db_part = rms ? nullptr : db_part;
+    q.dxs_part = dx_colsum ? dxs_part : nullptr;
+    q.rows = rows; q.C = C; q.rms = rms;
+    rc = norm_bwd_bulk_launch(q, blocks, s);
+    if (rc) return rc;
+    if (dx_colsum) {
+      colsum_final_kernel<<<(C + 31) / 32, 256, 0, s>>>(dxs_part, blocks, C, dx_colsum, 1, 0);
+      note_launches(1);
+    }
+  } else {
+    blocks = idrak_norm_bwd_blocks(rows);
+    db_part = part + size_t(blocks) * C;
+    const int rpb = (rows + blocks - 1) / blocks;
+    const int nvec = C / 8;
+#define NW(V) norm_bwd_warp_kernel<V><<<blocks, 256, size_t(2) * C * sizeof(float), s>>>(CBF(dy), CBF(x), CBF(w), mean, rstd, CBF(dres_in), BF(dx), dw_part, rms ? nullptr : db_part, rows, C, rms, rpb)
+#define NB(V) norm_bwd_kernel<V><<<blocks, 128, 0, s>>>(CBF(dy), CBF(x), CBF(w), mean, rstd, CBF(dres_in), BF(dx), dw_part, rms ? nullptr : db_part, rows, C, rms, rpb)
+    if (nvec <= 32 * 1) NW(1);
+    else if (nvec <= 32 * 2) NW(2);
+    else if (nvec <= 32 * 3) NW(3);
+    else if (nvec <= 32 * 4) NW(4);
+    else if (nvec <= 128 * 2) NB(2);
+    else if (nvec <= 128 * 4) NB(4);
+    else NB(8);
+#undef NW
+#undef NB
+    note_launches(1);
+    rc = int(cudaGetLastError());
+    if (rc) return rc;
+    if (dx_colsum) {
+      rc = idrak_colsum(dx, rows, C, C, part + size_t(2) * blocks * C, dx_colsum, 1, 0, stream_);
+      if (rc) return rc;
+    }
+  }
+  colsum_final_kernel<<<(C + 31) / 32, 256, 0, s>>>(dw_part, blocks, C, dw, grads_fp32, accumulate);
+  note_launches(1);
+  if (!rms && db) {
+    colsum_final_kernel<<<(C + 31) / 32, 256, 0, s>>>(db_part, blocks, C, db, grads_fp32, accumulate);
+    note_launches(1);
+  }
+  return int(cudaGetLastError());
+}
+
+// Whether a call of these sizes gets the column sums of dx without a pass of their own (1) or not (0).
+IDRAK_API int idrak_norm_bwd_sums_dx(int rows, int C) { return norm_bwd_bulk_blocks(rows, C) > 0 ? 1 : 0; }
+
+// The same without the column sums of dx; `dw_part` and `db_part` are the two halves of one 2 * blocks * C scratch.
 IDRAK_API int idrak_norm_bwd(const void* dy, const void* x, const void* w, const float* mean, const float* rstd,
                              const void* dres_in, void* dx, float* dw_part, float* db_part, void* dw, void* db,
                              int grads_fp32, int accumulate, int rows, int C, int rms, void* stream_) {
-  if (C % 8 || C > 8192 || rows <= 0) return -2;
-  cudaStream_t s = static_cast<cudaStream_t>(stream_);
-  const int blocks = idrak_norm_bwd_blocks(rows);
-  const int rpb = (rows + blocks - 1) / blocks;
-  const int nvec = C / 8;
-#define NW(V) norm_bwd_warp_kernel<V><<<blocks, 256, size_t(2) * C * sizeof(float), s>>>(CBF(dy), CBF(x), CBF(w), mean, rstd, CBF(dres_in), BF(dx), dw_part, rms ? nullptr : db_part, rows, C, rms, rpb)
-#define NB(V) norm_bwd_kernel<V><<<blocks, 128, 0, s>>>(CBF(dy), CBF(x), CBF(w), mean, rstd, CBF(dres_in), BF(dx), dw_part, rms ? nullptr : db_part, rows, C, rms, rpb)
-  if (nvec <= 32 * 1) NW(1);
-  else if (nvec <= 32 * 2) NW(2);
-  else if (nvec <= 32 * 3) NW(3);
-  else if (nvec <= 32 * 4) NW(4);
-  else if (nvec <= 128 * 2) NB(2);
-  else if (nvec <= 128 * 4) NB(4);
-  else NB(8);
-#undef NW
-#undef NB
-  note_launches(1);
-  int rc = int(cudaGetLastError());
-  if (rc) return rc;
-  colsum_final_kernel<<<(C + 31) / 32, 256, 0, s>>>(dw_part, blocks, C, dw, grads_fp32, accumulate);
-  note_launches(1);
-  if (!rms && db) colsum_final_kernel<<<(C + 31) / 32, 256, 0, s>>>(db_part, blocks, C, db, grads_fp32, accumulate);
-  note_launches(1);
-  return int(cudaGetLastError());
+  (void)db_part;
+  return idrak_norm_bwd_fused(dy, x, w, mean, rstd, dres_in, dx, dw_part, dw, db, nullptr, grads_fp32, accumulate, rows,
+                              C, rms, stream_);
 }
 
 IDRAK_API int idrak_colsum_blocks(int rows) {

@@ -183,6 +183,10 @@ __global__ void __launch_bounds__(1024) sum_rows_kernel(const float* __restrict_
   if (threadIdx.x == 0) out[0] = s * scale;
 }
 
+// xent_bulk.cu: the pipelined kernel for rows that fit shared memory twice; -100 = sizes do not fit.
+int xent_bulk_launch(void* logits, const int* targets, float* losses, float* lse, int rows, int vocab, int ld,
+                     float scale, int ignore_index, int write_grad, cudaStream_t stream);
+
 }  // namespace idrak
 
 using namespace idrak;
@@ -195,6 +199,10 @@ IDRAK_API int idrak_softmax_xent(void* logits, const int* targets, float* losses
   const int nv = (nvec + kXentThreads - 1) / kXentThreads;
   cudaStream_t s = static_cast<cudaStream_t>(stream_);
   __nv_bfloat16* l = static_cast<__nv_bfloat16*>(logits);
+  {
+    const int rc = xent_bulk_launch(logits, targets, losses, lse, rows, vocab, ld, scale, ignore_index, write_grad, s);
+    if (rc != -100) return rc;
+  }
   if (nv > kXentMaxVec) {
     xent_stream_kernel<<<rows, kXentThreads, 0, s>>>(l, targets, losses, lse, vocab, ld, scale, ignore_index, write_grad);
     note_launches(1);

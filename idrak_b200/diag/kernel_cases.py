@@ -91,18 +91,19 @@ def case_gemm(a) -> Tuple[Callable, float, float]:
     out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
     flops, nbytes = 2.0 * a.m * a.n * a.k, 2.0 * (a.m * a.k + a.n * a.k + a.m * a.n)
     epi = getattr(a, "epi", "plain")
-    if epi == "gelu_grad":
+    if epi in ("gelu_grad", "mul_aux"):
         w = torch.randn(a.k, a.n, device="cuda", dtype=torch.bfloat16)          # [out, in] of the layer: B stored [K, N]
         aux = torch.randn(a.m, a.n, device="cuda", dtype=torch.bfloat16)
-        return (lambda: gemm(x, w, b_mn=True, act="gelu_grad", aux=aux, out=out)), flops, nbytes + 2.0 * a.m * a.n
+        return (lambda: gemm(x, w, b_mn=True, act=epi, aux=aux, out=out)), flops, nbytes + 2.0 * a.m * a.n
     w = torch.randn(a.n, a.k, device="cuda", dtype=torch.bfloat16)
     bias = torch.randn(a.n, device="cuda", dtype=torch.bfloat16) if epi != "plain" else None
     if epi == "bias_res":
         res = torch.randn(a.m, a.n, device="cuda", dtype=torch.bfloat16)
         return (lambda: gemm(x, w, bias=bias, residual=res, out=out)), flops, nbytes + 2.0 * a.m * a.n
-    if epi == "bias_gelu":
+    if epi in ("bias_gelu", "bias_gelu_d"):
         aux = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
-        return (lambda: gemm(x, w, bias=bias, act="gelu", aux=aux, out=out)), flops, nbytes + 2.0 * a.m * a.n
+        act = "gelu" if epi == "bias_gelu" else "gelu_d"
+        return (lambda: gemm(x, w, bias=bias, act=act, aux=aux, out=out)), flops, nbytes + 2.0 * a.m * a.n
     return (lambda: gemm(x, w, bias=bias, out=out)), flops, nbytes
 
 
@@ -161,6 +162,17 @@ def case_norm(a):
     return (lambda: norm_forward(x, w, b, 1e-5, False)), 0.0, 4.0 * a.m * a.n
 
 
+def case_norm_bwd(a):
+    """LayerNorm backward with the residual gradient added and the column sums of dx produced (--m rows, --n columns)."""
+    from ..ops.rowops import norm_backward, norm_forward
+    x = torch.randn(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(a.n, device="cuda", dtype=torch.bfloat16)
+    b = torch.zeros(a.n, device="cuda", dtype=torch.bfloat16)
+    _, mean, rstd, _ = norm_forward(x, w, b, 1e-5, False)
+    dy, dres = torch.randn_like(x), torch.randn_like(x)
+    return (lambda: norm_backward(dy, x, w, mean, rstd, False, True, dres, sums_of_dx=True)), 0.0, 8.0 * a.m * a.n
+
+
 def case_adamw(a):
     from ..ops.optim import FusedAdamW
     n = a.m * a.n
@@ -217,7 +229,7 @@ def _role_timers(fn: Callable[[], None]) -> dict:
 
 CASES: Dict[str, Callable] = {
     "gemm": case_gemm, "gemm_wgrad": case_gemm_wgrad, "cublas": case_cublas, "flash_fwd": case_flash_fwd,
-    "flash_bwd": case_flash_bwd, "xent": case_xent, "norm": case_norm, "adamw": case_adamw,
+    "flash_bwd": case_flash_bwd, "xent": case_xent, "norm": case_norm, "norm_bwd": case_norm_bwd, "adamw": case_adamw,
     "decode_attn": case_decode_attn, "qgemm": case_qgemm,
 }
 
@@ -229,7 +241,7 @@ def main(argv=None) -> int:
                           ("seq", 1024), ("dim", 64), ("warmup", 3), ("iters", 10)):
         ap.add_argument(f"--{name}", type=int, default=default)
     ap.add_argument("--kind", default="int4", choices=["int4", "int8"])
-    ap.add_argument("--epi", default="plain", choices=["plain", "bias", "bias_res", "bias_gelu", "gelu_grad"])
+    ap.add_argument("--epi", default="plain", choices=["plain", "bias", "bias_res", "bias_gelu", "gelu_grad", "bias_gelu_d", "mul_aux"])
     ap.add_argument("--role-timers", action="store_true",
                     help="gemm cases: after timing, run one more launch with the kernel's role timers on and print "
                          "the mean cycles per tile each warp role spent waiting")

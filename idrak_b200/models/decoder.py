@@ -40,6 +40,10 @@ class Norm(nn.Module):
             return ops.layer_norm(x, w, self.bias, self.eps)
         return ops.rms_norm(x, w, self.eps)
 
+    def branch(self, x):
+        """``(norm(x), x)`` for a pre-norm residual block; see ``ops.norm_branch``."""
+        return ops.norm_branch(x, self.effective_weight(), self.bias, self.eps, self.kind != "layer")
+
 
 def project(x, weight, packed, bias=None, residual=None):
     """``x W^T + b (+ residual)`` over the dense weight, or over its packed int8 / int4 replacement."""
@@ -79,33 +83,27 @@ class SelfAttention(nn.Module):
         else:
             qkv = project(x, self.qkv_weight, packed.get("qkv"), self.qkv_bias)
         window = spec.sliding_window if spec.is_windowed(self.layer) else None
-        simple = not spec.qk_norm and window is None and spec.attention_softcap is None and (
-            self.rope is None or self.rope.scaling is None)
-        def attend(part, pos):
-            if simple:
-                theta = self.rope.theta if self.rope is not None else None
-                rdim = self.rope.rotary_dim if self.rope is not None else None
-                return ops.qkv_attention(part, H, Hkv, D, True, self.scale, theta, rdim, 1.0, pos)
-            return self._general(part, pos, window)
-
-        if spans is None:
-            a = attend(qkv, positions)
+        # sequences packed into one row: one launch, every position bounded below by the start of its own sequence
+        row_start = None
+        if spans is not None:
+            row_start = spans if torch.is_tensor(spans) else ops.row_starts_from_spans(
+                spans, qkv.shape[0], qkv.shape[1], qkv.device)
+        simple = not spec.qk_norm and (self.rope is None or self.rope.scaling is None)
+        if simple:
+            theta = self.rope.theta if self.rope is not None else None
+            rdim = self.rope.rotary_dim if self.rope is not None else None
+            a = ops.qkv_attention(qkv, H, Hkv, D, True, self.scale, theta, rdim, 1.0, positions, window, row_start,
+                                  spec.attention_softcap)
         else:
-            # several sequences packed into one row: attention runs per sequence, everything else over the pack
-            pieces = []
-            for lo, hi in spans:
-                pos = (positions.reshape(qkv.shape[0], -1)[:, lo:hi].reshape(-1).contiguous()
-                       if positions is not None else None)
-                pieces.append(attend(qkv[:, lo:hi].contiguous(), pos))
-            a = torch.cat(pieces, dim=1)
+            a = self._general(qkv, positions, window, row_start)
         if adapters is not None and "o" in adapters:
             from ..adapters.lora import project_with_adapters
             return project_with_adapters(a, self.o_weight, self.o_bias, adapters,
                                          {"o": (0, spec.dim)}, residual, packed=packed.get("o"))
         return project(a, self.o_weight, packed.get("o"), self.o_bias, residual)
 
-    def _general(self, qkv, positions, window):
-        """qk-norm, scaled RoPE tables, sliding windows and soft-capping: composed from primitives."""
+    def _general(self, qkv, positions, window, row_start=None):
+        """qk-norm and scaled RoPE tables ahead of the attention kernel."""
         from ..ops.fused import _split_qkv
         spec = self.spec
         B, S, _ = qkv.shape
@@ -114,10 +112,8 @@ class SelfAttention(nn.Module):
             q, k = self.q_norm(q.contiguous()), self.k_norm(k.contiguous())
         if self.rope is not None:
             q, k = apply_rope_table(q, self.rope, positions), apply_rope_table(k, self.rope, positions)
-        if window is None and spec.attention_softcap is None:
-            a = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), True, self.scale)
-        else:
-            a = masked_attention(q, k, v, self.scale, window, spec.attention_softcap)
+        a = ops.attention(q.contiguous(), k.contiguous(), v.contiguous(), True, self.scale, window, row_start,
+                          spec.attention_softcap)
         return a.reshape(B, S, spec.heads * spec.head_dim)
 
 
@@ -139,24 +135,8 @@ def apply_rope_table(x, rope, positions=None):
 
 
 def masked_attention(q, k, v, scale, window=None, softcap=None):
-    """Causal attention with a sliding window and/or tanh soft-capping (fp32 math)."""
-    B, S, H, D = q.shape
-    Hkv = k.shape[2]
-    qf = q.float().permute(0, 2, 1, 3)
-    kf = k.float().permute(0, 2, 1, 3).repeat_interleave(H // Hkv, 1)
-    vf = v.float().permute(0, 2, 1, 3).repeat_interleave(H // Hkv, 1)
-    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
-    if softcap:
-        s = torch.tanh(s / softcap) * softcap
-    i = torch.arange(S, device=q.device)[:, None]
-    j = torch.arange(k.shape[1], device=q.device)[None, :]
-    off = k.shape[1] - S
-    mask = j > i + off
-    if window is not None:
-        mask = mask | (j <= i + off - window)
-    s = s.masked_fill(mask, float("-inf"))
-    o = torch.matmul(torch.softmax(s, -1), vf)
-    return o.permute(0, 2, 1, 3).to(q.dtype)
+    """Causal attention with a sliding window and/or tanh soft-capping (fp32 math): the oracle of the kernels' modes."""
+    return ops.attention_reference(q, k, v, True, scale, window, None, softcap)
 
 
 class FeedForward(nn.Module):
@@ -282,8 +262,10 @@ class DecoderBlock(nn.Module):
                 m = self.post_mlp_norm(m)
             return x + self._drop(m)
         # plain pre-norm block: residual additions happen inside the GEMM epilogues
-        x = self.attn(self.attn_norm(x), x, positions, spans)
-        return self.mlp(self.mlp_norm(x), x)
+        h, x = self.attn_norm.branch(x)
+        x = self.attn(h, x, positions, spans)
+        h, x = self.mlp_norm.branch(x)
+        return self.mlp(h, x)
 
     def _drop(self, t):
         if self.drop > 0 and self.training:
@@ -355,6 +337,8 @@ class Decoder(nn.Module):
             x = x * spec.embedding_scale
         if spec.dropout > 0 and self.training:
             x = torch.nn.functional.dropout(x, spec.dropout, True)
+        if spans is not None and not torch.is_tensor(spans):
+            spans = ops.row_starts_from_spans(spans, B, S, x.device)     # once per pass, not per layer
         for blk in self.blocks:
             if self.checkpoint_blocks and self.training and torch.is_grad_enabled():
                 from ..core.checkpointing import checkpoint
@@ -367,8 +351,9 @@ class Decoder(nn.Module):
         return self.embed if self.head is None else self.head
 
     def forward(self, ids: torch.Tensor, positions: Optional[torch.Tensor] = None, spans=None) -> torch.Tensor:
-        """Logits ``[B, S, vocabulary]``. ``spans``: ``[(lo, hi), ...]`` token ranges of the sequences packed into a
-        single row (B = 1); attention stays inside each range."""
+        """Logits ``[B, S, vocabulary]``. ``spans``: ``[(lo, hi), ...]`` token ranges of the sequences packed back to
+        back into every row; attention stays inside each range (one kernel launch per layer: each position carries
+        the start of its own sequence as a lower bound on the keys it sees)."""
         h = self.hidden(ids, positions, spans)
         logits = ops.linear(h, self.head_weight(), self.head_bias)[..., : self.spec.vocabulary]
         if self.spec.logit_softcap:

@@ -27,6 +27,8 @@ def _bind():
     vp, i, f, ll = C.c_void_p, C.c_int, C.c_float, C.c_longlong
     _native.bind("idrak_decode_partial_floats", ll, [i, i, i, i])
     _native.bind("idrak_paged_decode", i, [vp, C.c_longlong, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, i, vp])
+    _native.bind("idrak_paged_decode_kv", i, [vp, C.c_longlong, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i, i, f, i, vp])
+    _native.bind("idrak_norm_rope_kv", i, [vp, ll, vp, vp, vp, vp, vp, vp, vp, vp, f, f, f, i, i, i, i, i, i, vp])
     _native.bind("idrak_kv_write_paged", i, [vp, vp, ll, vp, vp, vp, i, i, vp])
     _native.bind("idrak_argmax_rows", i, [vp, i, i, i, ll, vp, vp])
     _native.bind("idrak_sample_rows", i, [vp, i, i, i, ll, vp, vp, vp, vp, vp, vp, vp, i, vp, vp, vp, vp, C.c_uint, vp])
@@ -54,7 +56,71 @@ def kv_write_paged(k_src: torch.Tensor, v_src: torch.Tensor, slots: torch.Tensor
     _native.check(rc, "idrak_kv_write_paged")
 
 
-def paged_decode_reference(q, k_cache, v_cache, block_table, seq_lens, scale=None, window: int = 0):
+def quantize_kv_reference(x: torch.Tensor):
+    """int8 codes and one fp32 scale per (token, head) of ``[tokens, heads, D]``: scale = max|x| / 127."""
+    xf = x.float()
+    mx = xf.abs().amax(-1)
+    scale = torch.where(mx > 0, mx / 127.0, torch.ones_like(mx))
+    q = torch.round(xf / scale[..., None]).clamp(-127, 127).to(torch.int8)
+    return q, scale
+
+
+def norm_rope_kv(qkv: torch.Tensor, heads: int, kv_heads: int, head_dim: int, positions: Optional[torch.Tensor],
+                 slots: Optional[torch.Tensor], k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                 k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None,
+                 q_norm_weight: Optional[torch.Tensor] = None, k_norm_weight: Optional[torch.Tensor] = None,
+                 eps: float = 1e-6, theta: Optional[float] = None, rot_dim: Optional[int] = None,
+                 freq_scale: float = 1.0) -> None:
+    """In place on the packed projection ``[T, (H + 2 Hkv) D]``: per-head RMS norm of queries and keys (when weights
+    are given), RoPE of both (when ``theta`` is given), and the write of keys / values into the paged cache rows
+    ``slots`` - bf16, or int8 codes with one scale per (slot, kv head) when ``k_scale`` / ``v_scale`` are given. One
+    kernel launch on the GPU; the CPU path composes the same steps."""
+    T = qkv.shape[0]
+    H, Hkv, D = heads, kv_heads, head_dim
+    rot = (rot_dim or D) if theta is not None else 0
+    fused = (qkv.is_cuda and qkv.dtype == torch.bfloat16 and D in (64, 128, 256) and rot % 64 == 0
+             and qkv.stride(1) == 1)
+    if fused:
+        _bind()
+        int8 = k_scale is not None
+        rc = _native.lib().idrak_norm_rope_kv(
+            qkv.data_ptr(), qkv.stride(0), ptr(positions), ptr(slots), ptr(k_cache), ptr(v_cache), ptr(k_scale),
+            ptr(v_scale), ptr(q_norm_weight), ptr(k_norm_weight), float(eps), float(theta or 10000.0), float(freq_scale),
+            int(rot), T, H, Hkv, D, int(int8), stream_ptr())
+        _native.check(rc, "idrak_norm_rope_kv")
+        return
+    from .rowops import rope_
+    qk = qkv[:, : (H + Hkv) * D].unflatten(-1, (H + Hkv, D))
+
+    def rms(x, w):
+        xf = x.float()
+        return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+    if q_norm_weight is not None:
+        qk[:, :H].copy_(rms(qk[:, :H], q_norm_weight))
+    if k_norm_weight is not None:
+        qk[:, H:].copy_(rms(qk[:, H:], k_norm_weight))
+    if theta is not None:
+        rope_(qk, positions, theta, rot_dim, freq_scale)
+    if slots is None:
+        return
+    k = qkv[:, H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D))
+    v = qkv[:, (H + Hkv) * D:].unflatten(-1, (Hkv, D))
+    if k_scale is None:
+        kv_write_paged(k, v, slots, k_cache, v_cache)
+        return
+    keep = slots >= 0
+    idx = slots[keep].long()
+    for src, cache, scales in ((k, k_cache, k_scale), (v, v_cache, v_scale)):
+        q8, sc = quantize_kv_reference(src[keep])
+        cache.view(-1, Hkv, D)[idx] = q8
+        scales.view(-1, Hkv)[idx] = sc
+
+
+def paged_decode_reference(q, k_cache, v_cache, block_table, seq_lens, scale=None, window: int = 0,
+                           k_scale=None, v_scale=None):
+    if k_scale is not None:
+        k_cache = (k_cache.float() * k_scale.view(*k_cache.shape[:3], 1)).to(q.dtype)
+        v_cache = (v_cache.float() * v_scale.view(*v_cache.shape[:3], 1)).to(q.dtype)
     seqs, H, D = q.shape
     _, bs, Hkv, _ = k_cache.shape
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
@@ -77,10 +143,12 @@ def paged_decode_reference(q, k_cache, v_cache, block_table, seq_lens, scale=Non
 
 def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, block_table: torch.Tensor,
                  seq_lens: torch.Tensor, scale: Optional[float] = None, window: int = 0,
-                 splits: Optional[int] = None, max_len_hint: Optional[int] = None) -> torch.Tensor:
-    """One query token per sequence against its cached keys / values. q: ``[seqs, H, D]``."""
+                 splits: Optional[int] = None, max_len_hint: Optional[int] = None,
+                 k_scale: Optional[torch.Tensor] = None, v_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One query token per sequence against its cached keys / values. q: ``[seqs, H, D]``. With ``k_scale`` /
+    ``v_scale`` (``[blocks, block_size, Hkv]`` fp32) the caches hold int8 codes."""
     if not q.is_cuda:
-        return paged_decode_reference(q, k_cache, v_cache, block_table, seq_lens, scale, window)
+        return paged_decode_reference(q, k_cache, v_cache, block_table, seq_lens, scale, window, k_scale, v_scale)
     _bind()
     seqs, H, D = q.shape
     _, bs, Hkv, _ = k_cache.shape
@@ -98,10 +166,11 @@ def paged_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, 
     if q.stride(2) != 1 or q.stride(1) != D or q.stride(0) % 8 or q.data_ptr() % 16:
         q = q.contiguous()                     # heads must be packed; sequences may be a strided view
     assert block_table.dtype == torch.int32 and seq_lens.dtype == torch.int32
-    rc = lib.idrak_paged_decode(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), block_table.data_ptr(),
-                                seq_lens.data_ptr(), out.data_ptr(), ptr(part), seqs, H, Hkv, D, bs,
-                                block_table.shape[1], splits, float(scale), int(window), stream_ptr())
-    _native.check(rc, "idrak_paged_decode")
+    rc = lib.idrak_paged_decode_kv(q.data_ptr(), q.stride(0), k_cache.data_ptr(), v_cache.data_ptr(), ptr(k_scale),
+                                   ptr(v_scale), block_table.data_ptr(), seq_lens.data_ptr(), out.data_ptr(), ptr(part),
+                                   seqs, H, Hkv, D, bs, block_table.shape[1], splits, float(scale), int(window),
+                                   stream_ptr())
+    _native.check(rc, "idrak_paged_decode_kv")
     return out
 
 

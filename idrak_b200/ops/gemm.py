@@ -18,8 +18,10 @@ import torch
 from .. import _native
 from ._util import ptr, scratch, stream_ptr
 
-ACT_NONE, ACT_GELU, ACT_GELU_GRAD = 0, 1, 2
-_ACT_IDS = {None: ACT_NONE, "none": ACT_NONE, "gelu": ACT_GELU, "gelu_grad": ACT_GELU_GRAD}
+ACT_NONE, ACT_GELU, ACT_GELU_GRAD, ACT_GELU_D, ACT_MUL_AUX = 0, 1, 2, 3, 4
+_ACT_IDS = {None: ACT_NONE, "none": ACT_NONE, "gelu": ACT_GELU, "gelu_grad": ACT_GELU_GRAD, "gelu_d": ACT_GELU_D,
+            "mul_aux": ACT_MUL_AUX}
+_TWO_OUTPUTS = (ACT_GELU, ACT_GELU_D)
 
 
 def _gelu_tanh(x: torch.Tensor) -> torch.Tensor:
@@ -47,6 +49,11 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, residual=None, ac
         v = _gelu_tanh(aux_out.float())
     elif _ACT_IDS[act] == ACT_GELU_GRAD:
         v = v * _gelu_tanh_grad(aux.float())
+    elif _ACT_IDS[act] == ACT_GELU_D:
+        aux_out = _gelu_tanh_grad(v).to(a.dtype)
+        v = _gelu_tanh(v)
+    elif _ACT_IDS[act] == ACT_MUL_AUX:
+        v = v * aux.float()
     if residual is not None:
         v = v + residual.float()
     dtype = out_dtype or (out.dtype if out is not None else a.dtype)
@@ -57,7 +64,7 @@ def gemm_reference(a, b, *, a_mn=False, b_mn=False, bias=None, residual=None, ac
         res = out
     else:
         res = v.to(dtype)
-    return (res, aux_out) if _ACT_IDS[act] == ACT_GELU else res
+    return (res, aux_out) if _ACT_IDS[act] in _TWO_OUTPUTS else res
 
 
 def _tuned_splits(a, b, a_mn, b_mn, M, N, K, default, out) -> int:
@@ -87,6 +94,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     ``a``: ``[M, K]`` (``a_mn=False``) or stored ``[K, M]`` (``a_mn=True``).
     ``b``: ``[N, K]`` (``b_mn=False``, the ``nn.Linear`` weight layout) or stored ``[K, N]`` (``b_mn=True``).
     ``act='gelu'`` returns ``(C, pre_activation)``; ``act='gelu_grad'`` multiplies by ``gelu'(aux)``.
+    ``act='gelu_d'`` returns ``(C, gelu'(pre_activation))`` - the derivative taken where the tanh is at hand - and
+    ``act='mul_aux'`` multiplies by ``aux``: the pair a training step uses, its backward epilogue one multiply.
     ``beta=True`` accumulates into ``out``. ``splits=None`` lets the library choose a split-K factor.
     """
     if not a.is_cuda:
@@ -117,7 +126,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
     c_fp32 = 1 if out.dtype == torch.float32 else 0
     assert c_fp32 or out.dtype == torch.bfloat16
     aux_t = aux
-    if act_id == ACT_GELU and aux_t is None:
+    if act_id in _TWO_OUTPUTS and aux_t is None:
         aux_t = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
     bn = 128 if N <= 128 else 256
     if splits is None:
@@ -138,7 +147,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, a_mn: bool = False, b_mn: bool = F
         act_id, ptr(aux_t), aux_t.stride(0) if aux_t is not None else 0,
         int(beta), float(alpha), int(splits), ptr(ws), 1 if a.dtype == torch.float16 else 0, stream_ptr())
     _native.check(rc, "idrak_gemm_bf16")
-    return (out, aux_t) if act_id == ACT_GELU else out
+    return (out, aux_t) if act_id in _TWO_OUTPUTS else out
 
 
 def weight_grad(dy2: torch.Tensor, x2: torch.Tensor, param: torch.Tensor | None):
@@ -154,14 +163,25 @@ def weight_grad(dy2: torch.Tensor, x2: torch.Tensor, param: torch.Tensor | None)
     return None
 
 
-def bias_grad(dy2: torch.Tensor, param: torch.Tensor | None):
+def bias_grad(dy2: torch.Tensor, param: torch.Tensor | None, dy: torch.Tensor | None = None):
+    """db = column sums of dy. ``dy`` is the gradient tensor as autograd delivered it: when the kernel that produced
+    it left its column sums on it (``_idrak_colsum``, see ``rowops.norm_backward``) no pass over dy is made."""
     from . import _grad
     from .rowops import colsum
+    ready = None
+    tagged = getattr(dy, "_idrak_colsum", None) if dy is not None else None
+    if tagged is not None and tagged[1] == dy._version and tagged[0].numel() == dy2.shape[1]:
+        ready = tagged[0]
     tgt = _grad.target(param)
     if tgt is None:
-        return colsum(dy2)
+        return colsum(dy2) if ready is None else ready.to(dy2.dtype)
     g, accumulate = tgt
-    colsum(dy2, out=g, accumulate=accumulate)
+    if ready is None:
+        colsum(dy2, out=g, accumulate=accumulate)
+    elif accumulate:
+        g.add_(ready.to(g.dtype))
+    else:
+        g.copy_(ready)
     _grad.written(param)
     return None
 
@@ -196,7 +216,7 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[1]:
             dw = weight_grad(dy2, x2, w_param)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = bias_grad(dy2, b_param)
+            db = bias_grad(dy2, b_param, dy)
         if ctx.has_res and ctx.needs_input_grad[3]:
             dres = dy
         return dx, dw, db, dres

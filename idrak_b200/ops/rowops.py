@@ -75,10 +75,13 @@ def norm_forward(x, weight, bias, eps, rms, residual=None):
     return out.reshape(x.shape), mean, rstd, (summed.reshape(x.shape) if summed is not None else None)
 
 
-def norm_backward(dy, x, weight, mean, rstd, rms, has_bias, dres=None, w_param=None, b_param=None):
+def norm_backward(dy, x, weight, mean, rstd, rms, has_bias, dres=None, w_param=None, b_param=None,
+                  sums_of_dx: bool = False):
     """Returns (dx, dweight, dbias). ``x`` is the tensor that was normalised. ``dres`` is added to dx.
     When ``w_param`` (and ``b_param``) take direct gradient writes, dweight / dbias go straight into their
-    ``.grad`` and come back as None."""
+    ``.grad`` and come back as None. With ``sums_of_dx`` the column sums of dx (fp32) are attached to the returned
+    dx as ``_idrak_colsum`` where the kernel produces them on the way (rows of up to 1024 elements): dx is the
+    output gradient of the linear layer before this norm, so ``ops.gemm.bias_grad`` finds its bias gradient there."""
     C = x.shape[-1]
     dy2, x2 = dy.reshape(-1, C), x.reshape(-1, C)
     rows = x2.shape[0]
@@ -98,7 +101,7 @@ def norm_backward(dy, x, weight, mean, rstd, rms, has_bias, dres=None, w_param=N
     dy2, x2 = dy2.contiguous(), x2.contiguous()
     dx = torch.empty_like(x2)
     blocks = lib.idrak_norm_bwd_blocks(rows)
-    part = scratch("norm_bwd", 2 * blocks * C, torch.float32, x.device)
+    part = scratch("norm_bwd", 3 * blocks * C, torch.float32, x.device)
     from . import _grad
     tw = _grad.target(w_param)
     tb = _grad.target(b_param) if has_bias else None
@@ -110,17 +113,23 @@ def norm_backward(dy, x, weight, mean, rstd, rms, has_bias, dres=None, w_param=N
         dw, accumulate = torch.empty_like(weight), False
         db = torch.empty_like(weight) if has_bias else None
     d2 = dres.reshape(-1, C).contiguous() if dres is not None else None
-    rc = lib.idrak_norm_bwd(dy2.data_ptr(), x2.data_ptr(), weight.data_ptr(), ptr(mean), rstd.data_ptr(), ptr(d2),
-                            dx.data_ptr(), part.data_ptr(), part.data_ptr() + 4 * blocks * C, dw.data_ptr(),
-                            ptr(db), 1 if dw.dtype == torch.float32 else 0, int(accumulate), rows, C, int(rms),
-                            stream_ptr())
-    _native.check(rc, "idrak_norm_bwd")
+    sums = None
+    if sums_of_dx and lib.idrak_norm_bwd_sums_dx(rows, C):
+        sums = torch.empty(C, dtype=torch.float32, device=x.device)
+    rc = lib.idrak_norm_bwd_fused(dy2.data_ptr(), x2.data_ptr(), weight.data_ptr(), ptr(mean), rstd.data_ptr(), ptr(d2),
+                                  dx.data_ptr(), part.data_ptr(), dw.data_ptr(), ptr(db), ptr(sums),
+                                  1 if dw.dtype == torch.float32 else 0, int(accumulate), rows, C, int(rms),
+                                  stream_ptr())
+    _native.check(rc, "idrak_norm_bwd_fused")
+    dx = dx.reshape(x.shape)
+    if sums is not None:
+        dx._idrak_colsum = (sums, dx._version)      # the version guards against a later in-place accumulation
     if direct:
         _grad.written(w_param)
         if has_bias:
             _grad.written(b_param)
-        return dx.reshape(x.shape), None, None
-    return dx.reshape(x.shape), dw, db
+        return dx, None, None
+    return dx, dw, db
 
 
 class _Norm(torch.autograd.Function):
@@ -137,6 +146,39 @@ class _Norm(torch.autograd.Function):
         x, weight, mean, rstd = ctx.saved_tensors
         dx, dw, db = norm_backward(dy, x, weight, mean, rstd, ctx.rms, ctx.has_bias, None, *ctx.params)
         return dx, dw, db, None, None
+
+
+class _NormBranch(torch.autograd.Function):
+    """``(norm(x), x)``: the second output is the residual path of a pre-norm block. Both gradients arrive in one
+    backward call, so the residual gradient is added inside the norm-backward kernel (no separate add) and the
+    column sums of the joint gradient come out of the same pass."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, eps, rms):
+        out, mean, rstd, _ = norm_forward(x, weight, bias, eps, rms)
+        ctx.save_for_backward(x, weight, mean, rstd)
+        ctx.params = (weight, bias)
+        ctx.rms, ctx.has_bias = rms, bias is not None
+        return out, x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, dy, dres):
+        x, weight, mean, rstd = ctx.saved_tensors
+        if dy is None:
+            return dres, None, None, None, None
+        dx, dw, db = norm_backward(dy, x, weight, mean, rstd, ctx.rms, ctx.has_bias, dres, *ctx.params,
+                                   sums_of_dx=True)
+        return dx, dw, db, None, None
+
+
+def norm_branch(x, weight, bias=None, eps: float = 1e-5, rms: bool = False):
+    """``(norm(x), x)`` for a pre-norm residual block: feed the first to the sub-layer and the second to its
+    residual input. Equal to computing the norm and reusing ``x``; on the GPU the backward pass is one kernel."""
+    if not _native_ok(x):
+        if rms:
+            return rms_norm(x, weight, eps), x
+        return torch.nn.functional.layer_norm(x, (x.shape[-1],), weight, bias, eps), x
+    return _NormBranch.apply(x, weight, bias, eps, rms)
 
 
 def layer_norm(x, weight, bias=None, eps: float = 1e-5):

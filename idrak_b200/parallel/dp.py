@@ -128,6 +128,9 @@ class DataParallel:
         params = [p for p in model.parameters() if p.requires_grad]
         self.device = params[0].device
         self.rs_blocks = rs_blocks
+        # the shard update and parameter all-gather run after the backward pass, with the machine to themselves:
+        # two CTAs of 512 threads per SM (the reduce-scatter, which shares the SMs with backward, keeps rs_blocks)
+        self.update_blocks = 2 * _native.lib().idrak_sm_count() if self.device.type == "cuda" else 2 * rs_blocks
         self._side = torch.cuda.Stream(device=self.device)
         self._handles = []
         self._pending = None
@@ -209,6 +212,43 @@ class DataParallel:
         """Per-rank gradient weights (tokens_r / sum of tokens) for token-weighted averaging; None = 1/world."""
         self.rank_weights = None if weights is None else weights.to(self.device, torch.float32).contiguous()
 
+    def step_header(self, tokens, loss=None, stop: bool = False, presence: Optional[torch.Tensor] = None) -> dict:
+        """The header every rank contributes before a step's gradients are reduced, exchanged in one small
+        all-reduce: this rank's token count, its loss times that count, a stop request and (optionally) one
+        presence flag per parameter. It sets the token weights of the gradient reduction on the device
+        (``tokens_r / sum of tokens``, so the reduced gradient is the token-weighted mean whatever the ranks' batch
+        sizes) and returns device tensors: ``tokens`` (global), ``loss`` (token-weighted mean), ``stop`` (> 0 when any
+        rank asked to stop at this step boundary) and ``presence`` (how many ranks hold a gradient for each
+        parameter). Nothing is read back to the host here. Call it before ``reduce_and_step`` of the step it
+        describes, identically on every rank.
+
+        Reference: the gradient header of GradientReduction (src/Idrak.Network/Training/GradientReduction.cs:780-812)
+        and the stop agreement it carries (AllReduceStopAgreement.cs)."""
+        W, r, dev = self.world, self.rank, self.device
+        n_pres = 0 if presence is None else int(presence.numel())
+        v = torch.zeros(W + 2 + n_pres, dtype=torch.float32, device=dev)
+        t = tokens if torch.is_tensor(tokens) else torch.tensor(float(tokens), device=dev)
+        t = t.to(dev, torch.float32).reshape(())
+        v[r] = t
+        if loss is not None:
+            v[W] = (loss if torch.is_tensor(loss) else torch.tensor(float(loss), device=dev)).to(dev, torch.float32).reshape(()) * t
+        v[W + 1] = 1.0 if stop else 0.0
+        if n_pres:
+            v[W + 2:] = presence.to(dev, torch.float32).reshape(-1)
+        if self.mode == "fused" and self.comm is not None and v.numel() <= self.comm.SLOT_FLOATS:
+            total = self.comm.all_reduce_small(v)
+        else:
+            total = v.clone()
+            dist.all_reduce(total, group=self.group)
+        tokens_all = total[:W].sum()
+        weights = total[:W] / tokens_all.clamp(min=1.0)
+        if self.mode == "fused":
+            self.rank_weights = weights.contiguous()
+        else:
+            self._nccl_weight = weights[r] * W          # scales this rank's gradients before the 1/W all-reduce mean
+        return {"tokens": tokens_all, "loss": total[W] / tokens_all.clamp(min=1.0), "stop": total[W + 1],
+                "presence": total[W + 2:] if n_pres else None, "weights": weights}
+
     # ------------------------------------------------------------------ hooks
     def _install_hooks(self, params):
         index_of = {id(p): i for i, p in enumerate(self.flat.params)}
@@ -262,6 +302,9 @@ class DataParallel:
         main = torch.cuda.current_stream()
         if self.mode == "nccl":
             view = self.flat.grad[s:e]
+            w = getattr(self, "_nccl_weight", None)
+            if w is not None:
+                view.mul_(w.to(view.dtype))
             view.div_(self.world)
             self._work.append(dist.all_reduce(view, group=self.group, async_op=True))
             return
@@ -308,7 +351,7 @@ class DataParallel:
                     self.comm.ctx, self._param_buf.ptr_array, s, e - s, self.shard_offsets[b],
                     self.shard_grad.data_ptr(), opt.master.data_ptr(), opt.m.data_ptr(), opt.v.data_ptr(),
                     self.decay_flags.data_ptr(), opt._hyper_dev.data_ptr(), float(opt.weight_decay), CH_STEP_DONE,
-                    1 if b == nb - 1 else 0, 2 * self.rs_blocks, s_ptr)
+                    1 if b == nb - 1 else 0, self.update_blocks, s_ptr)
                 _native.check(rc, "idrak_dp_adamw_allgather")
             # every peer's last update kernel has published "done": their stores into my parameters landed and
             # they no longer read my gradients

@@ -100,7 +100,12 @@ class LLMEngine:
     def __init__(self, model: Decoder, num_blocks: Optional[int] = None, block_size: int = 16, max_batch: int = 64,
                  max_prefill_tokens: int = 8192, queue_limit: int = 0, prefix_sharing: bool = True,
                  eos_token_ids: Sequence[int] = (), cache_bytes: Optional[int] = None,
-                 clock: Callable[[], float] = time.monotonic, use_graph: bool = True):
+                 clock: Callable[[], float] = time.monotonic, use_graph: bool = True, tp=None,
+                 kv_dtype: Optional[torch.dtype] = None):
+        """``tp``: a ``parallel.tp_serve.TPServeContext`` when ``model`` is one rank's slice of a tensor-parallel
+        decoder. Every rank of the group then runs an engine of its own over the same requests in lock-step: the
+        scheduler is deterministic and the sampled tokens are equal on every rank, so the engines stay in step
+        without exchanging anything but the activations."""
         spec = model.spec
         p = next(model.parameters())
         if num_blocks is None:
@@ -110,11 +115,24 @@ class LLMEngine:
                     cache_bytes = int(free * 0.8)
                 else:
                     cache_bytes = 256 << 20
-            num_blocks = ModelRunner.blocks_that_fit(spec, cache_bytes, block_size, p.element_size())
+            num_blocks = ModelRunner.blocks_that_fit(spec, cache_bytes, block_size,
+                                                     1 if kv_dtype == torch.int8 else p.element_size())
             # no point in holding more than every slot at full context
             num_blocks = min(num_blocks, max_batch * ((spec.max_positions + block_size - 1) // block_size))
+            if tp is not None:
+                # the ranks' schedulers must make the same decisions: size every cache like the smallest
+                import torch.distributed as dist
+                t = torch.tensor([num_blocks], dtype=torch.int64, device=p.device)
+                dist.all_reduce(t, op=dist.ReduceOp.MIN, group=tp.comm.group)
+                num_blocks = int(t.item())
         self.spec, self.block_size = spec, block_size
-        self.runner = ModelRunner(model, num_blocks, block_size, max_batch)
+        self.tp = tp
+        if tp is not None:
+            from .tp_runner import TPModelRunner
+            self.runner = TPModelRunner(model, num_blocks, block_size, max_batch, kv_dtype, tp=tp)
+            self.spec = spec = model.tp_full_spec       # token ids, end-of-sequence checks and limits are the whole model's
+        else:
+            self.runner = ModelRunner(model, num_blocks, block_size, max_batch, kv_dtype)
         self.sched = Scheduler(num_blocks, block_size, max_batch, max_prefill_tokens, queue_limit, prefix_sharing)
         self.eos = set(int(t) for t in eos_token_ids)
         self.clock = clock
@@ -192,7 +210,14 @@ class LLMEngine:
         """Pick one token per row on the device; one host read of ``len(reqs)`` ints."""
         vocab, dev = self.spec.vocabulary, logits.device
         want_lp = any(r.options.return_logprobs for r in reqs)
-        if all(r.options.greedy and not r.options.penalised for r in reqs):
+        all_greedy = all(r.options.greedy and not r.options.penalised for r in reqs)
+        if self.tp is not None:
+            if all_greedy and not want_lp:
+                # per-rank arg-max of the vocabulary slice, merged across ranks on the device
+                ids = self.tp.argmax(logits, self.runner.vocab_local, self.runner.vocab_offset)
+                return ids.tolist(), None
+            logits = self.tp.gather_logits(logits)      # the whole distribution for samplers that need it
+        if all_greedy:
             ids = dops.argmax_rows(logits, vocab)
         else:
             o = [r.options for r in reqs]

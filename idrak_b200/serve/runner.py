@@ -46,6 +46,13 @@ class ModelRunner:
         self.k_cache = [torch.zeros(num_blocks + 1, block_size, s.kv_heads, s.head_dim, dtype=cd, device=self.device)
                         for _ in range(s.layers)]
         self.v_cache = [torch.zeros_like(k) for k in self.k_cache]
+        # an int8 cache keeps one fp32 scale per (slot, kv head) beside the codes
+        self.kv_int8 = cd == torch.int8
+        self.k_scale = self.v_scale = [None] * s.layers
+        if self.kv_int8:
+            self.k_scale = [torch.zeros(num_blocks + 1, block_size, s.kv_heads, dtype=torch.float32, device=self.device)
+                            for _ in range(s.layers)]
+            self.v_scale = [torch.zeros_like(k) for k in self.k_scale]
         self.trash_block = num_blocks
         self.max_blocks_per_seq = (s.max_positions + block_size - 1) // block_size
         self._graphs = {}
@@ -55,7 +62,7 @@ class ModelRunner:
     # ------------------------------------------------------------------ sizing
     @staticmethod
     def blocks_that_fit(spec, bytes_available: int, block_size: int = 16, elem_bytes: int = 2) -> int:
-        per_block = 2 * spec.layers * block_size * spec.kv_heads * spec.head_dim * elem_bytes
+        per_block = 2 * spec.layers * block_size * spec.kv_heads * (spec.head_dim * elem_bytes + (4 if elem_bytes == 1 else 0))
         return max(int(bytes_available // per_block), 1)
 
     # ------------------------------------------------------------------ shared pieces
@@ -86,6 +93,32 @@ class ModelRunner:
             return project_with_adapters(a, attn.o_weight, attn.o_bias, adapters, {"o": (0, self.spec.dim)}, residual,
                                          packed=packed.get("o"))
         return project(a, attn.o_weight, packed.get("o"), attn.o_bias, residual)
+
+    def _rotate_and_cache(self, attn, qkv2, positions, slots, li: int) -> None:
+        """Query / key norms, RoPE (both in place on the packed projection) and the cache write of the new keys and
+        values: one fused launch where the kernel covers the model's settings, the separate steps otherwise."""
+        s = self.spec
+        rope = attn.rope
+        if rope is None or rope.scaling is None:
+            qn = attn.q_norm.effective_weight() if s.qk_norm else None
+            kn = attn.k_norm.effective_weight() if s.qk_norm else None
+            dops.norm_rope_kv(qkv2, s.heads, s.kv_heads, s.head_dim, positions, slots, self.k_cache[li], self.v_cache[li],
+                              self.k_scale[li], self.v_scale[li], qn, kn, s.norm_epsilon,
+                              rope.theta if rope is not None else None, rope.rotary_dim if rope is not None else None)
+            return
+        self._rotate(attn, qkv2, positions)
+        dops.norm_rope_kv(qkv2, s.heads, s.kv_heads, s.head_dim, None, slots, self.k_cache[li], self.v_cache[li],
+                          self.k_scale[li], self.v_scale[li])
+
+    def _cached_kv(self, li: int, blocks: torch.Tensor, total: int, dtype):
+        """Keys and values of positions ``0 .. total`` of one sequence read back from its blocks: ``[1, total, Hkv, D]``."""
+        s = self.spec
+        k = self.k_cache[li][blocks].reshape(-1, s.kv_heads, s.head_dim)[:total]
+        v = self.v_cache[li][blocks].reshape(-1, s.kv_heads, s.head_dim)[:total]
+        if self.kv_int8:
+            k = k.float() * self.k_scale[li][blocks].reshape(-1, s.kv_heads)[:total, :, None]
+            v = v.float() * self.v_scale[li][blocks].reshape(-1, s.kv_heads)[:total, :, None]
+        return k[None].to(dtype), v[None].to(dtype)
 
     def _rotate(self, attn, qkv2, positions):
         """RoPE (and query / key norms) in place on the packed ``[T, (H + 2 Hkv) D]`` projection."""
@@ -166,11 +199,10 @@ class ModelRunner:
             li = layer_index[id(attn)]
             qkv = self._qkv(attn, h)
             qkv2 = qkv.view(-1, qkv.shape[-1])
-            self._rotate(attn, qkv2, pos_t)
+            self._rotate_and_cache(attn, qkv2, pos_t, slots_t, li)
             q = qkv2[:, : H * D].unflatten(-1, (H, D))
             k = qkv2[:, H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D))
             v = qkv2[:, (H + Hkv) * D:].unflatten(-1, (Hkv, D))
-            dops.kv_write_paged(k, v, slots_t, self.k_cache[li], self.v_cache[li])
             window = s.sliding_window if s.is_windowed(attn.layer) else None
             fast = window is None and s.attention_softcap is None
             out = torch.empty(qkv2.shape[0], H * D, dtype=qkv.dtype, device=dev)
@@ -190,8 +222,7 @@ class ModelRunner:
                 qi = q[a:b][None]
                 if it.start > 0:     # queries see the shared prefix too: read keys / values back from the cache
                     total = it.start + (b - a)
-                    ki = self.k_cache[li][tables[i]].reshape(-1, Hkv, D)[:total][None].to(qkv.dtype)
-                    vi = self.v_cache[li][tables[i]].reshape(-1, Hkv, D)[:total][None].to(qkv.dtype)
+                    ki, vi = self._cached_kv(li, tables[i], total, qkv.dtype)
                 else:
                     ki, vi = k[a:b][None], v[a:b][None]
                 if fast:
@@ -229,15 +260,13 @@ class ModelRunner:
             li = layer_index[id(attn)]
             qkv = self._qkv(attn, h)
             qkv2 = qkv.view(-1, qkv.shape[-1])
-            self._rotate(attn, qkv2, positions)
+            self._rotate_and_cache(attn, qkv2, positions, slots, li)
             q = qkv2[:, : H * D].unflatten(-1, (H, D))
-            k = qkv2[:, H * D: (H + Hkv) * D].unflatten(-1, (Hkv, D))
-            v = qkv2[:, (H + Hkv) * D:].unflatten(-1, (Hkv, D))
-            dops.kv_write_paged(k, v, slots, self.k_cache[li], self.v_cache[li])
             window = s.sliding_window if s.is_windowed(attn.layer) else 0
             if s.attention_softcap is None:
                 o = dops.paged_decode(q, self.k_cache[li], self.v_cache[li], block_table, lens,
-                                      attn.scale, window or 0, max_len_hint=max_len_hint)
+                                      attn.scale, window or 0, max_len_hint=max_len_hint,
+                                      k_scale=self.k_scale[li], v_scale=self.v_scale[li])
             else:
                 o = self._decode_softcap(q, li, block_table, lens, attn.scale, window or None)
             return self._out(attn, o.reshape(1, n, H * D), residual)
@@ -303,8 +332,7 @@ class ModelRunner:
         for i in range(q.shape[0]):
             n = int(lens[i])
             blocks = block_table[i, : (n + self.block_size - 1) // self.block_size].long()
-            k = self.k_cache[li][blocks].reshape(-1, s.kv_heads, s.head_dim)[:n][None].to(q.dtype)
-            v = self.v_cache[li][blocks].reshape(-1, s.kv_heads, s.head_dim)[:n][None].to(q.dtype)
+            k, v = self._cached_kv(li, blocks, n, q.dtype)
             out[i] = masked_attention(q[i][None, None], k, v, scale, window, s.attention_softcap)[0, 0]
         return out
 

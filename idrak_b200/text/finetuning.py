@@ -56,8 +56,11 @@ class FineTuningOptions:
     non_finite_steps: int = 8            # give up after this many skipped steps in a row
     checkpoint_blocks: bool = False      # recompute block activations in backward
     activation_ladder: bool = True       # estimate activation memory before the first step, step down on out-of-memory
-    loss: str = "sft"                    # sft | dpo
+    loss: str = "sft"                    # sft | dpo | orpo | simpo (or a name registered in PREFERENCE_LOSSES)
     dpo_beta: float = 0.1
+    orpo_lambda: float = 0.1             # weight of ORPO's odds-ratio term
+    simpo_beta: float = 2.0              # SimPO's reward scale and target margin
+    simpo_gamma: float = 1.0
     save_every: int = 0                  # steps; 0 = only at the end
     eval_every: int = 0
     seed: int = 0
@@ -210,14 +213,60 @@ def adapters_disabled(model):
             mod.adapters = a
 
 
-def sequence_logprobs(model, batch: PackedBatch, device) -> torch.Tensor:
-    """Sum of the trained tokens' log-probabilities of every sequence of a packed batch ``[len(spans)]``."""
+def sequence_logprobs(model, batch: PackedBatch, device, mean: bool = False) -> torch.Tensor:
+    """Sum (or, with ``mean``, the per-token mean) of the trained tokens' log-probabilities of every sequence of a
+    packed batch ``[len(spans)]``."""
     logits = model(batch.ids.to(device), batch.positions.to(device), spans=batch.spans)[0].float()
     lp = torch.log_softmax(logits, -1)
     tgt = batch.targets[0].to(device)
     keep = tgt != IGNORE
     tok = lp.gather(1, tgt.clamp(min=0)[:, None])[:, 0] * keep
+    if mean:
+        return torch.stack([tok[lo:hi].sum() / keep[lo:hi].sum().clamp(min=1) for lo, hi in batch.spans])
     return torch.stack([tok[lo:hi].sum() for lo, hi in batch.spans])
+
+
+# --------------------------------------------------------------------------- preference losses
+# Each takes (tuner, batch) with the chosen answer as sequence 0 and the rejected one as sequence 1 of the batch and
+# returns a scalar. Registered by name so an application can add its own (the reference's PreferenceLosses registry,
+# src/Idrak.Text/FineTuningLosses.cs:560-660).
+def _dpo_loss(tuner, b):
+    policy = sequence_logprobs(tuner.model, b, tuner.device)
+    with torch.no_grad(), adapters_disabled(tuner.model):
+        ref = sequence_logprobs(tuner.model, b, tuner.device)
+    margin = (policy[0] - policy[1]) - (ref[0] - ref[1])
+    return -torch.nn.functional.logsigmoid(tuner.o.dpo_beta * margin)
+
+
+def orpo_from_means(chosen_mean: torch.Tensor, rejected_mean: torch.Tensor, lam: float) -> torch.Tensor:
+    """Odds-ratio preference optimisation (Hong et al. 2024) from the answers' mean token log-probabilities a < 0:
+    ``-a_c - lam * log sigmoid(log odds_c - log odds_r)`` with ``log odds = a - log(1 - exp a)``; no reference model."""
+    def log_odds(a):
+        return a - torch.log(1.0 - torch.exp(a) + 1e-7)
+    return -chosen_mean - lam * torch.nn.functional.logsigmoid(log_odds(chosen_mean) - log_odds(rejected_mean))
+
+
+def simpo_from_means(chosen_mean: torch.Tensor, rejected_mean: torch.Tensor, beta: float, gamma: float) -> torch.Tensor:
+    """Simple preference optimisation (Meng et al. 2024): ``-log sigmoid(beta (a_c - a_r) - gamma)`` with a the mean
+    token log-probability of an answer (a length-normalised reward) and gamma a target margin; no reference model."""
+    return -torch.nn.functional.logsigmoid(beta * (chosen_mean - rejected_mean) - gamma)
+
+
+def _orpo_loss(tuner, b):
+    if tuner.o.orpo_lambda < 0:
+        raise ValueError("orpo_lambda must not be negative")
+    means = sequence_logprobs(tuner.model, b, tuner.device, mean=True)
+    return orpo_from_means(means[0], means[1], tuner.o.orpo_lambda)
+
+
+def _simpo_loss(tuner, b):
+    if tuner.o.simpo_beta <= 0:
+        raise ValueError("simpo_beta must be positive")
+    means = sequence_logprobs(tuner.model, b, tuner.device, mean=True)
+    return simpo_from_means(means[0], means[1], tuner.o.simpo_beta, tuner.o.simpo_gamma)
+
+
+PREFERENCE_LOSSES: Dict[str, Callable] = {"dpo": _dpo_loss, "orpo": _orpo_loss, "simpo": _simpo_loss}
 
 
 class FineTuner:
@@ -280,8 +329,10 @@ class FineTuner:
     # ------------------------------------------------------------------ data
     def batches(self, examples: Iterable[Dict[str, Any]]) -> List[PackedBatch]:
         o = self.o
-        if o.loss == "dpo":
+        if o.loss in PREFERENCE_LOSSES:
             return self._preference_batches(examples)
+        if o.loss != "sft":
+            raise ValueError(f"unknown loss '{o.loss}'; known: sft, {', '.join(sorted(PREFERENCE_LOSSES))}")
         enc = [encode_example(e, self.tokenizer, self.template, o.max_length) for e in examples]
         return pack_batches(enc, o.batch_tokens, o.max_length, o.packing)
 
@@ -296,12 +347,10 @@ class FineTuner:
     # ------------------------------------------------------------------ losses
     def batch_loss(self, b: PackedBatch) -> torch.Tensor:
         dev = self.device
-        if self.o.loss == "dpo":
-            policy = sequence_logprobs(self.model, b, dev)
-            with torch.no_grad(), adapters_disabled(self.model):
-                ref = sequence_logprobs(self.model, b, dev)
-            margin = (policy[0] - policy[1]) - (ref[0] - ref[1])
-            return -torch.nn.functional.logsigmoid(self.o.dpo_beta * margin)
+        if self.o.loss in PREFERENCE_LOSSES:
+            if len(b.spans) < 2:          # chosen, rejected (and possibly an untrained padding tail)
+                raise ValueError(f"the '{self.o.loss}' loss needs pairs: examples with 'prompt', 'chosen' and 'rejected'")
+            return PREFERENCE_LOSSES[self.o.loss](self, b)
         return self.model.loss(b.ids.to(dev), b.targets.to(dev), b.positions.to(dev), ignore_index=IGNORE, spans=b.spans)
 
     @torch.no_grad()

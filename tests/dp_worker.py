@@ -24,13 +24,21 @@ def main():
 
     spec = DecoderSpec.gpt2(layers=2, dim=256, heads=4, vocab=1000, max_positions=128)
     model = build_decoder(spec, seed=7).to(dev, torch.bfloat16)
+    uneven = mode.endswith("_header")         # ranks hold different numbers of sequences; the header carries the weights
+    mode = mode.replace("_header", "")
     sync = DataParallel(model, lr=1e-3, weight_decay=0.1, max_grad_norm=1.0, mode=mode, bucket_mb=0.5)
     step = TrainStep(model, sync.optimizer, sync=sync, use_graph=False, ignore_index=None)
     g = torch.Generator().manual_seed(100)
     data = torch.randint(0, 1000, (steps, world * 4, 129), generator=g)
     losses = []
+    total = world * 4
+    cuts = [0] + [2 + 4 * r for r in range(world - 1)] + [total] if uneven else [4 * r for r in range(world + 1)]
+    headers = []
     for s in range(steps):
-        mine = data[s, rank * 4:(rank + 1) * 4].to(dev)
+        mine = data[s, cuts[rank]:cuts[rank + 1]].to(dev)
+        if uneven:
+            h = sync.step_header(mine.shape[0] * 128, stop=(s == steps - 1 and rank == world - 1))
+            headers.append((float(h["tokens"]), float(h["stop"])))
         loss = step(mine[:, :-1].contiguous(), mine[:, 1:].contiguous())
         losses.append(float(loss.item()))
     torch.cuda.synchronize()
@@ -41,8 +49,8 @@ def main():
     dist.all_gather(gathered, flat)
     same = all(torch.equal(gathered[0], t) for t in gathered)
     if rank == 0:
-        torch.save({"weights": flat.cpu(), "losses": losses, "same": same, "grad_norm": sync.optimizer.grad_norm()},
-                   out_path)
+        torch.save({"weights": flat.cpu(), "losses": losses, "same": same, "grad_norm": sync.optimizer.grad_norm(),
+                    "headers": headers}, out_path)
     sync.close()
     dist.destroy_process_group()
 

@@ -109,3 +109,69 @@ def test_sampler_ties_do_not_crowd_out_larger_logits():
         assert torch.equal(a, b)
         seen |= set(a.tolist())
     assert seen <= allowed and set(big) <= seen, sorted(seen)
+
+
+@pytest.mark.parametrize("H,Hkv,Dh,rot", [(8, 2, 64, 64), (32, 8, 128, 128), (4, 4, 128, 64), (6, 2, 256, 128)])
+@pytest.mark.parametrize("qk_norm", [False, True])
+def test_fused_norm_rope_kv_write_matches_the_separate_steps(H, Hkv, Dh, rot, qk_norm):
+    """One launch = query / key RMS norm + RoPE (in place on the packed projection) + paged cache write; compared with
+    the same steps composed on the CPU path of the op."""
+    T, bs, nb = 45, 16, 12
+    qkv = _rand((T, (H + 2 * Hkv) * Dh), 1)
+    pos = torch.randint(0, 3000, (T,), dtype=torch.int32, device="cuda")
+    slots = torch.randperm(nb * bs)[:T].to(torch.int32).cuda()
+    slots[7] = -1
+    qn = (_rand((Dh,), 2).float() * 0.1 + 1).to(torch.bfloat16) if qk_norm else None
+    kn = (_rand((Dh,), 3).float() * 0.1 + 1).to(torch.bfloat16) if qk_norm else None
+    kc = torch.zeros((nb, bs, Hkv, Dh), dtype=torch.bfloat16, device="cuda")
+    vc = torch.zeros_like(kc)
+    got = qkv.clone()
+    D.norm_rope_kv(got, H, Hkv, Dh, pos, slots, kc, vc, None, None, qn, kn, 1e-6, 10000.0, rot)
+    want = qkv.cpu().clone()
+    kc2, vc2 = torch.zeros_like(kc).cpu(), torch.zeros_like(vc).cpu()
+    D.norm_rope_kv(want, H, Hkv, Dh, pos.cpu(), slots.cpu(), kc2, vc2, None, None,
+                   qn.cpu() if qn is not None else None, kn.cpu() if kn is not None else None, 1e-6, 10000.0, rot)
+    assert (got.float().cpu() - want.float()).abs().max().item() < 3e-2
+    assert (kc.float().cpu() - kc2.float()).abs().max().item() < 3e-2
+    assert torch.equal(vc.cpu(), vc2)                       # values are copied, bit for bit
+    # what the cache holds for keys is exactly what stayed in the projection buffer
+    k_rows = got[:, H * Dh:(H + Hkv) * Dh].unflatten(-1, (Hkv, Dh))
+    keep = slots >= 0
+    assert torch.equal(kc.view(-1, Hkv, Dh)[slots[keep].long()], k_rows[keep])
+
+
+@pytest.mark.parametrize("H,Hkv,Dh", [(32, 8, 128), (12, 12, 64), (4, 1, 128)])
+@pytest.mark.parametrize("splits", [1, 4, None])
+def test_int8_kv_cache_write_and_decode(H, Hkv, Dh, splits):
+    """int8 codes + one scale per (slot, kv head): the fused write against the plain quantiser, and decode attention
+    over the codes against the reference over the de-quantised cache."""
+    bs, nblocks, seqs, T = 16, 120, 4, 600
+    lens = [1, 50, 333, 216]
+    table = torch.randperm(nblocks)[: seqs * 24].reshape(seqs, 24).to(torch.int32).cuda()
+    kc = torch.zeros((nblocks, bs, Hkv, Dh), dtype=torch.int8, device="cuda")
+    vc = torch.zeros_like(kc)
+    ks = torch.zeros((nblocks, bs, Hkv), dtype=torch.float32, device="cuda")
+    vs = torch.zeros_like(ks)
+    qkv = _rand((T, (H + 2 * Hkv) * Dh), 5)
+    slots, t = [], 0
+    for s_, n in enumerate(lens):
+        for p_ in range(n):
+            slots.append(int(table[s_, p_ // bs]) * bs + p_ % bs)
+    slots = torch.tensor(slots, dtype=torch.int32, device="cuda")
+    D.norm_rope_kv(qkv, H, Hkv, Dh, None, slots, kc, vc, ks, vs)
+    k_src = qkv[:, H * Dh:(H + Hkv) * Dh].unflatten(-1, (Hkv, Dh))
+    q8, sc = D.quantize_kv_reference(k_src)
+    got_codes = kc.view(-1, Hkv, Dh)[slots.long()].to(torch.int16)
+    assert (got_codes - q8.to(torch.int16)).abs().max().item() <= 1          # division vs reciprocal at a tie
+    assert torch.allclose(ks.view(-1, Hkv)[slots.long()], sc, rtol=1e-6)
+    lens_t = torch.tensor(lens, dtype=torch.int32, device="cuda")
+    q = _rand((seqs, H, Dh), 6)
+    out = D.paged_decode(q, kc, vc, table, lens_t, splits=splits, k_scale=ks, v_scale=vs)
+    ref = D.paged_decode_reference(q, kc, vc, table, lens_t, k_scale=ks, v_scale=vs)
+    assert (out.float() - ref.float()).abs().max().item() < 2e-2
+    # and close to attention over the unquantised keys / values (what the int8 cache costs)
+    kb = torch.zeros((nblocks, bs, Hkv, Dh), dtype=torch.bfloat16, device="cuda")
+    vb = torch.zeros_like(kb)
+    D.norm_rope_kv(qkv, H, Hkv, Dh, None, slots, kb, vb)
+    exact = D.paged_decode_reference(q, kb, vb, table, lens_t)
+    assert (out.float() - exact.float()).abs().max().item() < 6e-2

@@ -77,3 +77,17 @@ def test_peer_memory_collectives_match_nccl_and_back_to_back_gathers_do_not_over
     for rank, ok in enumerate(torch.load(out)):
         bad = [k for k, v in ok.items() if not v]
         assert not bad, f"rank {rank}: {bad}"
+
+
+def test_step_header_gives_the_token_weighted_mean_when_ranks_hold_different_batches(tmp_path):
+    """Rank 0 trains on 2 sequences, rank 1 on 6: with the header's token weights the fused path must still follow
+    the single process that sees all 8, and the stop request of the last rank must reach everyone."""
+    fused = _run("fused_header", tmp_path / "h.pt", port=29645)
+    assert fused["same"]
+    single_w, _ = _single(4)
+    ulp = 2.0 ** -7 + 1e-6
+    d = (fused["weights"] - single_w).abs()
+    assert d.max().item() <= ulp, d.max().item()
+    assert (d > 5e-3).float().mean().item() < 2e-3
+    assert [h[0] for h in fused["headers"]] == [8 * 128.0] * 4
+    assert [h[1] for h in fused["headers"]] == [0.0, 0.0, 0.0, 1.0]

@@ -101,6 +101,28 @@ def test_dpo_prefers_chosen_and_non_finite_steps_stop():
     assert ft.result.skipped_steps == 3 and ft.result.steps == 0
 
 
+def test_orpo_and_simpo_need_no_reference_and_prefer_the_chosen_answer():
+    """Closed forms on hand-made mean log-probabilities, then a short run of each through the tuner."""
+    from idrak_b200.text.finetuning import PREFERENCE_LOSSES, orpo_from_means, simpo_from_means
+    a_c, a_r = torch.tensor(-0.5), torch.tensor(-1.5)
+    odds = lambda a: a - math.log(1 - math.exp(a) + 1e-7)
+    want = 0.5 - 0.1 * math.log(1 / (1 + math.exp(-(odds(-0.5) - odds(-1.5)))))
+    assert float(orpo_from_means(a_c, a_r, 0.1)) == pytest.approx(want, rel=1e-5)
+    assert float(simpo_from_means(a_c, a_r, 2.0, 1.0)) == pytest.approx(math.log(1 + math.exp(-(2.0 * 1.0 - 1.0))), rel=1e-5)
+    assert float(simpo_from_means(a_r, a_c, 2.0, 1.0)) > float(simpo_from_means(a_c, a_r, 2.0, 1.0))
+    assert {"dpo", "orpo", "simpo"} <= set(PREFERENCE_LOSSES)
+    pairs = [{"prompt": "q: ", "chosen": "yes yes", "rejected": "no no"}] * 4
+    for name in ("orpo", "simpo"):
+        model, tok = _model()
+        o = FineTuningOptions(rank=4, alpha=8, learning_rate=5e-2, loss=name, max_length=32, max_steps=12,
+                              warmup_fraction=0.1)
+        res = FineTuner.train(model, tok, pairs, options=o)
+        assert res.losses[-1] < 0.7 * res.losses[0], (name, res.losses[0], res.losses[-1])
+    model, tok = _model()
+    with pytest.raises(ValueError, match="unknown loss"):
+        FineTuner(model, tok, FineTuningOptions(loss="ppo", max_length=32)).batches(pairs)
+
+
 def test_activation_estimate_and_ladder():
     from idrak_b200.models import DecoderSpec
     from idrak_b200.text import activation_memory as am

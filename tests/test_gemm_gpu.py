@@ -77,6 +77,12 @@ def test_gemm_epilogues():
     _check(out, ref)
     g = gemm(a, b, act="gelu_grad", aux=pre)
     _check(g, gemm_reference(a, b, act="gelu_grad", aux=pre, out_dtype=torch.float32))
+    # the training pair: activation and derivative out of the forward epilogue, one multiply in the backward one
+    out_d, dact = gemm(a, b, bias=bias, act="gelu_d")
+    ref_d, ref_dact = gemm_reference(a, b, bias=bias, act="gelu_d", out_dtype=torch.float32)
+    _check(out_d, ref_d)
+    _check(dact, ref_dact)
+    _check(gemm(a, b, act="mul_aux", aux=dact), gemm_reference(a, b, act="mul_aux", aux=dact, out_dtype=torch.float32))
     acc = torch.ones((M, N), dtype=torch.float32, device="cuda")
     gemm(a, b, out=acc, beta=True, alpha=0.5)
     _check(acc, gemm_reference(a, b, alpha=0.5, out_dtype=torch.float32) + 1.0)
@@ -135,6 +141,11 @@ def _pair_case(M, N, K, a_mn, b_mn):
         _check(pre, r_pre)
         _check(o, r)
         _check(gemm(a, b, act="gelu_grad", aux=pre, splits=1), gemm_reference(a, b, act="gelu_grad", aux=pre, out_dtype=torch.float32))
+        o, dact = gemm(a, b, bias=bias, act="gelu_d", splits=1)
+        r, r_dact = gemm_reference(a, b, bias=bias, act="gelu_d", out_dtype=torch.float32)
+        _check(dact, r_dact)
+        _check(o, r)
+        _check(gemm(a, b, act="mul_aux", aux=dact, splits=1), gemm_reference(a, b, act="mul_aux", aux=dact, out_dtype=torch.float32))
         acc = torch.ones((M, N), dtype=torch.float32, device="cuda")
         gemm(a, b, out=acc, beta=True, alpha=0.5, splits=1)
         _check(acc, gemm_reference(a, b, alpha=0.5, out_dtype=torch.float32) + 1.0)

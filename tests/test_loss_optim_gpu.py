@@ -28,6 +28,35 @@ def test_softmax_xent_loss_and_grad(rows, vocab, ld):
     assert work[:, vocab:].abs().max().item() == 0 if ld > vocab else True
 
 
+@pytest.mark.parametrize("rows,vocab,ld", [(300, 1000, 1000), (301, 50257, 50304), (1024, 257, 264), (777, 32000, 32000)])
+def test_softmax_xent_pipelined_rows(rows, vocab, ld):
+    """Enough rows for one persistent CTA per SM with two rows in flight (the bulk-copy kernel): loss, gradient,
+    zero padding columns, an ignored row, the no-gradient mode leaving the logits untouched, and equal bits on a
+    second run."""
+    logits = _rand((rows, ld), 2.0, 5)
+    g = torch.Generator(device="cuda").manual_seed(6)
+    t = torch.randint(0, vocab, (rows,), generator=g, device="cuda")
+    t[3] = -100
+    t[5] = vocab - 1
+    ref_l = logits[:, :vocab].float().requires_grad_()
+    loss_ref = torch.nn.functional.cross_entropy(ref_l, t, ignore_index=-100, reduction="none")
+    loss_ref.sum().backward()
+    keep = logits.clone()
+    only = ops.softmax_xent_(keep, t, vocab, 1.0, -100, False)
+    assert torch.equal(keep, logits)
+    assert (only - loss_ref).abs().max().item() < 2e-2
+    work = logits.clone()
+    losses = ops.softmax_xent_(work, t, vocab, 0.5, -100, True)
+    assert (losses - loss_ref).abs().max().item() < 2e-2
+    assert (work[:, :vocab].float() - 0.5 * ref_l.grad).abs().max().item() < 1e-2
+    assert work[3].abs().max().item() == 0
+    if ld > vocab:
+        assert work[:, vocab:].abs().max().item() == 0
+    again = logits.clone()
+    losses2 = ops.softmax_xent_(again, t, vocab, 0.5, -100, True)
+    assert torch.equal(again, work) and torch.equal(losses, losses2)
+
+
 def test_token_cross_entropy_chunked_matches_torch():
     T, C, V, Vp = 512, 256, 1000, 1024
     h = _rand((T, C), 1.0, 1).requires_grad_()

@@ -130,3 +130,24 @@ def test_tiny_gpt_trains_on_cpu():
         first = first if first is not None else loss.item()
         last = loss.item()
     assert abs(first - 5.545) < 0.2 and last < first - 0.5
+
+
+def test_packed_spans_equal_separate_sequences_on_the_host():
+    """``spans`` turn into one lower key bound per position; logits of a packed row equal those of each sequence run
+    alone (host statement of what the attention kernels do in one launch)."""
+    import torch
+    from idrak_b200 import ops
+    from idrak_b200.models import DecoderSpec, build_decoder
+    spec = DecoderSpec.llama(layers=2, dim=64, heads=4, kv_heads=2, ff_dim=128, vocab=97, max_positions=64)
+    model = build_decoder(spec, seed=3).float().eval()
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 97, (1, 40), generator=g)
+    spans = [(0, 13), (13, 14), (14, 40)]
+    pos = torch.cat([torch.arange(hi - lo) for lo, hi in spans]).to(torch.int32)
+    rs = ops.row_starts_from_spans(spans, 1, 40)
+    assert rs[0, 12].item() == 0 and rs[0, 13].item() == 13 and rs[0, 39].item() == 14
+    with torch.no_grad():
+        packed = model(ids, pos, spans=spans)
+        for lo, hi in spans:
+            alone = model(ids[:, lo:hi], pos[lo:hi])
+            assert torch.allclose(packed[:, lo:hi], alone, atol=1e-4, rtol=1e-4)

@@ -41,6 +41,61 @@ def test_norm_forward_backward(rows, C, rms):
         _close(b.grad, br.grad, 3e-2)
 
 
+@pytest.mark.parametrize("rows,C", [(64, 64), (1000, 768), (4099, 1024), (16384, 768), (70, 256), (40, 4096)])
+@pytest.mark.parametrize("rms", [False, True])
+def test_norm_branch_adds_the_residual_gradient_and_leaves_column_sums(rows, C, rms):
+    """``(norm(x), x)``: one backward kernel gives d(norm) + d(residual), the norm's parameter gradients and - where
+    the row length fits the pipelined kernel - the column sums of that dx, which a following bias gradient reuses."""
+    x = _rand((rows, C), 1.0, 1).requires_grad_()
+    w = (_rand((C,), 0.2, 2).float() + 1).to(torch.bfloat16).requires_grad_()
+    b = None if rms else _rand((C,), 0.2, 3).requires_grad_()
+    y, xr_out = ops.norm_branch(x, w, b, 1e-5, rms)
+    dy, dres = _rand((rows, C), 1.0, 4), _rand((rows, C), 1.0, 5)
+    got = {}
+    x.register_hook(lambda g: got.setdefault("dx", g))
+    torch.autograd.backward([y, xr_out], [dy, dres])
+    xr, wr = x.detach().float().requires_grad_(), w.detach().float().requires_grad_()
+    br = None if rms else b.detach().float().requires_grad_()
+    if rms:
+        yr = xr * torch.rsqrt(xr.pow(2).mean(-1, keepdim=True) + 1e-5) * wr
+    else:
+        yr = torch.nn.functional.layer_norm(xr, (C,), wr, br, 1e-5)
+    torch.autograd.backward([yr, xr], [dy.float(), dres.float()])
+    _close(y, yr)
+    _close(x.grad, xr.grad)
+    _close(w.grad, wr.grad, 3e-2)
+    if not rms:
+        _close(b.grad, br.grad, 3e-2)
+    tagged = getattr(got["dx"], "_idrak_colsum", None)
+    from idrak_b200 import _native
+    if _native.lib().idrak_norm_bwd_sums_dx(rows, C):
+        assert 256 <= C <= 1024
+        assert tagged is not None and tagged[1] == got["dx"]._version
+        want = got["dx"].float().sum(0)
+        assert (tagged[0] - want).abs().max().item() <= 1e-3 * max(1.0, want.abs().max().item())
+        # deterministic: a second pass gives the same bits
+        x2 = x.detach().clone().requires_grad_()
+        y2, r2 = ops.norm_branch(x2, w.detach().requires_grad_(), None if rms else b.detach().requires_grad_(), 1e-5, rms)
+        again = {}
+        x2.register_hook(lambda g: again.setdefault("dx", g))
+        torch.autograd.backward([y2, r2], [dy, dres])
+        assert torch.equal(again["dx"], got["dx"]) and torch.equal(again["dx"]._idrak_colsum[0], tagged[0])
+
+
+def test_bias_gradient_reuses_the_sums_left_by_the_norm_backward():
+    """linear (with bias) -> pre-norm block input: the bias gradient must equal the one computed by a column-sum pass,
+    and an in-place change of the gradient tensor must make the stale sums unusable."""
+    from idrak_b200.ops.gemm import bias_grad
+    dy = _rand((512, 768), 1.0, 7)
+    ref = ops.colsum(dy)
+    dy._idrak_colsum = (dy.float().sum(0), dy._version)
+    got = bias_grad(dy.reshape(-1, 768), None, dy)
+    _close(got, ref, 1e-2)
+    dy.add_(1.0)                                    # version moves on: the attached sums no longer describe dy
+    got = bias_grad(dy.reshape(-1, 768), None, dy)
+    _close(got, dy.float().sum(0), 1e-2)
+
+
 def test_norm_with_residual_sum():
     x, r = _rand((64, 768), 1.0, 1), _rand((64, 768), 1.0, 2)
     w, b = _rand((768,), 1.0, 3), _rand((768,), 1.0, 4)

@@ -132,3 +132,24 @@ def test_engine_abort_and_queue_timeout():
     eng.abort(a)
     assert eng.requests[a].finish_reason == "abort" and not eng.has_work()
     assert eng.stats()["free_blocks"] == 16
+
+
+def test_engine_with_an_int8_kv_cache_generates_like_the_bf16_cache():
+    """The same greedy continuation (CPU path) with the cache held as int8 codes + scales: first tokens equal, the
+    cache tensors really are int8, and block accounting counts the scales."""
+    import torch
+    from idrak_b200.models import DecoderSpec, build_decoder
+    from idrak_b200.serve import GenerationOptions, LLMEngine
+    from idrak_b200.serve.runner import ModelRunner
+    spec = DecoderSpec.llama(layers=2, dim=64, heads=4, kv_heads=2, ff_dim=128, vocab=300, max_positions=128)
+    model = build_decoder(spec, seed=3).eval()
+    prompts = [list(range(5, 25)), list(range(40, 47))]
+    opts = GenerationOptions.greedy_options(6)
+    a = LLMEngine(model, num_blocks=32, max_batch=4, prefix_sharing=False, use_graph=False)
+    b = LLMEngine(model, num_blocks=32, max_batch=4, prefix_sharing=False, use_graph=False, kv_dtype=torch.int8)
+    out_a = [r.output for r in a.generate(prompts, opts)]
+    out_b = [r.output for r in b.generate(prompts, opts)]
+    assert b.runner.k_cache[0].dtype == torch.int8 and b.runner.k_scale[0] is not None
+    assert [o[0] for o in out_a] == [o[0] for o in out_b]
+    assert sum(x == y for oa, ob in zip(out_a, out_b) for x, y in zip(oa, ob)) >= 10
+    assert ModelRunner.blocks_that_fit(spec, 1 << 20, 16, 1) > ModelRunner.blocks_that_fit(spec, 1 << 20, 16, 2)
