@@ -93,6 +93,29 @@ def cmd_check(a) -> int:
         torch.cuda.synchronize()
         _native.check_status("check")
     report["ok"] = report["decode_tokens"] == 8 and report["train_step_loss"] > 0
+    if getattr(a, "conformance", False):
+        # every operation call of the scenario table, recorded on the CPU and replayed on the device
+        from ..testing import check
+        rep = check(dev)
+        report["conformance"] = json.loads(rep.to_json())
+        report["ok"] = report["ok"] and rep.ok
+    if getattr(a, "contracts", False):
+        from ..testing import SUITES
+        report["contracts"] = {name: make().self_test() for name, make in sorted(SUITES.items())}
+        report["ok"] = report["ok"] and not any(report["contracts"].values())
+    if getattr(a, "stress", 0):
+        from ..testing import run_stress
+        from ..testing.stress import default_workload
+        rep = run_stress(default_workload(dev), steps=a.stress, warmup=14, device=dev,
+                         allowed_growth=0 if dev.startswith("cuda") else 1 << 16)
+        report["stress"] = {"steps": rep.steps, "seconds": round(rep.seconds, 2), "growth_bytes": rep.growth,
+                            "peak_bytes": rep.peak, "errors": rep.errors}
+        report["ok"] = report["ok"] and rep.ok
+    if getattr(a, "regressions", None):
+        from ..testing import replay_folder
+        outs = replay_folder(a.regressions, dev)
+        report["regressions"] = {"cases": len(outs), "failing": [f"{o.op}: {o.detail}" for o in outs if o.status != "ok"]}
+        report["ok"] = report["ok"] and not report["regressions"]["failing"]
     print(json.dumps(report, indent=1))
     return 0 if report["ok"] else 1
 
@@ -503,7 +526,12 @@ def build_parser() -> argparse.ArgumentParser:
     add("devices", cmd_devices, "list CUDA devices")
     p = add("tuning", cmd_tuning, "show the measured per-device decisions (split-K factors, ...)")
     p.add_argument("--forget", nargs="?", const="", metavar="PREFIX", help="drop decisions whose name starts with PREFIX (all without one)")
-    add("check", cmd_check, "run one tiny training step and one decode").add_argument("--device")
+    p = add("check", cmd_check, "run one tiny training step and one decode; optionally the conformance kit")
+    p.add_argument("--device")
+    p.add_argument("--conformance", action="store_true", help="replay every recorded operation call on the device against the CPU")
+    p.add_argument("--contracts", action="store_true", help="run the contract suites against their references and broken twins")
+    p.add_argument("--stress", type=int, default=0, metavar="STEPS", help="run STEPS mixed steps; device memory must not grow")
+    p.add_argument("--regressions", metavar="FOLDER", help="replay saved failing cases")
     from . import extra, more
     extra.register(add)
     more.register(add)
