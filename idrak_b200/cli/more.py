@@ -379,8 +379,15 @@ def cmd_train_tokenizer(a) -> int:
             else:
                 with open(p, "r", encoding="utf-8", errors="replace") as f:
                     yield from f
-    tok = train_bpe(lines(), a.vocab, special_tokens=a.special, min_frequency=a.min_frequency)
     os.makedirs(a.output, exist_ok=True)
+    if getattr(a, "kind", "bpe") == "unigram":
+        from ..text.sentencepiece_model import write_model
+        from ..text.unigram_trainer import train_unigram
+        specials = a.special if a.special != ["<|endoftext|>"] else ["<unk>", "<s>", "</s>"]
+        tok = train_unigram(lines(), a.vocab, special_tokens=specials, byte_fallback=a.byte_fallback)
+        write_model(tok.model, os.path.join(a.output, "tokenizer.model"))       # the SentencePiece form beside the json
+    else:
+        tok = train_bpe(lines(), a.vocab, special_tokens=a.special, min_frequency=a.min_frequency)
     tok.save(os.path.join(a.output, "tokenizer.json"))
     cfg = {}
     if tok.eos_token_ids:
@@ -455,4 +462,6 @@ def register(add) -> None:
     p.add_argument("--vocab", type=int, default=8192)
     p.add_argument("--special", nargs="*", default=["<|endoftext|>"])
     p.add_argument("--min-frequency", type=int, default=2)
+    p.add_argument("--kind", choices=["bpe", "unigram"], default="bpe")
+    p.add_argument("--byte-fallback", action="store_true", help="unigram: add the 256 byte pieces")
     p.add_argument("--field", default="text")

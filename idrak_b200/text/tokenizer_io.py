@@ -45,7 +45,12 @@ def load_tokenizer(folder: str) -> Tokenizer:
         return HfTokenizer.from_file(tj, config, gen)
     tm = os.path.join(folder, "tokenizer.model")
     if os.path.isfile(tm):
-        t = SentencePieceTokenizer(tm, add_bos=bool(config.get("add_bos_token", True)))
+        from .. import config as settings
+        if settings.get("IDRAK_TOKENIZER") == "own":
+            from .sentencepiece_model import load_sentencepiece
+            t = load_sentencepiece(tm)          # this package's reader: no sentencepiece import
+        else:
+            t = SentencePieceTokenizer(tm, add_bos=bool(config.get("add_bos_token", True)))
         if isinstance(config.get("chat_template"), str):
             t.chat_template = config["chat_template"]
         return t

@@ -113,6 +113,11 @@ def build_normalizer(d: Optional[dict]) -> Callable[[str], str]:
         return lambda s: pre + s if s else s
     if t == "BertNormalizer":
         return _bert_normalizer(d)
+    if t == "Precompiled":
+        # SentencePiece's compiled character map (T5, ALBERT, XLM-R ...): base64 of [trie | replacement strings]
+        import base64
+        from .sentencepiece_model import PrecompiledNormalizer
+        return PrecompiledNormalizer(base64.b64decode(d["precompiled_charsmap"]))
     raise ValueError(f"tokenizer.json: normalizer {t!r} is not supported")
 
 
