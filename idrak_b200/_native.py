@@ -74,11 +74,33 @@ _SIGNATURES = {
     "idrak_opt_sgd": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_float, c_int, c_void_p]),
     "idrak_flash_fwd": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 7 + [c_float, c_int, c_void_p]),
     "idrak_flash_bwd": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 9 + [c_float, c_int, c_void_p]),
+    "idrak_route_capacity": (c_int, [c_int, c_int, c_int]),
+    "idrak_route_blocks": (c_int, [c_int]),
+    "idrak_route_choose": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "idrak_route_plan": (c_int, [c_void_p, c_int, c_int, c_int] + [c_void_p] * 9),
+    "idrak_route_gather": (c_int, [c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "idrak_route_combine": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p, c_void_p]),
+    "idrak_gemm_grouped_rows": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                        c_int, c_void_p, c_void_p, c_void_p]),
+    "idrak_gemm_grouped_k": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                     c_int, c_void_p, c_void_p]),
+    "idrak_skinny_gemm": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
+                                  c_void_p, c_int, c_int, c_float, c_void_p]),
+    "idrak_skinny_splits": (c_int, [c_int, c_int]),
     "idrak_flash_fwd_ex": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 7 + [c_float, c_int, c_int, c_void_p, c_float,
                                                                               c_void_p]),
     "idrak_flash_bwd_ex": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 9 + [c_float, c_int, c_int, c_void_p,
                                                                                c_float, c_void_p]),
 }
+
+
+def has(symbol: str) -> bool:
+    """Whether the built library exports ``symbol`` (a library older than the Python sources may not)."""
+    try:
+        getattr(lib(), symbol)
+        return True
+    except (AttributeError, RuntimeError):
+        return False
 
 
 def lib_path() -> Path:

@@ -40,6 +40,12 @@ struct GemmParams {
   unsigned long long* prof;       // role timers [grid][8] (cycles), or null: see idrak_gemm_role_timers
   int epi_mode;                   // EpiMode: which compile-time variant of the staged epilogue fits this product
   Status* st;
+  // grouped products (mixture of experts): rows sorted by expert in segments padded to 128 rows
+  const int* tile_group;          // per-row-tile mode: expert of every 128-row M tile
+  const int* tiles_in_use;        // per-row-tile mode: device scalar, M tiles that hold rows (the rest are skipped)
+  int group_b_rows;               // per-row-tile mode: rows of one expert in the stacked B array
+  const int* group_kb;            // per-expert-K mode: [groups + 1] bounds of each expert's rows in 64-row blocks
+  int groups;                     // per-expert-K mode: experts; C is the stacked [groups * M_per, N] array
 };
 
 // Element-wise part of the epilogue on 8 consecutive columns of one row: bias, activation, residual.
@@ -178,17 +184,21 @@ __device__ __forceinline__ void epilogue8(const GemmParams& p, int row, int col,
   }
 }
 
-__device__ __forceinline__ void unit_to_tile(const GemmParams& p, int unit, int& tm, int& tn, int& split) {
-  const int tiles = p.m_tiles * p.n_tiles;
+__device__ __forceinline__ void unit_to_tile_n(int m_tiles, int n_tiles, int unit, int& tm, int& tn, int& split) {
+  const int tiles = m_tiles * n_tiles;
   split = unit / tiles;
   int t = unit - split * tiles;
-  const int per_group = kGroupM * p.n_tiles;
+  const int per_group = kGroupM * n_tiles;
   int group = t / per_group;
   int first_m = group * kGroupM;
-  int gsz = min(p.m_tiles - first_m, kGroupM);
+  int gsz = min(m_tiles - first_m, kGroupM);
   int r = t - group * per_group;
   tm = first_m + (r % gsz);
   tn = r / gsz;
+}
+
+__device__ __forceinline__ void unit_to_tile(const GemmParams& p, int unit, int& tm, int& tn, int& split) {
+  unit_to_tile_n(p.m_tiles, p.n_tiles, unit, tm, tn, split);
 }
 
 // ---------------------------------------------------------------------------------------------------------------

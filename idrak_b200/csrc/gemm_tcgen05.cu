@@ -37,7 +37,13 @@ struct GemmSmem {
 
 // F8 = 1: both operands are e4m3 bytes, K-major; a 128-byte swizzle row then holds 128 elements of K, the MMA is
 // kind::f8f6f4 (K = 32 per instruction, the same 32 bytes per step), everything else is unchanged.
-template <int BN, int A_MN, int B_MN, int F8 = 0>
+//
+// GROUPED (mixture-of-experts products over rows sorted by expert, segments padded to 128 rows):
+//   1  every M tile belongs to one expert (p.tile_group): the B tile comes from that expert's slice of the stacked
+//      weights; tiles beyond p.tiles_in_use (a device scalar) are not visited. Forward and input-gradient products.
+//   2  one output per expert, C stacked [groups * M, N]; expert g contracts over its own rows only, blocks
+//      [group_kb[g], group_kb[g + 1]) of K. An expert without rows gets zeros. Weight-gradient products.
+template <int BN, int A_MN, int B_MN, int F8 = 0, int GROUPED = 0>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
@@ -59,7 +65,23 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   constexpr int kKB = F8 ? 2 * kBK : kBK;          // elements of K per shared-memory stage
   const int k_blocks_total = (p.K + kKB - 1) / kKB;
   const int kb_per_split = (k_blocks_total + p.splits - 1) / p.splits;
-  const int units = p.m_tiles * p.n_tiles * p.splits;
+  const int m_tiles = (GROUPED == 1) ? min(p.m_tiles, *p.tiles_in_use) : p.m_tiles;
+  const int units = (GROUPED == 2 ? p.groups : p.splits) * m_tiles * p.n_tiles;
+  // unit -> tile (and expert / K range in the grouped modes); every role walks the same sequence
+  auto tile_of = [&](int unit, int& tm, int& tn, int& split, int& group, int& kb0, int& kb1) {
+    if (GROUPED == 2) {
+      const int tiles = m_tiles * p.n_tiles;
+      group = unit / tiles;
+      unit_to_tile_n(m_tiles, p.n_tiles, unit - group * tiles, tm, tn, split);
+      kb0 = p.group_kb[group];
+      kb1 = p.group_kb[group + 1];
+    } else {
+      unit_to_tile_n(m_tiles, p.n_tiles, unit, tm, tn, split);
+      group = (GROUPED == 1) ? p.tile_group[tm] : 0;
+      kb0 = split * kb_per_split;
+      kb1 = min(k_blocks_total, kb0 + kb_per_split);
+    }
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
@@ -92,10 +114,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       uint32_t issued_mask = 0, issued_phase = 0;   // which stages have a copy in flight and on which parity
       bool ok = true;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
-        int tm, tn, split;
-        unit_to_tile(p, unit, tm, tn, split);
-        const int kb0 = split * kb_per_split;
-        const int kb1 = min(k_blocks_total, kb0 + kb_per_split);
+        int tm, tn, split, group, kb0, kb1;
+        tile_of(unit, tm, tn, split, group, kb0, kb1);
+        const int b_row = (GROUPED == 1) ? group * p.group_b_rows : 0;     // the expert's slice of the stacked B
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (1u << 16) | stage)) {
             ok = false;
@@ -112,9 +133,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           }
           if (B_MN) {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB, &full[stage], tn * BN + j * 64, kb * kKB);
+            for (int j = 0; j < BN / 64; ++j)
+              tma_load_2d(sb + j * 8192, &tmB, &full[stage], tn * BN + j * 64, kb * kKB + b_row);
           } else {
-            tma_load_2d(sb, &tmB, &full[stage], kb * kKB, tn * BN);
+            tma_load_2d(sb, &tmB, &full[stage], kb * kKB, tn * BN + b_row);
           }
           issued_mask |= 1u << stage;
           issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
@@ -143,10 +165,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       unsigned long long t_acc = 0, t_ops = 0;
       const long long t_begin = p.prof ? clock64() : 0;
       for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++local) {
-        int tm, tn, split;
-        unit_to_tile(p, unit, tm, tn, split);
-        const int kb0 = split * kb_per_split;
-        const int kb1 = min(k_blocks_total, kb0 + kb_per_split);
+        int tm, tn, split, group, kb0, kb1;
+        tile_of(unit, tm, tn, split, group, kb0, kb1);
         const int buf = local & 1;
         const uint32_t acc_phase = (local >> 1) & 1;
         const long long c0 = p.prof ? clock64() : 0;
@@ -197,18 +217,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     ahead.ready = false;
     ahead.ring = 0;
     for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++local) {
-      int tm, tn, split;
-      unit_to_tile(p, unit, tm, tn, split);
+      int tm, tn, split, group, kb0, kb1;
+      tile_of(unit, tm, tn, split, group, kb0, kb1);
       NextTile next{false, 0, 0};
       if (unit + int(gridDim.x) < units) {
-        int nm, nn, ns;
-        unit_to_tile(p, unit + gridDim.x, nm, nn, ns);
-        next = NextTile{true, nm * kBM, nn * BN};
+        int nm, nn, ns, ng, n0, n1;
+        tile_of(unit + gridDim.x, nm, nn, ns, ng, n0, n1);
+        next = NextTile{true, ((GROUPED == 2 ? ng * m_tiles : 0) + nm) * kBM, nn * BN};
       }
       const int buf = local & 1;
       const uint32_t acc_phase = (local >> 1) & 1;
-      const int kb0 = split * kb_per_split;
-      const bool has_k = kb0 < k_blocks_total;   // a split past the end of K contributes zeros
+      const bool has_k = kb0 < kb1;              // a split past the end of K (or an expert without rows) gives zeros
+      const int row_base = ((GROUPED == 2 ? group * m_tiles : 0) + tm) * kBM;    // stacked outputs: expert g's rows
       const long long c0 = p.prof ? clock64() : 0;
       if (!mbar_wait(&tmem_full[buf], acc_phase, abort_flag, p.st, kTimeoutTmemFull, (1u << 16) | buf)) {
         ok = false;
@@ -217,7 +237,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_after();
       const long long c1 = p.prof ? clock64() : 0;
       uint64_t* done = &tmem_empty[buf];
-      drain_accumulator<BN, 1>(p, &tmC, &tmAux, tmem_base + buf * BN, ewarp, lane, tm * kBM, tn * BN, split, has_k,
+      drain_accumulator<BN, 1>(p, &tmC, &tmAux, tmem_base + buf * BN, ewarp, lane, row_base, tn * BN, split, has_k,
                             staging, ahead, next, [done]() {
                               tc_fence_before();
                               mbar_arrive(done);
@@ -274,11 +294,11 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) 
 // ---------------------------------------------------------------------------
 // host launcher
 // ---------------------------------------------------------------------------
-template <int BN, int A_MN, int B_MN, int F8 = 0>
+template <int BN, int A_MN, int B_MN, int F8 = 0, int GROUPED = 0>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
                        const CUtensorMap& tmAux, const GemmParams& p, int grid, cudaStream_t stream) {
   using L = GemmSmem<BN>;
-  auto kern = gemm_kernel<BN, A_MN, B_MN, F8>;
+  auto kern = gemm_kernel<BN, A_MN, B_MN, F8, GROUPED>;
   static DeviceOnce configured;
   if (int e = configured.run([&] {
         return int(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
@@ -509,4 +529,97 @@ IDRAK_API int idrak_gemm_fp8(const void* A, int lda, const void* B, int ldb, voi
   const int grid = min(units, sm_count());
   if (bn == 256) return launch_gemm<256, 0, 0, 1>(tmA, tmB, tmC, tmAux, p, grid, stream);
   return launch_gemm<128, 0, 0, 1>(tmA, tmB, tmC, tmAux, p, grid, stream);
+}
+
+// ---------------------------------------------------------------------------
+// grouped products for mixture-of-experts layers (rows sorted by expert, segments padded to 128 rows)
+// ---------------------------------------------------------------------------
+namespace {
+
+int grouped_store_map(CUtensorMap* tm, void* C, int rows, int N, int ldc) {
+  uint64_t dims[2] = {uint64_t(N), uint64_t(rows)};
+  uint32_t box[2] = {64, 128};
+  uint64_t str_c[1] = {uint64_t(ldc) * 2};
+  return encode_tensor_map(tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, dims, str_c, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+}  // namespace
+
+// C[cap, N] = A[cap, K] x B_e, expert e = tile_group[row / 128], for the first *tiles_in_use row tiles.
+//   b_mn = 0: B stacked [E * N, K] (the nn.Linear layout per expert): C = A B_e^T        (forward)
+//   b_mn = 1: B stacked [E * K, N]:                                   C = A B_e          (input gradient)
+// K must be a multiple of 64 (a K block must not run into the next expert's rows), lda / ldb / ldc multiples of 8.
+// Reference: expert_matmul (src/Idrak.Gpu/Cuda/PtxKernels.Routing.cs:30-35), which loops over experts on the host.
+IDRAK_API int idrak_gemm_grouped_rows(const void* A, int lda, const void* B, int ldb, int b_mn, void* C, int ldc,
+                                      int cap, int N, int K, int experts, const int* tile_group,
+                                      const int* tiles_in_use, void* stream_) {
+  if (cap <= 0 || N <= 0 || K <= 0) return 0;
+  if ((cap % kBM) || (K % kBK) || (lda & 7) || (ldb & 7) || (ldc & 7) || (N & 7)) return -2;
+  if (!tile_group || !tiles_in_use) return -3;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int bn = (N <= 128) ? 128 : 256;
+  GemmParams p{};
+  p.M = cap; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc;
+  p.alpha = 1.f;
+  p.splits = 1;
+  p.m_tiles = cap / kBM;
+  p.n_tiles = (N + bn - 1) / bn;
+  p.st = status_device_ptr();
+  p.tile_group = tile_group;
+  p.tiles_in_use = tiles_in_use;
+  p.group_b_rows = b_mn ? K : N;
+  CUtensorMap tmA, tmB, tmC, tmAux;
+  memset(&tmAux, 0, sizeof(tmAux));
+  if (make_operand_map(&tmA, A, cap, K, lda, 0, kBM, 0)) return -10;
+  // the stacked weights as one 2-D array: [E * N rows, K] or [E * K rows, N]
+  if (b_mn ? make_operand_map(&tmB, B, N, experts * K, ldb, 1, bn, 0)
+           : make_operand_map(&tmB, B, experts * N, K, ldb, 0, bn, 0))
+    return -12;
+  if ((reinterpret_cast<uintptr_t>(C) & 15) || grouped_store_map(&tmC, C, cap, N, ldc)) return -13;
+  p.tma_store = 1;
+  p.epi_mode = pick_epi_mode(p);
+  p.prof = nullptr;
+  const int grid = min(p.m_tiles * p.n_tiles, sm_count());
+  if (bn == 256)
+    return b_mn ? launch_gemm<256, 0, 1, 0, 1>(tmA, tmB, tmC, tmAux, p, grid, stream)
+                : launch_gemm<256, 0, 0, 0, 1>(tmA, tmB, tmC, tmAux, p, grid, stream);
+  return b_mn ? launch_gemm<128, 0, 1, 0, 1>(tmA, tmB, tmC, tmAux, p, grid, stream)
+              : launch_gemm<128, 0, 0, 0, 1>(tmA, tmB, tmC, tmAux, p, grid, stream);
+}
+
+// dW_e [M, N] = A[rows of e, M]^T x B[rows of e, N] for every expert e, written to C stacked [E * M, N] (bf16, or
+// fp32 with `c_fp32`; `beta` adds to what C holds). Rows of expert e are blocks [group_kb[e], group_kb[e + 1]) of
+// 64 rows of A and B; padding rows inside a segment must be zero. M must be a multiple of 128.
+IDRAK_API int idrak_gemm_grouped_k(const void* A, int lda, const void* B, int ldb, void* C, int ldc, int c_fp32,
+                                   int beta, int cap, int M, int N, int experts, const int* group_kb, void* stream_) {
+  if (cap <= 0 || M <= 0 || N <= 0 || experts <= 0) return 0;
+  if ((M % kBM) || (cap % kBK) || (lda & 7) || (ldb & 7) || (N & 7)) return -2;
+  if (!group_kb) return -3;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int bn = (N <= 128) ? 128 : 256;
+  GemmParams p{};
+  p.M = experts * M; p.N = N; p.K = cap;
+  p.C = C; p.ldc = ldc; p.c_fp32 = c_fp32;
+  p.beta = beta;
+  p.alpha = 1.f;
+  p.splits = 1;
+  p.m_tiles = M / kBM;
+  p.n_tiles = (N + bn - 1) / bn;
+  p.st = status_device_ptr();
+  p.group_kb = group_kb;
+  p.groups = experts;
+  CUtensorMap tmA, tmB, tmC, tmAux;
+  memset(&tmC, 0, sizeof(tmC));
+  memset(&tmAux, 0, sizeof(tmAux));
+  if (make_operand_map(&tmA, A, M, cap, lda, 1, kBM, 0)) return -10;
+  if (make_operand_map(&tmB, B, N, cap, ldb, 1, bn, 0)) return -12;
+  p.tma_store = 0;
+  if (!c_fp32 && !beta && (ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0)
+    p.tma_store = grouped_store_map(&tmC, C, experts * M, N, ldc) == 0 ? 1 : 0;
+  p.epi_mode = pick_epi_mode(p);
+  p.prof = nullptr;
+  const int grid = min(experts * p.m_tiles * p.n_tiles, sm_count());
+  if (bn == 256) return launch_gemm<256, 1, 1, 0, 2>(tmA, tmB, tmC, tmAux, p, grid, stream);
+  return launch_gemm<128, 1, 1, 0, 2>(tmA, tmB, tmC, tmAux, p, grid, stream);
 }

@@ -195,6 +195,29 @@ def case_decode_attn(a):
     return (lambda: paged_decode(q, kc, vc, table, lens, max_len_hint=a.seq)), 4.0 * a.batch * a.heads * a.seq * a.dim, 4.0 * kc.numel()
 
 
+def case_skinny(a):
+    """Few-row projection (--m <= 64 rows, --n features, --k): --epi plain | bias_res | gated | norm picks the epilogue;
+    bytes are the weights streamed once."""
+    from ..ops.skinny import skinny_linear
+    gate = "silu" if a.epi == "gated" else None
+    rows = 2 * a.n if gate else a.n
+    w = torch.randn(rows, a.k, device="cuda", dtype=torch.bfloat16) * a.k ** -0.5
+    x = torch.randn(a.m, a.k, device="cuda", dtype=torch.bfloat16)
+    bias = torch.randn(rows, device="cuda", dtype=torch.bfloat16) if a.epi == "bias_res" else None
+    res = torch.randn(a.m, a.n, device="cuda", dtype=torch.bfloat16) if a.epi == "bias_res" else None
+    eps = 1e-5 if a.epi == "norm" else None
+    out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    return (lambda: skinny_linear(x, w, bias, res, gate, eps, out)), 2.0 * a.m * rows * a.k, 2.0 * rows * a.k
+
+
+def case_skinny_dense(a):
+    """The same product on the dense GEMM with its split-K choice (what decode used before) for comparison."""
+    from ..ops.gemm import gemm
+    w = torch.randn(a.n, a.k, device="cuda", dtype=torch.bfloat16) * a.k ** -0.5
+    x = torch.randn(a.m, a.k, device="cuda", dtype=torch.bfloat16)
+    return (lambda: gemm(x, w)), 2.0 * a.m * a.n * a.k, 2.0 * a.n * a.k
+
+
 def case_qgemm(a):
     from ..quant.weights import qgemm, quantize_weight
     w = quantize_weight(torch.randn(a.k, a.n, device="cuda", dtype=torch.bfloat16), a.kind)
@@ -230,6 +253,7 @@ def _role_timers(fn: Callable[[], None]) -> dict:
 CASES: Dict[str, Callable] = {
     "gemm": case_gemm, "gemm_wgrad": case_gemm_wgrad, "cublas": case_cublas, "flash_fwd": case_flash_fwd,
     "flash_bwd": case_flash_bwd, "xent": case_xent, "norm": case_norm, "norm_bwd": case_norm_bwd, "adamw": case_adamw,
+    "skinny": case_skinny, "skinny_dense": case_skinny_dense,
     "decode_attn": case_decode_attn, "qgemm": case_qgemm,
 }
 
@@ -241,7 +265,7 @@ def main(argv=None) -> int:
                           ("seq", 1024), ("dim", 64), ("warmup", 3), ("iters", 10)):
         ap.add_argument(f"--{name}", type=int, default=default)
     ap.add_argument("--kind", default="int4", choices=["int4", "int8"])
-    ap.add_argument("--epi", default="plain", choices=["plain", "bias", "bias_res", "bias_gelu", "gelu_grad", "bias_gelu_d", "mul_aux"])
+    ap.add_argument("--epi", default="plain", choices=["plain", "bias", "bias_res", "bias_gelu", "gelu_grad", "bias_gelu_d", "mul_aux", "gated", "norm"])
     ap.add_argument("--role-timers", action="store_true",
                     help="gemm cases: after timing, run one more launch with the kernel's role timers on and print "
                          "the mean cycles per tile each warp role spent waiting")

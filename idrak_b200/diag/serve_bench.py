@@ -39,6 +39,8 @@ def main(argv=None) -> int:
     ap.add_argument("--prompt-min", type=int, default=0, help="with --prompt-max: prompt lengths uniform in [min, max]")
     ap.add_argument("--prompt-max", type=int, default=0)
     ap.add_argument("--arm", choices=["fused", "nccl"], default="fused")
+    ap.add_argument("--fold-norms", action="store_true", help="fold the RMS norm weights into the projections (one GPU)")
+    ap.add_argument("--kv", choices=["bf16", "int8"], default="bf16", help="key / value cache element type")
     a = ap.parse_args(argv)
     import os
     from .. import _native
@@ -75,7 +77,8 @@ def main(argv=None) -> int:
     longest = a.prompt_max if a.prompt_max > 0 else a.prompt
     blocks_needed = a.max_batch * ((longest + a.gen + 15) // 16 + 1)
     eng = LLMEngine(model, num_blocks=blocks_needed + 64, max_batch=a.max_batch, max_prefill_tokens=a.prefill_tokens,
-                    prefix_sharing=False, use_graph=not a.no_graph, tp=tp)
+                    prefix_sharing=False, use_graph=not a.no_graph, tp=tp, fold_norms=a.fold_norms,
+                    kv_dtype=torch.int8 if a.kv == "int8" else None)
     if tp is not None and a.arm == "nccl":
         _use_nccl_arm(eng.runner)
     g = torch.Generator().manual_seed(0)

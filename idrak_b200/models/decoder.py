@@ -196,9 +196,26 @@ class FeedForward(nn.Module):
                                      {"down": (0, spec.dim)}, residual, packed=packed.get("down"))
 
 
+class _AsStacked(torch.autograd.Function):
+    """The stacked buffer as a function of the per-expert parameters that are views of its slices: forward hands out the
+    buffer (no copy), backward splits the stacked gradient into one view per parameter."""
+
+    @staticmethod
+    def forward(ctx, buffer, *params):
+        return buffer.view_as(buffer)
+
+    @staticmethod
+    def backward(ctx, grad):
+        return (None,) + tuple(grad[i] for i in range(grad.shape[0]))
+
+
 class MixtureOfExperts(nn.Module):
     """Top-k routed experts (+ optional shared expert). Single-device, as in the reference
-    (src/Idrak/Layers/MixtureOfExperts.cs:34): ties go to the lowest index, weights optionally renormalised."""
+    (src/Idrak/Layers/MixtureOfExperts.cs:34): ties go to the lowest index, weights optionally renormalised.
+
+    The experts' matrices live side by side in two stacked buffers and every expert's parameter is a view of its slice,
+    so checkpoints, optimizers and adapters keep seeing per-expert parameters while the device path (``ops.moe``:
+    routing kernels + grouped tensor-core products, no host read) reads the stacked arrays."""
 
     def __init__(self, spec: DecoderSpec):
         super().__init__()
@@ -210,14 +227,68 @@ class MixtureOfExperts(nn.Module):
             self.shared_gate = nn.Parameter(torch.empty(1, spec.dim))
         else:
             self.shared = None
+        self._stacked = None
+        self._stack()
+
+    def _apply(self, fn, *args, **kwargs):          # .to() / .cuda() / .bfloat16() give every parameter new storage
+        out = super()._apply(fn, *args, **kwargs)
+        self._stack()
+        return out
+
+    def _stack(self) -> None:
+        ups, downs = [e.up_weight for e in self.experts], [e.down_weight for e in self.experts]
+        self._stacked = None
+        if any(e.up_bias is not None or e.down_bias is not None for e in self.experts):
+            return
+        if len({(p.dtype, p.device, tuple(p.shape)) for p in ups}) != 1 or ups[0].device.type == "meta":
+            return
+        with torch.no_grad():
+            up, down = torch.stack([p.data for p in ups]), torch.stack([p.data for p in downs])
+            for i, e in enumerate(self.experts):
+                e.up_weight.data = up[i]
+                e.down_weight.data = down[i]
+        self._stacked = (up, down)
+
+    def _stacked_now(self):
+        """The stacked buffers when every expert's parameters still are their slices (something that re-homes
+        parameters, a flat-bucket optimizer for one, ends that), else None."""
+        if self._stacked is None:
+            return None
+        up, down = self._stacked
+        for i, e in enumerate(self.experts):
+            if (e.up_weight.data_ptr() != up[i].data_ptr() or e.down_weight.data_ptr() != down[i].data_ptr()
+                    or getattr(e, "adapters", None) is not None or getattr(e, "packed", None)):
+                return None
+        return up, down
 
     def forward(self, x, residual=None):
+        spec = self.spec
+        from ..ops import moe
+        kind = {"silu": "silu", "gelu": "gelu", "relu": "relu"}.get(spec.activation)
+        st = self._stacked_now() if (x.is_cuda and kind is not None) else None
+        if st is not None and moe.supported(x, st[0], st[1], spec.gated, kind):
+            up = _AsStacked.apply(st[0], *[e.up_weight for e in self.experts])
+            down = _AsStacked.apply(st[1], *[e.down_weight for e in self.experts])
+            shared_res = residual
+            if self.shared is not None:
+                x2 = x.reshape(-1, x.shape[-1])
+                g = torch.sigmoid((x2.float() * self.shared_gate.float()).sum(-1, keepdim=True)).to(x.dtype)
+                sh = (self.shared(x2) * g).reshape(x.shape)
+                shared_res = sh if residual is None else sh + residual
+            return moe.routed_experts(x, self.router, up, down, spec.experts_per_token, spec.normalize_top_k,
+                                      spec.gated, kind, shared_res)
+        return self._forward_loop(x, residual)
+
+    def _forward_loop(self, x, residual=None):
+        """One pass per expert over the tokens that chose it: the host statement (and the path for shapes, adapters or
+        packed weights the grouped kernels do not take)."""
         spec = self.spec
         shape = x.shape
         x2 = x.reshape(-1, shape[-1])
         logits = torch.nn.functional.linear(x2.float(), self.router.float())
         probs = torch.softmax(logits, -1)
-        top_p, top_i = torch.topk(probs, spec.experts_per_token, dim=-1)
+        top_i = torch.sort(probs, dim=-1, descending=True, stable=True).indices[:, : spec.experts_per_token]
+        top_p = probs.gather(1, top_i)
         if spec.normalize_top_k:
             top_p = top_p / top_p.sum(-1, keepdim=True)
         out = torch.zeros_like(x2, dtype=torch.float32)

@@ -1,0 +1,66 @@
+"""Few-row projections for decoding (at most 64 token rows): one launch per projection with its epilogue inside.
+
+``skinny_linear(x, w, ...)`` computes ``x @ w.T`` on the cluster split-K kernel (``csrc/skinny_gemm.cu``) and, in the
+same launch, any of: a folded RMS norm of ``x`` (``norm_eps``: ``w`` must carry the norm weight in its columns, see
+``fold_norm``), a bias, a residual add, and - with ``gate`` - the gated activation of a stacked ``[gate; up]`` matrix.
+``skinny_reference`` is the fp32 statement of the same thing and the CPU path.
+
+Reference: the fused few-row GEMV family (src/Idrak.Gpu/Cuda/PtxKernels.Quantized.cs:454-495).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import _native
+from ._util import ptr, stream_ptr
+from .rowops import GATE_KINDS, _gate_ref
+
+MAX_ROWS = 64
+_KINDS = {"silu": 0, "swiglu": 0, "gelu": 1, "geglu": 1, "relu": 2, "reglu": 2}
+
+
+def fold_norm(weight: torch.Tensor, norm_weight: torch.Tensor) -> torch.Tensor:
+    """``weight * norm_weight[None, :]``: the projection that, applied to ``x * rstd``, equals ``norm(x) @ weight.T``."""
+    return (weight.float() * norm_weight.float()[None, :]).to(weight.dtype)
+
+
+def skinny_reference(x, w, bias=None, residual=None, gate: Optional[str] = None, norm_eps: Optional[float] = None):
+    xf = x.float()
+    if norm_eps is not None:
+        xf = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + norm_eps)
+    y = xf @ w.float().t()
+    if bias is not None:
+        y = y + bias.float()
+    if gate is not None:
+        ff = y.shape[-1] // 2
+        y = _gate_ref(y[..., :ff], GATE_KINDS[gate]) * y[..., ff:]
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(x.dtype)
+
+
+def supported(x: torch.Tensor, w: torch.Tensor, gate: Optional[str] = None) -> bool:
+    return (x.is_cuda and _native.has("idrak_skinny_gemm") and x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.dim() == 2
+            and x.shape[0] <= MAX_ROWS and x.shape[1] % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and (gate is None or (gate in _KINDS and (w.shape[0] // 2) % 8 == 0)))
+
+
+def skinny_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                  residual: Optional[torch.Tensor] = None, gate: Optional[str] = None,
+                  norm_eps: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x [M <= 64, K]``, ``w [N, K]`` (or ``[2 ff, K]`` with ``gate``) -> ``[M, N]`` (``[M, ff]``)."""
+    if not supported(x, w, gate):
+        return skinny_reference(x, w, bias, residual, gate, norm_eps)
+    M, K = x.shape
+    N = w.shape[0] // 2 if gate is not None else w.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    rc = _native.lib().idrak_skinny_gemm(
+        x.data_ptr(), x.stride(0), w.data_ptr(), w.stride(0), out.data_ptr(), out.stride(0), M, N, K, ptr(bias),
+        ptr(residual), residual.stride(0) if residual is not None else 0, _KINDS[gate] if gate is not None else -1,
+        float(norm_eps) if norm_eps is not None else -1.0, stream_ptr())
+    _native.check(rc, "idrak_skinny_gemm")
+    return out

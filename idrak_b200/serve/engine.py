@@ -101,8 +101,12 @@ class LLMEngine:
                  max_prefill_tokens: int = 8192, queue_limit: int = 0, prefix_sharing: bool = True,
                  eos_token_ids: Sequence[int] = (), cache_bytes: Optional[int] = None,
                  clock: Callable[[], float] = time.monotonic, use_graph: bool = True, tp=None,
-                 kv_dtype: Optional[torch.dtype] = None):
-        """``tp``: a ``parallel.tp_serve.TPServeContext`` when ``model`` is one rank's slice of a tensor-parallel
+                 kv_dtype: Optional[torch.dtype] = None, fold_norms: bool = False):
+        """``fold_norms``: rewrite the model (in place, inference only) so that each RMS norm's weight is multiplied into
+        the projection that follows it; decode steps of up to 64 sequences then run the norm inside the projection
+        kernels (``serve.runner.fold_norms_into_projections``).
+
+        ``tp``: a ``parallel.tp_serve.TPServeContext`` when ``model`` is one rank's slice of a tensor-parallel
         decoder. Every rank of the group then runs an engine of its own over the same requests in lock-step: the
         scheduler is deterministic and the sampled tokens are equal on every rank, so the engines stay in step
         without exchanging anything but the activations."""
@@ -132,6 +136,9 @@ class LLMEngine:
             self.runner = TPModelRunner(model, num_blocks, block_size, max_batch, kv_dtype, tp=tp)
             self.spec = spec = model.tp_full_spec       # token ids, end-of-sequence checks and limits are the whole model's
         else:
+            if fold_norms:
+                from .runner import fold_norms_into_projections
+                fold_norms_into_projections(model)
             self.runner = ModelRunner(model, num_blocks, block_size, max_batch, kv_dtype)
         self.sched = Scheduler(num_blocks, block_size, max_batch, max_prefill_tokens, queue_limit, prefix_sharing)
         self.eos = set(int(t) for t in eos_token_ids)

@@ -15,6 +15,8 @@ decode primitives (src/Idrak.Abstraction/Generation/Decoding.cs:243, Tensors/Ten
 """
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
@@ -30,6 +32,35 @@ class PrefillItem:
     tokens: List[int]          # the tokens to compute (positions start .. start + len - 1)
     start: int                 # number of leading tokens already in the cache (shared prefix)
     blocks: List[int]          # block table covering positions 0 .. start + len
+
+
+def fold_norms_into_projections(model: Decoder) -> bool:
+    """Rewrites an inference copy of a pre-norm decoder so that every RMS norm's weight lives in the projection that
+    follows it (query/key/value, gate/up, the head) and the norm itself has unit weight: ``norm(x) W^T`` becomes
+    ``(x rstd) (W diag(w))^T``. Same function up to bf16 rounding of the folded weights, for every path (prefill, decode,
+    training forward), and it lets the few-row decode kernel apply ``rstd`` in its epilogue instead of a norm launch.
+    Returns False (and changes nothing) for models it does not cover: LayerNorm, post-norms, parallel blocks, experts,
+    adapters or packed weights, tied embeddings (the head shares the embedding matrix)."""
+    s = model.spec
+    if getattr(model, "_norms_folded", False):
+        return True
+    if s.norm != "rms" or s.post_norms or s.parallel_blocks or s.experts > 0 or model.head is None:
+        return False
+    from ..ops.skinny import fold_norm
+    blocks = list(model.blocks)
+    for blk in blocks:
+        if any(getattr(m, "adapters", None) is not None or getattr(m, "packed", None) for m in (blk.attn, blk.mlp)):
+            return False
+    with torch.no_grad():
+        def fold(weight: torch.nn.Parameter, norm) -> None:
+            weight.copy_(fold_norm(weight, norm.effective_weight()))
+            norm.weight.fill_(1.0 - (s.norm_offset or 0.0))          # effective weight 1 from here on
+        for blk in blocks:
+            fold(blk.attn.qkv_weight, blk.attn_norm)
+            fold(blk.mlp.up_weight, blk.mlp_norm)
+        fold(model.head, model.norm)
+    model._norms_folded = True
+    return True
 
 
 class ModelRunner:
@@ -254,6 +285,8 @@ class ModelRunner:
         slots = (blk_of * bs + positions % bs).to(torch.int32)
         lens = (positions + 1).to(torch.int32)
         x = self._embed(tokens, positions)
+        if n <= 64 and self._few_row_path():
+            return self._decode_few_rows(x.view(n, -1), positions, slots, block_table, lens, max_len_hint)
         layer_index = {id(blk.attn): i for i, blk in enumerate(self.model.blocks)}
 
         def attend(attn, h, residual):
@@ -274,6 +307,58 @@ class ModelRunner:
         for blk in self.model.blocks:
             x = self._block(blk, x, attend)
         return self._logits(self.model.norm(x))
+
+    # ------------------------------------------------------------------ decode of at most 64 rows: fused projections
+    def _few_row_path(self) -> bool:
+        """Whether decode steps of up to 64 sequences run on the few-row kernels: one launch per projection with bias,
+        residual add, gated activation and (with folded norms) the RMS norm inside it."""
+        cached = getattr(self, "_few_rows_ok", None)
+        if cached is not None:
+            return cached
+        from ..ops import skinny
+        from .. import _native
+        s = self.spec
+        ok = (self.device.type == "cuda" and self.dtype == torch.bfloat16 and _native.has("idrak_skinny_gemm")
+              and os.environ.get("IDRAK_FEW_ROW_DECODE", "1") != "0"
+              and not s.parallel_blocks and not s.post_norms and s.experts == 0 and s.attention_softcap is None
+              and s.gated and s.activation in skinny._KINDS and s.dim % 8 == 0 and s.ff_dim % 8 == 0
+              and not s.logit_softcap)
+        for blk in self.model.blocks:
+            if not ok:
+                break
+            rope = blk.attn.rope
+            ok = (not any(getattr(m, "adapters", None) is not None or getattr(m, "packed", None)
+                          for m in (blk.attn, blk.mlp)) and (rope is None or rope.scaling is None))
+        self._few_rows_ok = bool(ok)
+        return self._few_rows_ok
+
+    def _decode_few_rows(self, x, positions, slots, block_table, lens, max_len_hint):
+        """Six or seven launches per layer: qkv (+norm) | norms of q, k + RoPE + cache write | paged attention
+        (+ its merge) | out + residual | gate/up (+norm) + activation | down + residual."""
+        from ..ops.skinny import skinny_linear
+        s, m = self.spec, self.model
+        H, Hkv, D = s.heads, s.kv_heads, s.head_dim
+        folded = bool(getattr(m, "_norms_folded", False))
+        eps = s.norm_epsilon if folded else None
+        n = x.shape[0]
+        for li, blk in enumerate(m.blocks):
+            attn, mlp = blk.attn, blk.mlp
+            h = x if folded else blk.attn_norm(x)
+            qkv = skinny_linear(h, attn.qkv_weight, attn.qkv_bias, norm_eps=eps)
+            self._rotate_and_cache(attn, qkv, positions, slots, li)
+            q = qkv[:, : H * D].unflatten(-1, (H, D))
+            window = s.sliding_window if s.is_windowed(attn.layer) else 0
+            o = dops.paged_decode(q, self.k_cache[li], self.v_cache[li], block_table, lens, attn.scale, window or 0,
+                                  max_len_hint=max_len_hint, k_scale=self.k_scale[li], v_scale=self.v_scale[li])
+            x = skinny_linear(o.reshape(n, H * D), attn.o_weight, attn.o_bias, residual=x)
+            h = x if folded else blk.mlp_norm(x)
+            g = skinny_linear(h, mlp.up_weight, mlp.up_bias, gate=s.activation, norm_eps=eps)
+            x = skinny_linear(g, mlp.down_weight, mlp.down_bias, residual=x)
+        if folded:
+            logits = skinny_linear(x, m.head_weight(), m.head_bias, norm_eps=s.norm_epsilon)
+        else:
+            logits = skinny_linear(m.norm(x), m.head_weight(), m.head_bias)
+        return logits.reshape(-1, logits.shape[-1])
 
     # ------------------------------------------------------------------ decode as a replayed CUDA graph
     BATCH_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)

@@ -151,3 +151,29 @@ def test_packed_spans_equal_separate_sequences_on_the_host():
         for lo, hi in spans:
             alone = model(ids[:, lo:hi], pos[lo:hi])
             assert torch.allclose(packed[:, lo:hi], alone, atol=1e-4, rtol=1e-4)
+
+
+def test_expert_parameters_stay_views_of_the_stacked_buffers():
+    """Moving or casting the module re-stacks; an optimizer step on the per-expert parameters changes the stacked
+    arrays the grouped kernels read; loading a state dict writes through."""
+    import torch
+    from idrak_b200.models import DecoderSpec, build_decoder
+    spec = DecoderSpec.llama(layers=1, dim=64, heads=2, kv_heads=2, ff_dim=128, vocab=50, max_positions=32)
+    spec.experts, spec.experts_per_token, spec.expert_ff_dim = 4, 2, 64
+    model = build_decoder(spec, seed=1)
+    moe = model.blocks[0].mlp
+    for m in (model, model.to(torch.bfloat16), model.float()):
+        up, down = moe._stacked_now()
+        assert up.shape == (4, 128, 64) and down.shape == (4, 64, 64)
+        assert all(e.up_weight.data_ptr() == up[i].data_ptr() for i, e in enumerate(moe.experts))
+    opt = torch.optim.SGD(model.parameters(), lr=0.5)
+    ids = torch.randint(0, 50, (2, 16))
+    model.loss(ids, ids).backward()
+    before = moe._stacked[0].clone()
+    opt.step()
+    assert moe._stacked_now() is not None and not torch.equal(before, moe._stacked[0])
+    sd = {k: torch.zeros_like(v) for k, v in model.state_dict().items()}
+    model.load_state_dict(sd)
+    assert moe._stacked_now() is not None and float(moe._stacked[0].abs().sum()) == 0.0
+    moe.experts[1].up_weight.data = torch.ones(128, 64)          # re-homed by someone else: the loop path takes over
+    assert moe._stacked_now() is None

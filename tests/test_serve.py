@@ -153,3 +153,33 @@ def test_engine_with_an_int8_kv_cache_generates_like_the_bf16_cache():
     assert [o[0] for o in out_a] == [o[0] for o in out_b]
     assert sum(x == y for oa, ob in zip(out_a, out_b) for x, y in zip(oa, ob)) >= 10
     assert ModelRunner.blocks_that_fit(spec, 1 << 20, 16, 1) > ModelRunner.blocks_that_fit(spec, 1 << 20, 16, 2)
+
+
+def test_folding_the_norm_weights_into_the_projections_keeps_the_function():
+    """``norm(x) W^T == (x rstd) (W diag(w))^T``: after the rewrite the norms have unit weight and logits are unchanged,
+    through the training forward and through the engine."""
+    import torch
+    from idrak_b200.models import DecoderSpec, build_decoder
+    from idrak_b200.serve import GenerationOptions, LLMEngine
+    from idrak_b200.serve.runner import fold_norms_into_projections
+    spec = DecoderSpec.llama(layers=2, dim=64, heads=4, kv_heads=2, ff_dim=128, vocab=97, max_positions=64)
+    spec.tie_embeddings = False
+    model = build_decoder(spec, seed=4).float().eval()
+    with torch.no_grad():
+        for blk in model.blocks:
+            blk.attn_norm.weight.uniform_(0.5, 1.5)
+            blk.mlp_norm.weight.uniform_(0.5, 1.5)
+        model.norm.weight.uniform_(0.5, 1.5)
+    ids = torch.randint(0, 97, (2, 20))
+    with torch.no_grad():
+        before = model(ids)
+    want = LLMEngine(model, num_blocks=32, max_batch=2).generate([[5, 6, 7]], GenerationOptions.greedy_options(6))[0].output
+    assert fold_norms_into_projections(model) and model._norms_folded
+    assert float((model.blocks[0].attn_norm.weight.detach() - 1).abs().max()) == 0.0
+    with torch.no_grad():
+        after = model(ids)
+    assert torch.allclose(before, after, atol=1e-4, rtol=1e-4)
+    got = LLMEngine(model, num_blocks=32, max_batch=2, fold_norms=True).generate([[5, 6, 7]], GenerationOptions.greedy_options(6))[0].output
+    assert got == want
+    tied = build_decoder(DecoderSpec.gpt2(layers=1, dim=32, heads=2, vocab=50, max_positions=16), seed=1)
+    assert not fold_norms_into_projections(tied)              # LayerNorm and a tied head: left alone
