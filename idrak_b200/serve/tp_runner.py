@@ -36,6 +36,9 @@ class TPModelRunner(ModelRunner):
         self.vocab_offset = lo
         self.vocab_local = max(0, min(hi, self.full_spec.vocabulary) - lo)      # columns of the slice that are real tokens
 
+    def _few_row_path(self) -> bool:
+        return False            # the single-GPU fused decode layer has no all-reduce in it
+
     def _sum_partials(self, partial: torch.Tensor, residual: torch.Tensor, norm=None):
         """``residual + sum over ranks(partial)`` (and the norm of that): ``[1, T, dim]`` in and out."""
         shape = partial.shape

@@ -54,6 +54,8 @@ class FineTuningOptions:
     accumulation: int = 1
     loss_chunk_rows: int = 512
     non_finite_steps: int = 8            # give up after this many skipped steps in a row
+    data_parallel: str = "fused"         # with several ranks on GPUs: fused (peer-memory reduce-scatter + sharded AdamW +
+                                         # all-gather kernels) | nccl (the same buckets over NCCL) | flat (one all-reduce)
     checkpoint_blocks: bool = False      # recompute block activations in backward
     activation_ladder: bool = True       # estimate activation memory before the first step, step down on out-of-memory
     loss: str = "sft"                    # sft | dpo | orpo | simpo (or a name registered in PREFERENCE_LOSSES)
@@ -292,8 +294,19 @@ class FineTuner:
             p.requires_grad_(True)
         model.checkpoint_blocks = o.checkpoint_blocks
         model.loss_chunk_rows = o.loss_chunk_rows
-        self.optimizer = FusedAdamW([{"params": self.params, "weight_decay": o.weight_decay}], lr=o.learning_rate,
-                                    weight_decay=o.weight_decay, max_grad_norm=o.clip)
+        self.sync = None
+        many = dist.is_initialized() and dist.get_world_size(group) > 1
+        if many and self.device.type == "cuda" and o.data_parallel in ("fused", "nccl"):
+            # adapter gradients go through the bucketed reduce-scatter, the sharded AdamW and the all-gather of the
+            # data-parallel engine, overlapped with the backward pass; the header carries token counts and the
+            # non-finite-loss agreement
+            from ..parallel.dp import DataParallel
+            self.sync = DataParallel(model, lr=o.learning_rate, weight_decay=o.weight_decay, max_grad_norm=o.clip,
+                                     mode=o.data_parallel, group=group, bucket_mb=8.0)
+            self.optimizer = self.sync.optimizer
+        else:
+            self.optimizer = FusedAdamW([{"params": self.params, "weight_decay": o.weight_decay}], lr=o.learning_rate,
+                                        weight_decay=o.weight_decay, max_grad_norm=o.clip)
         self.template = ChatTemplate.for_tokenizer(tokenizer)
         self.step = 0
         self.result = FineTuningResult()
@@ -403,18 +416,40 @@ class FineTuner:
             group = [batches[order[cursor + k]] for k in range(o.accumulation)]
             cursor += o.accumulation
             tokens = sum(max(b.trained_tokens, 1) for b in group)
-            self.optimizer.zero_grad()
+            if self.sync is not None:
+                self.sync.zero_grad()
+            else:
+                self.optimizer.zero_grad()
             loss_value, finite = 0.0, True
             try:
-                for b in group:
+                for i, b in enumerate(group):
                     w = max(b.trained_tokens, 1) / tokens          # token-weighted mean over the accumulated batches
                     loss = self.batch_loss(b)
                     value = float(loss.detach())                   # the one host read per batch
                     if not math.isfinite(value):
                         finite = False
+                    if self.sync is None:
+                        if not finite:
+                            break
+                        (loss * w).backward()
+                        loss_value += value * w
+                        continue
+                    # several ranks: nobody may leave the step alone. Every rank reaches the header before the last
+                    # backward; a non-finite loss anywhere makes the header's loss non-finite everywhere.
+                    if finite:
+                        loss_value += value * w
+                    if i + 1 < len(group):
+                        if finite:
+                            (loss * w).backward()
+                        continue
+                    header = self.sync.step_header(tokens, loss_value if finite else float("nan"))
+                    agreed = float(header["loss"])                 # the ranks' token-weighted mean loss
+                    if not math.isfinite(agreed):
+                        finite = False
                         break
-                    (loss * w).backward()
-                    loss_value += value * w
+                    with self.sync.overlap():
+                        (loss * w).backward()
+                    loss_value = agreed
             except torch.OutOfMemoryError:
                 loss = None
                 if not self._step_down():
@@ -428,9 +463,12 @@ class FineTuner:
                     raise FloatingPointError(f"{bad_streak} steps in a row had a non-finite loss")
                 continue
             bad_streak = 0
-            self._reduce_grads()
             self.optimizer.lr = _lr_at(self.step, total, o)
-            self.optimizer.step()
+            if self.sync is not None:
+                self.sync.reduce_and_step()
+            else:
+                self._reduce_grads()
+                self.optimizer.step()
             self.step += 1
             res.steps, res.tokens = self.step, res.tokens + tokens
             res.losses.append(loss_value)
@@ -456,12 +494,15 @@ class FineTuner:
 
     # ------------------------------------------------------------------ checkpoints
     def save_checkpoint(self, folder: str) -> None:
+        # the sharded optimizer's state is gathered by all ranks (one file whatever the world size), then one writes
+        state = self.sync.optimizer_state() if self.sync is not None else None
         if not self._is_writer():
             return
         os.makedirs(folder, exist_ok=True)
         save_adapters(self.model, folder)
         from ..formats.safetensors import save_file
-        state = self.optimizer.state_dict()
+        if state is None:
+            state = self.optimizer.state_dict()
         save_file({k: v for k, v in state.items() if isinstance(v, torch.Tensor)},
                   os.path.join(folder, "optimizer.safetensors"), metadata={"format": "idrak-optimizer", "optimizer": "AdamW"})
         with open(os.path.join(folder, "train-state.json"), "w") as f:
@@ -472,7 +513,10 @@ class FineTuner:
         from ..formats.safetensors import load_file
         path = os.path.join(folder, "optimizer.safetensors")
         if os.path.isfile(path):
-            self.optimizer.load_state_dict(load_file(path))
+            if self.sync is not None:
+                self.sync.load_optimizer_state(load_file(path))
+            else:
+                self.optimizer.load_state_dict(load_file(path))
         with open(os.path.join(folder, "train-state.json")) as f:
             st = json.load(f)
         self.step, self.result.tokens = int(st["step"]), int(st.get("tokens", 0))

@@ -59,6 +59,23 @@ def test_fused_dp_matches_nccl_and_single_process(tmp_path):
     assert abs(fused["grad_norm"] - nccl["grad_norm"]) < 0.05 * nccl["grad_norm"] + 1e-3
 
 
+@pytest.mark.parametrize("world", [4, 8])
+def test_fused_dp_matches_nccl_and_single_process_on_more_ranks(tmp_path, world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    fused = _run("fused", tmp_path / "fused.pt", nproc=world, port=29650 + world)
+    nccl = _run("nccl", tmp_path / "nccl.pt", nproc=world, port=29660 + world)
+    assert fused["same"] and nccl["same"]
+    single_w, _ = _single(4, world)
+    ulp = 2.0 ** -7 + 1e-6
+    for other in (nccl["weights"], single_w):
+        d = (fused["weights"] - other).abs()
+        assert d.max().item() <= ulp, d.max().item()
+        assert (d > 5e-3).float().mean().item() < 1e-3
+    again = _run("fused", tmp_path / "again.pt", nproc=world, port=29670 + world)
+    assert torch.equal(fused["weights"], again["weights"]), "bit-identical from run to run"
+
+
 def test_fused_dp_is_deterministic(tmp_path):
     a = _run("fused", tmp_path / "a.pt", port=29643)
     b = _run("fused", tmp_path / "b.pt", port=29644)
@@ -91,3 +108,23 @@ def test_step_header_gives_the_token_weighted_mean_when_ranks_hold_different_bat
     assert (d > 5e-3).float().mean().item() < 2e-3
     assert [h[0] for h in fused["headers"]] == [8 * 128.0] * 4
     assert [h[1] for h in fused["headers"]] == [0.0, 0.0, 0.0, 1.0]
+
+
+def test_fine_tuner_trains_through_the_fused_data_parallel_engine(tmp_path):
+    """``FineTuner.fit`` under torchrun: the fused path (bucketed peer-memory reduce-scatter, sharded AdamW, all-gather)
+    must leave every rank with the same adapters, close to what one flat all-reduce per step gives."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    got = {}
+    for i, mode in enumerate(("fused", "flat")):
+        out = tmp_path / f"{mode}.pt"
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+               "127.0.0.1", "--master-port", str(29681 + i), os.path.join(HERE, "finetune_dp_worker.py"), mode, str(out)]
+        r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+        assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+        got[mode] = torch.load(out)
+    assert got["fused"]["sync"] == "DataParallel" and got["flat"]["sync"] == "NoneType"
+    assert got["fused"]["same"] and got["flat"]["same"]
+    assert len(got["fused"]["losses"]) == 6 and got["fused"]["losses"][-1] < got["fused"]["losses"][0]
+    d = (got["fused"]["weights"] - got["flat"]["weights"]).abs().max().item()
+    assert d <= 0.02 * max(1.0, got["flat"]["weights"].abs().max().item()), d
+    assert abs(got["fused"]["losses"][0] - got["flat"]["losses"][0]) < 0.05

@@ -111,8 +111,10 @@ def test_routed_layer_records_into_a_cuda_graph_and_replays_bit_for_bit():
     dy = _rand((T, dim), 1.0, 6)
 
     def step():
-        y = moe.routed_experts(x, router, up, down, k)
-        gx, gu = torch.autograd.grad(y, [x, up], dy)
+        # fresh leaves every time: a leaf remembers the stream it was first used on, and the capture runs on its own
+        xx, uu = x.detach().requires_grad_(), up.detach().requires_grad_()
+        y = moe.routed_experts(xx, router.detach(), uu, down.detach(), k)
+        gx, gu = torch.autograd.grad(y, [xx, uu], dy)
         return y, gx, gu
     eager = [t.clone() for t in step()]
     side = torch.cuda.Stream()
