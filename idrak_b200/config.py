@@ -86,6 +86,19 @@ TABLE: List[Setting] = [
             ("float32", "bfloat16", "float16", "float8")),
     Setting("IDRAK_TOKENIZER", "choice", "library", "runtime for tokenizer.json files: the tokenizers library, or this package's "
             "own BPE / WordPiece / Unigram runtime (native merge engine)", ("library", "own")),
+    Setting("IDRAK_DEVICE", "text", "", "default device of Device.default() and the command line (cpu, cuda, cuda:N, gpu:N)"),
+    Setting("IDRAK_PLUGINS", "text", "", "comma-separated plug-in modules imported by load_plugins()"),
+    Setting("IDRAK_NORM_BULK", "bool", True, "norm backward: the pipelined kernel (rows staged through shared memory by bulk copies)"),
+    Setting("IDRAK_XENT_BULK", "bool", True, "cross-entropy: the pipelined one-pass kernel when a row fits shared memory"),
+    Setting("IDRAK_FEW_ROW_DECODE", "bool", True, "serving: decode steps of up to 64 sequences on the few-row projection kernels"),
+    Setting("IDRAK_TP_AR", "choice", "auto", "tensor-parallel serving: all-reduce of the partial rows (auto picks one-shot "
+            "up to 256 rows)", ("auto", "oneshot", "twoshot", "nccl")),
+    Setting("IDRAK_WAIT_BUDGET_NS", "int", 2_000_000_000, "how long a device-side wait (barrier, flag) may spin before it "
+            "records where it gave up and returns"),
+    Setting("IDRAK_NVCC", "text", "", "compiler used by python -m idrak_b200.build (default: nvcc on PATH or /usr/local/cuda)"),
+    Setting("IDRAK_B200_AUTOBUILD", "bool", False, "build the native library on first use when it is missing"),
+    Setting("IDRAK_REFERENCE_DATA", "text", "", "tests: folder with the reference project's test fixtures"),
+    Setting("IDRAK_COMM_CANARIES", "bool", True, "communicator: check the guard bands of symmetric buffers at close"),
 ]
 _BY_NAME: Dict[str, Setting] = {s.name: s for s in TABLE}
 

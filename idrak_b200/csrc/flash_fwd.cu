@@ -276,21 +276,12 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int c = 0; c < 4; ++c) {
         float pv[32];
         float l4[4] = {0.f, 0.f, 0.f, 0.f};
-        if (!need_mask) {          // every block but the diagonal one (and a window's first): no compare / select per element
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const float e = fast_exp2(__uint_as_float(s[c][i]) * sl2 - m_sub);
-            pv[i] = e;
-            l4[i & 3] += e;
-          }
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float e = fast_exp2(__uint_as_float(s[c][i]) * sl2 - m_sub);
-            if (c * 32 + i >= lim || c * 32 + i < lo) e = 0.f;
-            pv[i] = e;
-            l4[i & 3] += e;
-          }
+        for (int i = 0; i < 32; ++i) {
+          float e = fast_exp2(__uint_as_float(s[c][i]) * sl2 - m_sub);
+          if (need_mask && (c * 32 + i >= lim || c * 32 + i < lo)) e = 0.f;
+          pv[i] = e;
+          l4[i & 3] += e;
         }
         l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
         uint8_t* atom = sP + (c >> 1) * 16384 + r * 128;

@@ -76,13 +76,23 @@ class _RawDeviceMemory:
 class SymmetricBuffer:
     """``nbytes`` of device memory on every rank of the communicator, peer-mapped into this process."""
 
-    def __init__(self, comm: "Communicator", nbytes: int):
+    GUARD = 256              # bytes of canary before and after the usable range
+    PATTERN = 0xA5
+
+    def __init__(self, comm: "Communicator", nbytes: int, name: str = ""):
         _bind()
         lib = _native.lib()
-        self.comm, self.nbytes = comm, int(nbytes)
+        self.comm, self.nbytes, self.name = comm, int(nbytes), name or f"buffer{len(comm._buffers)}"
         base = C.c_void_p()
-        _native.check(lib.idrak_symm_alloc(C.byref(base), self.nbytes), "idrak_symm_alloc")
-        self.local_ptr = base.value
+        total = self.nbytes + 2 * self.GUARD
+        _native.check(lib.idrak_symm_alloc(C.byref(base), total), "idrak_symm_alloc")
+        self._base = base.value
+        # guard bands around the usable range: a kernel (this rank's or a peer's) that runs past either end of the
+        # buffer lands here, and check_canaries() names the buffer instead of the damage showing up elsewhere
+        self._whole = torch.as_tensor(_RawDeviceMemory(self._base, total), device=comm.device)
+        self._whole[: self.GUARD].fill_(self.PATTERN)
+        self._whole[self.GUARD + self.nbytes:].fill_(self.PATTERN)
+        self.local_ptr = self._base + self.GUARD
         hb = lib.idrak_ipc_handle_bytes()
         handle = (C.c_ubyte * hb)()
         _native.check(lib.idrak_ipc_get_handle(base, handle), "idrak_ipc_get_handle")
@@ -97,11 +107,20 @@ class SymmetricBuffer:
             out = C.c_void_p()
             buf = (C.c_ubyte * hb).from_buffer_copy(handles[r])
             _native.check(lib.idrak_ipc_open(buf, C.byref(out)), f"idrak_ipc_open(rank {r})")
-            self.peer_ptrs.append(out.value)
+            self.peer_ptrs.append(out.value + self.GUARD)
             self._opened.append(out.value)
         self.ptr_array = (C.c_void_p * comm.world)(*self.peer_ptrs)
         self._holder = _RawDeviceMemory(self.local_ptr, self.nbytes)
         self.bytes_tensor = torch.as_tensor(self._holder, device=comm.device)
+        comm._buffers.append(self)
+
+    def canaries_intact(self) -> bool:
+        """Whether both guard bands still hold the pattern (one small device read)."""
+        if not self._base:
+            return True
+        g = self.GUARD
+        lo, hi = self._whole[:g], self._whole[g + self.nbytes:]
+        return bool(((lo == self.PATTERN).all() & (hi == self.PATTERN).all()).item())
 
     def tensor(self, dtype: torch.dtype, numel: Optional[int] = None, offset_bytes: int = 0) -> torch.Tensor:
         """A typed view of the local copy."""
@@ -116,8 +135,11 @@ class SymmetricBuffer:
         self._opened = []
         if self.local_ptr:
             self.bytes_tensor = None
-            lib.idrak_symm_free(C.c_void_p(self.local_ptr))
-            self.local_ptr = 0
+            self._whole = None
+            lib.idrak_symm_free(C.c_void_p(self._base))
+            self.local_ptr = self._base = 0
+        if self in self.comm._buffers:
+            self.comm._buffers.remove(self)
 
 
 class Communicator:
@@ -133,14 +155,17 @@ class Communicator:
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.native = self.device.type == "cuda"
         self._closed = False
+        self._buffers: list = []
+        # per-collective call and byte counters of this rank: name -> [calls, bytes sent to peers, bytes read from peers]
+        self.traffic: dict = {}
         if not self.native:
             return
         _bind()
         lib = _native.lib()
         if self.world > lib.idrak_comm_max_ranks():
             raise ValueError(f"peer-memory communicator supports up to {lib.idrak_comm_max_ranks()} ranks")
-        self.flags = SymmetricBuffer(self, lib.idrak_comm_flag_bytes())
-        self.slots = SymmetricBuffer(self, lib.idrak_comm_max_ranks() * self.SLOT_FLOATS * 4)
+        self.flags = SymmetricBuffer(self, lib.idrak_comm_flag_bytes(), "flags")
+        self.slots = SymmetricBuffer(self, lib.idrak_comm_max_ranks() * self.SLOT_FLOATS * 4, "slots")
         self.local = torch.zeros(1 + lib.idrak_comm_flag_channels(), dtype=torch.int32, device=self.device)
         self.ctx = (C.c_ubyte * lib.idrak_comm_ctx_bytes())()
         lib.idrak_comm_ctx_init(self.ctx, self.rank, self.world, self.flags.ptr_array, self.slots.ptr_array,
@@ -153,8 +178,33 @@ class Communicator:
         from ..ops._util import stream_ptr
         return stream_ptr()
 
-    def symmetric(self, nbytes: int) -> SymmetricBuffer:
-        return SymmetricBuffer(self, (int(nbytes) + 255) // 256 * 256)
+    def symmetric(self, nbytes: int, name: str = "") -> SymmetricBuffer:
+        return SymmetricBuffer(self, (int(nbytes) + 255) // 256 * 256, name)
+
+    def _count(self, what: str, sent: float, read: float) -> None:
+        c = self.traffic.setdefault(what, [0, 0, 0])
+        c[0] += 1
+        c[1] += int(sent)
+        c[2] += int(read)
+
+    def check_canaries(self) -> None:
+        """Raises when a guard band of any symmetric buffer of this rank was written (something ran past an end)."""
+        bad = [b.name for b in self._buffers if not b.canaries_intact()]
+        if bad:
+            raise RuntimeError(f"rank {self.rank}: guard bytes of symmetric buffer(s) {', '.join(bad)} were overwritten")
+
+    def network_summary(self, gather: bool = False):
+        """This rank's collectives so far: calls, bytes stored into peers' memory, bytes loaded from it. ``gather=True``
+        collects every rank's summary (a collective call) - one row per rank, e.g. for an end-of-run report."""
+        mine = {"rank": self.rank, "collectives": {k: {"calls": v[0], "bytes_sent": v[1], "bytes_read": v[2]}
+                                                   for k, v in sorted(self.traffic.items())},
+                "bytes_sent": sum(v[1] for v in self.traffic.values()),
+                "bytes_read": sum(v[2] for v in self.traffic.values())}
+        if not gather:
+            return mine
+        rows = [None] * self.world
+        dist.all_gather_object(rows, mine, group=self.group)
+        return rows
 
     def bump_epoch(self):
         """Advance the epoch every collective of this step will publish. Call once per step on the stream
@@ -180,6 +230,7 @@ class Communicator:
             return out
         v = values.float().contiguous()
         out = torch.empty_like(v)
+        self._count("all_reduce_small", 0, (self.world - 1) * v.numel() * 4)
         self.bump_epoch()
         _native.check(_native.lib().idrak_allreduce_oneshot(self.ctx, v.data_ptr(), out.data_ptr(), v.numel(),
                                                             1 if op == "max" else 0, CH_ONESHOT, self._s()),
@@ -197,6 +248,8 @@ class Communicator:
             return t
         per = self.world * (8 if dtype == torch.bfloat16 else 4)
         assert numel % per == 0, f"numel must be a multiple of {per}"
+        moved = (self.world - 1) / self.world * numel * t.element_size()
+        self._count("all_reduce", moved, moved)           # reduce-scatter by loads, then all-gather by stores
         self.bump_epoch()
         _native.check(_native.lib().idrak_allreduce_twoshot(self.ctx, buf.ptr_array, numel,
                                                             1 if dtype == torch.bfloat16 else 0, float(scale), CH_AR,
@@ -212,6 +265,7 @@ class Communicator:
             dist.reduce_scatter_tensor(tmp, t, group=self.group)
             out.copy_(tmp.float() * scale if out.dtype == torch.float32 else tmp * scale)
             return out
+        self._count("reduce_scatter", 0, (self.world - 1) / self.world * numel * (2 if dtype == torch.bfloat16 else 4))
         self.bump_epoch()
         _native.check(_native.lib().idrak_reduce_scatter(self.ctx, buf.ptr_array, out.data_ptr(), numel,
                                                          1 if dtype == torch.bfloat16 else 0,
@@ -229,6 +283,7 @@ class Communicator:
             t = buf.tensor(local_slice.dtype, local_slice.numel() * self.world)
             dist.all_gather_into_tensor(t, local_slice.contiguous(), group=self.group)
             return t
+        self._count("all_gather", (self.world - 1) * nbytes, 0)
         self.bump_epoch()
         _native.check(_native.lib().idrak_all_gather(self.ctx, buf.ptr_array, local_slice.data_ptr(), nbytes, CH_AG,
                                                      max_blocks, self._s()), "all_gather")
@@ -240,6 +295,7 @@ class Communicator:
             dist.broadcast(buf.tensor(torch.uint8, nbytes), src=dist.get_global_rank(self.group, root)
                            if self.group is not None else root, group=self.group)
             return
+        self._count("broadcast", (self.world - 1) * nbytes if self.rank == root else 0, 0)
         self.bump_epoch()
         _native.check(_native.lib().idrak_broadcast(self.ctx, buf.ptr_array, (nbytes + 15) // 16 * 16, root, CH_BCAST,
                                                     max_blocks, self._s()), "broadcast")
@@ -249,6 +305,13 @@ class Communicator:
             return
         torch.cuda.synchronize()
         dist.barrier(group=self.group)
+        problem = None
+        try:
+            self.check_canaries()
+        except RuntimeError as e:
+            problem = e
         self.flags.close()
         self.slots.close()
         self._closed = True
+        if problem is not None:
+            raise problem

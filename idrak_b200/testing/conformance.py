@@ -148,7 +148,7 @@ def _bf16_values(shape, gen, scale=1.0):
 
 # --------------------------------------------------------------------------- scenarios (run on the CPU, recorded)
 def _scenario_products(ops, g):
-    for (M, N, K) in ((64, 96, 32), (300, 136, 200), (1024, 768, 256)):
+    for (M, N, K) in ((64, 96, 32), (304, 136, 200), (1024, 768, 256)):      # leading dimensions in whole 16-byte units
         a, b = _bf16_values((M, K), g), _bf16_values((N, K), g, 0.1)
         bias, res = _bf16_values((N,), g, 0.1), _bf16_values((M, N), g)
         ops.gemm(a, b)

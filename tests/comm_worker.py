@@ -87,6 +87,23 @@ def main():
     ok["small"] = bool(small[0].item() == sum(1.0 + r for r in range(world)) and small[1].item() == 2.0 * world)
     torch.cuda.synchronize()
     _native.check_status("comm worker")
+    # guard bands: intact after every collective above; a write one byte past the end of a buffer is noticed
+    comm.check_canaries()
+    ok["canaries_intact"] = True
+    probe = comm.symmetric(1024, "probe")
+    probe._whole[probe.GUARD + probe.nbytes] = 0              # what an overrunning kernel would do
+    try:
+        comm.check_canaries()
+        ok["canary_trips"] = False
+    except RuntimeError as e:
+        ok["canary_trips"] = "probe" in str(e)
+    probe.close()
+    rows = comm.network_summary(gather=True)
+    mine = rows[rank]["collectives"]
+    ok["summary_rows"] = len(rows) == world and rows[rank]["rank"] == rank
+    ok["summary_counts"] = (mine["all_reduce"]["calls"] == 2 and mine["all_gather"]["calls"] == 2
+                            and mine["all_gather"]["bytes_sent"] == 2 * (world - 1) * sl * 2
+                            and mine["reduce_scatter"]["bytes_read"] == (world - 1) * n * 2 // world)
     gathered = [None] * world
     dist.all_gather_object(gathered, ok)
     if rank == 0:

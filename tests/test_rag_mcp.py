@@ -63,3 +63,44 @@ def test_mcp_server_lists_and_calls_tools():
     assert by_id[4]["result"]["isError"] is True and "ZeroDivisionError" in by_id[4]["result"]["content"][0]["text"]
     assert by_id[5]["error"]["code"] == -32602 and by_id[6]["error"]["code"] == -32601
     assert by_id[None]["error"]["code"] == -32700 and len(out) == 7
+
+
+def test_mcp_client_over_http_stdio_and_in_process(tmp_path):
+    import sys
+    from idrak_b200.serve.mcp import McpClient, McpError, McpServer, serve_http
+    server = McpServer(None, name="tools")
+    server.register("add", "Add two numbers.", {"type": "object", "properties": {"a": {"type": "number"}, "b": {"type": "number"}},
+                                               "required": ["a", "b"]}, lambda args: str(args["a"] + args["b"]))
+    server.register("fail", "Always fails.", {"type": "object"}, lambda args: 1 / 0)
+    local = McpClient.local(server)
+    assert local.server_info["name"] == "tools" and local.ping()
+    assert [t["name"] for t in local.list_tools()] == ["add", "fail"] and local.call("add", a=2, b=3) == "5"
+    with pytest.raises(McpError, match="ZeroDivisionError"):
+        local.call("fail")
+    with pytest.raises(McpError, match="unknown tool"):
+        local.call("nope")
+    tools = local.as_tool_functions()
+    assert tools["add"](a=1, b=1) == "2" and tools["add"].__doc__ == "Add two numbers." and "a" in tools["add"].schema["properties"]
+    httpd = serve_http(server, token="secret")
+    url = f"http://127.0.0.1:{httpd.server_address[1]}/mcp"
+    try:
+        remote = McpClient.http(url, token="secret")
+        assert remote.call("add", a=10, b=-4) == "6" and len(remote.list_tools()) == 2
+        import urllib.error
+        with pytest.raises(urllib.error.HTTPError):
+            McpClient.http(url, token="wrong")
+    finally:
+        httpd.shutdown()
+    script = tmp_path / "srv.py"
+    script.write_text(
+        "import sys\n"
+        f"sys.path.insert(0, {str(__import__('os').path.dirname(__import__('os').path.dirname(__import__('os').path.abspath(__file__))))!r})\n"
+        "from idrak_b200.serve.mcp import McpServer\n"
+        "s = McpServer(None)\n"
+        "s.register('echo', 'Echo.', {'type': 'object'}, lambda a: a.get('text', ''))\n"
+        "s.serve(sys.stdin, sys.stdout)\n")
+    child = McpClient.stdio([sys.executable, str(script)])
+    try:
+        assert child.call("echo", text="hello") == "hello"
+    finally:
+        child.close()
