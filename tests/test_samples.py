@@ -46,3 +46,34 @@ def test_house_prices_api_sample():
 def test_quantization_sample():
     out = _load("quantization").main(["--kind", "int4", "--layers", "2", "--dim", "512"])
     assert out["relative_error"] < 0.25 and out["reload_identical"]
+
+
+def test_spirals_sample_separates_the_classes():
+    out = _load("spirals").main(quiet=True)
+    assert out["accuracy"] > 0.9 and out["picture"].shape == (24, 24)
+
+
+def test_override_sample_swaps_a_kernel_in_and_out():
+    out = _load("override").main(quiet=True)
+    assert out["source_while_registered"] == "plug-in" and out["restored"]
+    assert 0.005 < out["largest_difference"] < 0.05
+    assert out["conformance"] and all(v == "ok" for v in out["conformance"]), "close enough at the bf16 tolerance"
+    assert all(v == "failed" for v in out["conformance_of_relu"])
+
+
+def test_onnx_import_sample_round_trips_and_trains():
+    out = _load("onnx_import").main(quiet=True)
+    assert out["largest_difference"] < 1e-5 and out["last_loss"] < 0.5 * out["first_loss"] and out["parameters"] > 2000
+
+
+def test_reranker_sample_puts_the_right_passage_first():
+    out = _load("reranker").main(quiet=True)
+    assert out["reranked"][0] == "collective.txt" and len(out["shortlist"]) >= 2
+
+
+def test_gpt_api_sample_answers_over_v1():
+    pytest.importorskip("fastapi")
+    out = _load("gpt_api").main(["--quiet"])
+    assert out["models"] == ["tiny"] and out["completion"]["usage"]["completion_tokens"] == 8
+    assert out["chat"]["choices"][0]["message"]["role"] == "assistant" and out["streamed_chunks"] >= 2
+    assert out["refused"] == 400
