@@ -37,6 +37,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   return y;
 }
 
+// Barrier `id` (1..15) over `threads` threads of the CTA (whole warps).
+__device__ __forceinline__ void flash_bar_sync(uint32_t id, uint32_t threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
 // First key index query `row` (position in its batch entry) may see; off = Skv - Sq.
 __device__ __forceinline__ int flash_row_lo(const FlashParams& p, int batch, int row, int off) {
   int lo = 0;

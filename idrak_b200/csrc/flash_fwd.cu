@@ -6,12 +6,14 @@
 //   warp 1      MMA issuer:   S = Q K^T into one of TWO score buffers in TMEM (tcgen05.mma, K-major x K-major), issued
 //                             one block ahead so the scores of block j+1 are being computed while block j is in the
 //                             softmax; then O += P V (P from shared memory, V as an MN-major operand, accumulator in TMEM)
-//   warps 2..5  softmax:      one thread per query row pulls its whole row of S into registers with four tcgen05.ld in
-//                             flight and one wait, hands the score buffer back at once, then takes the
-//                             online max / sum in the log2 domain, writes P as bf16 into the swizzled
-//                             operand layout, rescales the TMEM accumulator only when the running max
-//                             moved by more than 2^8 (warp-uniform decision), and finally normalises
-//                             and stores O plus the row log-sum-exp for the backward pass.
+//   warps 2..9  softmax:      two threads per query row, each with 64 of the block's 128 score columns in registers
+//                             (two tcgen05.ld in flight, one wait); the score buffer goes back to the MMA warp at
+//                             once; the halves exchange row maxima through shared memory, take the online max /
+//                             sum in the log2 domain, write P as bf16 into the swizzled operand layout, rescale
+//                             their half of the TMEM accumulator only when the running max moved by more than 2^8
+//                             (warp-uniform decision), and finally normalise and store O plus the row
+//                             log-sum-exp for the backward pass. Eight softmax warps per CTA, two CTAs per SM at
+//                             head size 64: four warps per scheduler to hide the latencies of the chain.
 // Q, K and V are addressed through 4-D tensor maps (d, position, head, batch) so fused-QKV buffers and
 // cache layouts need no copy.
 //
@@ -29,13 +31,16 @@ struct FwdSmem {
   static constexpr int kK = kQ + kTile;            // two stages
   static constexpr int kV = kK + 2 * kTile;        // two stages
   static constexpr int kPOff = kV + 2 * kTile;
-  static constexpr int kBar = kPOff + kP;
+  static constexpr int kXch = kPOff + kP;          // row maxima / sums exchanged between the two halves: 2 x 2 x 128 floats
+  static constexpr int kBar = kXch + 2048;
   static constexpr int kTotal = kBar + 256 + 1024;
 };
 
+constexpr int kFwdThreads = 320;   // TMA warp, MMA warp, eight softmax warps
+
 // MODES = false compiles the window / packed-sequence / soft-cap code out: the plain causal kernel is unchanged by them
 template <int D, bool MODES>
-__global__ void __launch_bounds__(192, (D == 64) ? 2 : 1)
+__global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
   using L = FwdSmem<D>;
@@ -79,9 +84,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(&s_full[b], 1);
-      mbar_init(&s_empty[b], 128);
+      mbar_init(&s_empty[b], 256);
     }
-    mbar_init(p_ready, 128);
+    mbar_init(p_ready, 256);
     mbar_init(o_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
@@ -186,71 +191,89 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     }
   } else {
     // ---------------------------------------------------------------- softmax / correction / epilogue
+    // Two threads per query row: warps 2..5 take key columns [0, 64) of a block, warps 6..9 columns [64, 128); the
+    // two warps that share a TMEM lane quarter (w and w + 4) own the same 32 rows. Eight softmax warps per CTA (and two
+    // CTAs per SM at head size 64) give every scheduler four of them to switch between while one waits on a load,
+    // the exponential unit or a barrier. The halves exchange their row maxima through shared memory once per block
+    // (slots alternate with the block's parity) and their row sums once at the end.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;            // which 64 columns of the block
     const int r = quarter * 32 + lane;           // row within the tile == TMEM lane
     const int row = q0 + r;                      // query position
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     uint8_t* sP = smem + L::kPOff;
+    float* xch = reinterpret_cast<float*>(smem + L::kXch);      // [2 parities][2 halves][128 rows]
+    const uint32_t pair_bar = 1 + quarter;       // named barrier of the two warps of this lane quarter
     float m_used = -INFINITY;                    // max the accumulator and the running sum are scaled by
-    float l = 0.f;
+    float l = 0.f;                               // this thread's part of the row sum
     bool ok = nkv > 0;
     const int row_lo = bounded ? flash_row_lo(p, batch, row, off) : 0;     // first key this row may see
     const bool capped = MODES && p.softcap > 0.f;
     const float cap_in = capped ? p.scale / p.softcap : 0.f;               // s -> softcap * tanh(s * scale / softcap)
     const float sl2 = capped ? p.softcap * 1.4426950408889634f : p.scale_log2;   // factor into the log2 domain
-    for (int j = 0; j < nkv && ok; ++j) {
+    constexpr int kOC = D / 2;                   // accumulator columns this thread rescales and stores
+    // A thread whose wait gave up keeps walking the loop (skipping the waits and the tensor-memory traffic): its partner
+    // meets it at the pair's barrier in every block, and that barrier has no time limit of its own.
+    for (int j = 0; j < nkv; ++j) {
       const int sb = (kSBufs == 2) ? (j & 1) : 0;
       const uint32_t sph = (kSBufs == 2) ? uint32_t((j >> 1) & 1) : uint32_t(j & 1);
-      if (!mbar_wait(&s_full[sb], sph, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 10)) { ok = false; break; }
+      if (ok && !mbar_wait(&s_full[sb], sph, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 10)) ok = false;
       tc_fence_after();
-      const int k0 = (jlo + j) * 128;
-      // keys visible to this row in this block: columns [lo, lim)
+      const int k0 = (jlo + j) * 128 + half * 64;          // first key of this thread's 64 columns
+      // keys visible to this row among its 64 columns: [lo, lim)
       int lim = p.Skv - k0;
       if (p.causal) lim = min(lim, row + off - k0 + 1);
-      lim = max(0, min(128, lim));
-      const int lo = max(0, min(128, row_lo - k0));
-      const bool need_mask = lim < 128 || lo > 0;
-      // the whole row of scores into registers: four loads in flight, one wait; then the buffer goes back to the MMA warp
-      uint32_t s[4][32];
-      const uint32_t s_addr = tmem_S + uint32_t(sb) * 128 + lane_addr;
-      tmem_ld_32x32b_x32(s_addr + 0, s[0]);
-      tmem_ld_32x32b_x32(s_addr + 32, s[1]);
-      tmem_ld_32x32b_x32(s_addr + 64, s[2]);
-      tmem_ld_32x32b_x32(s_addr + 96, s[3]);
-      tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(&s_empty[sb]);
+      lim = max(0, min(64, lim));
+      const int lo = max(0, min(64, row_lo - k0));
+      const bool need_mask = lim < 64 || lo > 0;
+      uint32_t s[2][32];
+      if (ok) {
+        const uint32_t s_addr = tmem_S + uint32_t(sb) * 128 + lane_addr + half * 64;
+        tmem_ld_32x32b_x32(s_addr + 0, s[0]);
+        tmem_ld_32x32b_x32(s_addr + 32, s[1]);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(&s_empty[sb]);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s[0][i] = s[1][i] = 0u;
+      }
       if (capped) {
 #pragma unroll
-        for (int c = 0; c < 4; ++c)
+        for (int c = 0; c < 2; ++c)
 #pragma unroll
           for (int i = 0; i < 32; ++i) s[c][i] = __float_as_uint(tanh_fast(__uint_as_float(s[c][i]) * cap_in));
       }
-      // four independent chains (one per 32-column chunk) keep the dependent latency short
-      float m4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+      float m2[2] = {-INFINITY, -INFINITY};
       if (!need_mask) {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
-#pragma unroll
-          for (int c = 0; c < 4; ++c) m4[c] = fmaxf(m4[c], __uint_as_float(s[c][i]));
+          m2[0] = fmaxf(m2[0], __uint_as_float(s[0][i]));
+          m2[1] = fmaxf(m2[1], __uint_as_float(s[1][i]));
         }
       } else {
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
 #pragma unroll
-          for (int c = 0; c < 4; ++c)
-            if (c * 32 + i < lim && c * 32 + i >= lo) m4[c] = fmaxf(m4[c], __uint_as_float(s[c][i]));
+          for (int c = 0; c < 2; ++c)
+            if (c * 32 + i < lim && c * 32 + i >= lo) m2[c] = fmaxf(m2[c], __uint_as_float(s[c][i]));
         }
       }
-      float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+      // the row maximum over both halves (every thread reaches this barrier, whatever `ok` says, so its partner never
+      // waits for nothing)
+      float* slot = xch + (j & 1) * 256;
+      slot[half * 128 + r] = fmaxf(m2[0], m2[1]);
+      flash_bar_sync(pair_bar, 64);
+      float mx = fmaxf(slot[r], slot[128 + r]);
       mx *= sl2;
       const float m_new = fmaxf(m_used, mx);
-      // the accumulator is rescaled only when some row of this warp moved its max by more than 2^8
+      // the accumulator is rescaled only when some row of this warp moved its max by more than 2^8 (both warps of a
+      // quarter hold the same rows and so decide alike)
       const bool need = (j > 0) && (m_new - m_used > 8.0f);
       const bool warp_rescale = __any_sync(0xffffffffu, need);
-      if (j > 0) {
+      if (j > 0 && ok) {
         // P of the previous block is still being read by its MMA until o_done completes
-        if (!mbar_wait(o_done, (j - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 11)) { ok = false; break; }
+        if (!mbar_wait(o_done, (j - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 11)) ok = false;
         tc_fence_after();
       }
       if (j == 0) {
@@ -259,65 +282,76 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
         const float alpha = (m_new == -INFINITY) ? 1.f : exp2f(m_used - m_new);
         m_used = m_new;
         l *= alpha;
+        if (ok) {
 #pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          tmem_ld_32x32b_x32(tmem_O + lane_addr + c * 32, o);
-          tmem_ld_wait();
+          for (int c = 0; c < kOC / 16; ++c) {          // 16 columns at a time: the 64 scores stay in registers beside them
+            uint32_t o[16];
+            tmem_ld_32x32b_x16(tmem_O + lane_addr + half * kOC + c * 16, o);
+            tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-          tmem_st_32x32b_x32(tmem_O + lane_addr + c * 32, o);
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st_32x32b_x16(tmem_O + lane_addr + half * kOC + c * 16, o);
+          }
+          tmem_st_wait();
         }
-        tmem_st_wait();
       }
       const float m_sub = (m_used == -INFINITY) ? 0.f : m_used;
       // probabilities -> bf16 operand tile (K-major, 128B swizzle: chunk ^= row % 8), from the registers
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        float pv[32];
+      for (int c = 0; c < 2; ++c) {
         float l4[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          float e = fast_exp2(__uint_as_float(s[c][i]) * sl2 - m_sub);
-          if (need_mask && (c * 32 + i >= lim || c * 32 + i < lo)) e = 0.f;
-          pv[i] = e;
-          l4[i & 3] += e;
-        }
-        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
-        uint8_t* atom = sP + (c >> 1) * 16384 + r * 128;
+        uint8_t* atom = sP + half * 16384 + r * 128;          // columns [64 half, 64 half + 64) are one 128-byte row
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
-          const int chunk = ((c & 1) * 4 + g) ^ (r & 7);
+          // eight exponentials, packed and stored at once: few values live at a time (96 registers per thread)
+          float pv[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            const int col = c * 32 + g * 8 + i;
+            float e = fast_exp2(__uint_as_float(s[c][g * 8 + i]) * sl2 - m_sub);
+            if (need_mask && (col >= lim || col < lo)) e = 0.f;
+            pv[i] = e;
+            l4[i & 3] += e;
+          }
+          const int chunk = (c * 4 + g) ^ (r & 7);
           uint4 o;
-          o.x = pack_bf16x2(pv[g * 8 + 0], pv[g * 8 + 1]);
-          o.y = pack_bf16x2(pv[g * 8 + 2], pv[g * 8 + 3]);
-          o.z = pack_bf16x2(pv[g * 8 + 4], pv[g * 8 + 5]);
-          o.w = pack_bf16x2(pv[g * 8 + 6], pv[g * 8 + 7]);
+          o.x = pack_bf16x2(pv[0], pv[1]);
+          o.y = pack_bf16x2(pv[2], pv[3]);
+          o.z = pack_bf16x2(pv[4], pv[5]);
+          o.w = pack_bf16x2(pv[6], pv[7]);
           *reinterpret_cast<uint4*>(atom + chunk * 16) = o;
         }
+        l += (l4[0] + l4[1]) + (l4[2] + l4[3]);
       }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(p_ready);
+      if (ok) {
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(p_ready);
+      }
     }
-    if (ok) {
+    if (ok && nkv > 0) {
       if (!mbar_wait(o_done, (nkv - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (2u << 16) | 12)) ok = false;
     }
     tc_fence_after();
+    // the row sum over both halves
+    float* slot = xch + (nkv & 1) * 256;
+    slot[half * 128 + r] = l;
+    flash_bar_sync(pair_bar, 64);
+    const float l_row = slot[r] + slot[128 + r];
     if (nkv <= 0) {
       // no visible key: output zeros, lse = -inf
       if (row < p.Sq) {
-        __nv_bfloat16* orow = p.O + (size_t(batch) * p.Sq + row) * p.o_row_stride + size_t(head) * D;
-        for (int i = 0; i < D; i += 8) *reinterpret_cast<uint4*>(orow + i) = make_uint4(0, 0, 0, 0);
-        if (p.lse) p.lse[(size_t(batch) * p.H + head) * p.Sq + row] = -INFINITY;
+        __nv_bfloat16* orow = p.O + (size_t(batch) * p.Sq + row) * p.o_row_stride + size_t(head) * D + half * kOC;
+        for (int i = 0; i < kOC; i += 8) *reinterpret_cast<uint4*>(orow + i) = make_uint4(0, 0, 0, 0);
+        if (p.lse && half == 0) p.lse[(size_t(batch) * p.H + head) * p.Sq + row] = -INFINITY;
       }
     } else if (ok) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = p.O + (size_t(batch) * p.Sq + row) * p.o_row_stride + size_t(head) * D;
+      const float inv = l_row > 0.f ? 1.f / l_row : 0.f;
+      __nv_bfloat16* orow = p.O + (size_t(batch) * p.Sq + row) * p.o_row_stride + size_t(head) * D + half * kOC;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < kOC / 32; ++c) {
         uint32_t o[32];
-        tmem_ld_32x32b_x32(tmem_O + lane_addr + c * 32, o);
+        tmem_ld_32x32b_x32(tmem_O + lane_addr + half * kOC + c * 32, o);
         tmem_ld_wait();
         if (row < p.Sq) {
 #pragma unroll
@@ -331,10 +365,10 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
           }
         }
       }
-      if (row < p.Sq && p.lse) {
+      if (row < p.Sq && p.lse && half == 0) {
         // natural-log LSE of the scaled scores
         p.lse[(size_t(batch) * p.H + head) * p.Sq + row] =
-            (l > 0.f) ? (m_used + log2f(l)) * 0.6931471805599453f : -INFINITY;
+            (l_row > 0.f) ? (m_used + log2f(l_row)) * 0.6931471805599453f : -INFINITY;
       }
     }
   }
@@ -358,7 +392,7 @@ static int launch_fwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
       }))
     return e;
   dim3 grid((p.Sq + 127) / 128, p.H, p.B);
-  kern<<<grid, 192, L::kTotal, stream>>>(tq, tk, tv, p);
+  kern<<<grid, kFwdThreads, L::kTotal, stream>>>(tq, tk, tv, p);
   note_launches(1);
   return int(cudaGetLastError());
 }
