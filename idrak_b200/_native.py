@@ -104,6 +104,11 @@ def has(symbol: str) -> bool:
 
 
 def lib_path() -> Path:
+    """The native library: ``lib/libidrak_b200.so`` beside this file, or the file ``IDRAK_B200_LIB`` names (a build with
+    other compile-time options, say)."""
+    override = os.environ.get("IDRAK_B200_LIB")
+    if override:
+        return Path(override).resolve()
     return Path(__file__).resolve().parent / "lib" / "libidrak_b200.so"
 
 

@@ -96,6 +96,8 @@ TABLE: List[Setting] = [
     Setting("IDRAK_WAIT_BUDGET_NS", "int", 2_000_000_000, "how long a device-side wait (barrier, flag) may spin before it "
             "records where it gave up and returns"),
     Setting("IDRAK_NVCC", "text", "", "compiler used by python -m idrak_b200.build (default: nvcc on PATH or /usr/local/cuda)"),
+    Setting("IDRAK_B200_LIB", "text", "", "load this native library instead of lib/libidrak_b200.so"),
+    Setting("IDRAK_TP_FEW_ROW_DECODE", "bool", True, "tensor-parallel serving: decode steps of up to 64 sequences on the few-row kernels"),
     Setting("IDRAK_B200_AUTOBUILD", "bool", False, "build the native library on first use when it is missing"),
     Setting("IDRAK_REFERENCE_DATA", "text", "", "tests: folder with the reference project's test fixtures"),
     Setting("IDRAK_COMM_CANARIES", "bool", True, "communicator: check the guard bands of symmetric buffers at close"),

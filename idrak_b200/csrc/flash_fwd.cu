@@ -28,8 +28,12 @@ struct FwdSmem {
   static constexpr int kTile = 128 * D * 2;        // one 128-row operand tile
   static constexpr int kP = 128 * 128 * 2;
   static constexpr int kQ = 0;
-  static constexpr int kK = kQ + kTile;            // two stages
-  static constexpr int kV = kK + 2 * kTile;        // two stages
+  // Head size 64 keeps ONE key stage: Q K^T of a block finishes before that block's softmax starts, so the next keys
+  // load during the softmax anyway, and the 16 KB saved are what lets two CTAs share an SM (2 x 100 KB): with one CTA
+  // per SM its set-up and write-out (about 6 us) ran unhidden, half of the time at 1024 tokens.
+  static constexpr int kKStages = (D == 64) ? 1 : 2;
+  static constexpr int kK = kQ + kTile;
+  static constexpr int kV = kK + kKStages * kTile;  // two stages
   static constexpr int kPOff = kV + 2 * kTile;
   static constexpr int kXch = kPOff + kP;          // row maxima / sums exchanged between the two halves: 2 x 2 x 128 floats
   static constexpr int kBar = kXch + 2048;
@@ -120,11 +124,13 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       for (int j = 0; j < nkv && ok; ++j) {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (2u << 16) | st)) { ok = false; break; }
-        mbar_expect_tx(&k_full[st], L::kTile);
+        const int kst = (L::kKStages == 2) ? st : 0;
+        const uint32_t kph = (L::kKStages == 2) ? ph : uint32_t(j & 1);
+        if (!mbar_wait(&k_empty[kst], kph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (2u << 16) | kst)) { ok = false; break; }
+        mbar_expect_tx(&k_full[kst], L::kTile);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c)
-          tma_load_4d(smem + L::kK + st * L::kTile + c * 16384, &tmK, &k_full[st], c * 64, (jlo + j) * 128, kv_head, batch);
+          tma_load_4d(smem + L::kK + kst * L::kTile + c * 16384, &tmK, &k_full[kst], c * 64, (jlo + j) * 128, kv_head, batch);
         inflight |= 1u << st;
         if (!mbar_wait(&v_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (2u << 16) | (2 + st))) { ok = false; break; }
         mbar_expect_tx(&v_full[st], L::kTile);
@@ -153,13 +159,15 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       auto issue_scores = [&](int j) -> bool {
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(&k_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (2u << 16) | st)) return false;
+        const int kst = (L::kKStages == 2) ? st : 0;
+        const uint32_t kph = (L::kKStages == 2) ? ph : uint32_t(j & 1);
+        if (!mbar_wait(&k_full[kst], kph, abort_flag, p.st, kTimeoutSmemFull, (2u << 16) | kst)) return false;
         // the buffer's previous use (block j - 2) has been read out by the softmax warps
         const int sb = (kSBufs == 2) ? st : 0;
         const uint32_t sph = (kSBufs == 2) ? (ph ^ 1) : uint32_t((j + 1) & 1);     // the buffer's previous use: block j - kSBufs
         if (!mbar_wait(&s_empty[sb], sph, abort_flag, p.st, kTimeoutTmemEmpty, (2u << 16) | (12 + sb))) return false;
         tc_fence_after();
-        const uint32_t sk = smem_u32(smem + L::kK + st * L::kTile);
+        const uint32_t sk = smem_u32(smem + L::kK + kst * L::kTile);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const uint32_t o = (kk >> 2) * 16384 + (kk & 3) * 32;
@@ -167,7 +175,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                         idesc_s, kk > 0 ? 1u : 0u);
         }
         tc_commit(&s_full[sb]);
-        tc_commit(&k_empty[st]);
+        tc_commit(&k_empty[kst]);
         return true;
       };
       if (ok) ok = issue_scores(0);

@@ -351,8 +351,14 @@ class ModelRunner:
             o = dops.paged_decode(q, self.k_cache[li], self.v_cache[li], block_table, lens, attn.scale, window or 0,
                                   max_len_hint=max_len_hint, k_scale=self.k_scale[li], v_scale=self.v_scale[li])
             x = skinny_linear(o.reshape(n, H * D), attn.o_weight, attn.o_bias, residual=x)
-            h = x if folded else blk.mlp_norm(x)
-            g = skinny_linear(h, mlp.up_weight, mlp.up_bias, gate=s.activation, norm_eps=eps)
+            if folded:
+                g = skinny_linear(x, mlp.up_weight, mlp.up_bias, gate=s.activation, norm_eps=eps)
+            else:
+                # the stacked gate / up matrix is wide enough for the dense kernel to stream it faster (measured:
+                # 56 + 8 us against 74 us at 64 rows of the 8 B shape); the few-row kernel earns its place where the
+                # norm is folded in as well
+                gu = ops.gemm(blk.mlp_norm(x), mlp.up_weight, bias=mlp.up_bias)
+                g = ops.gated_activation(gu, s.activation)
             x = skinny_linear(g, mlp.down_weight, mlp.down_bias, residual=x)
         if folded:
             logits = skinny_linear(x, m.head_weight(), m.head_bias, norm_eps=s.norm_epsilon)

@@ -37,7 +37,38 @@ class TPModelRunner(ModelRunner):
         self.vocab_local = max(0, min(hi, self.full_spec.vocabulary) - lo)      # columns of the slice that are real tokens
 
     def _few_row_path(self) -> bool:
-        return False            # the single-GPU fused decode layer has no all-reduce in it
+        """Decode steps of up to 64 sequences on the few-row projection kernels, as on one GPU, with the row-parallel
+        products written straight into the symmetric buffer the all-reduce kernel reads."""
+        import os
+        return os.environ.get("IDRAK_TP_FEW_ROW_DECODE", "1") != "0" and super()._few_row_path()
+
+    def _decode_few_rows(self, x, positions, slots, block_table, lens, max_len_hint):
+        """Eight or nine launches per layer: qkv | q/k norms + RoPE + cache write | paged attention (+ merge) | out
+        (partial, into the symmetric buffer) | all-reduce + residual + norm | gate/up + activation | down (partial) |
+        all-reduce + residual + the next layer's norm."""
+        from ..ops import decode as dops
+        from ..ops.skinny import skinny_linear
+        s, m, tp = self.spec, self.model, self.tp
+        H, Hkv, D = s.heads, s.kv_heads, s.head_dim
+        n = x.shape[0]
+        blocks = list(m.blocks)
+        h = blocks[0].attn_norm(x)
+        for li, blk in enumerate(blocks):
+            attn, mlp = blk.attn, blk.mlp
+            qkv = skinny_linear(h, attn.qkv_weight, attn.qkv_bias)
+            self._rotate_and_cache(attn, qkv, positions, slots, li)
+            q = qkv[:, : H * D].unflatten(-1, (H, D))
+            window = s.sliding_window if s.is_windowed(attn.layer) else 0
+            o = dops.paged_decode(q, self.k_cache[li], self.v_cache[li], block_table, lens, attn.scale, window or 0,
+                                  max_len_hint=max_len_hint, k_scale=self.k_scale[li], v_scale=self.v_scale[li])
+            part = skinny_linear(o.reshape(n, H * D), attn.o_weight, attn.o_bias, out=tp.partial_buffer(n))
+            x, h = tp.all_reduce_rows(part, x, blk.mlp_norm)
+            g = skinny_linear(h, mlp.up_weight, mlp.up_bias, gate=s.activation)
+            part = skinny_linear(g, mlp.down_weight, mlp.down_bias, out=tp.partial_buffer(n))
+            nxt = blocks[li + 1].attn_norm if li + 1 < len(blocks) else m.norm
+            x, h = tp.all_reduce_rows(part, x, nxt)
+        logits = skinny_linear(h, m.tp_head, m.tp_head_bias)
+        return logits.reshape(-1, logits.shape[-1])
 
     def _sum_partials(self, partial: torch.Tensor, residual: torch.Tensor, norm=None):
         """``residual + sum over ranks(partial)`` (and the norm of that): ``[1, T, dim]`` in and out."""
