@@ -10,7 +10,10 @@
 //   flash_delta   delta[b,h,s] = sum_d dO * O.
 //
 // Warp roles match the forward kernel: warp 0 feeds shared memory with TMA, warp 1 issues tcgen05.mma,
-// warps 2..5 do the element-wise work one row per thread. The same 128B-swizzled tile serves as a
+// warps 2..9 do the element-wise work, two threads per tile row with 64 of the block's 128 columns each (the row
+// statistics come from the forward pass, so the halves are independent). The operand tiles the element-wise warps
+// produce (dS; P^T and dS^T) are double-buffered, each buffer with its own "product done" barrier, so the next block is
+// filled while the tensor cores still accumulate from the previous one. The same 128B-swizzled tile serves as a
 // K-major operand for one product and as an MN-major operand for the other, so nothing is transposed.
 //
 // Reference counterparts: flash_tc_bwd_q_d{64,128}, flash_tc_bwd_kv_d{64,128}, flash_tc_delta
@@ -21,7 +24,8 @@ namespace idrak {
 
 constexpr float kLog2e = 1.4426950408889634f;
 
-__device__ __forceinline__ void softmax_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+constexpr int kBwdThreads = 320;      // TMA warp, MMA warp, eight element-wise warps (two threads per tile row)
+__device__ __forceinline__ void softmax_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // Write 32 consecutive columns [c*32, c*32+32) of row r of a 128x128 bf16 K-major operand tile.
 __device__ __forceinline__ void store_operand_chunk(uint8_t* tile, int r, int c, const float (&v)[32]) {
@@ -89,13 +93,13 @@ struct BwdQSmem {
   static constexpr int kDO = kQ + kTile;
   static constexpr int kK = kDO + kTile;
   static constexpr int kV = kK + kStages * kTile;
-  static constexpr int kDS = kV + kStages * kTile;
-  static constexpr int kBar = kDS + 32768;
+  static constexpr int kDS = kV + kStages * kTile;          // two dS tiles: the next one is filled while the tensor
+  static constexpr int kBar = kDS + 2 * 32768;              // cores still read the previous one for dQ
   static constexpr int kTotal = kBar + 256 + 1024;
 };
 
 template <int D, bool MODES>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                    const FlashParams p) {
@@ -109,9 +113,9 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* kv_empty = bars + 3;    // [2]
   uint64_t* sdp_full = bars + 5;
   uint64_t* ds_ready = bars + 6;
-  uint64_t* dq_done = bars + 7;
-  uint64_t* sdp_taken = bars + 8;   // the element-wise warps hold S and dP of the block in registers: TMEM may be rewritten
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* dq_done = bars + 7;     // [2]: one per dS tile
+  uint64_t* sdp_taken = bars + 9;   // the element-wise warps hold S and dP of the block in registers: TMEM may be rewritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -135,9 +139,10 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       mbar_init(&kv_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(ds_ready, 128);
-    mbar_init(dq_done, 1);
-    mbar_init(sdp_taken, 128);
+    mbar_init(ds_ready, 256);
+    mbar_init(&dq_done[0], 1);
+    mbar_init(&dq_done[1], 1);
+    mbar_init(sdp_taken, 256);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -213,19 +218,22 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         if (!mbar_wait(ds_ready, j & 1, abort_flag, p.st, kTimeoutGeneric, (3u << 16) | 9)) break;
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + L::kK + st * L::kTile);
+        const uint32_t sds_b = sds + (j & 1) * 32768;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          tc_mma_f16_ss(tmem_dQ, kmajor_desc(sds, kk), mnmajor_desc(sk, kk), idesc_dq, (j > 0 || kk > 0) ? 1u : 0u);
+          tc_mma_f16_ss(tmem_dQ, kmajor_desc(sds_b, kk), mnmajor_desc(sk, kk), idesc_dq, (j > 0 || kk > 0) ? 1u : 0u);
         tc_commit(&kv_empty[st]);
-        tc_commit(dq_done);
+        tc_commit(&dq_done[j & 1]);
       }
     }
   } else {
+    // Two threads per query row: warps 2..5 take key columns [0, 64) of a block, warps 6..9 columns [64, 128); the
+    // row's statistics come from the forward pass, so the halves are independent.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
     const int row = q0 + r;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-    uint8_t* sDS = smem + L::kDS;
     float lse2 = INFINITY, dlt = 0.f;
     if (row < p.Sq) {
       const size_t idx = (size_t(batch) * p.H + head) * p.Sq + row;
@@ -242,76 +250,77 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     for (int j = 0; j < nkv && ok; ++j) {
       if (!mbar_wait(sdp_full, j & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 10)) { ok = false; break; }
       tc_fence_after();
-      const int k0 = (jlo + j) * 128;
+      uint8_t* sDS = smem + L::kDS + (j & 1) * 32768;
+      const int k0 = (jlo + j) * 128 + half * 64;            // first key of this thread's 64 columns
       int lim = p.Skv - k0;
       if (p.causal) lim = min(lim, row + off - k0 + 1);
-      lim = max(0, min(128, lim));
-      const int lo = max(0, min(128, row_lo - k0));          // keys below the row's window / sequence start
-      // two halves of 64 columns: four loads in flight and one wait each; after the second half is in registers the
-      // MMA warp may overwrite S and dP with the next block's
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t s[2][32], dp[2][32];
-        tmem_ld_32x32b_x32(tmem_S + lane_addr + h * 64, s[0]);
-        tmem_ld_32x32b_x32(tmem_S + lane_addr + h * 64 + 32, s[1]);
-        tmem_ld_32x32b_x32(tmem_dP + lane_addr + h * 64, dp[0]);
-        tmem_ld_32x32b_x32(tmem_dP + lane_addr + h * 64 + 32, dp[1]);
-        tmem_ld_wait();
-        if (h == 1) {
-          tc_fence_before();
-          mbar_arrive(sdp_taken);
-        }
-        if (h == 0 && j > 0) {
-          // the previous dQ product still reads the dS tile until dq_done completes
-          if (!mbar_wait(dq_done, (j - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 11)) { ok = false; }
-        }
-#pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = h * 2 + cc;
-          float ds[32];
-          if (!special) {
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - lse2);
-              float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * p.scale;
-              ds[i] = (c * 32 + i < lim) ? v : 0.f;
-            }
-          } else {
-            // lower key bound and / or soft-capped scores: u = cap * tanh(s * scale / cap), du/ds = scale * (1 - tanh^2)
-#pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              float sc = __uint_as_float(s[cc][i]), g = p.scale;
-              if (capped) {
-                const float t = tanh_fast(sc * cap_in);
-                sc = t * cap_l2;
-                g *= 1.f - t * t;
-              } else {
-                sc *= p.scale_log2;
-              }
-              float pr = fast_exp2(sc - lse2);
-              float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * g;
-              ds[i] = (c * 32 + i < lim && c * 32 + i >= lo) ? v : 0.f;
-            }
-          }
-          if (ok) store_operand_chunk(sDS, r, c, ds);
+      lim = max(0, min(64, lim));
+      const int lo = max(0, min(64, row_lo - k0));           // keys below the row's window / sequence start
+      // four loads in flight and one wait; once every thread holds its part the MMA warp may overwrite S and dP with
+      // the next block's
+      uint32_t s[2][32], dp[2][32];
+      tmem_ld_32x32b_x32(tmem_S + lane_addr + half * 64, s[0]);
+      tmem_ld_32x32b_x32(tmem_S + lane_addr + half * 64 + 32, s[1]);
+      tmem_ld_32x32b_x32(tmem_dP + lane_addr + half * 64, dp[0]);
+      tmem_ld_32x32b_x32(tmem_dP + lane_addr + half * 64 + 32, dp[1]);
+      tmem_ld_wait();
+      tc_fence_before();
+      mbar_arrive(sdp_taken);
+      if (j >= 2) {
+        // the dQ product that last read this dS tile (block j - 2) must be complete
+        if (!mbar_wait(&dq_done[j & 1], uint32_t((j >> 1) - 1) & 1u, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 11)) {
+          ok = false;
+          break;
         }
       }
-      if (!ok) break;
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        float ds[32];
+        if (!special) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - lse2);
+            float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * p.scale;
+            ds[i] = (cc * 32 + i < lim) ? v : 0.f;
+          }
+        } else {
+          // lower key bound and / or soft-capped scores: u = cap * tanh(s * scale / cap), du/ds = scale * (1 - tanh^2)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            float sc = __uint_as_float(s[cc][i]), g = p.scale;
+            if (capped) {
+              const float t = tanh_fast(sc * cap_in);
+              sc = t * cap_l2;
+              g *= 1.f - t * t;
+            } else {
+              sc *= p.scale_log2;
+            }
+            float pr = fast_exp2(sc - lse2);
+            float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * g;
+            ds[i] = (cc * 32 + i < lim && cc * 32 + i >= lo) ? v : 0.f;
+          }
+        }
+        store_operand_chunk(sDS, r, half * 2 + cc, ds);
+      }
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(ds_ready);
     }
     if (ok && nkv > 0) {
-      if (!mbar_wait(dq_done, (nkv - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 12)) ok = false;
+      const int last = nkv - 1;
+      if (!mbar_wait(&dq_done[last & 1], uint32_t(last >> 1) & 1u, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 12))
+        ok = false;
     }
     tc_fence_after();
     if (ok || nkv <= 0) {     // warp-uniform: every thread of the warp waited on the same barriers
-      __nv_bfloat16* drow = p.dQ + (size_t(batch) * p.Sq + row) * p.dq_row_stride + size_t(head) * D;
+      // each half writes D / 2 columns of the row
+      constexpr int kOC = D / 2;
+      __nv_bfloat16* drow = p.dQ + (size_t(batch) * p.Sq + row) * p.dq_row_stride + size_t(head) * D + half * kOC;
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = 0; c < kOC / 32; ++c) {
         uint32_t o[32];
         if (nkv > 0) {
-          tmem_ld_32x32b_x32(tmem_dQ + lane_addr + c * 32, o);   // aligned: all 32 lanes take part
+          tmem_ld_32x32b_x32(tmem_dQ + lane_addr + half * kOC + c * 32, o);   // aligned: all 32 lanes take part
           tmem_ld_wait();
         } else {
 #pragma unroll
@@ -350,15 +359,18 @@ struct BwdKVSmem {
   static constexpr int kV = kK + kTile;
   static constexpr int kQ = kV + kTile;
   static constexpr int kDO = kQ + kStages * kTile;
+  // head size 64: two P^T / dS^T buffers, so the element-wise warps fill the next pair while the tensor cores still
+  // accumulate dV / dK from the previous one (224 KB in all; at head size 128 there is room for one pair only)
+  static constexpr int kPBufs = (D == 64) ? 2 : 1;
   static constexpr int kPT = kDO + kStages * kTile;
-  static constexpr int kDST = kPT + 32768;
-  static constexpr int kStat = kDST + 32768;       // lse2[128], delta[128], lo[128]
+  static constexpr int kDST = kPT + kPBufs * 32768;
+  static constexpr int kStat = kDST + kPBufs * 32768;       // lse2[128], delta[128], lo[128]
   static constexpr int kBar = kStat + 1536;
   static constexpr int kTotal = kBar + 256 + 1024;
 };
 
 template <int D, bool MODES>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                     const FlashParams p) {
@@ -372,9 +384,9 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* qdo_empty = bars + 3;   // [2]
   uint64_t* sdp_full = bars + 5;
   uint64_t* pds_ready = bars + 6;
-  uint64_t* acc_done = bars + 7;
-  uint64_t* sdp_taken = bars + 8;   // S^T and dP^T of the block are in registers: TMEM may be rewritten
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 9);
+  uint64_t* acc_done = bars + 7;    // [2]: one per P^T / dS^T buffer
+  uint64_t* sdp_taken = bars + 9;   // S^T and dP^T of the block are in registers: TMEM may be rewritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   float* s_lse2 = reinterpret_cast<float*>(smem + L::kStat);
   float* s_delta = s_lse2 + 128;
@@ -411,9 +423,10 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       mbar_init(&qdo_empty[s], 1);
     }
     mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 128);
-    mbar_init(acc_done, 1);
-    mbar_init(sdp_taken, 128);
+    mbar_init(pds_ready, 256);
+    mbar_init(&acc_done[0], 1);
+    mbar_init(&acc_done[1], 1);
+    mbar_init(sdp_taken, 256);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -493,35 +506,43 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         if (!mbar_wait(pds_ready, it & 1, abort_flag, p.st, kTimeoutGeneric, (4u << 16) | 9)) break;
         tc_fence_after();
         const uint32_t sq = smem_u32(smem + L::kQ + st * L::kTile), sdo = smem_u32(smem + L::kDO + st * L::kTile);
+        const int pb = it % L::kPBufs;
+        const uint32_t spt_b = spt + pb * 32768, sdst_b = sdst + pb * 32768;
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          tc_mma_f16_ss(tmem_dV, kmajor_desc(spt, kk), mnmajor_desc(sdo, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+          tc_mma_f16_ss(tmem_dV, kmajor_desc(spt_b, kk), mnmajor_desc(sdo, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk)
-          tc_mma_f16_ss(tmem_dK, kmajor_desc(sdst, kk), mnmajor_desc(sq, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+          tc_mma_f16_ss(tmem_dK, kmajor_desc(sdst_b, kk), mnmajor_desc(sq, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
         tc_commit(&qdo_empty[st]);
-        tc_commit(acc_done);
+        tc_commit(&acc_done[pb]);
       }
     }
   } else {
+    // Two threads per key row: warps 2..5 take query columns [0, 64) of the block, warps 6..9 columns [64, 128). The
+    // columns are independent here (the row statistics come from the forward pass), so the halves never talk.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;       // key row within the block
     const int key = k0 + r;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-    uint8_t* sPT = smem + L::kPT;
-    uint8_t* sDST = smem + L::kDST;
     bool ok = true;
     const bool capped = MODES && p.softcap > 0.f;
     const bool special = bounded || capped;
     const float cap_in = capped ? p.scale / p.softcap : 0.f;
     const float cap_l2 = p.softcap * kLog2e;
-    for (int it = 0; it < iters && ok; ++it) {
+    // A thread whose wait gave up keeps walking the loop without touching tensor memory: the block-wide barrier of the
+    // element-wise warps has no time limit of its own, so nobody may leave early.
+    for (int it = 0; it < iters; ++it) {
       const int head = kv_head * group + it / per_head;
       const int qi = i_min + it % per_head;
       const int qrow0 = qi * 128;
-      // stage this query block's row statistics (thread r loads query r)
+      const int pb = it % L::kPBufs;
+      uint8_t* sPT = smem + L::kPT + pb * 32768;
+      uint8_t* sDST = smem + L::kDST + pb * 32768;
+      // stage this query block's row statistics (thread r of the first half loads query r)
       softmax_bar_sync();    // readers of the previous block's statistics are done
-      {
+      if (half == 0) {
         const int qr = qrow0 + r;
         float l2 = INFINITY, dl = 0.f;
         if (qr < p.Sq) {
@@ -535,101 +556,103 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         s_lo[r] = bounded ? flash_row_lo(p, batch, qr, off) : 0;
       }
       softmax_bar_sync();
-      if (!mbar_wait(sdp_full, it & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 10)) { ok = false; break; }
+      if (ok && !mbar_wait(sdp_full, it & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 10)) ok = false;
       tc_fence_after();
       // query q (column) sees this key iff key <= q + off  <=>  q >= key - off
       const int first_q = p.causal ? (key - off - qrow0) : 0;    // columns below this are masked
-      // two halves of 64 columns: four loads in flight and one wait each; the MMA warp may rewrite S^T and dP^T once
-      // the second half is in registers
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        uint32_t s[2][32], dp[2][32];
-        tmem_ld_32x32b_x32(tmem_ST + lane_addr + h * 64, s[0]);
-        tmem_ld_32x32b_x32(tmem_ST + lane_addr + h * 64 + 32, s[1]);
-        tmem_ld_32x32b_x32(tmem_dPT + lane_addr + h * 64, dp[0]);
-        tmem_ld_32x32b_x32(tmem_dPT + lane_addr + h * 64 + 32, dp[1]);
+      // this thread's 64 columns: four loads in flight and one wait; the MMA warp may rewrite S^T and dP^T once every
+      // thread holds its part in registers
+      uint32_t s[2][32], dp[2][32];
+      if (ok) {
+        tmem_ld_32x32b_x32(tmem_ST + lane_addr + half * 64, s[0]);
+        tmem_ld_32x32b_x32(tmem_ST + lane_addr + half * 64 + 32, s[1]);
+        tmem_ld_32x32b_x32(tmem_dPT + lane_addr + half * 64, dp[0]);
+        tmem_ld_32x32b_x32(tmem_dPT + lane_addr + half * 64 + 32, dp[1]);
         tmem_ld_wait();
-        if (h == 1) {
-          tc_fence_before();
-          mbar_arrive(sdp_taken);
-        }
-        if (h == 0 && it > 0) {
-          // the previous accumulation still reads the P^T and dS^T tiles until acc_done completes
-          if (!mbar_wait(acc_done, (it - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 11)) ok = false;
-        }
+        tc_fence_before();
+        mbar_arrive(sdp_taken);
+      } else {
 #pragma unroll
-        for (int cc = 0; cc < 2; ++cc) {
-          const int c = h * 2 + cc;
-          float pt[32], dst[32];
-          if (!special) {
+        for (int i = 0; i < 32; ++i) s[0][i] = s[1][i] = dp[0][i] = dp[1][i] = 0u;
+      }
+      if (ok && it >= L::kPBufs) {
+        // the accumulation that last read this P^T / dS^T buffer (iteration it - kPBufs) must be complete
+        const uint32_t use = uint32_t(it / L::kPBufs) - 1u;
+        if (!mbar_wait(&acc_done[pb], use & 1u, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 11)) ok = false;
+      }
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int col = c * 32 + i;
-              float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - s_lse2[col]);
-              if (col < first_q) pr = 0.f;
-              pt[i] = pr;
-              dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * p.scale;
-            }
-          } else {
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = half * 2 + cc;
+        float pt[32], dst[32];
+        if (!special) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              const int col = c * 32 + i;
-              float sc = __uint_as_float(s[cc][i]), g = p.scale;
-              if (capped) {
-                const float t = tanh_fast(sc * cap_in);
-                sc = t * cap_l2;
-                g *= 1.f - t * t;
-              } else {
-                sc *= p.scale_log2;
-              }
-              float pr = fast_exp2(sc - s_lse2[col]);
-              if (col < first_q || key < s_lo[col]) pr = 0.f;
-              pt[i] = pr;
-              dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * g;
-            }
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - s_lse2[col]);
+            if (col < first_q) pr = 0.f;
+            pt[i] = pr;
+            dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * p.scale;
           }
-          if (ok) {
-            store_operand_chunk(sPT, r, c, pt);
-            store_operand_chunk(sDST, r, c, dst);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int col = c * 32 + i;
+            float sc = __uint_as_float(s[cc][i]), g = p.scale;
+            if (capped) {
+              const float t = tanh_fast(sc * cap_in);
+              sc = t * cap_l2;
+              g *= 1.f - t * t;
+            } else {
+              sc *= p.scale_log2;
+            }
+            float pr = fast_exp2(sc - s_lse2[col]);
+            if (col < first_q || key < s_lo[col]) pr = 0.f;
+            pt[i] = pr;
+            dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * g;
           }
+        }
+        if (ok) {
+          store_operand_chunk(sPT, r, c, pt);
+          store_operand_chunk(sDST, r, c, dst);
         }
       }
-      if (!ok) break;
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(pds_ready);
+      if (ok) {
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(pds_ready);
+      }
     }
     if (ok && iters > 0) {
-      if (!mbar_wait(acc_done, (iters - 1) & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 12)) ok = false;
+      const int last = iters - 1;
+      if (!mbar_wait(&acc_done[last % L::kPBufs], uint32_t(last / L::kPBufs) & 1u, abort_flag, p.st, kTimeoutTmemFull,
+                     (4u << 16) | 12))
+        ok = false;
     }
     tc_fence_after();
     if (ok || iters == 0) {   // warp-uniform
-      __nv_bfloat16* dkrow = p.dK + (size_t(batch) * p.Skv + key) * p.dk_row_stride + size_t(kv_head) * D;
-      __nv_bfloat16* dvrow = p.dV + (size_t(batch) * p.Skv + key) * p.dv_row_stride + size_t(kv_head) * D;
+      // the first half writes dV, the second dK
+      __nv_bfloat16* drow = (half ? p.dK + (size_t(batch) * p.Skv + key) * p.dk_row_stride
+                                  : p.dV + (size_t(batch) * p.Skv + key) * p.dv_row_stride) + size_t(kv_head) * D;
+      const uint32_t t = half ? tmem_dK : tmem_dV;
 #pragma unroll 1
-      for (int which = 0; which < 2; ++which) {
-        __nv_bfloat16* drow = which ? dkrow : dvrow;
-        const uint32_t t = which ? tmem_dK : tmem_dV;
-#pragma unroll 1
-        for (int c = 0; c < D / 32; ++c) {
-          uint32_t o[32];
-          if (iters > 0) {
-            tmem_ld_32x32b_x32(t + lane_addr + c * 32, o);
-            tmem_ld_wait();
-          } else {
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t o[32];
+        if (iters > 0) {
+          tmem_ld_32x32b_x32(t + lane_addr + c * 32, o);
+          tmem_ld_wait();
+        } else {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = 0u;
-          }
-          if (key >= p.Skv) continue;
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (key >= p.Skv) continue;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            uint4 w;
-            w.x = pack_bf16x2(__uint_as_float(o[g * 8 + 0]), __uint_as_float(o[g * 8 + 1]));
-            w.y = pack_bf16x2(__uint_as_float(o[g * 8 + 2]), __uint_as_float(o[g * 8 + 3]));
-            w.z = pack_bf16x2(__uint_as_float(o[g * 8 + 4]), __uint_as_float(o[g * 8 + 5]));
-            w.w = pack_bf16x2(__uint_as_float(o[g * 8 + 6]), __uint_as_float(o[g * 8 + 7]));
-            *reinterpret_cast<uint4*>(drow + c * 32 + g * 8) = w;
-          }
+        for (int g = 0; g < 4; ++g) {
+          uint4 w;
+          w.x = pack_bf16x2(__uint_as_float(o[g * 8 + 0]), __uint_as_float(o[g * 8 + 1]));
+          w.y = pack_bf16x2(__uint_as_float(o[g * 8 + 2]), __uint_as_float(o[g * 8 + 3]));
+          w.z = pack_bf16x2(__uint_as_float(o[g * 8 + 4]), __uint_as_float(o[g * 8 + 5]));
+          w.w = pack_bf16x2(__uint_as_float(o[g * 8 + 6]), __uint_as_float(o[g * 8 + 7]));
+          *reinterpret_cast<uint4*>(drow + c * 32 + g * 8) = w;
         }
       }
     }
@@ -656,12 +679,12 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
       }))
     return e;
   dim3 gq((p.Sq + 127) / 128, p.H, p.B);
-  kq<<<gq, 192, BwdQSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  kq<<<gq, kBwdThreads, BwdQSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
   note_launches(1);
   int rc = int(cudaGetLastError());
   if (rc) return rc;
   dim3 gkv((p.Skv + 127) / 128, p.Hkv, p.B);
-  kkv<<<gkv, 192, BwdKVSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  kkv<<<gkv, kBwdThreads, BwdKVSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
   note_launches(1);
   return int(cudaGetLastError());
 }
