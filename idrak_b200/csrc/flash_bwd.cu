@@ -88,7 +88,9 @@ __global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o, const __
 template <int D>
 struct BwdQSmem {
   static constexpr int kTile = 128 * D * 2;
-  static constexpr int kStages = (D == 64) ? 2 : 1;
+  // three K / V stages at head size 64: a stage is freed only by the dQ product of its block, and with two the load of
+  // block j + 2 (about 1500 cycles from L2) sat on the critical path of every block
+  static constexpr int kStages = (D == 64) ? 3 : 1;
   static constexpr int kQ = 0;
   static constexpr int kDO = kQ + kTile;
   static constexpr int kK = kDO + kTile;
@@ -109,13 +111,13 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
   uint64_t* qdo_full = bars + 0;
-  uint64_t* kv_full = bars + 1;     // [2]
-  uint64_t* kv_empty = bars + 3;    // [2]
-  uint64_t* sdp_full = bars + 5;
-  uint64_t* ds_ready = bars + 6;
-  uint64_t* dq_done = bars + 7;     // [2]: one per dS tile
-  uint64_t* sdp_taken = bars + 9;   // the element-wise warps hold S and dP of the block in registers: TMEM may be rewritten
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* kv_full = bars + 1;     // [3]
+  uint64_t* kv_empty = bars + 4;    // [3]
+  uint64_t* sdp_full = bars + 7;
+  uint64_t* ds_ready = bars + 8;
+  uint64_t* dq_done = bars + 9;     // [2]: one per dS tile
+  uint64_t* sdp_taken = bars + 11;  // the element-wise warps hold S and dP of the block in registers: TMEM may be rewritten
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -134,7 +136,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < 3; ++s) {
       mbar_init(&kv_full[s], 1);
       mbar_init(&kv_empty[s], 1);
     }
@@ -531,31 +533,47 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const bool special = bounded || capped;
     const float cap_in = capped ? p.scale / p.softcap : 0.f;
     const float cap_l2 = p.softcap * kLog2e;
+    auto load_stats = [&](int it, float& l2, float& dl, int& lo) {
+      const int head = kv_head * group + it / per_head;
+      const int qr = (i_min + it % per_head) * 128 + r;
+      l2 = INFINITY;
+      dl = 0.f;
+      if (qr < p.Sq) {
+        const size_t idx = (size_t(batch) * p.H + head) * p.Sq + qr;
+        const float l = p.lse[idx];
+        l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+        dl = p.delta[idx];
+      }
+      lo = bounded ? flash_row_lo(p, batch, qr, off) : 0;
+    };
+    auto store_stats = [&](float l2, float dl, int lo) {
+      s_lse2[r] = l2;
+      s_delta[r] = dl;
+      s_lo[r] = lo;
+    };
+    if (half == 0 && iters > 0) {
+      float l2, dl;
+      int lo;
+      load_stats(0, l2, dl, lo);
+      store_stats(l2, dl, lo);
+    }
+    softmax_bar_sync();
     // A thread whose wait gave up keeps walking the loop without touching tensor memory: the block-wide barrier of the
     // element-wise warps has no time limit of its own, so nobody may leave early.
     for (int it = 0; it < iters; ++it) {
-      const int head = kv_head * group + it / per_head;
       const int qi = i_min + it % per_head;
       const int qrow0 = qi * 128;
       const int pb = it % L::kPBufs;
       uint8_t* sPT = smem + L::kPT + pb * 32768;
       uint8_t* sDST = smem + L::kDST + pb * 32768;
-      // stage this query block's row statistics (thread r of the first half loads query r)
-      softmax_bar_sync();    // readers of the previous block's statistics are done
-      if (half == 0) {
-        const int qr = qrow0 + r;
-        float l2 = INFINITY, dl = 0.f;
-        if (qr < p.Sq) {
-          const size_t idx = (size_t(batch) * p.H + head) * p.Sq + qr;
-          const float l = p.lse[idx];
-          l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
-          dl = p.delta[idx];
-        }
-        s_lse2[r] = l2;
-        s_delta[r] = dl;
-        s_lo[r] = bounded ? flash_row_lo(p, batch, qr, off) : 0;
-      }
-      softmax_bar_sync();
+      // the statistics of this query block were staged at the end of the previous iteration; those of the next block
+      // are fetched now and stored at the end of this one, so their latency hides behind this block's arithmetic
+      const float* c_lse2 = s_lse2;
+      const float* c_delta = s_delta;
+      const int* c_lo = s_lo;
+      float n_l2 = INFINITY, n_dl = 0.f;
+      int n_lo = 0;
+      if (half == 0 && it + 1 < iters) load_stats(it + 1, n_l2, n_dl, n_lo);
       if (ok && !mbar_wait(sdp_full, it & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 10)) ok = false;
       tc_fence_after();
       // query q (column) sees this key iff key <= q + off  <=>  q >= key - off
@@ -588,10 +606,10 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
             const int col = c * 32 + i;
-            float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - s_lse2[col]);
+            float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - c_lse2[col]);
             if (col < first_q) pr = 0.f;
             pt[i] = pr;
-            dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * p.scale;
+            dst[i] = pr * (__uint_as_float(dp[cc][i]) - c_delta[col]) * p.scale;
           }
         } else {
 #pragma unroll
@@ -605,10 +623,10 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
             } else {
               sc *= p.scale_log2;
             }
-            float pr = fast_exp2(sc - s_lse2[col]);
-            if (col < first_q || key < s_lo[col]) pr = 0.f;
+            float pr = fast_exp2(sc - c_lse2[col]);
+            if (col < first_q || key < c_lo[col]) pr = 0.f;
             pt[i] = pr;
-            dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * g;
+            dst[i] = pr * (__uint_as_float(dp[cc][i]) - c_delta[col]) * g;
           }
         }
         if (ok) {
@@ -621,6 +639,9 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         tc_fence_before();
         mbar_arrive(pds_ready);
       }
+      softmax_bar_sync();    // this block's statistics are no longer read
+      if (half == 0 && it + 1 < iters) store_stats(n_l2, n_dl, n_lo);
+      softmax_bar_sync();    // the next block's are visible
     }
     if (ok && iters > 0) {
       const int last = iters - 1;
