@@ -147,6 +147,23 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(sdp_taken, 256);
     *abort_flag = 0;
     fence_barrier_init();
+    if (nkv > 0) {
+      // first loads before the CTA-wide sync (this thread is also the producer): their latency overlaps the
+      // tensor-memory allocation
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmDO);
+      mbar_expect_tx(qdo_full, 2 * L::kTile);
+      mbar_expect_tx(&kv_full[0], 2 * L::kTile);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_4d(smem + L::kQ + c * 16384, &tmQ, qdo_full, c * 64, q0, head, batch);
+        tma_load_4d(smem + L::kDO + c * 16384, &tmDO, qdo_full, c * 64, q0, head, batch);
+        tma_load_4d(smem + L::kK + c * 16384, &tmK, &kv_full[0], c * 64, jlo * 128, kv_head, batch);
+        tma_load_4d(smem + L::kV + c * 16384, &tmV, &kv_full[0], c * 64, jlo * 128, kv_head, batch);
+      }
+    }
   }
   constexpr uint32_t kTmemCols = 512;   // S [0,128) | dP [128,256) | dQ [256, 256+D)
   if (warp == 1) {
@@ -161,17 +178,7 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 
   if (warp == 0) {
     if (lane == 0 && nkv > 0) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      tma_prefetch_desc(&tmDO);
-      mbar_expect_tx(qdo_full, 2 * L::kTile);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        tma_load_4d(smem + L::kQ + c * 16384, &tmQ, qdo_full, c * 64, q0, head, batch);
-        tma_load_4d(smem + L::kDO + c * 16384, &tmDO, qdo_full, c * 64, q0, head, batch);
-      }
-      for (int j = 0; j < nkv; ++j) {
+      for (int j = 1; j < nkv; ++j) {          // block 0 was requested before the sync
         const int st = j % NS;
         const uint32_t ph = (j / NS) & 1;
         if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (3u << 16) | st)) break;
@@ -431,6 +438,22 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(sdp_taken, 256);
     *abort_flag = 0;
     fence_barrier_init();
+    if (iters > 0) {
+      // first loads before the CTA-wide sync (this thread is also the producer)
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      tma_prefetch_desc(&tmDO);
+      mbar_expect_tx(kv_full, 2 * L::kTile);
+      mbar_expect_tx(&qdo_full[0], 2 * L::kTile);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_4d(smem + L::kK + c * 16384, &tmK, kv_full, c * 64, k0, kv_head, batch);
+        tma_load_4d(smem + L::kV + c * 16384, &tmV, kv_full, c * 64, k0, kv_head, batch);
+        tma_load_4d(smem + L::kQ + c * 16384, &tmQ, &qdo_full[0], c * 64, i_min * 128, kv_head * group, batch);
+        tma_load_4d(smem + L::kDO + c * 16384, &tmDO, &qdo_full[0], c * 64, i_min * 128, kv_head * group, batch);
+      }
+    }
   }
   constexpr uint32_t kTmemCols = 512;   // S^T [0,128) | dP^T [128,256) | dV [256,256+D) | dK [256+D, 256+2D)
   if (warp == 1) {
@@ -446,17 +469,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (warp == 0) {
     if (lane == 0 && iters > 0) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      tma_prefetch_desc(&tmDO);
-      mbar_expect_tx(kv_full, 2 * L::kTile);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        tma_load_4d(smem + L::kK + c * 16384, &tmK, kv_full, c * 64, k0, kv_head, batch);
-        tma_load_4d(smem + L::kV + c * 16384, &tmV, kv_full, c * 64, k0, kv_head, batch);
-      }
-      for (int it = 0; it < iters; ++it) {
+      for (int it = 1; it < iters; ++it) {          // iteration 0 was requested before the sync
         const int st = it % NS;
         const uint32_t ph = (it / NS) & 1;
         const int head = kv_head * group + it / per_head;

@@ -94,6 +94,22 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     mbar_init(o_done, 1);
     *abort_flag = 0;
     fence_barrier_init();
+    if (nkv > 0) {
+      // The first loads go out before the CTA-wide sync below (this thread is also the producer): their latency
+      // overlaps the tensor-memory allocation instead of following it.
+      tma_prefetch_desc(&tmQ);
+      tma_prefetch_desc(&tmK);
+      tma_prefetch_desc(&tmV);
+      mbar_expect_tx(q_full, L::kTile);
+      mbar_expect_tx(&k_full[0], L::kTile);
+      mbar_expect_tx(&v_full[0], L::kTile);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        tma_load_4d(smem + L::kQ + c * 16384, &tmQ, q_full, c * 64, q0, head, batch);
+        tma_load_4d(smem + L::kK + c * 16384, &tmK, &k_full[0], c * 64, jlo * 128, kv_head, batch);
+        tma_load_4d(smem + L::kV + c * 16384, &tmV, &v_full[0], c * 64, jlo * 128, kv_head, batch);
+      }
+    }
   }
   // D = 64: one score buffer [0,128) and O at [128,192) in 256 columns, so two CTAs share an SM (one CTA's prologue and
   // epilogue hide behind the other's main loop); the buffer is handed back as soon as the row sits in registers, which
@@ -113,15 +129,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0 && nkv > 0) {
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      mbar_expect_tx(q_full, L::kTile);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) tma_load_4d(smem + L::kQ + c * 16384, &tmQ, q_full, c * 64, q0, head, batch);
       uint32_t inflight = 0;
       bool ok = true;
-      for (int j = 0; j < nkv && ok; ++j) {
+      for (int j = 1; j < nkv && ok; ++j) {          // block 0 was requested before the sync
         const int st = j & 1;
         const uint32_t ph = (j >> 1) & 1;
         const int kst = (L::kKStages == 2) ? st : 0;
