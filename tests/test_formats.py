@@ -253,3 +253,31 @@ def test_peft_folder_round_trip_and_refusals(tmp_path):
     (bad / "adapter_config.json").write_text(json.dumps(c3))
     with pytest.raises(peft.PeftConfigError, match="lora_magnitude_vector"):
         peft.load_adapters(build_decoder(spec, seed=2), bad)
+
+
+def test_pth_reader_is_an_allow_list_unpickler_of_its_own(tmp_path):
+    """Tensors (views, scalars, bf16, parameters) come back equal; a pickle that wants to call anything else is refused
+    by name before anything runs."""
+    import collections
+    import os
+    from idrak_b200.formats import pth
+    sd = collections.OrderedDict(a=torch.randn(3, 4), b=torch.arange(6).reshape(2, 3).t(), c=torch.tensor(2.5),
+                                 d=torch.randn(4).to(torch.bfloat16), e=torch.nn.Parameter(torch.ones(2)))
+    sd["module.view"] = sd["a"][1:, :2]
+    torch.save({"state_dict": sd, "epoch": 3}, tmp_path / "m.pth")
+    got = pth.load_checkpoint(tmp_path / "m.pth")
+    assert set(got) == {"a", "b", "c", "d", "e", "view"}
+    for k, v in sd.items():
+        assert torch.equal(got[k.replace("module.", "")], v.detach())
+    marker = tmp_path / "ran"
+
+    class Evil:
+        def __reduce__(self):
+            return (os.system, (f"touch {marker}",))
+    torch.save({"x": Evil()}, tmp_path / "evil.pth")
+    with pytest.raises(pth.UnsafeCheckpoint, match="system"):
+        pth.load_checkpoint(tmp_path / "evil.pth")
+    assert not marker.exists()
+    torch.save([1, 2], tmp_path / "list.pth")
+    with pytest.raises(ValueError, match="not a mapping"):
+        pth.load_checkpoint(tmp_path / "list.pth")
