@@ -163,6 +163,42 @@ def cmd_cluster(a) -> int:
                 t = predict_all_reduce(topo, a.bytes, algorithm, measured)
                 print(f"predicted {algorithm:12s} all-reduce of {a.bytes} bytes: {t * 1e3:.3f} ms")
         return 0
+    if a.action == "ui":
+        # path: the folder the ranks write their status files to
+        from ..cluster import dashboard
+        if a.serve is not None:
+            httpd = dashboard.serve(a.path, port=a.serve)
+            print(f"http://127.0.0.1:{httpd.server_address[1]}/  (Ctrl-C stops)")
+            try:
+                while True:
+                    time.sleep(1.0)
+            except KeyboardInterrupt:
+                httpd.shutdown()
+            return 0
+        while True:
+            rows = dashboard.read_status(a.path)
+            print(dashboard.render_text(rows))
+            if a.once or not rows or all(r["state"] not in ("running",) for r in rows):
+                return 0 if not any(r["state"] == "silent" for r in rows) else 1
+            time.sleep(a.refresh)
+            print()
+    if a.action == "start":
+        # path: topology file; everything after "--" is the program every rank runs
+        import subprocess
+        from ..cluster import dashboard
+        topo = load_topology(a.path)
+        node = a.node or topo.nodes[0].name
+        jobs = dashboard.local_rank_commands(topo, node, a.program or [sys.executable, "-c", "print('rank up')"], a.master_port)
+        if a.dry_run:
+            for j in jobs:
+                print(f"rank {j['rank']} cuda:{j['device']}: " + " ".join(f"{k}={v}" for k, v in j["env"].items()) + "  " + " ".join(j["command"]))
+            return 0
+        procs = [subprocess.Popen(j["command"], env={**os.environ, **j["env"]}) for j in jobs]
+        codes = [p.wait() for p in procs]
+        bad = [(j["rank"], c) for j, c in zip(jobs, codes) if c != 0]
+        for r, c in bad:
+            print(f"rank {r} exited with {c}")
+        return 1 if bad else 0
     if a.action == "calibrate":
         # path: CSV of "bytes,seconds" rows measured on the link (the link bench prints them); stored under --link
         from ..cluster.links import ClusterCache, LinkCalibration
@@ -419,9 +455,16 @@ def register(add) -> None:
     p = add("runs", cmd_runs, "list run folders")
     p.add_argument("folder", nargs="?", default=".")
     p.add_argument("--json", action="store_true")
-    p = add("cluster", cmd_cluster, "topology files and the in-process cluster simulator: init / inspect / sim / replay / calibrate")
-    p.add_argument("action", choices=["init", "inspect", "sim", "replay", "calibrate"])
+    p = add("cluster", cmd_cluster, "topology files, the in-process simulator, local rank launch and the dashboard: init / inspect / sim / replay / calibrate / start / ui")
+    p.add_argument("action", choices=["init", "inspect", "sim", "replay", "calibrate", "start", "ui"])
     p.add_argument("path", nargs="?")
+    p.add_argument("program", nargs="*", help="start: the program every rank runs (after --)")
+    p.add_argument("--node", help="start: which node of the topology this machine is (default: the first)")
+    p.add_argument("--master-port", type=int, default=29500)
+    p.add_argument("--dry-run", action="store_true", help="start: print what would run")
+    p.add_argument("--serve", type=int, nargs="?", const=0, default=None, metavar="PORT", help="ui: serve the page over HTTP")
+    p.add_argument("--once", action="store_true", help="ui: print the table once")
+    p.add_argument("--refresh", type=float, default=2.0)
     p.add_argument("--nodes", type=int, default=1)
     p.add_argument("--gpus", type=int, default=8)
     p.add_argument("--memory", default="180GiB")

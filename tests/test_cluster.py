@@ -130,3 +130,53 @@ def test_topology_file_and_advisor():
     loud = advise(1.0, 0.5, 500 << 20, 10e9, world=16, same_switch=False)
     names = [a.setting for a in loud]
     assert "compression" in names and "gradient_sync" in names and "collectives" in names and "accumulation" in names
+
+
+def test_dashboard_rows_summary_pages_and_local_launch(tmp_path):
+    import json
+    import time
+    import urllib.request
+    from idrak_b200.cluster import dashboard
+    from idrak_b200.cluster.topology import load_topology
+    folder = str(tmp_path / "status")
+    w0, w1, w2 = (dashboard.StatusWriter(folder, r, 4, "run") for r in range(3))
+    w0.update(step=12, loss=2.5, tokens_per_s=1000.0, memory_bytes=3 << 30,
+              network={"bytes_sent": 5 << 20, "bytes_read": 1 << 20})
+    w1.update(step=12, loss=2.6, tokens_per_s=900.0)
+    w2.update(step=11)
+    w2.finish("stopped")
+    now = time.time()
+    rows = dashboard.read_status(folder, stale_after=5.0, now=now + 1)
+    assert [r["rank"] for r in rows] == [0, 1, 2] and [r["state"] for r in rows] == ["running", "running", "stopped"]
+    late = dashboard.read_status(folder, stale_after=5.0, now=now + 60)
+    assert [r["state"] for r in late] == ["silent", "silent", "stopped"]          # what a rank wrote itself stays
+    s = dashboard.summary(rows)
+    assert s["running"] == 2 and s["tokens_per_s"] == 1900.0 and (s["step_min"], s["step_max"]) == (11, 12)
+    text = dashboard.render_text(rows)
+    assert "3.0 GiB" in text and "5.0 MiB" in text and "2 of 4 ranks running" in text and "1 never reported" in text
+    assert "silent: [0, 1]" in dashboard.render_text(late)
+    page = dashboard.render_html(late)
+    assert "<tr class='silent'>" in page and "http-equiv='refresh'" in page
+    (tmp_path / "status" / "rank-0009.json").write_text("{half a file")            # mid-replace: skipped, not fatal
+    assert len(dashboard.read_status(folder)) == 3
+    httpd = dashboard.serve(folder)
+    try:
+        base = f"http://127.0.0.1:{httpd.server_address[1]}"
+        got = json.loads(urllib.request.urlopen(base + "/status.json").read())
+        assert got["summary"]["ranks"] == 3 and got["ranks"][0]["loss"] == 2.5
+        assert b"<table>" in urllib.request.urlopen(base + "/").read()
+    finally:
+        httpd.shutdown()
+    topo_path = tmp_path / "topo.json"
+    topo_path.write_text(json.dumps({"format": "idrak-topology/1", "links": {"intra-node": "nvlink", "inter-node": "tcp"},
+                                     "nodes": [{"name": "a", "address": "10.0.0.1", "gpus": [{"device": 0, "memory": "80GiB"}, {"device": 1, "memory": "80GiB"}]},
+                                               {"name": "b", "address": "10.0.0.2", "gpus": [{"device": 0, "memory": "80GiB"}]}]}))
+    jobs = dashboard.local_rank_commands(load_topology(str(topo_path)), "b", ["python", "train.py"], 29511)
+    assert len(jobs) == 1 and jobs[0]["env"] == {"RANK": "2", "LOCAL_RANK": "0", "WORLD_SIZE": "3", "LOCAL_WORLD_SIZE": "1",
+                                                  "MASTER_ADDR": "10.0.0.1", "MASTER_PORT": "29511"}
+    import pytest as _pytest
+    with _pytest.raises(KeyError, match="known: a, b"):
+        dashboard.local_rank_commands(load_topology(str(topo_path)), "c", ["x"])
+    from idrak_b200.cli.__main__ import main
+    assert main(["cluster", "ui", folder, "--once"]) == 0
+    assert main(["cluster", "start", str(topo_path), "--node", "a", "--dry-run"]) == 0
