@@ -100,6 +100,44 @@ struct BwdQSmem {
   static constexpr int kTotal = kBar + 256 + 1024;
 };
 
+// Persistent, like the dK / dV kernel below: one CTA per SM walks (query block, head, batch) units, heaviest first; the
+// next unit's Q and dO load while the current unit's last block is in its element-wise and dQ steps, and the write-out of
+// dQ overlaps the next unit's first score products.
+// Unit `round` of this CTA. The units are sorted heaviest first; the CTAs take them in rounds, forwards in even rounds and
+// backwards in odd ones, so a CTA that drew a heavier unit than its neighbours in one round draws a lighter one in the
+// next (the static counterpart of handing units out one by one).
+__device__ __forceinline__ int snake_unit(int round, int units) {
+  const int g = int(gridDim.x), c = int(blockIdx.x);
+  const int u = round * g + ((round & 1) ? (g - 1 - c) : c);
+  return u < units ? u : -1;
+}
+__device__ __forceinline__ int snake_rounds(int units) { return (units + int(gridDim.x) - 1) / int(gridDim.x); }
+
+struct QUnit {
+  int qb, head, batch, kv_head, q0, jlo, nkv;
+};
+
+template <bool MODES>
+__device__ __forceinline__ QUnit q_unit(const FlashParams& p, int u, int off, int nqt) {
+  QUnit t;
+  const int per_qb = p.H * p.B;
+  const int slot = u / per_qb;
+  t.qb = p.causal ? (nqt - 1 - slot) : slot;      // later query blocks see more keys: they go first
+  const int rem = u - slot * per_qb;
+  t.head = rem % p.H;
+  t.batch = rem / p.H;
+  t.kv_head = t.head / (p.H / p.Hkv);
+  t.q0 = t.qb * 128;
+  int nkv_end = (p.Skv + 127) / 128;
+  if (p.causal) nkv_end = min(nkv_end, (t.q0 + 127 + off) / 128 + 1);
+  if (nkv_end < 0) nkv_end = 0;
+  // key blocks wholly below what the tile's first row may see are skipped (window / packed-sequence bounds)
+  const bool bounded = MODES && p.causal && (p.window > 0 || p.row_start != nullptr);
+  t.jlo = bounded ? min(nkv_end, max(0, flash_row_lo(p, t.batch, min(t.q0, p.Sq - 1), off)) / 128) : 0;
+  t.nkv = nkv_end - t.jlo;      // key block of iteration j is jlo + j
+  return t;
+}
+
 template <int D, bool MODES>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -117,22 +155,16 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   uint64_t* ds_ready = bars + 8;
   uint64_t* dq_done = bars + 9;     // [2]: one per dS tile
   uint64_t* sdp_taken = bars + 11;  // the element-wise warps hold S and dP of the block in registers: TMEM may be rewritten
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+  uint64_t* qdo_free = bars + 12;   // the unit's last score products have read Q and dO: the next unit's may land
+  uint64_t* dq_free = bars + 13;    // dQ of the unit sits in registers: the next unit may accumulate
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = p.causal ? (gridDim.x - 1 - blockIdx.x) : blockIdx.x;
-  const int head = blockIdx.y, batch = blockIdx.z;
-  const int kv_head = head / (p.H / p.Hkv);
-  const int q0 = qb * 128;
   const int off = p.Skv - p.Sq;
-  int nkv_end = (p.Skv + 127) / 128;
-  if (p.causal) nkv_end = min(nkv_end, (q0 + 127 + off) / 128 + 1);
-  if (nkv_end < 0) nkv_end = 0;
-  // key blocks wholly below what the tile's first row may see are skipped (window / packed-sequence bounds)
+  const int nqt = (p.Sq + 127) / 128;
+  const int units = nqt * p.H * p.B;
   const bool bounded = MODES && p.causal && (p.window > 0 || p.row_start != nullptr);
-  const int jlo = bounded ? min(nkv_end, max(0, flash_row_lo(p, batch, min(q0, p.Sq - 1), off)) / 128) : 0;
-  const int nkv = nkv_end - jlo;      // key block of iteration j is jlo + j
 
   if (threadIdx.x == 0) {
     mbar_init(qdo_full, 1);
@@ -145,25 +177,14 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(&dq_done[0], 1);
     mbar_init(&dq_done[1], 1);
     mbar_init(sdp_taken, 256);
+    mbar_init(qdo_free, 1);
+    mbar_init(dq_free, 256);
     *abort_flag = 0;
     fence_barrier_init();
-    if (nkv > 0) {
-      // first loads before the CTA-wide sync (this thread is also the producer): their latency overlaps the
-      // tensor-memory allocation
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      tma_prefetch_desc(&tmDO);
-      mbar_expect_tx(qdo_full, 2 * L::kTile);
-      mbar_expect_tx(&kv_full[0], 2 * L::kTile);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        tma_load_4d(smem + L::kQ + c * 16384, &tmQ, qdo_full, c * 64, q0, head, batch);
-        tma_load_4d(smem + L::kDO + c * 16384, &tmDO, qdo_full, c * 64, q0, head, batch);
-        tma_load_4d(smem + L::kK + c * 16384, &tmK, &kv_full[0], c * 64, jlo * 128, kv_head, batch);
-        tma_load_4d(smem + L::kV + c * 16384, &tmV, &kv_full[0], c * 64, jlo * 128, kv_head, batch);
-      }
-    }
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
   }
   constexpr uint32_t kTmemCols = 512;   // S [0,128) | dP [128,256) | dQ [256, 256+D)
   if (warp == 1) {
@@ -176,34 +197,52 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_S = tmem_base, tmem_dP = tmem_base + 128, tmem_dQ = tmem_base + 256;
 
+  // Every role walks the same units and counts alike: n = units with work so far, g = key blocks so far over all units.
   if (warp == 0) {
-    if (lane == 0 && nkv > 0) {
-      for (int j = 1; j < nkv; ++j) {          // block 0 was requested before the sync
-        const int st = j % NS;
-        const uint32_t ph = (j / NS) & 1;
-        if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (3u << 16) | st)) break;
-        mbar_expect_tx(&kv_full[st], 2 * L::kTile);
+    if (lane == 0) {
+      int n = 0, g = 0;
+      bool ok = true;
+      for (int round = 0; round < snake_rounds(units) && ok; ++round) {
+        const int u = snake_unit(round, units);
+        if (u < 0) continue;
+        const QUnit t = q_unit<MODES>(p, u, off, nqt);
+        if (t.nkv <= 0) continue;
+        if (n > 0 && !mbar_wait(qdo_free, (n - 1) & 1, abort_flag, p.st, kTimeoutSmemEmpty, (3u << 16) | 14)) break;
+        mbar_expect_tx(qdo_full, 2 * L::kTile);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
-          tma_load_4d(smem + L::kK + st * L::kTile + c * 16384, &tmK, &kv_full[st], c * 64, (jlo + j) * 128, kv_head, batch);
-          tma_load_4d(smem + L::kV + st * L::kTile + c * 16384, &tmV, &kv_full[st], c * 64, (jlo + j) * 128, kv_head, batch);
+          tma_load_4d(smem + L::kQ + c * 16384, &tmQ, qdo_full, c * 64, t.q0, t.head, t.batch);
+          tma_load_4d(smem + L::kDO + c * 16384, &tmDO, qdo_full, c * 64, t.q0, t.head, t.batch);
         }
+        for (int j = 0; j < t.nkv; ++j, ++g) {
+          const int st = g % NS;
+          const uint32_t ph = (g / NS) & 1;
+          if (!mbar_wait(&kv_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (3u << 16) | st)) { ok = false; break; }
+          mbar_expect_tx(&kv_full[st], 2 * L::kTile);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) {
+            tma_load_4d(smem + L::kK + st * L::kTile + c * 16384, &tmK, &kv_full[st], c * 64, (t.jlo + j) * 128, t.kv_head, t.batch);
+            tma_load_4d(smem + L::kV + st * L::kTile + c * 16384, &tmV, &kv_full[st], c * 64, (t.jlo + j) * 128, t.kv_head, t.batch);
+          }
+        }
+        ++n;
       }
       if (*abort_flag) __nanosleep(50000);
     }
   } else if (warp == 1) {
-    if (lane == 0 && nkv > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0, 1);
       constexpr uint32_t idesc_dq = make_idesc_f16(128, D, 0, 1, 1);
-      bool ok = mbar_wait(qdo_full, 0, abort_flag, p.st, kTimeoutSmemFull, (3u << 16) | 8);
       const uint32_t sq = smem_u32(smem + L::kQ), sdo = smem_u32(smem + L::kDO), sds = smem_u32(smem + L::kDS);
-      // S and dP of block j; with two K/V stages they are issued one block ahead, as soon as the element-wise warps
+      int n = 0, g0 = 0;
+      bool ok = true;
+      // S and dP of global block g; within a unit they are issued one block ahead, as soon as the element-wise warps
       // have taken the previous block's S and dP into registers
-      auto issue_scores = [&](int j) -> bool {
-        const int st = j % NS;
-        const uint32_t ph = (j / NS) & 1;
+      auto issue_scores = [&](int g) -> bool {
+        const int st = g % NS;
+        const uint32_t ph = (g / NS) & 1;
         if (!mbar_wait(&kv_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (3u << 16) | st)) return false;
-        if (j > 0 && !mbar_wait(sdp_taken, (j - 1) & 1, abort_flag, p.st, kTimeoutTmemEmpty, (3u << 16) | 13)) return false;
+        if (g > 0 && !mbar_wait(sdp_taken, (g - 1) & 1, abort_flag, p.st, kTimeoutTmemEmpty, (3u << 16) | 13)) return false;
         tc_fence_after();
         const uint32_t sk = smem_u32(smem + L::kK + st * L::kTile), sv = smem_u32(smem + L::kV + st * L::kTile);
 #pragma unroll
@@ -216,23 +255,44 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
         return true;
       };
       constexpr bool kAhead = NS >= 2;      // one stage: the next K / V cannot land before this block's dQ product is done
-      if (ok && kAhead) ok = issue_scores(0);
-      for (int j = 0; j < nkv && ok; ++j) {
-        const int st = j % NS;
+      for (int round = 0; round < snake_rounds(units) && ok; ++round) {
+        const int u = snake_unit(round, units);
+        if (u < 0) continue;
+        const QUnit t = q_unit<MODES>(p, u, off, nqt);
+        if (t.nkv <= 0) continue;
+        if (!mbar_wait(qdo_full, n & 1, abort_flag, p.st, kTimeoutSmemFull, (3u << 16) | 8)) break;
         if (kAhead) {
-          if (j + 1 < nkv && !issue_scores(j + 1)) break;
-        } else if (!issue_scores(j)) {
-          break;
+          ok = issue_scores(g0);
+          if (ok && t.nkv == 1) tc_commit(qdo_free);
         }
-        if (!mbar_wait(ds_ready, j & 1, abort_flag, p.st, kTimeoutGeneric, (3u << 16) | 9)) break;
-        tc_fence_after();
-        const uint32_t sk = smem_u32(smem + L::kK + st * L::kTile);
-        const uint32_t sds_b = sds + (j & 1) * 32768;
+        for (int j = 0; j < t.nkv && ok; ++j) {
+          const int g = g0 + j;
+          const int st = g % NS;
+          if (kAhead) {
+            if (j + 1 < t.nkv) {
+              if (!issue_scores(g + 1)) { ok = false; break; }
+              if (j + 2 == t.nkv) tc_commit(qdo_free);        // the unit's last score products are on their way
+            }
+          } else {
+            if (!issue_scores(g)) { ok = false; break; }
+            if (j + 1 == t.nkv) tc_commit(qdo_free);
+          }
+          if (!mbar_wait(ds_ready, g & 1, abort_flag, p.st, kTimeoutGeneric, (3u << 16) | 9)) { ok = false; break; }
+          if (j == 0 && n > 0) {
+            // dQ of the previous unit must have been read out before this unit starts its own sum
+            if (!mbar_wait(dq_free, (n - 1) & 1, abort_flag, p.st, kTimeoutTmemEmpty, (3u << 16) | 15)) { ok = false; break; }
+          }
+          tc_fence_after();
+          const uint32_t sk = smem_u32(smem + L::kK + st * L::kTile);
+          const uint32_t sds_b = sds + (g & 1) * 32768;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          tc_mma_f16_ss(tmem_dQ, kmajor_desc(sds_b, kk), mnmajor_desc(sk, kk), idesc_dq, (j > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(&kv_empty[st]);
-        tc_commit(&dq_done[j & 1]);
+          for (int kk = 0; kk < 8; ++kk)
+            tc_mma_f16_ss(tmem_dQ, kmajor_desc(sds_b, kk), mnmajor_desc(sk, kk), idesc_dq, (j > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(&kv_empty[st]);
+          tc_commit(&dq_done[g & 1]);
+        }
+        g0 += t.nkv;
+        ++n;
       }
     }
   } else {
@@ -241,111 +301,120 @@ flash_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;
-    const int row = q0 + r;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
-    float lse2 = INFINITY, dlt = 0.f;
-    if (row < p.Sq) {
-      const size_t idx = (size_t(batch) * p.H + head) * p.Sq + row;
-      const float l = p.lse[idx];
-      lse2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
-      dlt = p.delta[idx];
-    }
-    bool ok = nkv > 0;
-    const int row_lo = bounded ? flash_row_lo(p, batch, row, off) : 0;
     const bool capped = MODES && p.softcap > 0.f;
     const bool special = bounded || capped;
     const float cap_in = capped ? p.scale / p.softcap : 0.f;
     const float cap_l2 = p.softcap * kLog2e;
-    for (int j = 0; j < nkv && ok; ++j) {
-      if (!mbar_wait(sdp_full, j & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 10)) { ok = false; break; }
+    constexpr int kOC = D / 2;               // each half writes D / 2 columns of the row
+    int g0 = 0;
+    bool ok = true;
+    for (int round = 0; round < snake_rounds(units) && ok; ++round) {
+      const int u = snake_unit(round, units);
+      if (u < 0) continue;
+      const QUnit t = q_unit<MODES>(p, u, off, nqt);
+      const int row = t.q0 + r;
+      __nv_bfloat16* drow = p.dQ + (size_t(t.batch) * p.Sq + row) * p.dq_row_stride + size_t(t.head) * D + half * kOC;
+      if (t.nkv <= 0) {
+        if (row < p.Sq)
+          for (int i = 0; i < kOC; i += 8) *reinterpret_cast<uint4*>(drow + i) = make_uint4(0, 0, 0, 0);
+        continue;
+      }
+      float lse2 = INFINITY, dlt = 0.f;
+      if (row < p.Sq) {
+        const size_t idx = (size_t(t.batch) * p.H + t.head) * p.Sq + row;
+        const float l = p.lse[idx];
+        lse2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+        dlt = p.delta[idx];
+      }
+      const int row_lo = bounded ? flash_row_lo(p, t.batch, row, off) : 0;
+      for (int j = 0; j < t.nkv && ok; ++j) {
+        const int g = g0 + j;
+        if (!mbar_wait(sdp_full, g & 1, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 10)) { ok = false; break; }
+        tc_fence_after();
+        uint8_t* sDS = smem + L::kDS + (g & 1) * 32768;
+        const int k0 = (t.jlo + j) * 128 + half * 64;          // first key of this thread's 64 columns
+        int lim = p.Skv - k0;
+        if (p.causal) lim = min(lim, row + off - k0 + 1);
+        lim = max(0, min(64, lim));
+        const int lo = max(0, min(64, row_lo - k0));           // keys below the row's window / sequence start
+        // four loads in flight and one wait; once every thread holds its part the MMA warp may overwrite S and dP with
+        // the next block's
+        uint32_t s[2][32], dp[2][32];
+        tmem_ld_32x32b_x32(tmem_S + lane_addr + half * 64, s[0]);
+        tmem_ld_32x32b_x32(tmem_S + lane_addr + half * 64 + 32, s[1]);
+        tmem_ld_32x32b_x32(tmem_dP + lane_addr + half * 64, dp[0]);
+        tmem_ld_32x32b_x32(tmem_dP + lane_addr + half * 64 + 32, dp[1]);
+        tmem_ld_wait();
+        tc_fence_before();
+        mbar_arrive(sdp_taken);
+        if (g >= 2) {
+          // the dQ product that last read this dS tile (block g - 2) must be complete
+          if (!mbar_wait(&dq_done[g & 1], uint32_t((g >> 1) - 1) & 1u, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 11)) {
+            ok = false;
+            break;
+          }
+        }
+#pragma unroll
+        for (int cc = 0; cc < 2; ++cc) {
+          float ds[32];
+          if (!special) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - lse2);
+              float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * p.scale;
+              ds[i] = (cc * 32 + i < lim) ? v : 0.f;
+            }
+          } else {
+            // lower key bound and / or soft-capped scores: u = cap * tanh(s * scale / cap), du/ds = scale * (1 - tanh^2)
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              float sc = __uint_as_float(s[cc][i]), gr = p.scale;
+              if (capped) {
+                const float th = tanh_fast(sc * cap_in);
+                sc = th * cap_l2;
+                gr *= 1.f - th * th;
+              } else {
+                sc *= p.scale_log2;
+              }
+              float pr = fast_exp2(sc - lse2);
+              float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * gr;
+              ds[i] = (cc * 32 + i < lim && cc * 32 + i >= lo) ? v : 0.f;
+            }
+          }
+          store_operand_chunk(sDS, r, half * 2 + cc, ds);
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(ds_ready);
+      }
+      if (!ok) break;
+      const int last = g0 + t.nkv - 1;
+      if (!mbar_wait(&dq_done[last & 1], uint32_t(last >> 1) & 1u, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 12)) {
+        ok = false;
+        break;
+      }
       tc_fence_after();
-      uint8_t* sDS = smem + L::kDS + (j & 1) * 32768;
-      const int k0 = (jlo + j) * 128 + half * 64;            // first key of this thread's 64 columns
-      int lim = p.Skv - k0;
-      if (p.causal) lim = min(lim, row + off - k0 + 1);
-      lim = max(0, min(64, lim));
-      const int lo = max(0, min(64, row_lo - k0));           // keys below the row's window / sequence start
-      // four loads in flight and one wait; once every thread holds its part the MMA warp may overwrite S and dP with
-      // the next block's
-      uint32_t s[2][32], dp[2][32];
-      tmem_ld_32x32b_x32(tmem_S + lane_addr + half * 64, s[0]);
-      tmem_ld_32x32b_x32(tmem_S + lane_addr + half * 64 + 32, s[1]);
-      tmem_ld_32x32b_x32(tmem_dP + lane_addr + half * 64, dp[0]);
-      tmem_ld_32x32b_x32(tmem_dP + lane_addr + half * 64 + 32, dp[1]);
+      // dQ leaves tensor memory first, so the next unit may start accumulating while the row is packed and stored
+      uint32_t o[kOC];
+#pragma unroll
+      for (int c = 0; c < kOC / 32; ++c)
+        tmem_ld_32x32b_x32(tmem_dQ + lane_addr + half * kOC + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[c * 32]));
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(sdp_taken);
-      if (j >= 2) {
-        // the dQ product that last read this dS tile (block j - 2) must be complete
-        if (!mbar_wait(&dq_done[j & 1], uint32_t((j >> 1) - 1) & 1u, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 11)) {
-          ok = false;
-          break;
-        }
-      }
+      mbar_arrive(dq_free);
+      if (row < p.Sq) {
 #pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        float ds[32];
-        if (!special) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - lse2);
-            float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * p.scale;
-            ds[i] = (cc * 32 + i < lim) ? v : 0.f;
-          }
-        } else {
-          // lower key bound and / or soft-capped scores: u = cap * tanh(s * scale / cap), du/ds = scale * (1 - tanh^2)
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            float sc = __uint_as_float(s[cc][i]), g = p.scale;
-            if (capped) {
-              const float t = tanh_fast(sc * cap_in);
-              sc = t * cap_l2;
-              g *= 1.f - t * t;
-            } else {
-              sc *= p.scale_log2;
-            }
-            float pr = fast_exp2(sc - lse2);
-            float v = pr * (__uint_as_float(dp[cc][i]) - dlt) * g;
-            ds[i] = (cc * 32 + i < lim && cc * 32 + i >= lo) ? v : 0.f;
-          }
-        }
-        store_operand_chunk(sDS, r, half * 2 + cc, ds);
-      }
-      fence_proxy_async_smem();
-      tc_fence_before();
-      mbar_arrive(ds_ready);
-    }
-    if (ok && nkv > 0) {
-      const int last = nkv - 1;
-      if (!mbar_wait(&dq_done[last & 1], uint32_t(last >> 1) & 1u, abort_flag, p.st, kTimeoutTmemFull, (3u << 16) | 12))
-        ok = false;
-    }
-    tc_fence_after();
-    if (ok || nkv <= 0) {     // warp-uniform: every thread of the warp waited on the same barriers
-      // each half writes D / 2 columns of the row
-      constexpr int kOC = D / 2;
-      __nv_bfloat16* drow = p.dQ + (size_t(batch) * p.Sq + row) * p.dq_row_stride + size_t(head) * D + half * kOC;
-#pragma unroll 1
-      for (int c = 0; c < kOC / 32; ++c) {
-        uint32_t o[32];
-        if (nkv > 0) {
-          tmem_ld_32x32b_x32(tmem_dQ + lane_addr + half * kOC + c * 32, o);   // aligned: all 32 lanes take part
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
-        }
-        if (row >= p.Sq) continue;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
+        for (int gq = 0; gq < kOC / 8; ++gq) {
           uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(o[g * 8 + 0]), __uint_as_float(o[g * 8 + 1]));
-          w.y = pack_bf16x2(__uint_as_float(o[g * 8 + 2]), __uint_as_float(o[g * 8 + 3]));
-          w.z = pack_bf16x2(__uint_as_float(o[g * 8 + 4]), __uint_as_float(o[g * 8 + 5]));
-          w.w = pack_bf16x2(__uint_as_float(o[g * 8 + 6]), __uint_as_float(o[g * 8 + 7]));
-          *reinterpret_cast<uint4*>(drow + c * 32 + g * 8) = w;
+          w.x = pack_bf16x2(__uint_as_float(o[gq * 8 + 0]), __uint_as_float(o[gq * 8 + 1]));
+          w.y = pack_bf16x2(__uint_as_float(o[gq * 8 + 2]), __uint_as_float(o[gq * 8 + 3]));
+          w.z = pack_bf16x2(__uint_as_float(o[gq * 8 + 4]), __uint_as_float(o[gq * 8 + 5]));
+          w.w = pack_bf16x2(__uint_as_float(o[gq * 8 + 6]), __uint_as_float(o[gq * 8 + 7]));
+          *reinterpret_cast<uint4*>(drow + gq * 8) = w;
         }
       }
+      g0 += t.nkv;
     }
   }
 
@@ -378,6 +447,42 @@ struct BwdKVSmem {
   static constexpr int kTotal = kBar + 256 + 1024;
 };
 
+// Persistent: the grid is one CTA per SM and every CTA walks a list of (key block, kv head, batch) units, heaviest
+// first. Barriers, tensor memory and the Q / dO ring are set up once; the next unit's K and V load while the last block of
+// the current unit is still in its element-wise and accumulation steps, and the write-out of dK / dV overlaps the first
+// score products of the next unit. With one launch of 1536 short CTAs the set-up, first-load and write-out latencies
+// (about 12 k cycles per CTA) ran unhidden, a third of the time at 1024 tokens.
+struct KvUnit {
+  int kb, kv_head, batch, k0, i_min, per_head, iters;
+};
+
+template <bool MODES>
+__device__ __forceinline__ KvUnit kv_unit(const FlashParams& p, int u, int off, int nq) {
+  KvUnit t;
+  const int per_kb = p.Hkv * p.B;
+  t.kb = u / per_kb;                         // ascending key block = most query blocks first under a causal mask
+  const int rem = u - t.kb * per_kb;
+  t.kv_head = rem % p.Hkv;
+  t.batch = rem / p.Hkv;
+  t.k0 = t.kb * 128;
+  t.i_min = p.causal ? max(0, (t.k0 - off) / 128) : 0;
+  // query blocks past the last one that can see these keys are skipped too: a sliding window bounds them directly,
+  // packed sequences by the first block whose first row already starts beyond this key block
+  int i_end = nq;
+  if (MODES && p.causal && (p.window > 0 || p.row_start != nullptr)) {
+    if (p.window > 0) i_end = min(i_end, (t.k0 + 127 + p.window - 1 - off) / 128 + 1);
+    if (p.row_start) {
+      int i = t.i_min;
+      while (i < i_end && p.row_start[size_t(t.batch) * p.Sq + min(i * 128, p.Sq - 1)] <= t.k0 + 127) ++i;
+      i_end = i;
+    }
+    i_end = max(i_end, t.i_min);
+  }
+  t.per_head = max(0, i_end - t.i_min);
+  t.iters = t.per_head * (p.H / p.Hkv);
+  return t;
+}
+
 template <int D, bool MODES>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
@@ -385,6 +490,7 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                     const FlashParams p) {
   using L = BwdKVSmem<D>;
   constexpr int NS = L::kStages;
+  constexpr int PB = L::kPBufs;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBar);
@@ -395,35 +501,20 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint64_t* pds_ready = bars + 6;
   uint64_t* acc_done = bars + 7;    // [2]: one per P^T / dS^T buffer
   uint64_t* sdp_taken = bars + 9;   // S^T and dP^T of the block are in registers: TMEM may be rewritten
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* kv_free = bars + 10;    // the unit's last score products have read K and V: the next unit's may land
+  uint64_t* acc_free = bars + 11;   // dV and dK of the unit sit in registers: the next unit may accumulate
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   float* s_lse2 = reinterpret_cast<float*>(smem + L::kStat);
   float* s_delta = s_lse2 + 128;
   int* s_lo = reinterpret_cast<int*>(s_delta + 128);      // first key each query of the block may see
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int kb = blockIdx.x, kv_head = blockIdx.y, batch = blockIdx.z;
   const int group = p.H / p.Hkv;
-  const int k0 = kb * 128;
   const int off = p.Skv - p.Sq;
   const int nq = (p.Sq + 127) / 128;
-  int i_min = 0;
-  if (p.causal) i_min = max(0, (k0 - off) / 128);
-  // query blocks past the last one that can see these keys are skipped too: a sliding window bounds them directly,
-  // packed sequences by the first block whose first row already starts beyond this key block
+  const int units = ((p.Skv + 127) / 128) * p.Hkv * p.B;
   const bool bounded = MODES && p.causal && (p.window > 0 || p.row_start != nullptr);
-  int i_end = nq;
-  if (bounded) {
-    if (p.window > 0) i_end = min(i_end, (k0 + 127 + p.window - 1 - off) / 128 + 1);
-    if (p.row_start) {
-      int i = i_min;
-      while (i < i_end && p.row_start[size_t(batch) * p.Sq + min(i * 128, p.Sq - 1)] <= k0 + 127) ++i;
-      i_end = i;
-    }
-    i_end = max(i_end, i_min);
-  }
-  const int per_head = max(0, i_end - i_min);
-  const int iters = per_head * group;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
@@ -436,24 +527,14 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(&acc_done[0], 1);
     mbar_init(&acc_done[1], 1);
     mbar_init(sdp_taken, 256);
+    mbar_init(kv_free, 1);
+    mbar_init(acc_free, 256);
     *abort_flag = 0;
     fence_barrier_init();
-    if (iters > 0) {
-      // first loads before the CTA-wide sync (this thread is also the producer)
-      tma_prefetch_desc(&tmQ);
-      tma_prefetch_desc(&tmK);
-      tma_prefetch_desc(&tmV);
-      tma_prefetch_desc(&tmDO);
-      mbar_expect_tx(kv_full, 2 * L::kTile);
-      mbar_expect_tx(&qdo_full[0], 2 * L::kTile);
-#pragma unroll
-      for (int c = 0; c < D / 64; ++c) {
-        tma_load_4d(smem + L::kK + c * 16384, &tmK, kv_full, c * 64, k0, kv_head, batch);
-        tma_load_4d(smem + L::kV + c * 16384, &tmV, kv_full, c * 64, k0, kv_head, batch);
-        tma_load_4d(smem + L::kQ + c * 16384, &tmQ, &qdo_full[0], c * 64, i_min * 128, kv_head * group, batch);
-        tma_load_4d(smem + L::kDO + c * 16384, &tmDO, &qdo_full[0], c * 64, i_min * 128, kv_head * group, batch);
-      }
-    }
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+    tma_prefetch_desc(&tmDO);
   }
   constexpr uint32_t kTmemCols = 512;   // S^T [0,128) | dP^T [128,256) | dV [256,256+D) | dK [256+D, 256+2D)
   if (warp == 1) {
@@ -467,37 +548,57 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   const uint32_t tmem_ST = tmem_base, tmem_dPT = tmem_base + 128, tmem_dV = tmem_base + 256,
                  tmem_dK = tmem_base + 256 + D;
 
+  // Every role walks the same units and counts the same things: n = units with work so far (parity of the per-unit
+  // barriers), g = query blocks so far over all units (stage and parity of the per-block barriers).
   if (warp == 0) {
-    if (lane == 0 && iters > 0) {
-      for (int it = 1; it < iters; ++it) {          // iteration 0 was requested before the sync
-        const int st = it % NS;
-        const uint32_t ph = (it / NS) & 1;
-        const int head = kv_head * group + it / per_head;
-        const int qi = i_min + it % per_head;
-        if (!mbar_wait(&qdo_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (4u << 16) | st)) break;
-        mbar_expect_tx(&qdo_full[st], 2 * L::kTile);
+    if (lane == 0) {
+      int n = 0, g = 0;
+      bool ok = true;
+      for (int round = 0; round < snake_rounds(units) && ok; ++round) {
+        const int u = snake_unit(round, units);
+        if (u < 0) continue;
+        const KvUnit t = kv_unit<MODES>(p, u, off, nq);
+        if (t.iters == 0) continue;
+        // K and V of this unit: once the previous unit's last score products have read theirs
+        if (n > 0 && !mbar_wait(kv_free, (n - 1) & 1, abort_flag, p.st, kTimeoutSmemEmpty, (4u << 16) | 14)) break;
+        mbar_expect_tx(kv_full, 2 * L::kTile);
 #pragma unroll
         for (int c = 0; c < D / 64; ++c) {
-          tma_load_4d(smem + L::kQ + st * L::kTile + c * 16384, &tmQ, &qdo_full[st], c * 64, qi * 128, head, batch);
-          tma_load_4d(smem + L::kDO + st * L::kTile + c * 16384, &tmDO, &qdo_full[st], c * 64, qi * 128, head, batch);
+          tma_load_4d(smem + L::kK + c * 16384, &tmK, kv_full, c * 64, t.k0, t.kv_head, t.batch);
+          tma_load_4d(smem + L::kV + c * 16384, &tmV, kv_full, c * 64, t.k0, t.kv_head, t.batch);
         }
+        for (int it = 0; it < t.iters; ++it, ++g) {
+          const int st = g % NS;
+          const uint32_t ph = (g / NS) & 1;
+          const int head = t.kv_head * group + it / t.per_head;
+          const int qi = t.i_min + it % t.per_head;
+          if (!mbar_wait(&qdo_empty[st], ph ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (4u << 16) | st)) { ok = false; break; }
+          mbar_expect_tx(&qdo_full[st], 2 * L::kTile);
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c) {
+            tma_load_4d(smem + L::kQ + st * L::kTile + c * 16384, &tmQ, &qdo_full[st], c * 64, qi * 128, head, t.batch);
+            tma_load_4d(smem + L::kDO + st * L::kTile + c * 16384, &tmDO, &qdo_full[st], c * 64, qi * 128, head, t.batch);
+          }
+        }
+        ++n;
       }
       if (*abort_flag) __nanosleep(50000);
     }
   } else if (warp == 1) {
-    if (lane == 0 && iters > 0) {
+    if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_f16(128, 128, 0, 0, 1);
       constexpr uint32_t idesc_acc = make_idesc_f16(128, D, 0, 1, 1);
-      bool ok = mbar_wait(kv_full, 0, abort_flag, p.st, kTimeoutSmemFull, (4u << 16) | 8);
       const uint32_t sk = smem_u32(smem + L::kK), sv = smem_u32(smem + L::kV);
       const uint32_t spt = smem_u32(smem + L::kPT), sdst = smem_u32(smem + L::kDST);
-      // S^T and dP^T of iteration `it`; with two Q / dO stages they are issued one iteration ahead, as soon as the
-      // element-wise warps hold the previous iteration's scores in registers
-      auto issue_scores = [&](int it) -> bool {
-        const int st = it % NS;
-        const uint32_t ph = (it / NS) & 1;
+      int n = 0, g0 = 0;
+      bool ok = true;
+      // S^T and dP^T of global block g; within a unit they are issued one block ahead (two Q / dO stages), as soon as
+      // the element-wise warps hold the previous block's scores in registers
+      auto issue_scores = [&](int g) -> bool {
+        const int st = g % NS;
+        const uint32_t ph = (g / NS) & 1;
         if (!mbar_wait(&qdo_full[st], ph, abort_flag, p.st, kTimeoutSmemFull, (4u << 16) | st)) return false;
-        if (it > 0 && !mbar_wait(sdp_taken, (it - 1) & 1, abort_flag, p.st, kTimeoutTmemEmpty, (4u << 16) | 13)) return false;
+        if (g > 0 && !mbar_wait(sdp_taken, (g - 1) & 1, abort_flag, p.st, kTimeoutTmemEmpty, (4u << 16) | 13)) return false;
         tc_fence_after();
         const uint32_t sq = smem_u32(smem + L::kQ + st * L::kTile), sdo = smem_u32(smem + L::kDO + st * L::kTile);
 #pragma unroll
@@ -510,27 +611,48 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
         return true;
       };
       constexpr bool kAhead = NS >= 2;
-      if (ok && kAhead) ok = issue_scores(0);
-      for (int it = 0; it < iters && ok; ++it) {
-        const int st = it % NS;
+      for (int round = 0; round < snake_rounds(units) && ok; ++round) {
+        const int u = snake_unit(round, units);
+        if (u < 0) continue;
+        const KvUnit t = kv_unit<MODES>(p, u, off, nq);
+        if (t.iters == 0) continue;
+        if (!mbar_wait(kv_full, n & 1, abort_flag, p.st, kTimeoutSmemFull, (4u << 16) | 8)) break;
         if (kAhead) {
-          if (it + 1 < iters && !issue_scores(it + 1)) break;
-        } else if (!issue_scores(it)) {
-          break;
+          ok = issue_scores(g0);
+          if (ok && t.iters == 1) tc_commit(kv_free);
         }
-        if (!mbar_wait(pds_ready, it & 1, abort_flag, p.st, kTimeoutGeneric, (4u << 16) | 9)) break;
-        tc_fence_after();
-        const uint32_t sq = smem_u32(smem + L::kQ + st * L::kTile), sdo = smem_u32(smem + L::kDO + st * L::kTile);
-        const int pb = it % L::kPBufs;
-        const uint32_t spt_b = spt + pb * 32768, sdst_b = sdst + pb * 32768;
+        for (int it = 0; it < t.iters && ok; ++it) {
+          const int g = g0 + it;
+          const int st = g % NS;
+          if (kAhead) {
+            if (it + 1 < t.iters) {
+              if (!issue_scores(g + 1)) { ok = false; break; }
+              if (it + 2 == t.iters) tc_commit(kv_free);       // the unit's last score products are on their way
+            }
+          } else {
+            if (!issue_scores(g)) { ok = false; break; }
+            if (it + 1 == t.iters) tc_commit(kv_free);
+          }
+          if (!mbar_wait(pds_ready, g & 1, abort_flag, p.st, kTimeoutGeneric, (4u << 16) | 9)) { ok = false; break; }
+          if (it == 0 && n > 0) {
+            // dV and dK of the previous unit must have been read out before this unit starts its own sums
+            if (!mbar_wait(acc_free, (n - 1) & 1, abort_flag, p.st, kTimeoutTmemEmpty, (4u << 16) | 15)) { ok = false; break; }
+          }
+          tc_fence_after();
+          const uint32_t sq = smem_u32(smem + L::kQ + st * L::kTile), sdo = smem_u32(smem + L::kDO + st * L::kTile);
+          const int pb = g % PB;
+          const uint32_t spt_b = spt + pb * 32768, sdst_b = sdst + pb * 32768;
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          tc_mma_f16_ss(tmem_dV, kmajor_desc(spt_b, kk), mnmajor_desc(sdo, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+          for (int kk = 0; kk < 8; ++kk)
+            tc_mma_f16_ss(tmem_dV, kmajor_desc(spt_b, kk), mnmajor_desc(sdo, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk)
-          tc_mma_f16_ss(tmem_dK, kmajor_desc(sdst_b, kk), mnmajor_desc(sq, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
-        tc_commit(&qdo_empty[st]);
-        tc_commit(&acc_done[pb]);
+          for (int kk = 0; kk < 8; ++kk)
+            tc_mma_f16_ss(tmem_dK, kmajor_desc(sdst_b, kk), mnmajor_desc(sq, kk), idesc_acc, (it > 0 || kk > 0) ? 1u : 0u);
+          tc_commit(&qdo_empty[st]);
+          tc_commit(&acc_done[pb]);
+        }
+        g0 += t.iters;
+        ++n;
       }
     }
   } else {
@@ -539,155 +661,164 @@ flash_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     const int quarter = warp & 3;
     const int half = (warp - 2) >> 2;
     const int r = quarter * 32 + lane;       // key row within the block
-    const int key = k0 + r;
     const uint32_t lane_addr = uint32_t(quarter * 32) << 16;
     bool ok = true;
     const bool capped = MODES && p.softcap > 0.f;
     const bool special = bounded || capped;
     const float cap_in = capped ? p.scale / p.softcap : 0.f;
     const float cap_l2 = p.softcap * kLog2e;
-    auto load_stats = [&](int it, float& l2, float& dl, int& lo) {
-      const int head = kv_head * group + it / per_head;
-      const int qr = (i_min + it % per_head) * 128 + r;
-      l2 = INFINITY;
-      dl = 0.f;
-      if (qr < p.Sq) {
-        const size_t idx = (size_t(batch) * p.H + head) * p.Sq + qr;
-        const float l = p.lse[idx];
-        l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
-        dl = p.delta[idx];
-      }
-      lo = bounded ? flash_row_lo(p, batch, qr, off) : 0;
-    };
-    auto store_stats = [&](float l2, float dl, int lo) {
-      s_lse2[r] = l2;
-      s_delta[r] = dl;
-      s_lo[r] = lo;
-    };
-    if (half == 0 && iters > 0) {
-      float l2, dl;
-      int lo;
-      load_stats(0, l2, dl, lo);
-      store_stats(l2, dl, lo);
-    }
-    softmax_bar_sync();
-    // A thread whose wait gave up keeps walking the loop without touching tensor memory: the block-wide barrier of the
-    // element-wise warps has no time limit of its own, so nobody may leave early.
-    for (int it = 0; it < iters; ++it) {
-      const int qi = i_min + it % per_head;
-      const int qrow0 = qi * 128;
-      const int pb = it % L::kPBufs;
-      uint8_t* sPT = smem + L::kPT + pb * 32768;
-      uint8_t* sDST = smem + L::kDST + pb * 32768;
-      // the statistics of this query block were staged at the end of the previous iteration; those of the next block
-      // are fetched now and stored at the end of this one, so their latency hides behind this block's arithmetic
-      const float* c_lse2 = s_lse2;
-      const float* c_delta = s_delta;
-      const int* c_lo = s_lo;
-      float n_l2 = INFINITY, n_dl = 0.f;
-      int n_lo = 0;
-      if (half == 0 && it + 1 < iters) load_stats(it + 1, n_l2, n_dl, n_lo);
-      if (ok && !mbar_wait(sdp_full, it & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 10)) ok = false;
-      tc_fence_after();
-      // query q (column) sees this key iff key <= q + off  <=>  q >= key - off
-      const int first_q = p.causal ? (key - off - qrow0) : 0;    // columns below this are masked
-      // this thread's 64 columns: four loads in flight and one wait; the MMA warp may rewrite S^T and dP^T once every
-      // thread holds its part in registers
-      uint32_t s[2][32], dp[2][32];
-      if (ok) {
-        tmem_ld_32x32b_x32(tmem_ST + lane_addr + half * 64, s[0]);
-        tmem_ld_32x32b_x32(tmem_ST + lane_addr + half * 64 + 32, s[1]);
-        tmem_ld_32x32b_x32(tmem_dPT + lane_addr + half * 64, dp[0]);
-        tmem_ld_32x32b_x32(tmem_dPT + lane_addr + half * 64 + 32, dp[1]);
-        tmem_ld_wait();
-        tc_fence_before();
-        mbar_arrive(sdp_taken);
-      } else {
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[0][i] = s[1][i] = dp[0][i] = dp[1][i] = 0u;
-      }
-      if (ok && it >= L::kPBufs) {
-        // the accumulation that last read this P^T / dS^T buffer (iteration it - kPBufs) must be complete
-        const uint32_t use = uint32_t(it / L::kPBufs) - 1u;
-        if (!mbar_wait(&acc_done[pb], use & 1u, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 11)) ok = false;
-      }
-#pragma unroll
-      for (int cc = 0; cc < 2; ++cc) {
-        const int c = half * 2 + cc;
-        float pt[32], dst[32];
-        if (!special) {
-#pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = c * 32 + i;
-            float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - c_lse2[col]);
-            if (col < first_q) pr = 0.f;
-            pt[i] = pr;
-            dst[i] = pr * (__uint_as_float(dp[cc][i]) - c_delta[col]) * p.scale;
+    int n = 0, g0 = 0;
+    // A thread whose wait gave up keeps walking units and blocks without touching tensor memory: the block-wide barrier
+    // of the element-wise warps has no time limit of its own, so nobody may leave early.
+    for (int round = 0; round < snake_rounds(units); ++round) {
+      const int u = snake_unit(round, units);
+      if (u < 0) continue;
+      const KvUnit t = kv_unit<MODES>(p, u, off, nq);
+      const int key = t.k0 + r;
+      if (t.iters > 0) {
+        auto load_stats = [&](int it, float& l2, float& dl, int& lo) {
+          const int head = t.kv_head * group + it / t.per_head;
+          const int qr = (t.i_min + it % t.per_head) * 128 + r;
+          l2 = INFINITY;
+          dl = 0.f;
+          if (qr < p.Sq) {
+            const size_t idx = (size_t(t.batch) * p.H + head) * p.Sq + qr;
+            const float l = p.lse[idx];
+            l2 = (l == -INFINITY) ? INFINITY : l * kLog2e;
+            dl = p.delta[idx];
           }
-        } else {
+          lo = bounded ? flash_row_lo(p, t.batch, qr, off) : 0;
+        };
+        auto store_stats = [&](float l2, float dl, int lo) {
+          s_lse2[r] = l2;
+          s_delta[r] = dl;
+          s_lo[r] = lo;
+        };
+        // the previous unit's last block ended with a barrier after its statistics were last read
+        if (half == 0) {
+          float l2, dl;
+          int lo;
+          load_stats(0, l2, dl, lo);
+          store_stats(l2, dl, lo);
+        }
+        softmax_bar_sync();
+        for (int it = 0; it < t.iters; ++it) {
+          const int g = g0 + it;
+          const int qrow0 = (t.i_min + it % t.per_head) * 128;
+          const int pb = g % PB;
+          uint8_t* sPT = smem + L::kPT + pb * 32768;
+          uint8_t* sDST = smem + L::kDST + pb * 32768;
+          // the statistics of this query block were staged at the end of the previous block; those of the next are
+          // fetched now and stored at the end of this one, so their latency hides behind this block's arithmetic
+          float n_l2 = INFINITY, n_dl = 0.f;
+          int n_lo = 0;
+          if (half == 0 && it + 1 < t.iters) load_stats(it + 1, n_l2, n_dl, n_lo);
+          if (ok && !mbar_wait(sdp_full, g & 1, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 10)) ok = false;
+          tc_fence_after();
+          // query q (column) sees this key iff key <= q + off  <=>  q >= key - off
+          const int first_q = p.causal ? (key - off - qrow0) : 0;    // columns below this are masked
+          // this thread's 64 columns: four loads in flight and one wait; the MMA warp may rewrite S^T and dP^T once
+          // every thread holds its part in registers
+          uint32_t s[2][32], dp[2][32];
+          if (ok) {
+            tmem_ld_32x32b_x32(tmem_ST + lane_addr + half * 64, s[0]);
+            tmem_ld_32x32b_x32(tmem_ST + lane_addr + half * 64 + 32, s[1]);
+            tmem_ld_32x32b_x32(tmem_dPT + lane_addr + half * 64, dp[0]);
+            tmem_ld_32x32b_x32(tmem_dPT + lane_addr + half * 64 + 32, dp[1]);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(sdp_taken);
+          } else {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int col = c * 32 + i;
-            float sc = __uint_as_float(s[cc][i]), g = p.scale;
-            if (capped) {
-              const float t = tanh_fast(sc * cap_in);
-              sc = t * cap_l2;
-              g *= 1.f - t * t;
+            for (int i = 0; i < 32; ++i) s[0][i] = s[1][i] = dp[0][i] = dp[1][i] = 0u;
+          }
+          if (ok && g >= PB) {
+            // the accumulation that last read this P^T / dS^T buffer (block g - PB) must be complete
+            const uint32_t use = uint32_t(g / PB) - 1u;
+            if (!mbar_wait(&acc_done[pb], use & 1u, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 11)) ok = false;
+          }
+#pragma unroll
+          for (int cc = 0; cc < 2; ++cc) {
+            const int c = half * 2 + cc;
+            float pt[32], dst[32];
+            if (!special) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int col = c * 32 + i;
+                float pr = fast_exp2(__uint_as_float(s[cc][i]) * p.scale_log2 - s_lse2[col]);
+                if (col < first_q) pr = 0.f;
+                pt[i] = pr;
+                dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * p.scale;
+              }
             } else {
-              sc *= p.scale_log2;
+#pragma unroll
+              for (int i = 0; i < 32; ++i) {
+                const int col = c * 32 + i;
+                float sc = __uint_as_float(s[cc][i]), gr = p.scale;
+                if (capped) {
+                  const float th = tanh_fast(sc * cap_in);
+                  sc = th * cap_l2;
+                  gr *= 1.f - th * th;
+                } else {
+                  sc *= p.scale_log2;
+                }
+                float pr = fast_exp2(sc - s_lse2[col]);
+                if (col < first_q || key < s_lo[col]) pr = 0.f;
+                pt[i] = pr;
+                dst[i] = pr * (__uint_as_float(dp[cc][i]) - s_delta[col]) * gr;
+              }
             }
-            float pr = fast_exp2(sc - c_lse2[col]);
-            if (col < first_q || key < c_lo[col]) pr = 0.f;
-            pt[i] = pr;
-            dst[i] = pr * (__uint_as_float(dp[cc][i]) - c_delta[col]) * g;
+            if (ok) {
+              store_operand_chunk(sPT, r, c, pt);
+              store_operand_chunk(sDST, r, c, dst);
+            }
           }
+          if (ok) {
+            fence_proxy_async_smem();
+            tc_fence_before();
+            mbar_arrive(pds_ready);
+          }
+          softmax_bar_sync();    // this block's statistics are no longer read
+          if (half == 0 && it + 1 < t.iters) store_stats(n_l2, n_dl, n_lo);
+          softmax_bar_sync();    // the next block's are visible
         }
         if (ok) {
-          store_operand_chunk(sPT, r, c, pt);
-          store_operand_chunk(sDST, r, c, dst);
+          const int last = g0 + t.iters - 1;
+          if (!mbar_wait(&acc_done[last % PB], uint32_t(last / PB) & 1u, abort_flag, p.st, kTimeoutTmemFull, (4u << 16) | 12))
+            ok = false;
         }
+        tc_fence_after();
       }
-      if (ok) {
-        fence_proxy_async_smem();
+      // write-out: the first half of the threads takes dV, the second dK; the sums leave tensor memory first so that the
+      // next unit may start accumulating while the rows are packed and stored
+      uint32_t o[D];
+      if (t.iters > 0 && ok) {
+        const uint32_t acc = half ? tmem_dK : tmem_dV;
+#pragma unroll
+        for (int c = 0; c < D / 32; ++c) tmem_ld_32x32b_x32(acc + lane_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&o[c * 32]));
+        tmem_ld_wait();
         tc_fence_before();
-        mbar_arrive(pds_ready);
+        mbar_arrive(acc_free);
+      } else {
+#pragma unroll
+        for (int i = 0; i < D; ++i) o[i] = 0u;
       }
-      softmax_bar_sync();    // this block's statistics are no longer read
-      if (half == 0 && it + 1 < iters) store_stats(n_l2, n_dl, n_lo);
-      softmax_bar_sync();    // the next block's are visible
-    }
-    if (ok && iters > 0) {
-      const int last = iters - 1;
-      if (!mbar_wait(&acc_done[last % L::kPBufs], uint32_t(last / L::kPBufs) & 1u, abort_flag, p.st, kTimeoutTmemFull,
-                     (4u << 16) | 12))
-        ok = false;
-    }
-    tc_fence_after();
-    if (ok || iters == 0) {   // warp-uniform
-      // the first half writes dV, the second dK
-      __nv_bfloat16* drow = (half ? p.dK + (size_t(batch) * p.Skv + key) * p.dk_row_stride
-                                  : p.dV + (size_t(batch) * p.Skv + key) * p.dv_row_stride) + size_t(kv_head) * D;
-      const uint32_t t = half ? tmem_dK : tmem_dV;
-#pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
-        uint32_t o[32];
-        if (iters > 0) {
-          tmem_ld_32x32b_x32(t + lane_addr + c * 32, o);
-          tmem_ld_wait();
-        } else {
+      if ((ok || t.iters == 0) && key < p.Skv) {
+        __nv_bfloat16* drow = (half ? p.dK + (size_t(t.batch) * p.Skv + key) * p.dk_row_stride
+                                    : p.dV + (size_t(t.batch) * p.Skv + key) * p.dv_row_stride) + size_t(t.kv_head) * D;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
-        }
-        if (key >= p.Skv) continue;
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
+        for (int gq = 0; gq < D / 8; ++gq) {
           uint4 w;
-          w.x = pack_bf16x2(__uint_as_float(o[g * 8 + 0]), __uint_as_float(o[g * 8 + 1]));
-          w.y = pack_bf16x2(__uint_as_float(o[g * 8 + 2]), __uint_as_float(o[g * 8 + 3]));
-          w.z = pack_bf16x2(__uint_as_float(o[g * 8 + 4]), __uint_as_float(o[g * 8 + 5]));
-          w.w = pack_bf16x2(__uint_as_float(o[g * 8 + 6]), __uint_as_float(o[g * 8 + 7]));
-          *reinterpret_cast<uint4*>(drow + c * 32 + g * 8) = w;
+          w.x = pack_bf16x2(__uint_as_float(o[gq * 8 + 0]), __uint_as_float(o[gq * 8 + 1]));
+          w.y = pack_bf16x2(__uint_as_float(o[gq * 8 + 2]), __uint_as_float(o[gq * 8 + 3]));
+          w.z = pack_bf16x2(__uint_as_float(o[gq * 8 + 4]), __uint_as_float(o[gq * 8 + 5]));
+          w.w = pack_bf16x2(__uint_as_float(o[gq * 8 + 6]), __uint_as_float(o[gq * 8 + 7]));
+          *reinterpret_cast<uint4*>(drow + gq * 8) = w;
         }
+      }
+      if (t.iters > 0) {
+        g0 += t.iters;
+        ++n;
       }
     }
   }
@@ -712,13 +843,13 @@ static int launch_bwd(const CUtensorMap& tq, const CUtensorMap& tk, const CUtens
         return int(cudaFuncSetAttribute(kkv, cudaFuncAttributeMaxDynamicSharedMemorySize, BwdKVSmem<D>::kTotal));
       }))
     return e;
-  dim3 gq((p.Sq + 127) / 128, p.H, p.B);
-  kq<<<gq, kBwdThreads, BwdQSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  const int q_units = ((p.Sq + 127) / 128) * p.H * p.B;
+  kq<<<min(q_units, sm_count()), kBwdThreads, BwdQSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
   note_launches(1);
   int rc = int(cudaGetLastError());
   if (rc) return rc;
-  dim3 gkv((p.Skv + 127) / 128, p.Hkv, p.B);
-  kkv<<<gkv, kBwdThreads, BwdKVSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
+  const int kv_units = ((p.Skv + 127) / 128) * p.Hkv * p.B;
+  kkv<<<min(kv_units, sm_count()), kBwdThreads, BwdKVSmem<D>::kTotal, stream>>>(tq, tk, tv, tdo, p);
   note_launches(1);
   return int(cudaGetLastError());
 }
