@@ -89,6 +89,46 @@ _SIGNATURES = {
     "idrak_skinny_splits": (c_int, [c_int, c_int]),
     "idrak_flash_fwd_ex": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 7 + [c_float, c_int, c_int, c_void_p, c_float,
                                                                               c_void_p]),
+    "idrak_gemm_lowrank": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,
+                                   c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "idrak_pw_unary": (c_int, [c_int, c_int, c_void_p, c_void_p, c_ll, c_float, c_float, c_void_p]),
+    "idrak_pw_unary_bwd": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_ll, c_float, c_float, c_int, c_void_p]),
+    "idrak_pw_binary": (c_int, [c_int, c_int, c_void_p, c_void_p, c_void_p, c_ll, c_float, c_float, c_void_p]),
+    "idrak_pw_muladd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p]),
+    "idrak_pw_extremum_bwd": (c_int, [c_int] + [c_void_p] * 5 + [c_ll, c_int, c_void_p]),
+    "idrak_pw_where": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p]),
+    "idrak_pw_fill": (c_int, [c_int, c_void_p, c_ll, c_float, c_void_p]),
+    "idrak_pw_add_rowvec": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_void_p]),
+    "idrak_pw_dropout": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_ll, c_float, C.c_ulonglong, c_void_p]),
+    "idrak_softmax": (c_int, [c_int, c_void_p, c_void_p, c_ll, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int,
+                              c_int, c_void_p]),
+    "idrak_softmax_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_float, c_int, c_void_p]),
+    "idrak_sum_axis": (c_int, [c_int, c_void_p, c_void_p, c_ll, c_int, c_ll, c_float, c_void_p]),
+    "idrak_broadcast_axis": (c_int, [c_int, c_void_p, c_void_p, c_ll, c_int, c_ll, c_int, c_void_p]),
+    "idrak_permute": (c_int, [c_int, c_void_p, c_void_p, c_int, C.POINTER(c_ll), C.POINTER(c_ll), c_void_p]),
+    "idrak_transpose": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "idrak_gather_rows": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_ll, c_void_p]),
+    "idrak_one_hot": (c_int, [c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p]),
+    "idrak_class_match": (c_int, [c_int, c_void_p, c_void_p, c_ll, c_int, c_void_p, c_void_p]),
+    "idrak_ctc_alpha_elems": (c_ll, [c_int, c_int, c_int]),
+    "idrak_ctc_row_elems": (c_ll, [c_int, c_int]),
+    "idrak_ctc_loss": (c_int, [c_void_p] * 7 + [c_int] * 5 + [c_void_p]),
+    "idrak_ctc_loss_bwd": (c_int, [c_void_p] * 10 + [c_int] * 5 + [c_void_p]),
+    "idrak_lstm_cell": (c_int, [c_int] + [c_void_p] * 5 + [c_int, c_int, c_void_p]),
+    "idrak_lstm_cell_bwd": (c_int, [c_int] + [c_void_p] * 7 + [c_int, c_int, c_void_p]),
+    "idrak_gru_cell": (c_int, [c_int] + [c_void_p] * 5 + [c_int, c_int, c_void_p]),
+    "idrak_gru_cell_bwd": (c_int, [c_int] + [c_void_p] * 6 + [c_int, c_int, c_void_p]),
+    "idrak_im2col": (c_int, [c_int, c_void_p, c_void_p, C.POINTER(c_int), c_int, c_void_p]),
+    "idrak_col2im": (c_int, [c_int, c_void_p, c_void_p, C.POINTER(c_int), c_int, c_int, c_void_p]),
+    "idrak_nchw_to_rows": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "idrak_rows_to_nchw": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "idrak_dw_conv": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, C.POINTER(c_int), c_void_p]),
+    "idrak_dw_conv_bwd_input": (c_int, [c_int, c_void_p, c_void_p, c_void_p, C.POINTER(c_int), c_void_p]),
+    "idrak_dw_conv_bwd_weight": (c_int, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, C.POINTER(c_int), c_void_p]),
+    "idrak_maxpool": (c_int, [c_int, c_void_p, c_void_p, c_void_p, C.POINTER(c_int), c_void_p]),
+    "idrak_maxpool_bwd": (c_int, [c_int, c_void_p, c_void_p, c_void_p, C.POINTER(c_int), c_void_p]),
+    "idrak_avgpool": (c_int, [c_int, c_void_p, c_void_p, C.POINTER(c_int), c_int, c_void_p]),
+    "idrak_avgpool_bwd": (c_int, [c_int, c_void_p, c_void_p, C.POINTER(c_int), c_int, c_void_p]),
     "idrak_flash_bwd_ex": (c_int, [c_void_p] * 10 + [c_int] * 6 + [c_ll] * 9 + [c_float, c_int, c_int, c_void_p,
                                                                                c_float, c_void_p]),
 }

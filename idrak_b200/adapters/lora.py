@@ -25,6 +25,7 @@ import torch
 from torch import nn
 
 from .. import ops
+from ..ops.gemm import lowrank_linear, lowrank_supported
 from ..models.decoder import Decoder, FeedForward, SelfAttention
 
 DEFAULT_TARGETS = ("q", "k", "v", "o", "gate", "up", "down")
@@ -211,6 +212,24 @@ def _merged(w: torch.Tensor, ad: LoraAdapter) -> torch.Tensor:
     return combined.to(w.dtype)
 
 
+def _stacked_adapters(x, adapters, slices, out_features):
+    """The adapters of one projection as a single pair ``A`` ``[R, in]``, ``B`` ``[out, R]``: the down matrices one under
+    the other, each scaled up matrix in its own column block and its own row slice (zeros elsewhere), so that
+    ``(x A^T) B^T`` is the sum of the adapters' contributions. ``None`` where the fused kernel does not apply."""
+    order = sorted(((lo, hi, n) for n, (lo, hi) in slices.items() if n in adapters), key=lambda t: t[0])
+    if not order:
+        return None
+    ads = [adapters[n] for _, _, n in order]
+    total = sum(ad.rank for ad in ads)
+    if not lowrank_supported(x, total) or any(ad.rank % 8 or ad.A.dtype != x.dtype for ad in ads):
+        return None
+    A = ads[0].A if len(ads) == 1 else torch.cat([ad.A for ad in ads], 0)
+    blocks = [torch.nn.functional.pad(ad.B * ad.scale, (0, 0, lo, out_features - hi))
+              for (lo, hi, _), ad in zip(order, ads)]
+    B = blocks[0] if len(blocks) == 1 else torch.cat(blocks, 1)
+    return A, B
+
+
 # --------------------------------------------------------------------------- forward helpers used by the decoder
 def project_with_adapters(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor],
                           adapters: Optional[AdapterSet], slices: Dict[str, Tuple[int, int]],
@@ -228,6 +247,14 @@ def project_with_adapters(x: torch.Tensor, weight: torch.Tensor, bias: Optional[
         return base(bias, residual)
     has_dora = any(isinstance(ad, DoraAdapter) for ad in adapters.items.values())
     if not has_dora:
+        stacked = _stacked_adapters(x, adapters, slices, out_features)
+        if stacked is not None:
+            # the adapters ride in the base product as extra blocks of K: no second pass over the output
+            A, B = stacked
+            if packed is not None:
+                from ..quant.weights import qlowrank_linear
+                return qlowrank_linear(x, packed, bias, residual, A, B)
+            return lowrank_linear(x, weight, bias, residual, A, B)
         y = base(bias, residual)
         parts, last = [], 0
         order = sorted(((lo, hi, n) for n, (lo, hi) in slices.items() if n in adapters), key=lambda t: t[0])

@@ -212,7 +212,7 @@ class CudaBackend(Backend):
         if torch.cuda.device_count() > 1:
             caps.append("peer_copy")
         for cap, symbol in (("float8_products", "idrak_gemm_fp8"), ("segmented_attention", "idrak_flash_fwd_ex"),
-                            ("fused_packed_kernels", "idrak_skinny_gemm")):
+                            ("fused_packed_kernels", "idrak_skinny_gemm"), ("recurrent_kernels", "idrak_lstm_cell")):
             if _native.has(symbol):
                 caps.append(cap)
         return caps
@@ -255,6 +255,17 @@ def _default_operations(table: SlotTable) -> None:
     for name in ("paged_decode", "kv_write_paged", "argmax_rows", "sample_rows", "norm_rope_kv"):
         if hasattr(dops, name):
             add(name, getattr(dops, name))
+    from ..ops import conv as cops, ctc as ctcops, pointwise as pops, recurrent as rops, reduce as redops
+    for name in ("unary", "binary", "muladd", "where", "add_rowvec", "dropout"):
+        add(name, getattr(pops, name))
+    for name in ("softmax", "log_softmax", "scale_mask_softmax", "sum_axis", "broadcast_axis", "permute", "transpose",
+                 "gather_rows", "one_hot", "class_match"):
+        add(name, getattr(redops, name))
+    for name in ("conv2d", "conv1d", "depthwise_conv2d", "max_pool2d", "avg_pool2d"):
+        add(name, getattr(cops, name))
+    add("ctc_loss", ctcops.ctc_loss)
+    for name in ("lstm_cell", "gru_cell", "lstm_layer", "gru_layer"):
+        add(name, getattr(rops, name))
     # composed: no kernel of its own anywhere, built from other operations through the dispatcher
     add("silu_mul", None, COMPOSED, composed=lambda backend, gate_up: run("gated_activation", gate_up, "silu", backend=backend),
         doc="SiLU(gate) * up over a packed [.., 2H] tensor")

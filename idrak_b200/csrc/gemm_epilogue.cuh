@@ -46,6 +46,7 @@ struct GemmParams {
   int group_b_rows;               // per-row-tile mode: rows of one expert in the stacked B array
   const int* group_kb;            // per-expert-K mode: [groups + 1] bounds of each expert's rows in 64-row blocks
   int groups;                     // per-expert-K mode: experts; C is the stacked [groups * M_per, N] array
+  int extra_kb;                   // second operand pair (low-rank term): its K extent in 64-element blocks, else 0
 };
 
 // Element-wise part of the epilogue on 8 consecutive columns of one row: bias, activation, residual.

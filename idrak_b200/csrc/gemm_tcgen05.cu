@@ -43,10 +43,15 @@ struct GemmSmem {
 //      weights; tiles beyond p.tiles_in_use (a device scalar) are not visited. Forward and input-gradient products.
 //   2  one output per expert, C stacked [groups * M, N]; expert g contracts over its own rows only, blocks
 //      [group_kb[g], group_kb[g + 1]) of K. An expert without rows gets zeros. Weight-gradient products.
+//   3  not a grouped product: a second operand pair (tmA2, tmB2; p.extra_kb blocks of K) is contracted after the first
+//      into the same accumulator, C = A B + A2 B2. This is how a low-rank adapter rides on its base projection: A2 is
+//      the [M, r] product of the input with the adapter's down matrix, B2 the (scaled) up matrix, and the adapter costs
+//      one more K block instead of a second pass over C. Columns of K beyond the operands' extent read as zeros.
 template <int BN, int A_MN, int B_MN, int F8 = 0, int GROUPED = 0>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux, const GemmParams p) {
+            const __grid_constant__ CUtensorMap tmC, const __grid_constant__ CUtensorMap tmAux,
+            const __grid_constant__ CUtensorMap tmA2, const __grid_constant__ CUtensorMap tmB2, const GemmParams p) {
   using L = GemmSmem<BN>;
   constexpr int kStages = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -80,6 +85,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       group = (GROUPED == 1) ? p.tile_group[tm] : 0;
       kb0 = split * kb_per_split;
       kb1 = min(k_blocks_total, kb0 + kb_per_split);
+      if (GROUPED == 3) kb1 += p.extra_kb;             // one pass over K (no split): the second pair follows the first
     }
   };
 
@@ -125,13 +131,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           uint8_t* sa = smem + stage * L::kStageBytes;
           uint8_t* sb = sa + L::kABytes;
           mbar_expect_tx(&full[stage], L::kStageBytes);
-          if (A_MN) {
+          if (GROUPED == 3 && kb >= k_blocks_total) {
+            const int k2 = (kb - k_blocks_total) * kKB;
+            tma_load_2d(sa, &tmA2, &full[stage], k2, tm * kBM);
+            if (B_MN) {
+#pragma unroll
+              for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmB2, &full[stage], tn * BN + j * 64, k2);
+            } else {
+              tma_load_2d(sb, &tmB2, &full[stage], k2, tn * BN);
+            }
+          } else if (A_MN) {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j) tma_load_2d(sa + j * 8192, &tmA, &full[stage], tm * kBM + j * 64, kb * kKB);
           } else {
             tma_load_2d(sa, &tmA, &full[stage], kb * kKB, tm * kBM);
           }
-          if (B_MN) {
+          if (GROUPED == 3 && kb >= k_blocks_total) {
+            // loaded above from the second pair
+          } else if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
               tma_load_2d(sb + j * 8192, &tmB, &full[stage], tn * BN + j * 64, kb * kKB + b_row);
@@ -296,7 +313,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const GemmParams p) 
 // ---------------------------------------------------------------------------
 template <int BN, int A_MN, int B_MN, int F8 = 0, int GROUPED = 0>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmC,
-                       const CUtensorMap& tmAux, const GemmParams& p, int grid, cudaStream_t stream) {
+                       const CUtensorMap& tmAux, const GemmParams& p, int grid, cudaStream_t stream,
+                       const CUtensorMap* tmA2 = nullptr, const CUtensorMap* tmB2 = nullptr) {
   using L = GemmSmem<BN>;
   auto kern = gemm_kernel<BN, A_MN, B_MN, F8, GROUPED>;
   static DeviceOnce configured;
@@ -304,7 +322,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
         return int(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
       }))
     return e;
-  kern<<<grid, kDenseThreads, L::kTotal, stream>>>(tmA, tmB, tmC, tmAux, p);
+  kern<<<grid, kDenseThreads, L::kTotal, stream>>>(tmA, tmB, tmC, tmAux, tmA2 ? *tmA2 : tmA, tmB2 ? *tmB2 : tmB, p);
   note_launches(1);
   return int(cudaGetLastError());
 }
@@ -477,6 +495,60 @@ IDRAK_API int idrak_gemm_bf16(const void* A, int lda, int a_mn, const void* B, i
     rc = int(cudaGetLastError());
   }
   return rc;
+}
+
+// C (bf16) = A op(B) + A2 op(B2) (+ bias) (+ residual): a product with a low-rank term contracted into the same
+// accumulator. A [M, K] and A2 [M, K2] are row-major; B and B2 share one layout: [N, K] / [N, K2] (b_mn = 0) or stored
+// [K, N] / [K2, N] (b_mn = 1). K2 is the adapter rank (or the ranks of several adapters side by side): any multiple
+// of 8 up to 256; the tail of its last 64-element block reads as zeros. Leading dimensions are multiples of 8.
+// Covers the reference's gemm_tc_{nn,nt}_lr_f32 family (src/Idrak.Gpu/Cuda/PtxKernels.TensorCore.cs:118-126): the
+// adapter as one more k step of the base product.
+IDRAK_API int idrak_gemm_lowrank(const void* A, int lda, const void* B, int ldb, int b_mn, const void* A2, int lda2,
+                                 const void* B2, int ldb2, void* C, int ldc, int M, int N, int K, int K2,
+                                 const void* bias, const void* residual, int ldr, void* stream_) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if (K2 <= 0 || K2 > 256 || (K2 & 7)) return -2;
+  if ((lda & 7) || (ldb & 7) || (lda2 & 7) || (ldb2 & 7)) return -2;
+  for (const void* q : {A, B, A2, B2})
+    if (reinterpret_cast<uintptr_t>(q) & 15) return -3;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int bn = (N <= 128) ? 128 : 256;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K;
+  p.C = C; p.ldc = ldc; p.c_fp32 = 0;
+  p.bias = static_cast<const __nv_bfloat16*>(bias);
+  p.residual = static_cast<const __nv_bfloat16*>(residual);
+  p.ldr = ldr;
+  p.act = kActNone;
+  p.alpha = 1.f;
+  p.splits = 1;
+  p.m_tiles = (M + kBM - 1) / kBM;
+  p.n_tiles = (N + bn - 1) / bn;
+  p.st = status_device_ptr();
+  p.extra_kb = (K2 + kBK - 1) / kBK;
+  CUtensorMap tmA, tmB, tmA2, tmB2, tmC, tmAux;
+  if (make_operand_map(&tmA, A, M, K, lda, 0, kBM, 0)) return -11;
+  if (make_operand_map(&tmB, B, N, K, ldb, b_mn, bn, 0)) return -12;
+  if (make_operand_map(&tmA2, A2, M, K2, lda2, 0, kBM, 0)) return -13;
+  if (make_operand_map(&tmB2, B2, N, K2, ldb2, b_mn, bn, 0)) return -14;
+  memset(&tmC, 0, sizeof(tmC));
+  memset(&tmAux, 0, sizeof(tmAux));
+  p.tma_store = 0;
+  if ((ldc % 8) == 0 && (reinterpret_cast<uintptr_t>(C) & 15) == 0) {
+    uint64_t dims[2] = {uint64_t(N), uint64_t(M)};
+    uint32_t box[2] = {64, 128};
+    uint64_t str_c[1] = {uint64_t(ldc) * 2};
+    p.tma_store = encode_tensor_map(&tmC, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, C, dims, str_c, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B) == 0;
+  }
+  p.epi_mode = pick_epi_mode(p);
+  p.prof = nullptr;
+  const int grid = min(p.m_tiles * p.n_tiles, sm_count());
+  if (bn == 256)
+    return b_mn ? launch_gemm<256, 0, 1, 0, 3>(tmA, tmB, tmC, tmAux, p, grid, stream, &tmA2, &tmB2)
+                : launch_gemm<256, 0, 0, 0, 3>(tmA, tmB, tmC, tmAux, p, grid, stream, &tmA2, &tmB2);
+  return b_mn ? launch_gemm<128, 0, 1, 0, 3>(tmA, tmB, tmC, tmAux, p, grid, stream, &tmA2, &tmB2)
+              : launch_gemm<128, 0, 0, 0, 3>(tmA, tmB, tmC, tmAux, p, grid, stream, &tmA2, &tmB2);
 }
 
 // C[M, N] (bf16) = (A B^T) * row_scale[m] * col_scale[n] (+ bias) with A [M, K] and B [N, K] e4m3 bytes, K-major

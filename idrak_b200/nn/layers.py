@@ -19,6 +19,8 @@ from torch import nn
 
 from .. import ops
 from ..core.registry import SlotTable
+from ..ops import conv as conv_ops
+from ..ops import recurrent as recurrent_ops
 
 
 def _fast(x: torch.Tensor) -> bool:
@@ -173,6 +175,39 @@ class TransformerEncoderLayer(nn.Module):
         return self.norm2(self._ff(x, x))
 
 
+class Conv2d(nn.Conv2d):
+    """``nn.Conv2d`` whose CUDA forward and backward run the package's kernels: patch rows around the tcgen05 GEMM for a
+    dense bf16 convolution, the depthwise kernel when every channel is its own group (``ops/conv.py``)."""
+
+    def forward(self, x):
+        if x.is_cuda and self.padding_mode == "zeros" and not isinstance(self.padding, str):
+            return conv_ops.conv2d(x, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups)
+        return super().forward(x)
+
+
+class Conv1d(nn.Conv1d):
+    def forward(self, x):
+        if x.is_cuda and self.padding_mode == "zeros" and not isinstance(self.padding, str):
+            return conv_ops.conv1d(x, self.weight, self.bias, self.stride[0], self.padding[0], self.dilation[0],
+                                   self.groups)
+        return super().forward(x)
+
+
+class MaxPool2d(nn.MaxPool2d):
+    def forward(self, x):
+        if x.is_cuda and x.dim() == 4 and not self.return_indices:
+            return conv_ops.max_pool2d(x, self.kernel_size, self.stride, self.padding, self.dilation, self.ceil_mode)
+        return super().forward(x)
+
+
+class AvgPool2d(nn.AvgPool2d):
+    def forward(self, x):
+        if x.is_cuda and x.dim() == 4 and self.divisor_override is None:
+            return conv_ops.avg_pool2d(x, self.kernel_size, self.stride, self.padding, self.ceil_mode,
+                                       self.count_include_pad)
+        return super().forward(x)
+
+
 class Recurrent(nn.Module):
     """LSTM / GRU over ``[N, T, in]``: all steps (``sequences=True``) or the last step's output."""
 
@@ -185,7 +220,10 @@ class Recurrent(nn.Module):
         self.cell = cls(in_features, hidden, num_layers=layers, batch_first=True, bidirectional=bidirectional)
 
     def forward(self, x):
-        out, _ = self.cell(x)
+        if x.is_cuda:
+            out, _ = recurrent_ops.run_module(self.cell, x)       # the package's cell kernels and products
+        else:
+            out, _ = self.cell(x)
         if self.sequences:
             return out
         if self.bidirectional:
@@ -250,12 +288,12 @@ def _defaults(t: SlotTable) -> None:
                    "padding": list(m.padding), "bias": m.bias is not None,
                    **({"dilation": list(m.dilation)} if tuple(m.dilation) != (1, 1) else {}),
                    **({"groups": m.groups} if m.groups != 1 else {})},
-        lambda d: nn.Conv2d(d["in"], d["out"], _pair(d["kernel"]), _pair(d.get("stride", 1)), _pair(d.get("padding", 0)),
+        lambda d: Conv2d(d["in"], d["out"], _pair(d["kernel"]), _pair(d.get("stride", 1)), _pair(d.get("padding", 0)),
                             _pair(d.get("dilation", 1)), d.get("groups", 1), d.get("bias", True)))
     reg("conv1d", nn.Conv1d,
         lambda m: {"in": m.in_channels, "out": m.out_channels, "kernel": m.kernel_size[0], "stride": m.stride[0],
                    "padding": m.padding[0], "bias": m.bias is not None},
-        lambda d: nn.Conv1d(d["in"], d["out"], d["kernel"], d.get("stride", 1), d.get("padding", 0), bias=d.get("bias", True)))
+        lambda d: Conv1d(d["in"], d["out"], d["kernel"], d.get("stride", 1), d.get("padding", 0), bias=d.get("bias", True)))
     reg("convtranspose2d", nn.ConvTranspose2d,
         lambda m: {"in": m.in_channels, "out": m.out_channels, "kernel": list(m.kernel_size), "stride": list(m.stride),
                    "padding": list(m.padding), "outputPadding": list(m.output_padding), "dilation": list(m.dilation),
@@ -270,12 +308,12 @@ def _defaults(t: SlotTable) -> None:
     reg("maxpool2d", nn.MaxPool2d,
         lambda m: {"kernel": list(_pair(m.kernel_size)), "stride": list(_pair(m.stride)), "padding": list(_pair(m.padding)),
                    **({"ceilMode": True} if m.ceil_mode else {})},
-        lambda d: nn.MaxPool2d(_pair(d["kernel"]), _pair(d.get("stride", d["kernel"])), _pair(d.get("padding", 0)),
+        lambda d: MaxPool2d(_pair(d["kernel"]), _pair(d.get("stride", d["kernel"])), _pair(d.get("padding", 0)),
                                ceil_mode=d.get("ceilMode", False)))
     reg("avgpool2d", nn.AvgPool2d,
         lambda m: {"kernel": list(_pair(m.kernel_size)), "stride": list(_pair(m.stride)), "padding": list(_pair(m.padding)),
                    "countIncludePad": m.count_include_pad, **({"ceilMode": True} if m.ceil_mode else {})},
-        lambda d: nn.AvgPool2d(_pair(d["kernel"]), _pair(d.get("stride", d["kernel"])), _pair(d.get("padding", 0)),
+        lambda d: AvgPool2d(_pair(d["kernel"]), _pair(d.get("stride", d["kernel"])), _pair(d.get("padding", 0)),
                                d.get("ceilMode", False), d.get("countIncludePad", True)))
     reg("adaptiveavgpool2d", nn.AdaptiveAvgPool2d, lambda m: {"size": list(_pair(m.output_size))},
         lambda d: nn.AdaptiveAvgPool2d(_pair(d["size"])))

@@ -73,6 +73,11 @@ def distillation_kl(student_logits, teacher_logits, temperature: float = 1.0, ma
 
 def ctc(log_probabilities, targets, input_lengths, target_lengths, blank: int = 0):
     """``log_probabilities`` [T, N, classes] (log-softmax already applied)."""
+    if log_probabilities.is_cuda and targets.dim() == 2:
+        from ..ops.ctc import ctc_loss
+        nll = ctc_loss(log_probabilities, targets, input_lengths, target_lengths, blank)      # per sequence
+        nll = torch.where(torch.isinf(nll), torch.zeros_like(nll), nll)                       # no alignment: counts as 0
+        return (nll / target_lengths.to(nll.device).clamp_min(1).to(nll.dtype)).mean()
     return F.ctc_loss(log_probabilities.float(), targets, input_lengths, target_lengths, blank=blank, zero_infinity=True)
 
 

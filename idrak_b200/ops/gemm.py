@@ -228,3 +228,94 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         y = torch.nn.functional.linear(x, weight, bias)
         return y + residual if residual is not None else y
     return _Linear.apply(x, weight, bias, residual)
+
+
+# --------------------------------------------------------------------------- product with a low-rank term
+def gemm_lowrank_reference(a, b, a2, b2, *, b_mn=False, bias=None, residual=None):
+    """fp32 statement of ``gemm_lowrank``."""
+    v = a.float() @ (b.float() if b_mn else b.float().t()) + a2.float() @ (b2.float() if b_mn else b2.float().t())
+    if bias is not None:
+        v = v + bias.float()
+    if residual is not None:
+        v = v + residual.float()
+    return v.to(a.dtype)
+
+
+def lowrank_supported(a: torch.Tensor, rank: int) -> bool:
+    """Whether the fused kernel takes this product: bf16 on the device, rank a multiple of 8 up to 256."""
+    return a.is_cuda and a.dtype == torch.bfloat16 and 0 < rank <= 256 and rank % 8 == 0 and a.shape[-1] % 8 == 0
+
+
+def gemm_lowrank(a, b, a2, b2, *, b_mn: bool = False, bias=None, residual=None):
+    """``C = A op(B) + A2 op(B2) (+ bias) (+ residual)`` in one kernel: the second pair is contracted after the first
+    into the same accumulator. ``a`` ``[M, K]``, ``a2`` ``[M, R]``; ``b`` / ``b2`` are ``[N, K]`` / ``[N, R]`` or, with
+    ``b_mn``, stored ``[K, N]`` / ``[R, N]``."""
+    if not lowrank_supported(a, a2.shape[1]):
+        return gemm_lowrank_reference(a, b, a2, b2, b_mn=b_mn, bias=bias, residual=residual)
+    a, b, a2, b2 = (t if t.stride(-1) == 1 else t.contiguous() for t in (a, b, a2, b2))
+    M, K = a.shape
+    R = a2.shape[1]
+    N = b.shape[1] if b_mn else b.shape[0]
+    assert (b.shape[0] if b_mn else b.shape[1]) == K and a2.shape[0] == M
+    assert tuple(b2.shape) == ((R, N) if b_mn else (N, R)), (b2.shape, R, N)
+    assert a.dtype == b.dtype == a2.dtype == b2.dtype == torch.bfloat16
+    out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == N
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, N) and residual.stride(1) == 1
+    rc = _native.lib().idrak_gemm_lowrank(
+        a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0), int(b_mn), a2.data_ptr(), a2.stride(0), b2.data_ptr(),
+        b2.stride(0), out.data_ptr(), out.stride(0), M, N, K, R, ptr(bias), ptr(residual),
+        residual.stride(0) if residual is not None else 0, stream_ptr())
+    _native.check(rc, "idrak_gemm_lowrank")
+    return out
+
+
+class _LowRankLinear(torch.autograd.Function):
+    """``y = x W^T + (x A^T) B^T (+ b) (+ residual)``. ``A`` ``[R, in]`` stacks the down matrices of the adapters on this
+    projection and ``B`` ``[out, R]`` their scaled up matrices, each in its own column block and zero outside its slice
+    of the output. Forward: one small product for ``x A^T`` and one product for the rest; backward likewise."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, residual, A, B):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        r2 = residual.reshape(-1, weight.shape[0]) if residual is not None else None
+        t = gemm(x2, A)                                                       # [M, R]
+        y = gemm_lowrank(x2, weight, t, B, bias=bias, residual=r2)
+        ctx.save_for_backward(x2, weight, A, B, t)
+        ctx.params = (weight, bias)
+        ctx.has_bias, ctx.has_res = bias is not None, residual is not None
+        return y.reshape(*shape[:-1], weight.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, A, B, t = ctx.saved_tensors
+        w_param, b_param = ctx.params
+        dy2 = dy.reshape(-1, weight.shape[0])
+        if dy2.stride(1) != 1 or dy2.stride(0) != dy2.shape[1]:
+            dy2 = dy2.contiguous()
+        dx = dw = db = dres = dA = dB = None
+        dt = gemm(dy2, B, b_mn=True)                                          # [M, R]
+        if ctx.needs_input_grad[0]:
+            dx = gemm_lowrank(dy2, weight, dt, A, b_mn=True).reshape(*dy.shape[:-1], weight.shape[1])
+        if ctx.needs_input_grad[1]:
+            dw = weight_grad(dy2, x2, w_param)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = bias_grad(dy2, b_param, dy)
+        if ctx.has_res and ctx.needs_input_grad[3]:
+            dres = dy
+        if ctx.needs_input_grad[4]:
+            dA = gemm(dt, x2, a_mn=True, b_mn=True)                           # [R, in]
+        if ctx.needs_input_grad[5]:
+            dB = gemm(dy2, t, a_mn=True, b_mn=True)                           # [out, R]
+        return dx, dw, db, dres, dA, dB
+
+
+def lowrank_linear(x, weight, bias, residual, A, B):
+    """``x W^T + (x A^T) B^T (+ bias) (+ residual)`` with the low-rank term inside the base product's kernel."""
+    if not lowrank_supported(x, A.shape[0]):
+        y = torch.nn.functional.linear(x, weight, bias) + torch.nn.functional.linear(torch.nn.functional.linear(x, A), B)
+        return y + residual if residual is not None else y
+    return _LowRankLinear.apply(x, weight, bias, residual, A, B)

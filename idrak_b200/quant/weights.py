@@ -259,6 +259,59 @@ class _QLinear(torch.autograd.Function):
         return dx, None, db, (dy if ctx.flags[1] else None)
 
 
+class _QLowRankLinear(torch.autograd.Function):
+    """``y = x W + (x A^T) B^T (+ b) (+ residual)`` over a packed ``W`` ``[in, out]`` for many rows: the weight is unpacked
+    once per pass and the low-rank term rides in the same tcgen05 product as one more block of K."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, residual, A, B):
+        from ..ops.gemm import gemm, gemm_lowrank
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        if x2.stride(1) != 1 or x2.stride(0) % 8:
+            x2 = x2.contiguous()
+        r2 = residual.reshape(-1, w.cols) if residual is not None else None
+        t = gemm(x2, A)                                                              # [M, R]
+        y = gemm_lowrank(x2, dequantize_bf16(w), t, B.t().contiguous(), b_mn=True, bias=bias, residual=r2)
+        ctx.w = w
+        ctx.save_for_backward(x2, A, B, t)
+        ctx.flags = (bias is not None, residual is not None)
+        return y.reshape(*shape[:-1], w.cols)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.gemm import gemm, gemm_lowrank
+        w = ctx.w
+        x2, A, B, t = ctx.saved_tensors
+        dy2 = dy.reshape(-1, w.cols)
+        if dy2.stride(1) != 1 or dy2.stride(0) != dy2.shape[1]:
+            dy2 = dy2.contiguous()
+        dt = gemm(dy2, B, b_mn=True)                                                 # [M, R]
+        dx = db = dA = dB = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm_lowrank(dy2, dequantize_bf16(w), dt, A.t().contiguous()).reshape(*dy.shape[:-1], w.rows)
+        if ctx.flags[0] and ctx.needs_input_grad[2]:
+            from ..ops.rowops import colsum
+            db = colsum(dy2)
+        if ctx.needs_input_grad[4]:
+            dA = gemm(dt, x2, a_mn=True, b_mn=True)
+        if ctx.needs_input_grad[5]:
+            dB = gemm(dy2, t, a_mn=True, b_mn=True)
+        return dx, None, db, (dy if ctx.flags[1] else None), dA, dB
+
+
+def qlowrank_linear(x, w, bias, residual, A, B):
+    """``qlinear`` plus the stacked adapters ``A`` ``[R, in]`` / ``B`` ``[out, R]``; the fused kernel for bf16 inputs of
+    ``DENSE_ROWS`` rows or more, separate products otherwise."""
+    from ..ops.gemm import lowrank_supported
+    rows = x.numel() // x.shape[-1]
+    if (lowrank_supported(x, A.shape[0]) and rows >= DENSE_ROWS and w.cols % 8 == 0 and w.rows % 8 == 0
+            and w.codes.is_cuda):
+        return _QLowRankLinear.apply(x, w, bias, residual, A, B)
+    from ..ops import linear
+    return qlinear(x, w, bias, residual) + linear(linear(x, A), B)
+
+
 def qlinear(x: torch.Tensor, w, bias: Optional[torch.Tensor] = None,
             residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``x @ W + bias (+ residual)`` over a packed weight ``W`` ``[in, out]``."""
