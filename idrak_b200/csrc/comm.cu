@@ -270,6 +270,10 @@ struct DpBucket {
   long long start, len, shard_off;
 };
 
+// U vectors per thread and pass: all U * world 16-byte loads of a pass are issued before the first one is used, so a
+// thread keeps about eight peer loads in flight whatever the world size (U = 4 / 2 / 1 for 2 / 4 / 8 ranks); with one
+// load per rank and pass a two-rank group had a single NVLink read outstanding per thread and stayed latency-bound.
+template <int U>
 __global__ void __launch_bounds__(512) dp_reduce_scatter_kernel(CommCtx c, PeerPtrs grads, DpBucket bk,
                                                                 float* __restrict__ shard_grad,
                                                                 float* __restrict__ sumsq_partial,
@@ -286,23 +290,33 @@ __global__ void __launch_bounds__(512) dp_reduce_scatter_kernel(CommCtx c, PeerP
   const long long base = bk.start + (long long)c.rank * slice;
   const long long nv = slice / 8;
   float sq = 0.f;
-  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nv;
-       i += (long long)gridDim.x * blockDim.x) {
-    uint4 vals[kMaxRanks];
+  constexpr int kRanksHere = kMaxRanks / U;             // the launcher picks U so that world <= kMaxRanks / U
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i0 = blockIdx.x * (long long)blockDim.x + threadIdx.x; i0 < nv; i0 += stride * U) {
+    uint4 vals[U][kRanksHere];
 #pragma unroll
-    for (int p = 0; p < kMaxRanks; ++p)
-      if (p < c.world) vals[p] = ld_peer16(static_cast<const __nv_bfloat16*>(grads.p[p]) + base + i * 8);
-    float acc[8];
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+      for (int p = 0; p < kRanksHere; ++p)
+        if (p < c.world && i < nv) vals[u][p] = ld_peer16(static_cast<const __nv_bfloat16*>(grads.p[p]) + base + i * 8);
+    }
 #pragma unroll
-    for (int p = 0; p < kMaxRanks; ++p)
-      if (p < c.world) accum_bf16x8(acc, vals[p], w[p]);
-    float* o = shard_grad + bk.shard_off + i * 8;
-    *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+    for (int u = 0; u < U; ++u) {
+      const long long i = i0 + u * stride;
+      if (i >= nv) break;
+      float acc[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) sq += acc[j] * acc[j];
+      for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+      for (int p = 0; p < kRanksHere; ++p)
+        if (p < c.world) accum_bf16x8(acc, vals[u][p], w[p]);
+      float* o = shard_grad + bk.shard_off + i * 8;
+      *reinterpret_cast<float4*>(o) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+      *reinterpret_cast<float4*>(o + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sq += acc[j] * acc[j];
+    }
   }
   sq = warp_sum(sq);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
@@ -563,9 +577,13 @@ IDRAK_API int idrak_dp_reduce_scatter(const void* ctx, void* const* grads, long 
   if (len % (c.world * 8)) return -2;
   PeerPtrs p = load_ptrs(grads, c.world);
   DpBucket bk{start, len, shard_off};
-  dp_reduce_scatter_kernel<<<blocks, 512, 0, static_cast<cudaStream_t>(stream_)>>>(c, p, bk, shard_grad,
-                                                                                  sumsq_partial, rank_weights,
-                                                                                  channel);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  if (c.world <= kMaxRanks / 4)
+    dp_reduce_scatter_kernel<4><<<blocks, 512, 0, stream>>>(c, p, bk, shard_grad, sumsq_partial, rank_weights, channel);
+  else if (c.world <= kMaxRanks / 2)
+    dp_reduce_scatter_kernel<2><<<blocks, 512, 0, stream>>>(c, p, bk, shard_grad, sumsq_partial, rank_weights, channel);
+  else
+    dp_reduce_scatter_kernel<1><<<blocks, 512, 0, stream>>>(c, p, bk, shard_grad, sumsq_partial, rank_weights, channel);
   note_launches(1);
   return int(cudaGetLastError());
 }

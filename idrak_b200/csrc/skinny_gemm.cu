@@ -25,6 +25,7 @@
 // Reference counterparts: the few-row GEMV family with fused epilogues (src/Idrak.Gpu/Cuda/PtxKernels.Quantized.cs:13,
 // 454-495: *_gemv_multi, _multi_act, _addnorm, _normaddnorm) and PtxKernels.Rows.cs:2047-2060.
 #include "common.cuh"
+#include <cstdlib>
 
 namespace idrak {
 
@@ -328,10 +329,19 @@ static int launch_skinny(const CUtensorMap& tmW, const CUtensorMap& tmX, const S
 using namespace idrak;
 
 // How many ways K is split (CTAs per cluster) for a product with `tiles` feature tiles and `kblocks` blocks of 64.
+// IDRAK_SKINNY_SPLITS = 1 | 2 | 4 | 8 overrides the choice (for measurements), as far as K has that many blocks.
 IDRAK_API int idrak_skinny_splits(int tiles, int kblocks) {
   const int slots = 2 * sm_count();
+  if (const char* forced = getenv("IDRAK_SKINNY_SPLITS")) {
+    const int f = atoi(forced);
+    if (f == 1 || f == 2 || f == 4 || f == 8) {
+      int c = f;
+      while (c > 1 && kblocks < c) c >>= 1;
+      return c;
+    }
+  }
   int c = 8;
-  while (c > 1 && (tiles * c > slots || kblocks / c < 4)) c >>= 1;
+  while (c > 1 && (tiles * c > slots || kblocks < c)) c >>= 1;     // measured: even one K block per CTA beats fewer CTAs
   return c;
 }
 

@@ -28,7 +28,7 @@ def main(argv=None) -> int:
     for name, default in (("layers", 32), ("dim", 4096), ("heads", 32), ("kv-heads", 8), ("ff", 14336), ("vocab", 128256),
                           ("seq", 2048), ("micro-batch", 4), ("steps", 5), ("warmup", 3), ("rank", 16)):
         ap.add_argument(f"--{name}", type=int, default=default)
-    ap.add_argument("--base", choices=["bf16", "int8", "int4"], default="int4")
+    ap.add_argument("--base", choices=["bf16", "int8", "int4", "fp8"], default="int4")
     ap.add_argument("--checkpoint-blocks", action="store_true")
     a = ap.parse_args(argv)
     world = int(os.environ.get("WORLD_SIZE", "1"))

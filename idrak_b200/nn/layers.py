@@ -39,7 +39,7 @@ class Linear(nn.Module):
             nn.init.uniform_(self.bias, -bound, bound)
 
     def forward(self, x, residual=None):
-        if _fast(x) and self.in_features % 8 == 0:
+        if _fast(x) and self.in_features % 8 == 0 and self.out_features % 8 == 0:   # 16-byte rows on both sides
             return ops.linear(x, self.weight, self.bias, residual)
         y = F.linear(x, self.weight, self.bias)
         return y if residual is None else y + residual

@@ -58,15 +58,19 @@ class _TokenCrossEntropy(torch.autograd.Function):
         dh = torch.empty_like(h2) if need_grad else None
         dw = None
         losses = []
+        inv_dev = None
         chunk_rows = chunk_rows or rows
         if ignore_index is None:
             inv = 1.0 / rows            # every row counts: no device-to-host read
             ignore_index = -(2 ** 31)
         else:
             if torch.cuda.is_current_stream_capturing():
-                raise RuntimeError("token_cross_entropy with ignore_index reads a count from the device; "
-                                   "pass ignore_index=None inside a graph capture")
-            inv = 1.0 / max(1, int((t != ignore_index).sum().item()))
+                # a recorded step cannot read the count back: the kernels work on sums and the division by the number
+                # of rows that count stays on the device, in the loss and (through backward's rescale) in the gradients
+                inv = 1.0
+                inv_dev = 1.0 / (t != ignore_index).sum().clamp(min=1).float()
+            else:
+                inv = 1.0 / max(1, int((t != ignore_index).sum().item()))
         for r0 in range(0, rows, chunk_rows):
             r1 = min(rows, r0 + chunk_rows)
             logits = gemm(h2[r0:r1], weight)                       # [chunk, Vpad]
@@ -78,6 +82,9 @@ class _TokenCrossEntropy(torch.autograd.Function):
                 else:
                     gemm(logits, h2[r0:r1], a_mn=True, b_mn=True, out=dw, beta=True)
         loss = torch.cat(losses).sum() * inv
+        if inv_dev is not None:
+            loss = loss * inv_dev
+        ctx.inv_dev = inv_dev
         ctx.save_for_backward(dh, dw)
         ctx.param = weight
         ctx.hshape, ctx.wdtype = hidden.shape, weight.dtype
@@ -87,6 +94,8 @@ class _TokenCrossEntropy(torch.autograd.Function):
     def backward(ctx, dloss):
         from . import _grad
         dh, dw = ctx.saved_tensors
+        if ctx.inv_dev is not None:
+            dloss = dloss * ctx.inv_dev
         gh = (dh * dloss.to(dh.dtype)).reshape(ctx.hshape) if dh is not None and ctx.needs_input_grad[0] else None
         gw = None
         if dw is not None and ctx.needs_input_grad[1]:

@@ -3,9 +3,9 @@ from __future__ import annotations
 
 import torch
 
-from .weights import (GROUP_SIZE, Int4Weight, Int8Weight, dequantize_bf16, qgemm, qlinear, quantize_weight)
+from .weights import (GROUP_SIZE, Fp8Weight, Int4Weight, Int8Weight, dequantize_bf16, qgemm, qlinear, quantize_weight)
 
-__all__ = ["GROUP_SIZE", "Int4Weight", "Int8Weight", "dequantize_bf16", "qgemm", "qlinear", "quantize_weight",
+__all__ = ["GROUP_SIZE", "Fp8Weight", "Int4Weight", "Int8Weight", "dequantize_bf16", "qgemm", "qlinear", "quantize_weight",
            "quantize_model", "dense_weight"]
 
 
@@ -83,7 +83,7 @@ def save_packed(model, folder) -> None:
             key = f"{prefix}.{name}"
             tensors[key + ".codes"] = w.codes.detach().cpu().contiguous()
             tensors[key + ".scales"] = w.scales.detach().cpu().contiguous()
-            packed_index[key] = {"bits": w.bits, "rows": w.rows, "cols": w.cols}
+            packed_index[key] = {"bits": w.bits, "rows": w.rows, "cols": w.cols, "kind": getattr(w, "kind", "int")}
     for n, p in model.named_parameters():
         if p is not None and "adapters" not in n:
             tensors[n] = p.detach().cpu().contiguous()
@@ -103,7 +103,7 @@ def load_packed(folder, device="cuda"):
     from ..formats.safetensors import load_file
     from ..models.decoder import build_decoder
     from ..models.spec import DecoderSpec
-    from .weights import Int4Weight, Int8Weight
+    from .weights import Fp8Weight, Int4Weight, Int8Weight
     folder = Path(folder)
     spec = DecoderSpec.from_json((folder / "spec.json").read_text())
     info = json.loads((folder / "quantization.json").read_text())
@@ -117,7 +117,7 @@ def load_packed(folder, device="cuda"):
     for key, meta in info["packed"].items():
         prefix, name = key.rsplit(".", 1)
         owner = owners[prefix]
-        cls = Int4Weight if meta["bits"] == 4 else Int8Weight
+        cls = Fp8Weight if meta.get("kind") == "fp8" else (Int4Weight if meta["bits"] == 4 else Int8Weight)
         w = cls(tensors[key + ".codes"].to(device), tensors[key + ".scales"].to(device), meta["rows"], meta["cols"])
         packed = dict(getattr(owner, "packed", {}))
         packed[name] = w

@@ -166,12 +166,70 @@ class Int4Weight:
         return [self.codes.contiguous().view(torch.float32), self.scales.float()]
 
 
+class Fp8Weight:
+    """A frozen weight held as e4m3 codes ``[out, in]`` (K-major, what the fp8 tensor-core product reads) with one fp32
+    scale per output unit. ``rows`` / ``cols`` follow the packed weights' ``[in, out]`` orientation. The forward product
+    quantises the activations per row and runs on the ``kind::f8f6f4`` GEMM; the input gradient multiplies by the
+    weight unpacked to bf16 (the gradient itself is not rounded to 8 bits)."""
+    bits = 8
+    kind = "fp8"
+
+    def __init__(self, codes: torch.Tensor, scales: torch.Tensor, rows: int, cols: int):
+        self.codes, self.scales, self.rows, self.cols = codes, scales, rows, cols      # codes [cols = out, rows = in]
+
+    @classmethod
+    def quantize(cls, w: torch.Tensor) -> "Fp8Weight":
+        """``w`` is ``[rows = in, cols = out]``."""
+        from ..ops.gemm8 import quantize_rows
+        rows, cols = w.shape
+        q = quantize_rows(w.detach().t().contiguous().to(torch.bfloat16))
+        return cls(q.codes, q.scales, rows, cols)
+
+    def as_rows(self):
+        from ..ops.gemm8 import Float8Rows
+        return Float8Rows(self.codes, self.scales)
+
+    def dense_out_in(self) -> torch.Tensor:
+        """The weight as bf16 ``[out, in]``."""
+        return self.as_rows().dequantize(torch.bfloat16)
+
+    def dequantize(self) -> torch.Tensor:
+        """fp32 ``[in, out]`` like the other packed weights."""
+        return self.as_rows().dequantize(torch.float32).t()
+
+    def to(self, device) -> "Fp8Weight":
+        return Fp8Weight(self.codes.to(device), self.scales.to(device), self.rows, self.cols)
+
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.scales.numel() * 4
+
+    def buffers(self):
+        return [self.codes, self.scales]
+
+
 def quantize_weight(w_in_out: torch.Tensor, kind: str):
     if kind == "int8":
         return Int8Weight.quantize(w_in_out)
     if kind == "int4":
         return Int4Weight.quantize(w_in_out)
-    raise ValueError(f"unknown packed format '{kind}' (int8, int4)")
+    if kind == "fp8":
+        return Fp8Weight.quantize(w_in_out)
+    raise ValueError(f"unknown packed format '{kind}' (int8, int4, fp8)")
+
+
+def _fp8_product(x2, w: "Fp8Weight", transposed, bias, residual, act, out):
+    from ..ops.gemm import gemm
+    from ..ops.gemm8 import gemm8, quantize_rows
+    if act is not None:
+        raise ValueError("the fp8 base has no fused activation epilogue")
+    if transposed:                                   # dy [M, out] -> dx [M, in]
+        return gemm(x2, w.dense_out_in(), b_mn=True, bias=bias, residual=residual, out=out)
+    if x2.is_cuda and w.rows % 16 == 0:
+        y = gemm8(quantize_rows(x2.to(torch.bfloat16)), w.as_rows(), bias, out=out)
+        if residual is not None:
+            y += residual
+        return y
+    return gemm(x2, w.dense_out_in(), bias=bias, residual=residual, out=out)
 
 
 # --------------------------------------------------------------------------- the op
@@ -185,6 +243,8 @@ def qgemm(x2: torch.Tensor, w, transposed: bool = False, bias=None, residual=Non
     N = w.rows if transposed else w.cols
     K = w.cols if transposed else w.rows
     assert x2.shape[1] == K and x2.stride(1) == 1
+    if isinstance(w, Fp8Weight):
+        return _fp8_product(x2, w, transposed, bias, residual, act, out)
     if not x2.is_cuda:
         wf = w.dequantize()
         y = x2.float() @ (wf.t() if transposed else wf)
@@ -222,6 +282,8 @@ def qgemm(x2: torch.Tensor, w, transposed: bool = False, bias=None, residual=Non
 
 def dequantize_bf16(w) -> torch.Tensor:
     """The packed weight as a bf16 ``[rows, cols]`` matrix (GPU kernel when on the device)."""
+    if isinstance(w, Fp8Weight):
+        return w.dense_out_in().t().contiguous()
     if not w.codes.is_cuda:
         return w.dequantize().to(torch.bfloat16)
     _bind()
@@ -306,7 +368,7 @@ def qlowrank_linear(x, w, bias, residual, A, B):
     from ..ops.gemm import lowrank_supported
     rows = x.numel() // x.shape[-1]
     if (lowrank_supported(x, A.shape[0]) and rows >= DENSE_ROWS and w.cols % 8 == 0 and w.rows % 8 == 0
-            and w.codes.is_cuda):
+            and w.codes.is_cuda and not isinstance(w, Fp8Weight)):
         return _QLowRankLinear.apply(x, w, bias, residual, A, B)
     from ..ops import linear
     return qlinear(x, w, bias, residual) + linear(linear(x, A), B)

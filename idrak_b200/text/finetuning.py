@@ -40,7 +40,8 @@ class FineTuningOptions:
     targets: Tuple[str, ...] = tuple(DEFAULT_TARGETS)
     dora: bool = False
     rslora: bool = False
-    base: str = "bf16"                   # how the frozen base is held: bf16 | int8 | int4
+    base: str = "bf16"                   # how the frozen base is held: bf16 | int8 | int4 | fp8 (e4m3 codes, the forward
+                                         # products on the 8-bit tensor-core path, input gradients in bf16)
     learning_rate: float = 2e-4
     weight_decay: float = 0.0
     warmup_fraction: float = 0.03
@@ -56,6 +57,8 @@ class FineTuningOptions:
     non_finite_steps: int = 8            # give up after this many skipped steps in a row
     data_parallel: str = "fused"         # with several ranks on GPUs: fused (peer-memory reduce-scatter + sharded AdamW +
                                          # all-gather kernels) | nccl (the same buckets over NCCL) | flat (one all-reduce)
+    capture_graph: bool = False          # one GPU, sft loss, no accumulation: pad every batch to one length, record
+                                         # forward + backward + update once as a CUDA graph and replay it per step
     checkpoint_blocks: bool = False      # recompute block activations in backward
     activation_ladder: bool = True       # estimate activation memory before the first step, step down on out-of-memory
     loss: str = "sft"                    # sft | dpo | orpo | simpo (or a name registered in PREFERENCE_LOSSES)
@@ -76,6 +79,7 @@ class FineTuningResult:
     losses: List[float] = field(default_factory=list)
     eval_losses: List[Tuple[int, float]] = field(default_factory=list)
     skipped_steps: int = 0
+    graph_replays: int = 0               # steps that were a replay of the recorded graph (``capture_graph``)
     adapter_folder: Optional[str] = None
     activation_policy: str = "held"
 
@@ -280,16 +284,22 @@ class FineTuner:
         self.group = group
         self.device = next(model.parameters()).device
         o = self.o
-        if o.base in ("int8", "int4") and self.device.type == "cuda":
+        if o.base in ("int8", "int4", "fp8") and self.device.type == "cuda":
             from ..quant import quantize_model
             quantize_model(model, o.base)
-        elif o.base not in ("bf16", "float32", "int8", "int4"):
-            raise ValueError(f"unknown base format '{o.base}' (bf16, int8, int4)")
+        elif o.base not in ("bf16", "float32", "int8", "int4", "fp8"):
+            raise ValueError(f"unknown base format '{o.base}' (bf16, int8, int4, fp8)")
         if o.resume_from:          # the checkpoint's adapters come first: the optimizer is built over them
             load_adapters(model, o.resume_from)
         has = any(getattr(m, "adapters", None) is not None for m in model.modules())
-        self.params = adapter_parameters(model) if has else add_adapters(
-            model, o.rank, o.alpha, o.targets, dora=o.dora, rslora=o.rslora)
+        if has:
+            self.params = adapter_parameters(model)
+        else:
+            # the adapters' initial values are a function of the seed, not of what else drew random numbers before
+            devices = [self.device] if self.device.type == "cuda" else []
+            with torch.random.fork_rng(devices=devices):
+                torch.manual_seed(o.seed)
+                self.params = add_adapters(model, o.rank, o.alpha, o.targets, dora=o.dora, rslora=o.rslora)
         for p in self.params:
             p.requires_grad_(True)
         model.checkpoint_blocks = o.checkpoint_blocks
@@ -305,6 +315,11 @@ class FineTuner:
                                      mode=o.data_parallel, group=group, bucket_mb=8.0)
             self.optimizer = self.sync.optimizer
         else:
+            if many:        # one all-reduce per step keeps equal weights equal: start them equal
+                with torch.no_grad():
+                    for p in self.params:
+                        dist.broadcast(p.data, src=dist.get_global_rank(group, 0) if group is not None else 0,
+                                       group=group)
             self.optimizer = FusedAdamW([{"params": self.params, "weight_decay": o.weight_decay}], lr=o.learning_rate,
                                         weight_decay=o.weight_decay, max_grad_norm=o.clip)
         self.template = ChatTemplate.for_tokenizer(tokenizer)
@@ -358,6 +373,51 @@ class FineTuner:
         return out
 
     # ------------------------------------------------------------------ losses
+    # ------------------------------------------------------------------ graph-recorded step
+    def _graph_eligible(self) -> bool:
+        o = self.o
+        return (o.capture_graph and self.device.type == "cuda" and self.sync is None and o.accumulation == 1
+                and o.loss == "sft" and not o.checkpoint_blocks)
+
+    def _graph_setup(self, batches: Sequence[PackedBatch]) -> None:
+        """Static device buffers of one padded length and a ``TrainStep`` that records the step over them. A batch
+        shorter than that length gets an untrained tail that is a sequence of its own (it attends to nothing else and
+        nothing attends to it)."""
+        from ..training.step import TrainStep
+        T = (max(b.ids.numel() for b in batches) + 7) // 8 * 8
+        dev = self.device
+        self._g_len = T
+        self._g_positions = torch.zeros(T, dtype=torch.int32, device=dev)
+        self._g_row_start = torch.zeros((1, T), dtype=torch.int32, device=dev)
+        pin = dict(pin_memory=True)
+        self._g_host = (torch.zeros((1, T), dtype=torch.int32, **pin), torch.zeros((1, T), dtype=torch.int32, **pin),
+                        torch.zeros(T, dtype=torch.int32, **pin), torch.zeros((1, T), dtype=torch.int32, **pin))
+
+        def loss_fn(model, ids, targets):
+            return model.loss(ids, targets, self._g_positions, ignore_index=IGNORE, spans=self._g_row_start)
+
+        self._g_step = TrainStep(self.model, self.optimizer, use_graph=True, loss_fn=loss_fn, direct_grads=False)
+
+    def _graph_step(self, b: PackedBatch) -> float:
+        """One recorded step on batch ``b``: four small host-to-device copies, one replay, one loss read."""
+        from ..ops.attention import row_starts_from_spans
+        T, n = self._g_len, b.ids.numel()
+        ids_h, tg_h, pos_h, rs_h = self._g_host
+        ids_h.zero_()
+        tg_h.fill_(IGNORE)
+        pos_h.zero_()
+        ids_h[0, :n] = b.ids.reshape(-1)
+        tg_h[0, :n] = b.targets.reshape(-1).to(torch.int32)
+        pos_h[:n] = b.positions.reshape(-1)
+        spans = list(b.spans)
+        if n < T:
+            pos_h[n:] = torch.arange(T - n, dtype=torch.int32)
+            spans.append((n, T))
+        rs_h.copy_(row_starts_from_spans(spans, 1, T))
+        self._g_positions.copy_(pos_h, non_blocking=True)
+        self._g_row_start.copy_(rs_h, non_blocking=True)
+        return self._g_step.step_from_host(ids_h, tg_h)
+
     def batch_loss(self, b: PackedBatch) -> torch.Tensor:
         dev = self.device
         if self.o.loss in PREFERENCE_LOSSES:
@@ -408,6 +468,10 @@ class FineTuner:
         self.plan_activation_memory(max(b.ids.numel() for b in batches))
         bad_streak = 0
         cursor = self.step * o.accumulation
+        graphed = self._graph_eligible()
+        if graphed:
+            self._graph_setup(batches)
+        res.graph_replays = 0
         while self.step < total:
             while len(order) <= cursor + o.accumulation:       # the draw order is a pure function of the seed
                 epoch_order = list(range(len(batches)))
@@ -416,6 +480,30 @@ class FineTuner:
             group = [batches[order[cursor + k]] for k in range(o.accumulation)]
             cursor += o.accumulation
             tokens = sum(max(b.trained_tokens, 1) for b in group)
+            if graphed:
+                # the recorded step holds forward, backward, clip and update; a non-finite gradient norm makes the
+                # update kernel leave the weights alone, so a bad step is skipped on the device and counted here
+                self.optimizer.set_lr(_lr_at(self.step, total, o))
+                value = self._graph_step(group[0])
+                res.graph_replays = self._g_step.replays
+                if not math.isfinite(value):
+                    res.skipped_steps += 1
+                    bad_streak += 1
+                    if bad_streak >= o.non_finite_steps:
+                        raise FloatingPointError(f"{bad_streak} steps in a row had a non-finite loss")
+                    continue
+                bad_streak = 0
+                self.step += 1
+                res.steps, res.tokens = self.step, res.tokens + tokens
+                res.losses.append(value)
+                if progress:
+                    progress(self.step, value)
+                if eval_batches and o.eval_every and self.step % o.eval_every == 0:
+                    res.eval_losses.append((self.step, self.evaluate(eval_batches)))
+                    self.model.train()
+                if out_dir and o.save_every and self.step % o.save_every == 0:
+                    self.save_checkpoint(os.path.join(out_dir, f"checkpoint-{self.step}"))
+                continue
             if self.sync is not None:
                 self.sync.zero_grad()
             else:

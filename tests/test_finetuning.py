@@ -163,3 +163,19 @@ def test_fine_tuner_steps_down_the_ladder_on_out_of_memory(monkeypatch):
     import pytest as _pytest
     with _pytest.raises(torch.OutOfMemoryError):
         ft.fit([{"prompt": "hello ", "completion": "world"}])
+
+
+def test_flat_data_parallel_ranks_start_and_stay_equal(tmp_path):
+    """Two gloo ranks that drew different random numbers before building the tuner: the adapters are a function of the
+    options' seed (and are broadcast), so one gradient all-reduce per step keeps the ranks bit-identical."""
+    import subprocess
+    import sys
+    here = os.path.dirname(os.path.abspath(__file__))
+    out = tmp_path / "flat.pt"
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", "29931", os.path.join(here, "finetune_flat_worker.py"), str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-3000:]
+    got = torch.load(out)
+    assert got["start"] and got["end"]
+    assert len(got["losses"]) == 4 and got["losses"][-1] < got["losses"][0]

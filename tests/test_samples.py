@@ -77,3 +77,23 @@ def test_gpt_api_sample_answers_over_v1():
     assert out["models"] == ["tiny"] and out["completion"]["usage"]["completion_tokens"] == 8
     assert out["chat"]["choices"][0]["message"]["role"] == "assistant" and out["streamed_chunks"] >= 2
     assert out["refused"] == 400
+
+
+def test_shape_recognition_sample_learns_the_four_shapes():
+    out = _load("shape_recognition").main(epochs=5, quiet=True)
+    assert out["accuracy"] > 0.9
+
+
+def test_sentiment_sample_needs_word_order():
+    scores = _load("sentiment").main(epochs=6, quiet=True, only=("bag of words", "lstm", "gru"))
+    assert scores["bag of words"] < 0.7 and scores["lstm"] > 0.95 and scores["gru"] > 0.95
+
+
+def test_ocr_sample_reads_lines_through_ctc():
+    out = _load("ocr").main(steps=450, quiet=True, train_lines=1000)
+    assert out["final_loss"] < 0.5 and out["characters"] > 0.8
+
+
+def test_summarizer_sample_beats_the_extractive_baselines():
+    out = _load("summarizer").main(steps=200, quiet=True)
+    assert out["scores"]["model"] > out["scores"]["best sentence"] + 0.1 and out["final_loss"] < 0.3
