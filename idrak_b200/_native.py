@@ -38,6 +38,7 @@ _SIGNATURES = {
     "idrak_launch_count": (c_ll, []),
     "idrak_bind_device": (c_int, [c_int]),
     "idrak_build_info": (C.c_char_p, []),
+    "idrak_device_limits": (c_int, [C.POINTER(c_ll), c_int]),
     "idrak_gemm_workspace_elems": (c_ll, [c_int, c_int, c_int, c_int]),
     "idrak_gemm_pick_splits": (c_int, [c_int, c_int, c_int, c_int]),
     "idrak_gemm_bf16": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,

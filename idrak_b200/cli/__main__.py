@@ -493,6 +493,23 @@ def cmd_tuning(a) -> int:
     return 0
 
 
+def cmd_limits(a) -> int:
+    """The device's limits and whether each tensor-core kernel's compile-time shape fits them."""
+    from ..runtime.limits import check_device, device_limits, kernel_shapes
+    lim = device_limits()
+    print("device limits" + ("" if lim.measured else " (no GPU here: the figures the kernels were written for)"))
+    for k, v in lim.as_dict().items():
+        if k != "measured":
+            print(f"  {k:32s} {v}")
+    print(f"  {'peak_memory_gbs (nominal)':32s} {lim.peak_memory_gbs:.0f}")
+    verdicts = check_device(lim)
+    print("kernel shapes")
+    for k in kernel_shapes():
+        print(f"  {k.kernel:26s} {k.tile}; {k.stages} stages, {k.threads} threads, {k.shared_bytes} B shared, "
+              f"{k.tensor_memory_columns} tensor-memory columns, {k.blocks_per_sm} per SM: {verdicts[k.kernel]}")
+    return 0 if all(v == "ok" for v in verdicts.values()) else 1
+
+
 # ------------------------------------------------------------------ parser
 def _sampling(p):
     p.add_argument("--max-tokens", type=int, default=256)
@@ -524,6 +541,7 @@ def build_parser() -> argparse.ArgumentParser:
         return p
 
     add("devices", cmd_devices, "list CUDA devices")
+    add("limits", cmd_limits, "the device's limits and which kernel shapes fit them")
     p = add("tuning", cmd_tuning, "show the measured per-device decisions (split-K factors, ...)")
     p.add_argument("--forget", nargs="?", const="", metavar="PREFIX", help="drop decisions whose name starts with PREFIX (all without one)")
     p = add("check", cmd_check, "run one tiny training step and one decode; optionally the conformance kit")

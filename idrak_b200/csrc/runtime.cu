@@ -143,6 +143,38 @@ IDRAK_API int idrak_bind_device(int device) { return int(cudaSetDevice(device));
 // Kernels launched by this library in this process so far.
 IDRAK_API long long idrak_launch_count() { return idrak::launches(); }
 
+// The limits of the current device that the launchers size their grids, tiles and shared memory by, in this order:
+//  0 SMs                         1 max threads per block          2 shared memory per block (opt-in), bytes
+//  3 shared memory per SM        4 L2 bytes                       5 registers per SM
+//  6 max resident blocks per SM  7 max resident threads per SM    8 warp size
+//  9 memory bus width, bits     10 memory clock, kHz             11 SM clock, kHz
+// 12 compute capability major   13 minor                         14 max cluster size the library uses (portable: 8)
+// 15 tensor-memory columns per SM (512 on compute capability 10, else 0)
+// Returns how many entries were written (at most `capacity`), or a negative CUDA error.
+IDRAK_API int idrak_device_limits(long long* out, int capacity) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return -int(e);
+  const cudaDeviceAttr attrs[14] = {
+      cudaDevAttrMultiProcessorCount, cudaDevAttrMaxThreadsPerBlock, cudaDevAttrMaxSharedMemoryPerBlockOptin,
+      cudaDevAttrMaxSharedMemoryPerMultiprocessor, cudaDevAttrL2CacheSize, cudaDevAttrMaxRegistersPerMultiprocessor,
+      cudaDevAttrMaxBlocksPerMultiprocessor, cudaDevAttrMaxThreadsPerMultiProcessor, cudaDevAttrWarpSize,
+      cudaDevAttrGlobalMemoryBusWidth, cudaDevAttrMemoryClockRate, cudaDevAttrClockRate,
+      cudaDevAttrComputeCapabilityMajor, cudaDevAttrComputeCapabilityMinor};
+  long long v[16];
+  for (int i = 0; i < 14; ++i) {
+    int x = 0;
+    e = cudaDeviceGetAttribute(&x, attrs[i], dev);
+    if (e != cudaSuccess) return -int(e);
+    v[i] = x;
+  }
+  v[14] = 8;
+  v[15] = v[12] == 10 ? 512 : 0;
+  const int n = capacity < 16 ? capacity : 16;
+  for (int i = 0; i < n; ++i) out[i] = v[i];
+  return n;
+}
+
 IDRAK_API const char* idrak_build_info() {
   return "idrak_b200 native kernels, sm_100a, built " __DATE__ " " __TIME__;
 }

@@ -20,6 +20,7 @@ from torch import nn
 from .. import ops
 from ..core.registry import SlotTable
 from ..ops import conv as conv_ops
+from ..ops import reduce as ops_reduce
 from ..ops import recurrent as recurrent_ops
 
 
@@ -145,6 +146,112 @@ class CrossAttention(nn.Module):
         mask = None if memory_padding is None else ~memory_padding[:, None, None, :]
         a = F.scaled_dot_product_attention(q, k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask)
         return self.out(a.transpose(1, 2).reshape(N, T, C))
+
+
+class RelativePositionAttention(nn.Module):
+    """Self-attention whose scores and outputs also depend on the distance between positions: a learned key vector and
+    a learned value vector per relative offset in ``[-window, window]`` (shared by the heads), added to the content
+    scores and to the attended values. Offsets beyond the window use the window's edge. ``lengths`` masks padding."""
+
+    def __init__(self, dim: int, heads: int, window: int = 4):
+        super().__init__()
+        if dim % heads:
+            raise ValueError("dim must be a multiple of heads")
+        self.dim, self.heads, self.window = dim, heads, window
+        d = dim // heads
+        self.qkv = Linear(dim, 3 * dim)
+        self.out = Linear(dim, dim)
+        self.rel_k = nn.Parameter(torch.randn(2 * window + 1, d) * d ** -0.5)
+        self.rel_v = nn.Parameter(torch.randn(2 * window + 1, d) * d ** -0.5)
+
+    def forward(self, x, lengths: Optional[torch.Tensor] = None):
+        N, T, _ = x.shape
+        H, D = self.heads, self.dim // self.heads
+        q, k, v = self.qkv(x).float().view(N, T, 3, H, D).permute(2, 0, 3, 1, 4)           # [N, H, T, D] each
+        pos = torch.arange(T, device=x.device)
+        offset = (pos[None, :] - pos[:, None]).clamp(-self.window, self.window) + self.window   # [T, T]
+        rk, rv = self.rel_k.float()[offset], self.rel_v.float()[offset]                       # [T, T, D]
+        scores = (q @ k.transpose(-1, -2) + torch.einsum("nhtd,tsd->nhts", q, rk)) * D ** -0.5
+        if lengths is not None:
+            keep = pos[None, :] < lengths.to(x.device)[:, None]                               # [N, T]
+            scores = scores.masked_fill(~keep[:, None, None, :], float("-inf"))
+        p = ops_reduce.softmax(scores, -1)
+        a = p @ v + torch.einsum("nhts,tsd->nhtd", p, rv)
+        return self.out(a.transpose(1, 2).reshape(N, T, self.dim).to(x.dtype))
+
+
+class WaveNetBlock(nn.Module):
+    """A stack of dilated, gated 1-D convolutions over ``[N, channels, T]`` with residual and skip connections and an
+    optional conditioning input added before the gate (the body of a flow's coupling network and of neural vocoders)."""
+
+    def __init__(self, channels: int, kernel: int = 5, layers: int = 4, dilation_rate: int = 2, condition: int = 0):
+        super().__init__()
+        self.channels, self.kernel, self.layers, self.dilation_rate, self.condition = channels, kernel, layers, dilation_rate, condition
+        self.dilated = nn.ModuleList()
+        self.mix = nn.ModuleList()
+        for i in range(layers):
+            d = dilation_rate ** i
+            self.dilated.append(nn.Conv1d(channels, 2 * channels, kernel, dilation=d, padding=(kernel - 1) * d // 2))
+            self.mix.append(nn.Conv1d(channels, 2 * channels if i + 1 < layers else channels, 1))
+        self.cond = nn.Conv1d(condition, 2 * channels * layers, 1) if condition else None
+
+    def forward(self, x, condition: Optional[torch.Tensor] = None, mask: Optional[torch.Tensor] = None):
+        skip = torch.zeros_like(x)
+        g = self.cond(condition) if self.cond is not None and condition is not None else None
+        for i in range(self.layers):
+            h = self.dilated[i](x)
+            if g is not None:
+                h = h + g[:, 2 * self.channels * i: 2 * self.channels * (i + 1)]
+            a, b = h.chunk(2, 1)
+            h = self.mix[i](torch.tanh(a) * torch.sigmoid(b))
+            if i + 1 < self.layers:
+                r, s = h.chunk(2, 1)
+                x = x + r if mask is None else (x + r) * mask
+                skip = skip + s
+            else:
+                skip = skip + h
+        return skip if mask is None else skip * mask
+
+
+class AffineCoupling(nn.Module):
+    """One step of a normalising flow over ``[N, channels, T]``: the first half of the channels passes through and
+    parameterises (through a WaveNet block) a shift and a log-scale for the second half. ``forward`` returns the
+    transformed tensor and the log-determinant per sequence; ``reverse`` inverts it exactly."""
+
+    def __init__(self, channels: int, hidden: int = 64, kernel: int = 5, layers: int = 3, condition: int = 0,
+                 mean_only: bool = False):
+        super().__init__()
+        if channels % 2:
+            raise ValueError("a coupling layer splits the channels in two halves")
+        self.channels, self.hidden, self.mean_only = channels, hidden, mean_only
+        half = channels // 2
+        self.pre = nn.Conv1d(half, hidden, 1)
+        self.body = WaveNetBlock(hidden, kernel, layers, 1, condition)
+        self.post = nn.Conv1d(hidden, half if mean_only else 2 * half, 1)
+        nn.init.zeros_(self.post.weight)             # starts as the identity
+        nn.init.zeros_(self.post.bias)
+
+    def _stats(self, x0, condition, mask):
+        h = self.pre(x0)
+        h = self.post(self.body(h if mask is None else h * mask, condition, mask))
+        if self.mean_only:
+            return h, torch.zeros_like(h)
+        shift, log_scale = h.chunk(2, 1)
+        return shift, log_scale
+
+    def forward(self, x, condition=None, mask=None):
+        x0, x1 = x.chunk(2, 1)
+        shift, log_scale = self._stats(x0, condition, mask)
+        y1 = shift + x1 * torch.exp(log_scale)
+        if mask is not None:
+            y1, log_scale = y1 * mask, log_scale * mask
+        return torch.cat([x0, y1], 1), log_scale.sum((1, 2))
+
+    def reverse(self, y, condition=None, mask=None):
+        y0, y1 = y.chunk(2, 1)
+        shift, log_scale = self._stats(y0, condition, mask)
+        x1 = (y1 - shift) * torch.exp(-log_scale)
+        return torch.cat([y0, x1 if mask is None else x1 * mask], 1)
 
 
 class TransformerEncoderLayer(nn.Module):
@@ -277,6 +384,17 @@ def _defaults(t: SlotTable) -> None:
         lambda m: {"dim": m.dim, "heads": m.attention.heads, "ffDim": m.ff_dim, "causal": m.attention.causal,
                    **({"norms": "after"} if m.norms == "after" else {})},
         lambda d: TransformerEncoderLayer(d["dim"], d["heads"], d["ffDim"], 0.0, d.get("causal", False), d.get("norms", "before")))
+    reg("relative_attention", RelativePositionAttention, lambda m: {"dim": m.dim, "heads": m.heads, "window": m.window},
+        lambda d: RelativePositionAttention(d["dim"], d["heads"], d.get("window", 4)))
+    reg("wavenet", WaveNetBlock,
+        lambda m: {"channels": m.channels, "kernel": m.kernel, "layers": m.layers, "dilationRate": m.dilation_rate,
+                   **({"condition": m.condition} if m.condition else {})},
+        lambda d: WaveNetBlock(d["channels"], d.get("kernel", 5), d.get("layers", 4), d.get("dilationRate", 2), d.get("condition", 0)))
+    reg("affine_coupling", AffineCoupling,
+        lambda m: {"channels": m.channels, "hidden": m.hidden, "kernel": m.body.kernel, "layers": m.body.layers,
+                   **({"condition": m.body.condition} if m.body.condition else {}), **({"meanOnly": True} if m.mean_only else {})},
+        lambda d: AffineCoupling(d["channels"], d.get("hidden", 64), d.get("kernel", 5), d.get("layers", 3), d.get("condition", 0),
+                                 d.get("meanOnly", False)))
     for kind in ("lstm", "gru"):
         reg(kind, None, lambda m: {"in": m.in_features, "hidden": m.hidden, "sequences": m.sequences,
                                    **({"bidirectional": True} if m.bidirectional else {}),

@@ -102,3 +102,38 @@ def test_losses():
     assert losses.hinge_discriminator(real, fake).item() == 0.0
     assert losses.least_squares_generator([torch.ones(3)]).item() == 0.0
     assert losses.feature_matching([[torch.ones(2, 2)]], [[torch.zeros(2, 2)]]).item() == 1.0
+
+
+def test_relative_attention_flow_and_wavenet_layers():
+    import torch
+    from idrak_b200.nn import layers as L
+    torch.manual_seed(0)
+    att = L.RelativePositionAttention(32, 4, window=3)
+    x = torch.randn(2, 9, 32)
+    y = att(x, lengths=torch.tensor([9, 5]))
+    assert y.shape == x.shape and torch.isfinite(y).all()
+    # padded keys do not reach the kept positions of the short sequence
+    x2 = x.clone()
+    x2[1, 5:] = 7.0
+    torch.testing.assert_close(att(x2, lengths=torch.tensor([9, 5]))[1, :5], y[1, :5])
+    flow = L.AffineCoupling(8, hidden=16, layers=2, condition=4)
+    with torch.no_grad():
+        flow.post.weight.normal_(0, 0.1)
+        flow.post.bias.normal_(0, 0.1)
+    z = torch.randn(3, 8, 20)
+    cond = torch.randn(3, 4, 20)
+    mask = (torch.arange(20)[None, None, :] < torch.tensor([20, 12, 7])[:, None, None]).float()
+    out, logdet = flow(z * mask, cond, mask)
+    back = flow.reverse(out, cond, mask)
+    torch.testing.assert_close(back, z * mask, rtol=1e-4, atol=1e-5)
+    assert logdet.shape == (3,) and (out[:, :4] == (z * mask)[:, :4]).all()
+    # the log-determinant is the one of the Jacobian: compare with autograd on one short sequence
+    small = L.AffineCoupling(4, hidden=8, layers=1)
+    with torch.no_grad():
+        small.post.weight.normal_(0, 0.2)
+    v = torch.randn(1, 4, 3)
+    jac = torch.autograd.functional.jacobian(lambda t: small(t)[0].reshape(-1), v).reshape(12, 12)
+    torch.testing.assert_close(torch.linalg.slogdet(jac)[1], small(v)[1][0], rtol=1e-4, atol=1e-5)
+    for m in (att, flow, L.WaveNetBlock(6, 3, 2, 2)):
+        twin = L.create(L.describe(m))
+        assert type(twin) is type(m) and sum(p.numel() for p in twin.parameters()) == sum(p.numel() for p in m.parameters())

@@ -97,3 +97,9 @@ def test_ocr_sample_reads_lines_through_ctc():
 def test_summarizer_sample_beats_the_extractive_baselines():
     out = _load("summarizer").main(steps=200, quiet=True)
     assert out["scores"]["model"] > out["scores"]["best sentence"] + 0.1 and out["final_loss"] < 0.3
+
+
+def test_text_generation_sample_continues_the_grammar_and_the_paths_agree():
+    out = _load("text_generation").main(steps=150, quiet=True, benchmark=True, length=48)
+    assert out["final_loss"] < 1.0 and out["benchmark"]["same_text"]
+    assert any(w in out["continuations"][0] for w in ("the ", "a ", "road", "key", "rain"))
