@@ -367,6 +367,13 @@ __device__ __forceinline__ void gelu_tanh_both(float x, float& g, float& d) {
   g = fmaf(hx, t, hx);
   d = fmaf(hx * du, fmaf(-t, t, 1.0f), fmaf(0.5f, t, 0.5f));
 }
+// Programmatic dependent launch. `pdl_launch_dependents` lets a kernel that follows in the stream and was launched with
+// the programmatic-serialization attribute start its CTAs (barrier and tensor-memory set-up, descriptor prefetch) while
+// this kernel is still running; `pdl_wait` is where such a kernel stops until every kernel before it has completed and
+// its writes are visible. Both are no-ops for kernels launched the ordinary way.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

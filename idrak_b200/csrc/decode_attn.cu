@@ -89,6 +89,7 @@ __device__ __forceinline__ void dequant16(const uint4& raw, float scale, uint4& 
 // tensor-core part below is unchanged and the cache costs half the bytes.
 template <int D, int KV8>
 __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const DecodeParams p) {
+  pdl_launch_dependents();     // a dependent launched programmatically may set itself up while this kernel runs
   constexpr int kRow = D * 2 + 16;                       // padded shared-memory row (bytes): conflict-free ldmatrix
   constexpr int kChunks = D / 8;                         // 16-byte chunks per key row
   constexpr int KS = D / 16;                             // k-steps of Q·K^T
@@ -309,6 +310,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
 // out[seq, head, :] = merge of the splits' partials, in split order
 __global__ void decode_merge_kernel(const float* __restrict__ partial, __nv_bfloat16* __restrict__ out, int rows,
                                     int splits, int D) {
+  pdl_launch_dependents();     // a dependent launched programmatically may set itself up while this kernel runs
   const int row = blockIdx.x;
   if (row >= rows) return;
   const float* base = partial + size_t(row) * splits * (D + 2);

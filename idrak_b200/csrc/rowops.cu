@@ -43,6 +43,7 @@ __global__ void __launch_bounds__(128) norm_fwd_kernel(const __nv_bfloat16* __re
                                                        __nv_bfloat16* __restrict__ sum_out,
                                                        float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                        int rows, int C, float eps, int rms) {
+  pdl_launch_dependents();     // a dependent launched programmatically may set itself up while this kernel runs
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= rows) return;
@@ -128,6 +129,7 @@ __global__ void __launch_bounds__(256) norm_fwd_block_kernel(const __nv_bfloat16
                                                              __nv_bfloat16* __restrict__ sum_out,
                                                              float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                                              int rows, int C, float eps, int rms) {
+  pdl_launch_dependents();     // a dependent launched programmatically may set itself up while this kernel runs
   __shared__ float red[8];
   const int row = blockIdx.x;
   const size_t base = size_t(row) * C;
@@ -515,6 +517,7 @@ __global__ void gelu_bwd_kernel(const __nv_bfloat16* __restrict__ x, const __nv_
 // gate_up: [rows, 2*H] with gate in columns [0,H) and up in [H,2H); out[r, h] = act(gate) * up.
 __global__ void gated_fwd_kernel(const __nv_bfloat16* __restrict__ gu, __nv_bfloat16* __restrict__ out, int rows,
                                  int H, int kind) {
+  pdl_launch_dependents();     // a dependent launched programmatically may set itself up while this kernel runs
   const int hv = H >> 3;
   const size_t total = size_t(rows) * hv;
   for (size_t i = blockIdx.x * size_t(blockDim.x) + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {

@@ -116,6 +116,26 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   const int per = (kblocks + csize - 1) / csize;
   const int kb0 = min(kblocks, rank * per), kb1 = min(kblocks, kb0 + per);
 
+  pdl_launch_dependents();
+  // one stage of operands: the weight tile (or the gate and up slices of a gated pair) and the token rows
+  auto issue = [&](int kb, int stage) {
+    uint8_t* sw = smem + stage * L::kStage;
+    uint8_t* sx = sw + L::kW;
+    mbar_expect_tx(&full[stage], L::kW + L::kX);
+    if (!gated) {
+      tma_load_2d(sw, &tmW, &full[stage], kb * kSkBK, tile * kSkFeat);
+    } else {
+      // slice r of the tile: S / 2 gate rows then the S / 2 up rows of the same features
+      const int half = S / 2;
+      for (int r = 0; r < csize; ++r) {
+        const int f = tile * 64 + r * half;
+        tma_load_2d(sw + (r * S) * 128, &tmW, &full[stage], kb * kSkBK, f);
+        tma_load_2d(sw + (r * S + half) * 128, &tmW, &full[stage], kb * kSkBK, p.up_offset + f);
+      }
+    }
+    tma_load_2d(sx, &tmX, &full[stage], kb * kSkBK, 0);
+  };
+  const int first = min(kSkStages, kb1 - kb0);          // stages filled before the CTA-wide sync (all are free then)
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSkStages; ++s) {
       mbar_init(&full[s], 1);
@@ -124,6 +144,10 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     fence_barrier_init();
+    tma_prefetch_desc(&tmW);
+    tma_prefetch_desc(&tmX);
+    pdl_wait();                                          // the kernels before this one have written the token rows
+    for (int i = 0; i < first; ++i) issue(kb0 + i, i);   // in flight while tensor memory is allocated below
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, 64);
@@ -132,36 +156,21 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();                                            // every thread that reads global memory (rows, bias, residual)
   const uint32_t tmem_acc = *tmem_slot;
   bool ok = true;
 
   if (warp == 0) {
     if (lane == 0) {
-      tma_prefetch_desc(&tmW);
-      tma_prefetch_desc(&tmX);
-      int stage = 0;
-      uint32_t phase = 0;
-      uint32_t issued_mask = 0, issued_phase = 0;
-      for (int kb = kb0; kb < kb1 && ok; ++kb) {
+      int stage = first % kSkStages;
+      uint32_t phase = first == kSkStages ? 1u : 0u;
+      uint32_t issued_mask = (1u << first) - 1u, issued_phase = 0;
+      for (int kb = kb0 + first; kb < kb1 && ok; ++kb) {
         if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag, p.st, kTimeoutSmemEmpty, (7u << 16) | stage)) {
           ok = false;
           break;
         }
-        uint8_t* sw = smem + stage * L::kStage;
-        uint8_t* sx = sw + L::kW;
-        mbar_expect_tx(&full[stage], L::kW + L::kX);
-        if (!gated) {
-          tma_load_2d(sw, &tmW, &full[stage], kb * kSkBK, tile * kSkFeat);
-        } else {
-          // slice r of the tile: S / 2 gate rows then the S / 2 up rows of the same features
-          const int half = S / 2;
-          for (int r = 0; r < csize; ++r) {
-            const int f = tile * 64 + r * half;
-            tma_load_2d(sw + (r * S) * 128, &tmW, &full[stage], kb * kSkBK, f);
-            tma_load_2d(sw + (r * S + half) * 128, &tmW, &full[stage], kb * kSkBK, p.up_offset + f);
-          }
-        }
-        tma_load_2d(sx, &tmX, &full[stage], kb * kSkBK, 0);
+        issue(kb, stage);
         issued_mask |= 1u << stage;
         issued_phase = (issued_phase & ~(1u << stage)) | (phase << stage);
         if (++stage == kSkStages) { stage = 0; phase ^= 1; }
@@ -312,13 +321,18 @@ static int launch_skinny(const CUtensorMap& tmW, const CUtensorMap& tmX, const S
   cfg.blockDim = dim3(kSkThreads);
   cfg.dynamicSmemBytes = L::kTotal;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = unsigned(p.csize);
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  // programmatic dependent launch: this kernel's CTAs may start while the kernel before it in the stream drains; they
+  // stop at pdl_wait() before their first read of global memory. IDRAK_PDL=0 launches the ordinary way.
+  static const bool pdl = [] { const char* e = getenv("IDRAK_PDL"); return !(e && e[0] == '0'); }();
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl ? 2 : 1;
   int rc = int(cudaLaunchKernelEx(&cfg, kern, tmW, tmX, p));
   note_launches(1);
   return rc;

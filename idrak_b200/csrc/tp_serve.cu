@@ -47,6 +47,7 @@ __global__ void __launch_bounds__(512) tp_allreduce_rows_kernel(CommCtx c, TpPee
                                                                 __nv_bfloat16* __restrict__ normed, float eps,
                                                                 int rms, int channel, uint32_t* seq,
                                                                 uint32_t* counter) {
+  pdl_launch_dependents();     // a dependent launched programmatically may set itself up while this kernel runs
   __shared__ float red[2][16];
   const uint32_t expected = *seq + 1u;
   if (blockIdx.x == 0) signal_peers(c, channel, expected);     // my partial rows are complete (stream order)

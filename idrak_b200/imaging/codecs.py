@@ -280,4 +280,7 @@ def encode(pixels: np.ndarray, format: str) -> bytes:
         return encode_bmp(pixels)
     if f in ("pnm", "pgm", "ppm"):
         return encode_pnm(pixels)
-    raise ImageFormatError(f"cannot write '{format}' (png, bmp, pgm / ppm)")
+    if f in ("jpg", "jpeg"):
+        from .jpeg import encode_jpeg
+        return encode_jpeg(pixels)
+    raise ImageFormatError(f"cannot write '{format}' (png, jpeg, bmp, pgm / ppm)")

@@ -241,3 +241,227 @@ def _decode_scan(data, at, frame, scan, quant, huff, restart_interval, adobe_tra
         cb, cr = cb - 128.0, cr - 128.0
         rgb = np.stack([y + 1.402 * cr, y - 0.344136 * cb - 0.714136 * cr, y + 1.772 * cb], -1)
     return np.clip(np.rint(rgb), 0, 255).astype(np.uint8)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# encoder
+# ---------------------------------------------------------------------------------------------------------------------
+_Q_LUMA = np.array([16, 11, 10, 16, 24, 40, 51, 61, 12, 12, 14, 19, 26, 58, 60, 55, 14, 13, 16, 24, 40, 57, 69, 56,
+                    14, 17, 22, 29, 51, 87, 80, 62, 18, 22, 37, 56, 68, 109, 103, 77, 24, 35, 55, 64, 81, 104, 113, 92,
+                    49, 64, 78, 87, 103, 121, 120, 101, 72, 92, 95, 98, 112, 100, 103, 99]).reshape(8, 8)
+_Q_CHROMA = np.array([17, 18, 24, 47, 99, 99, 99, 99, 18, 21, 26, 66, 99, 99, 99, 99, 24, 26, 56, 99, 99, 99, 99, 99,
+                      47, 66, 99, 99, 99, 99, 99, 99] + [99] * 32).reshape(8, 8)
+
+
+def _scaled_table(base: np.ndarray, quality: int) -> np.ndarray:
+    """The base table scaled the way the Independent JPEG Group's quality setting does (50 = the table itself)."""
+    q = min(max(int(quality), 1), 100)
+    scale = 5000 // q if q < 50 else 200 - 2 * q
+    return np.clip((base * scale + 50) // 100, 1, 255).astype(np.int32)
+
+
+def _code_lengths(freq: Dict[int, int]) -> Dict[int, int]:
+    """Huffman code lengths of at most 16 bits for the symbols of ``freq`` (no code of all ones: one code point is kept
+    free, as the format demands). Plain Huffman merging, then the longest codes are shortened by moving symbols up."""
+    import heapq
+    items = [(f, i, (s,)) for i, (s, f) in enumerate(sorted(freq.items()))]
+    items.append((0, len(items), (-1,)))                       # the reserved code point
+    if len(items) == 2:
+        return {items[0][2][0]: 1}
+    depth = {s: 0 for _, _, (s,) in items}
+    heapq.heapify(items)
+    tie = len(items)
+    while len(items) > 1:
+        a = heapq.heappop(items)
+        b = heapq.heappop(items)
+        for s in a[2] + b[2]:
+            depth[s] += 1
+        heapq.heappush(items, (a[0] + b[0], tie, a[2] + b[2]))
+        tie += 1
+    counts = [0] * 64
+    for d in depth.values():
+        counts[d] += 1
+    for length in range(len(counts) - 1, 16, -1):              # the standard's adjustment: pull long codes under 17 bits
+        while counts[length] > 0:
+            j = length - 2
+            while counts[j] == 0:
+                j -= 1
+            counts[length] -= 2
+            counts[length - 1] += 1
+            counts[j + 1] += 2
+            counts[j] -= 1
+    # hand the lengths out again: most frequent symbols get the shortest codes; the reserved point takes the longest
+    order = sorted((s for s in depth if s != -1), key=lambda s: (-freq[s], s))
+    lengths, at = {}, 0
+    pool = [length for length in range(1, 17) for _ in range(counts[length])]
+    pool = pool[:-1] if len(pool) > len(order) else pool       # drop the reserved code point's slot
+    for s, length in zip(order, pool):
+        lengths[s] = length
+    return lengths
+
+
+def _canonical(lengths: Dict[int, int]):
+    """(counts per length 1..16, symbols in code order, symbol -> (code, length))."""
+    by_len = sorted(lengths.items(), key=lambda kv: (kv[1], kv[0]))
+    counts = [0] * 16
+    codes, code, prev = {}, 0, 0
+    for s, length in by_len:
+        code <<= length - prev
+        prev = length
+        codes[s] = (code, length)
+        counts[length - 1] += 1
+        code += 1
+    return counts, [s for s, _ in by_len], codes
+
+
+class _BitWriter:
+    def __init__(self):
+        self.out = bytearray()
+        self.acc = self.n = 0
+
+    def put(self, code: int, length: int):
+        self.acc = (self.acc << length) | (code & ((1 << length) - 1))
+        self.n += length
+        while self.n >= 8:
+            self.n -= 8
+            byte = (self.acc >> self.n) & 0xFF
+            self.out.append(byte)
+            if byte == 0xFF:
+                self.out.append(0)                             # a data byte of all ones is followed by a zero
+        self.acc &= (1 << self.n) - 1
+
+    def finish(self) -> bytes:
+        if self.n:
+            self.put((1 << (8 - self.n)) - 1, 8 - self.n)      # pad with ones
+        return bytes(self.out)
+
+
+def _category(v: int) -> int:
+    return int(abs(v)).bit_length()
+
+
+def _symbols(blocks: np.ndarray):
+    """Per component: the (DC symbol, extra bits) and (AC symbol, extra bits) stream of its zig-zagged blocks."""
+    dc, ac, prev = [], [], 0
+    for block in blocks:
+        d = int(block[0]) - prev
+        prev = int(block[0])
+        c = _category(d)
+        dc.append((c, d if d >= 0 else d + (1 << c) - 1, c))
+        run = 0
+        row = []
+        last = int(np.max(np.nonzero(block)[0])) if block[1:].any() else 0
+        for k in range(1, last + 1):
+            v = int(block[k])
+            if v == 0:
+                run += 1
+                continue
+            while run > 15:
+                row.append((0xF0, 0, 0))
+                run -= 16
+            c = _category(v)
+            row.append(((run << 4) | c, v if v >= 0 else v + (1 << c) - 1, c))
+            run = 0
+        if last < 63:
+            row.append((0x00, 0, 0))                           # end of block
+        ac.append(row)
+    return dc, ac
+
+
+def encode_jpeg(pixels: np.ndarray, quality: int = 90, subsample: bool = False) -> bytes:
+    """Baseline JPEG (JFIF) of a uint8 grey ``[H, W]`` or colour ``[H, W, 3]`` image. ``quality`` 1..100 scales the standard
+    quantisation tables; ``subsample`` stores the chroma planes at half resolution in both directions (4:2:0). The
+    Huffman tables are built from the image's own symbol statistics."""
+    px = np.asarray(pixels)
+    if px.dtype != np.uint8 or px.ndim not in (2, 3) or (px.ndim == 3 and px.shape[2] not in (1, 3)):
+        raise ImageFormatError("encode_jpeg takes uint8 pixels shaped [H, W] or [H, W, 3]")
+    if px.ndim == 3 and px.shape[2] == 1:
+        px = px[:, :, 0]
+    H, W = px.shape[:2]
+    if H < 1 or W < 1 or H > 65535 or W > 65535:
+        raise ImageFormatError("image size must be 1..65535 in both directions")
+    grey = px.ndim == 2
+    f = px.astype(np.float64)
+    if grey:
+        planes = [f]
+    else:
+        r, g, b = f[..., 0], f[..., 1], f[..., 2]
+        planes = [0.299 * r + 0.587 * g + 0.114 * b,
+                  -0.168735892 * r - 0.331264108 * g + 0.5 * b + 128.0,
+                  0.5 * r - 0.418687589 * g - 0.081312411 * b + 128.0]
+    sub = bool(subsample) and not grey
+    mcu = 16 if sub else 8
+    Hp, Wp = -(-H // mcu) * mcu, -(-W // mcu) * mcu
+    planes = [np.pad(p, ((0, Hp - H), (0, Wp - W)), mode="edge") for p in planes]
+    if sub:
+        planes[1:] = [p.reshape(Hp // 2, 2, Wp // 2, 2).mean((1, 3)) for p in planes[1:]]
+    tables = [_scaled_table(_Q_LUMA, quality), _scaled_table(_Q_CHROMA, quality)]
+    D = _idct_matrix()                                         # forward transform: D X D^T
+    comp_blocks = []
+    for ci, p in enumerate(planes):
+        h, w = p.shape
+        blocks = (p - 128.0).reshape(h // 8, 8, w // 8, 8).transpose(0, 2, 1, 3)          # [by, bx, 8, 8]
+        coeff = np.einsum("ui,yxij,vj->yxuv", D, blocks, D)
+        q = np.rint(coeff / tables[0 if ci == 0 else 1]).astype(np.int32)
+        comp_blocks.append(q.reshape(h // 8, w // 8, 64)[:, :, ZIGZAG])
+    # block order of the scan: component by component inside each minimum coded unit
+    by, bx = Hp // mcu, Wp // mcu
+    order: List[Tuple[int, np.ndarray]] = []
+    per_comp: List[List[np.ndarray]] = [[] for _ in planes]
+    for y in range(by):
+        for x in range(bx):
+            if sub:
+                for dy in (0, 1):
+                    for dx in (0, 1):
+                        per_comp[0].append(comp_blocks[0][2 * y + dy, 2 * x + dx])
+                        order.append((0, len(per_comp[0]) - 1))
+                for ci in (1, 2):
+                    per_comp[ci].append(comp_blocks[ci][y, x])
+                    order.append((ci, len(per_comp[ci]) - 1))
+            else:
+                for ci in range(len(planes)):
+                    per_comp[ci].append(comp_blocks[ci][y, x])
+                    order.append((ci, len(per_comp[ci]) - 1))
+    streams = [_symbols(np.stack(blocks)) for blocks in per_comp]
+    # statistics -> tables: one DC and one AC table for luma, one pair for chroma
+    def table_for(kind: int, comps) -> Dict[int, int]:
+        freq: Dict[int, int] = {}
+        for ci in comps:
+            rows = streams[ci][kind]
+            for row in (rows if kind else [rows]):
+                for sym, _, _ in row:
+                    freq[sym] = freq.get(sym, 0) + 1
+        return _code_lengths(freq)
+    groups = [(0,)] if grey else [(0,), (1, 2)]
+    huff = [[_canonical(table_for(kind, comps)) for kind in (0, 1)] for comps in groups]
+    # ---- the file
+    out = bytearray(b"\xFF\xD8")
+    out += b"\xFF\xE0" + struct.pack(">H5sHBHHBB", 16, b"JFIF\0", 0x0101, 0, 1, 1, 0, 0)
+    for ti, t in enumerate(tables[: 1 if grey else 2]):
+        out += b"\xFF\xDB" + struct.pack(">HB", 67, ti) + bytes(int(v) for v in t.reshape(64)[ZIGZAG])
+    n = len(planes)
+    out += b"\xFF\xC0" + struct.pack(">HBHHB", 8 + 3 * n, 8, H, W, n)
+    for ci in range(n):
+        out += bytes([ci + 1, (0x22 if sub else 0x11) if ci == 0 else 0x11, 0 if ci == 0 else 1])
+    for gi, pair in enumerate(huff):
+        for kind, (counts, symbols, _) in enumerate(pair):
+            out += b"\xFF\xC4" + struct.pack(">HB", 19 + len(symbols), (kind << 4) | gi) + bytes(counts) + bytes(symbols)
+    out += b"\xFF\xDA" + struct.pack(">HB", 6 + 2 * n, n)
+    for ci in range(n):
+        gi = 0 if ci == 0 else 1
+        out += bytes([ci + 1, (gi << 4) | gi])
+    out += b"\x00\x3F\x00"
+    bits = _BitWriter()
+    for ci, bi in order:
+        gi = 0 if ci == 0 else 1
+        dc_codes, ac_codes = huff[gi][0][2], huff[gi][1][2]
+        sym, extra, nbits = streams[ci][0][bi]
+        bits.put(*dc_codes[sym])
+        if nbits:
+            bits.put(extra, nbits)
+        for sym, extra, nbits in streams[ci][1][bi]:
+            bits.put(*ac_codes[sym])
+            if nbits:
+                bits.put(extra, nbits)
+    out += bits.finish() + b"\xFF\xD9"
+    return bytes(out)

@@ -64,3 +64,31 @@ def skinny_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]
         float(norm_eps) if norm_eps is not None else -1.0, stream_ptr())
     _native.check(rc, "idrak_skinny_gemm")
     return out
+
+
+# Rows of the weight matrix from which the dense GEMM (with its own split-K choice) streams a few-row product faster than
+# the cluster kernel; measured at 64 activation rows, K = 4096: 6144 rows 23.7 / 24.4 us (few-row / dense), 7168 rows
+# 25.5 / 25.3, 16032 rows 46.1 / 40.2, 32064 rows 78.6 / 61.1, 128256 rows 266 / 192; the stacked gate / up matrix with
+# the activation: 28672 rows 73.9 us against 56.3 + 3 us for the dense product and the activation kernel.
+DENSE_FROM_ROWS = 12288
+
+
+def few_row_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None,
+                   residual: Optional[torch.Tensor] = None, gate: Optional[str] = None,
+                   norm_eps: Optional[float] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """A decode-sized product on whichever of the two kernels measured faster for the weight's size: the few-row cluster
+    kernel (fused epilogues, small and medium weights) or the dense GEMM followed, for a gated pair, by the activation
+    kernel (wide weights). A folded norm (``norm_eps``) exists only in the few-row kernel."""
+    if norm_eps is not None or w.shape[0] < DENSE_FROM_ROWS or not x.is_cuda:
+        return skinny_linear(x, w, bias, residual, gate, norm_eps, out)
+    from .gemm import gemm
+    if gate is None:
+        return gemm(x, w, bias=bias, residual=residual, out=out)
+    from .rowops import gated_activation
+    y = gated_activation(gemm(x, w, bias=bias), gate)
+    if residual is not None:
+        y = y + residual
+    if out is not None:
+        out.copy_(y)
+        return out
+    return y

@@ -335,7 +335,7 @@ class ModelRunner:
     def _decode_few_rows(self, x, positions, slots, block_table, lens, max_len_hint):
         """Six or seven launches per layer: qkv (+norm) | norms of q, k + RoPE + cache write | paged attention
         (+ its merge) | out + residual | gate/up (+norm) + activation | down + residual."""
-        from ..ops.skinny import skinny_linear
+        from ..ops.skinny import few_row_linear, skinny_linear
         s, m = self.spec, self.model
         H, Hkv, D = s.heads, s.kv_heads, s.head_dim
         folded = bool(getattr(m, "_norms_folded", False))
@@ -363,7 +363,7 @@ class ModelRunner:
         if folded:
             logits = skinny_linear(x, m.head_weight(), m.head_bias, norm_eps=s.norm_epsilon)
         else:
-            logits = skinny_linear(m.norm(x), m.head_weight(), m.head_bias)
+            logits = few_row_linear(m.norm(x), m.head_weight(), m.head_bias)      # a wide head streams faster densely
         return logits.reshape(-1, logits.shape[-1])
 
     # ------------------------------------------------------------------ decode as a replayed CUDA graph

@@ -47,7 +47,7 @@ class TPModelRunner(ModelRunner):
         (partial, into the symmetric buffer) | all-reduce + residual + norm | gate/up + activation | down (partial) |
         all-reduce + residual + the next layer's norm."""
         from ..ops import decode as dops
-        from ..ops.skinny import skinny_linear
+        from ..ops.skinny import few_row_linear, skinny_linear
         s, m, tp = self.spec, self.model, self.tp
         H, Hkv, D = s.heads, s.kv_heads, s.head_dim
         n = x.shape[0]
@@ -63,11 +63,11 @@ class TPModelRunner(ModelRunner):
                                   max_len_hint=max_len_hint, k_scale=self.k_scale[li], v_scale=self.v_scale[li])
             part = skinny_linear(o.reshape(n, H * D), attn.o_weight, attn.o_bias, out=tp.partial_buffer(n))
             x, h = tp.all_reduce_rows(part, x, blk.mlp_norm)
-            g = skinny_linear(h, mlp.up_weight, mlp.up_bias, gate=s.activation)
+            g = few_row_linear(h, mlp.up_weight, mlp.up_bias, gate=s.activation)
             part = skinny_linear(g, mlp.down_weight, mlp.down_bias, out=tp.partial_buffer(n))
             nxt = blocks[li + 1].attn_norm if li + 1 < len(blocks) else m.norm
             x, h = tp.all_reduce_rows(part, x, nxt)
-        logits = skinny_linear(h, m.tp_head, m.tp_head_bias)
+        logits = few_row_linear(h, m.tp_head, m.tp_head_bias)
         return logits.reshape(-1, logits.shape[-1])
 
     def _sum_partials(self, partial: torch.Tensor, residual: torch.Tensor, norm=None):

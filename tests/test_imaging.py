@@ -232,3 +232,44 @@ def test_baseline_jpeg_decoder_against_libjpeg():
     Image.fromarray(img).save(buf, "JPEG", progressive=True)
     with pytest.raises(im.ImageFormatError, match="progressive"):
         im.decode(buf.getvalue())
+
+
+def test_jpeg_encoder_round_trips_and_an_independent_decoder_reads_it():
+    import io
+
+    import numpy as np
+
+    from idrak_b200.imaging import codecs
+    from idrak_b200.imaging.jpeg import _canonical, _code_lengths, decode_jpeg, encode_jpeg
+    rng = np.random.default_rng(0)
+    y, x = np.mgrid[0:70, 0:93]
+    img = np.stack([128 + 100 * np.sin(x / 9.0) * np.cos(y / 7.0), (x * 2.5) % 256, (y * 3 + x) % 256], -1)
+    img = (img + rng.normal(0, 3, img.shape)).clip(0, 255).astype(np.uint8)
+
+    def psnr(a, b):
+        return 10 * np.log10(255 ** 2 / ((a.astype(float) - b.astype(float)) ** 2).mean())
+
+    sizes = {}
+    for quality, sub, floor in ((95, False, 37.0), (75, False, 33.0), (50, True, 27.0)):
+        data = encode_jpeg(img, quality, sub)
+        back = decode_jpeg(data)
+        assert back.shape == img.shape and psnr(img, back) > floor, (quality, psnr(img, back))
+        sizes[quality] = len(data)
+    assert sizes[95] > sizes[75] > sizes[50]
+    grey = encode_jpeg(img[..., 0], 85)
+    assert decode_jpeg(grey).shape == (70, 93) and psnr(img[..., 0], decode_jpeg(grey)) > 36
+    assert codecs.decode(codecs.encode(img, "jpeg")).shape == img.shape
+    try:
+        from PIL import Image
+    except ImportError:
+        Image = None
+    if Image is not None:                       # a decoder that shares no code with this package reads the file
+        seen = np.array(Image.open(io.BytesIO(encode_jpeg(img, 90))).convert("RGB"))
+        assert psnr(img, seen) > 35
+    # code lengths: never longer than 16 bits, a prefix code with one code point to spare (Kraft sum below one)
+    freq = {s: 2 ** min(s, 40) for s in range(60)}
+    lengths = _code_lengths(freq)
+    assert max(lengths.values()) <= 16 and sum(2.0 ** -v for v in lengths.values()) < 1.0
+    counts, symbols, codes = _canonical(lengths)
+    assert sum(counts) == len(symbols) == 60 and all(code < (1 << n) - 1 or n < max(lengths.values()) for code, n in codes.values())
+    assert _code_lengths({7: 10}) == {7: 1}
