@@ -100,6 +100,21 @@ def write_wav(path: str, samples: torch.Tensor, rate: int, bits: int = 16) -> No
 # ---------------------------------------------------------------------------------------------------------------------
 # resampling
 # ---------------------------------------------------------------------------------------------------------------------
+def decode_audio(data: bytes) -> Tuple[torch.Tensor, int]:
+    """Decode by content: RIFF / WAVE or FLAC. float32 ``[channels, n]`` and the sample rate."""
+    if data[:4] == b"RIFF":
+        return decode_wav(data)
+    if data[:4] == b"fLaC":
+        from .flac import decode_flac
+        return decode_flac(data)
+    raise AudioFormatError("unknown audio format (WAV and FLAC are read)")
+
+
+def read_audio(path: str) -> Tuple[torch.Tensor, int]:
+    with open(path, "rb") as f:
+        return decode_audio(f.read())
+
+
 def resample(x: torch.Tensor, rate_in: int, rate_out: int, zeros: int = 16, rolloff: float = 0.95) -> torch.Tensor:
     """Band-limited polyphase resampling of ``[..., n]`` by the rational factor ``rate_out / rate_in``: a Hann-windowed
     sinc low-pass at ``rolloff`` x the lower Nyquist, one filter phase per output position modulo the up factor, applied

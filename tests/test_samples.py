@@ -103,3 +103,8 @@ def test_text_generation_sample_continues_the_grammar_and_the_paths_agree():
     out = _load("text_generation").main(steps=150, quiet=True, benchmark=True, length=48)
     assert out["final_loss"] < 1.0 and out["benchmark"]["same_text"]
     assert any(w in out["continuations"][0] for w in ("the ", "a ", "road", "key", "rain"))
+
+
+def test_vision_sample_detects_and_segments_the_shapes():
+    out = _load("idrak_vision").main(steps=120, quiet=True)
+    assert out["map50"] > 0.8 and out["miou"] > 0.9
