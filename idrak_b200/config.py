@@ -98,6 +98,10 @@ TABLE: List[Setting] = [
     Setting("IDRAK_NVCC", "text", "", "compiler used by python -m idrak_b200.build (default: nvcc on PATH or /usr/local/cuda)"),
     Setting("IDRAK_B200_LIB", "text", "", "load this native library instead of lib/libidrak_b200.so"),
     Setting("IDRAK_TP_FEW_ROW_DECODE", "bool", True, "tensor-parallel serving: decode steps of up to 64 sequences on the few-row kernels"),
+    Setting("IDRAK_PDL", "bool", True, "few-row decode products are launched programmatically dependent on the kernel "
+                                       "before them (their set-up overlaps its tail); 0 launches them the ordinary way"),
+    Setting("IDRAK_SKINNY_SPLITS", "choice", "", "few-row products: force the number of CTAs that share K (for measurements)",
+            ("", "1", "2", "4", "8")),
     Setting("IDRAK_B200_AUTOBUILD", "bool", False, "build the native library on first use when it is missing"),
     Setting("IDRAK_REFERENCE_DATA", "text", "", "tests: folder with the reference project's test fixtures"),
     Setting("IDRAK_COMM_CANARIES", "bool", True, "communicator: check the guard bands of symmetric buffers at close"),

@@ -68,8 +68,19 @@ __device__ __forceinline__ void load_codes8(const QWeight& w, int row, int col, 
       for (int i = 0; i < 8; ++i) q[i] = (col + i < w.cols) ? p[i] : int8_t(0);
     }
     if (w.scale_in_producer) {
+      const __half* sc = w.scales + col;
+      if (col + 8 <= w.cols && (reinterpret_cast<uintptr_t>(sc) & 15) == 0) {
+        const uint4 s4 = __ldg(reinterpret_cast<const uint4*>(sc));
+        const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) out[i] = (col + i < w.cols) ? float(q[i]) * __half2float(w.scales[col + i]) : 0.f;
+        for (int i = 0; i < 8; ++i) {
+          const __half h = __ushort_as_half((unsigned short)((sw[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu));
+          out[i] = float(q[i]) * __half2float(h);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) out[i] = (col + i < w.cols) ? float(q[i]) * __half2float(w.scales[col + i]) : 0.f;
+      }
     } else {
 #pragma unroll
       for (int i = 0; i < 8; ++i) out[i] = float(q[i]);
@@ -77,6 +88,18 @@ __device__ __forceinline__ void load_codes8(const QWeight& w, int row, int col, 
   } else {
     const uint32_t word = __ldg(static_cast<const uint32_t*>(w.codes) + size_t(row) * w.ld + (col >> 3));
     const __half* sc = w.scales + size_t(row >> 5) * w.scale_ld + col;
+    if ((reinterpret_cast<uintptr_t>(sc) & 15) == 0) {
+      // the scale rows are padded to eight columns: one 16-byte load brings the eight scales of this chunk
+      const uint4 s4 = __ldg(reinterpret_cast<const uint4*>(sc));
+      const uint32_t sw[4] = {s4.x, s4.y, s4.z, s4.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int q = int(word << (28 - 4 * i)) >> 28;        // sign-extended nibble i
+        const __half h = __ushort_as_half((unsigned short)((sw[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu));
+        out[i] = (col + i < w.cols) ? float(q) * __half2float(h) : 0.f;
+      }
+      return;
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int q = int(word << (28 - 4 * i)) >> 28;          // sign-extended nibble i
@@ -399,7 +422,15 @@ __global__ void qdequant_kernel(QWeight w, __nv_bfloat16* __restrict__ out, int 
     const int r = int(i / chunks), c = int(i - (long long)r * chunks) * 8;
     float v[8];
     load_codes8(w, r, c, v);
-    for (int j = 0; j < 8 && c + j < w.cols; ++j) out[size_t(r) * ld_out + c + j] = __float2bfloat16(v[j]);
+    __nv_bfloat16* o = out + size_t(r) * ld_out + c;
+    if (c + 8 <= w.cols && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+      uint4 q;                                            // one 16-byte store per eight columns
+      q.x = pack_bf16x2(v[0], v[1]); q.y = pack_bf16x2(v[2], v[3]);
+      q.z = pack_bf16x2(v[4], v[5]); q.w = pack_bf16x2(v[6], v[7]);
+      *reinterpret_cast<uint4*>(o) = q;
+    } else {
+      for (int j = 0; j < 8 && c + j < w.cols; ++j) o[j] = __float2bfloat16(v[j]);
+    }
   }
 }
 

@@ -226,6 +226,14 @@ def case_qgemm(a):
     return (lambda: qgemm(x, w)), 2.0 * a.m * a.n * a.k, a.k * a.n * bits / 8 + 2.0 * a.m * (a.k + a.n)
 
 
+def case_qdequant(a):
+    """Unpack a packed [--k, --n] weight (--kind int4 | int8) to bf16: bytes = codes + scales read, bf16 written."""
+    from ..quant.weights import dequantize_bf16, quantize_weight
+    w = quantize_weight(torch.randn(a.k, a.n, device="cuda", dtype=torch.bfloat16), a.kind)
+    bits = 4 if a.kind == "int4" else 8
+    return (lambda: dequantize_bf16(w)), 0.0, a.k * a.n * (bits / 8 + 2.0)
+
+
 def _role_timers(fn: Callable[[], None]) -> dict:
     """One launch with the dense GEMM's role timers on: mean cycles per tile, over the CTAs that ran tiles."""
     import ctypes as C
@@ -254,7 +262,7 @@ CASES: Dict[str, Callable] = {
     "gemm": case_gemm, "gemm_wgrad": case_gemm_wgrad, "cublas": case_cublas, "flash_fwd": case_flash_fwd,
     "flash_bwd": case_flash_bwd, "xent": case_xent, "norm": case_norm, "norm_bwd": case_norm_bwd, "adamw": case_adamw,
     "skinny": case_skinny, "skinny_dense": case_skinny_dense,
-    "decode_attn": case_decode_attn, "qgemm": case_qgemm,
+    "decode_attn": case_decode_attn, "qgemm": case_qgemm, "qdequant": case_qdequant,
 }
 
 

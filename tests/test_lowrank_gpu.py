@@ -14,7 +14,7 @@ def _rand(g, *shape, scale=1.0):
 
 
 @pytest.mark.parametrize("M,N,K,R", [(256, 512, 256, 16), (1000, 384, 520, 48), (128, 128, 64, 8), (513, 1032, 4096, 64),
-                                     (300, 260, 192, 136)])
+                                     (300, 264, 192, 136)])
 @pytest.mark.parametrize("b_mn", [False, True])
 def test_lowrank_product_against_fp32(M, N, K, R, b_mn):
     g = torch.Generator(device=DEV).manual_seed(M + R)
