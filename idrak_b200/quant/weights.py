@@ -233,6 +233,7 @@ def _fp8_product(x2, w: "Fp8Weight", transposed, bias, residual, act, out):
 
 
 # --------------------------------------------------------------------------- the op
+FEW_ROWS = 64           # up to this many rows (decode steps) the weight is unpacked first as well: see qgemm
 DENSE_ROWS = 512        # from this many activation rows on, the weight is unpacked to bf16 first and multiplied densely
 
 
@@ -258,9 +259,12 @@ def qgemm(x2: torch.Tensor, w, transposed: bool = False, bias=None, residual=Non
             y = y + residual.float()
         y = y.to(x2.dtype)
         return (y, aux) if aux is not None else y
-    if M >= DENSE_ROWS and x2.dtype == torch.bfloat16 and w.cols % 8 == 0 and x2.stride(0) % 8 == 0:
+    if ((M >= DENSE_ROWS or M <= FEW_ROWS) and x2.dtype == torch.bfloat16 and w.cols % 8 == 0
+            and x2.stride(0) % 8 == 0):
         # many rows: unpacking the weight once (a bandwidth-bound pass over it) and running the dense tensor-core GEMM
-        # beats unpacking inside the GEMM's producer warps, which is sized for decode-like row counts
+        # beats unpacking inside the GEMM's producer warps. Few rows (decoding): the same holds, measured at 64 rows of
+        # a 4096 x 4096 int8 weight 81 us in the unpacking GEMM against 13 us to unpack (the bf16 copy of one
+        # projection stays in L2) plus 17 us for the split-K product over it
         from ..ops.gemm import gemm
         return gemm(x2, dequantize_bf16(w), b_mn=not transposed, bias=bias, residual=residual, act=act, out=out)
     _bind()

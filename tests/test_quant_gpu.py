@@ -55,3 +55,16 @@ def test_many_rows_take_the_dense_path_and_agree_with_the_fused_kernel(monkeypat
     for y in (dense, fused):
         assert (y.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
     assert (dense.float() - fused.float()).abs().max().item() < 2e-2 * ref.abs().max().item()
+
+
+@pytest.mark.parametrize("cls", [Int8Weight, Int4Weight])
+def test_few_rows_unpack_first_and_agree_with_the_fused_kernel(cls, monkeypatch):
+    from idrak_b200.quant import weights
+    qw = cls.quantize(_rand((1024, 768), 0.05, 1).float())
+    x = _rand((16, 1024), 1.0, 2)
+    unpacked = qgemm(x, qw)
+    monkeypatch.setattr(weights, "FEW_ROWS", 0)
+    fused = qgemm(x, qw)
+    ref = x.float() @ qw.dequantize()
+    for y in (unpacked, fused):
+        assert (y.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item()
