@@ -88,6 +88,8 @@ _SIGNATURES = {
     "idrak_skinny_gemm": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p,
                                   c_void_p, c_int, c_int, c_float, c_void_p]),
     "idrak_skinny_splits": (c_int, [c_int, c_int]),
+    "idrak_skinny8_gemm": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                   c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "idrak_flash_fwd_ex": (c_int, [c_void_p] * 5 + [c_int] * 6 + [c_ll] * 7 + [c_float, c_int, c_int, c_void_p, c_float,
                                                                               c_void_p]),
     "idrak_gemm_lowrank": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p,

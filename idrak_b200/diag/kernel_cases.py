@@ -210,6 +210,20 @@ def case_skinny(a):
     return (lambda: skinny_linear(x, w, bias, res, gate, eps, out)), 2.0 * a.m * rows * a.k, 2.0 * rows * a.k
 
 
+def case_skinny8(a):
+    """The few-row product over int8 weights (--m <= 64, --n, --k; --epi gated for a stacked gate / up matrix): bytes
+    are the codes streamed once."""
+    from ..ops.skinny import skinny8_linear
+    from ..quant import Int8Weight
+    gate = "silu" if a.epi == "gated" else None
+    cols = 2 * a.n if gate else a.n
+    w8 = Int8Weight.quantize(torch.randn(a.k, cols, device="cuda") * a.k ** -0.5)
+    w8.kmajor()
+    x = torch.randn(a.m, a.k, device="cuda", dtype=torch.bfloat16)
+    out = torch.empty(a.m, a.n, device="cuda", dtype=torch.bfloat16)
+    return (lambda: skinny8_linear(x, w8, None, None, gate, out)), 2.0 * a.m * cols * a.k, 1.0 * cols * a.k
+
+
 def case_skinny_dense(a):
     """The same product on the dense GEMM with its split-K choice (what decode used before) for comparison."""
     from ..ops.gemm import gemm
@@ -261,7 +275,7 @@ def _role_timers(fn: Callable[[], None]) -> dict:
 CASES: Dict[str, Callable] = {
     "gemm": case_gemm, "gemm_wgrad": case_gemm_wgrad, "cublas": case_cublas, "flash_fwd": case_flash_fwd,
     "flash_bwd": case_flash_bwd, "xent": case_xent, "norm": case_norm, "norm_bwd": case_norm_bwd, "adamw": case_adamw,
-    "skinny": case_skinny, "skinny_dense": case_skinny_dense,
+    "skinny": case_skinny, "skinny8": case_skinny8, "skinny_dense": case_skinny_dense,
     "decode_attn": case_decode_attn, "qgemm": case_qgemm, "qdequant": case_qdequant,
 }
 

@@ -92,3 +92,51 @@ def few_row_linear(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
         out.copy_(y)
         return out
     return y
+
+
+def skinny8_reference(x, w8, bias=None, residual=None, gate: Optional[str] = None):
+    """fp32 statement of ``skinny8_linear``; ``w8`` is an ``Int8Weight`` ([in, out]; gated: out = [gate | up])."""
+    y = x.float() @ w8.dequantize().to(x.device)
+    if bias is not None:
+        y = y + bias.float()
+    if gate is not None:
+        g, u = y.chunk(2, -1)
+        act = {"silu": torch.nn.functional.silu, "swiglu": torch.nn.functional.silu, "relu": torch.relu, "reglu": torch.relu,
+               "gelu": lambda t: torch.nn.functional.gelu(t, approximate="tanh"),
+               "geglu": lambda t: torch.nn.functional.gelu(t, approximate="tanh")}[gate]
+        y = act(g) * u
+    if residual is not None:
+        y = y + residual.float()
+    return y.to(x.dtype)
+
+
+def skinny8_linear(x: torch.Tensor, w8, bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None,
+                   gate: Optional[str] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``x [M <= 64, K]`` times an int8 weight with one scale per output (``quant.Int8Weight``, ``[K, N]``) ->
+    ``[M, N]``; with ``gate`` the weight's outputs are ``[gate | up]`` and the result is ``act(gate) * up`` ``[M, N / 2]``.
+    The kernel reads the codes in their K-major copy (``Int8Weight.kmajor``) and expands them in shared memory."""
+    M, K = x.shape
+    n_out = w8.cols // 2 if gate is not None else w8.cols
+    if not (x.is_cuda and x.dtype == torch.bfloat16 and M <= 64 and K % 16 == 0 and K == w8.rows
+            and (gate is None or (gate in _KINDS and n_out % 8 == 0))):
+        res = skinny8_reference(x, w8, bias, residual, gate)
+        if out is not None:
+            out.copy_(res)
+            return out
+        return res
+    from ._util import ptr, stream_ptr
+    codes = w8.kmajor()
+    x = x if x.stride(1) == 1 and x.stride(0) % 8 == 0 else x.contiguous()
+    if out is None:
+        out = torch.empty((M, n_out), dtype=torch.bfloat16, device=x.device)
+    assert out.dtype == torch.bfloat16 and out.shape == (M, n_out) and out.stride(1) == 1
+    if bias is not None:
+        assert bias.dtype == torch.bfloat16 and bias.numel() == w8.cols
+    if residual is not None:
+        assert residual.dtype == torch.bfloat16 and residual.shape == (M, n_out) and residual.stride(1) == 1
+    rc = _native.lib().idrak_skinny8_gemm(x.data_ptr(), x.stride(0), codes.data_ptr(), codes.stride(0), w8.scales.data_ptr(),
+                                          out.data_ptr(), out.stride(0), M, n_out, K, ptr(bias), ptr(residual),
+                                          residual.stride(0) if residual is not None else 0,
+                                          _KINDS[gate] if gate is not None else -1, stream_ptr())
+    _native.check(rc, "idrak_skinny8_gemm")
+    return out

@@ -75,6 +75,17 @@ class Int8Weight:
     def to(self, device) -> "Int8Weight":
         return Int8Weight(self.codes.to(device), self.scales.to(device), self.rows, self.cols)
 
+    def kmajor(self) -> torch.Tensor:
+        """The codes transposed to ``[out, in]`` with the input index contiguous (rows padded to 16 bytes): what the
+        few-row decode kernel streams. Made on first use and kept (it doubles the weight's code bytes)."""
+        t = getattr(self, "_kmajor", None)
+        if t is None or t.device != self.codes.device:
+            kp = (self.rows + 15) // 16 * 16
+            t = torch.zeros((self.cols, kp), dtype=torch.int8, device=self.codes.device)
+            t[:, : self.rows] = self.codes[:, : self.cols].t()
+            self._kmajor = t
+        return t
+
     @property
     def ld(self) -> int:
         return self.codes.stride(0)
@@ -233,6 +244,7 @@ def _fp8_product(x2, w: "Fp8Weight", transposed, bias, residual, act, out):
 
 
 # --------------------------------------------------------------------------- the op
+FEW_ROW_INT8_KERNEL = True   # int8 weights, few rows: the few-row kernel that reads the codes directly (csrc/skinny8_gemm.cu)
 FEW_ROWS = 64           # up to this many rows (decode steps) the weight is unpacked first as well: see qgemm
 DENSE_ROWS = 512        # from this many activation rows on, the weight is unpacked to bf16 first and multiplied densely
 
@@ -259,6 +271,13 @@ def qgemm(x2: torch.Tensor, w, transposed: bool = False, bias=None, residual=Non
             y = y + residual.float()
         y = y.to(x2.dtype)
         return (y, aux) if aux is not None else y
+    if (M <= FEW_ROWS and isinstance(w, Int8Weight) and not transposed and act is None and x2.is_cuda
+            and x2.dtype == torch.bfloat16 and K % 16 == 0 and x2.stride(0) % 8 == 0 and FEW_ROW_INT8_KERNEL
+            and _native.has("idrak_skinny8_gemm")):
+        # decode steps over int8 weights: the codes are streamed once (half the bytes of bf16) and expanded to bf16
+        # operand tiles inside the few-row kernel
+        from ..ops.skinny import skinny8_linear
+        return skinny8_linear(x2, w, bias, residual, out=out)
     if ((M >= DENSE_ROWS or M <= FEW_ROWS) and x2.dtype == torch.bfloat16 and w.cols % 8 == 0
             and x2.stride(0) % 8 == 0):
         # many rows: unpacking the weight once (a bandwidth-bound pass over it) and running the dense tensor-core GEMM
