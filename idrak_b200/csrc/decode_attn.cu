@@ -138,17 +138,21 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
   for (int t = t0 + warp; t < t1; t += kDecWarps) {
     const int key0 = t * kDecTile;
     // ---- stage 32 keys x D of K and V with asynchronous 16-byte copies (all in flight at once)
+    // lane r looks up the cache slot of key row r once (one division and one table read per lane and tile); the copy
+    // loops below fetch a row's slot by shuffle, so a 16-byte copy costs a shuffle and a multiply-add, not a division,
+    // a remainder and a table read
+    int my_slot = -1;
+    {
+      const int pos = key0 + lane;
+      if (pos < len) my_slot = table[pos / p.block_size] * p.block_size + pos % p.block_size;
+    }
     if (!KV8) {
 #pragma unroll 4
       for (int i = lane; i < kDecTile * kChunks; i += 32) {
-        const int r = i / kChunks, c = i - r * kChunks;
-        const int pos = key0 + r;
-        const bool live = pos < len;
-        size_t off = 0;
-        if (live) {
-          const int blk = table[pos / p.block_size];
-          off = (size_t(blk) * p.block_size + pos % p.block_size) * tok_stride + size_t(kvh) * D + c * 8;
-        }
+        const int r = i / kChunks, c = i - r * kChunks;              // kChunks is a power of two: shifts
+        const int slot = __shfl_sync(0xffffffffu, my_slot, r);
+        const bool live = slot >= 0;
+        const size_t off = live ? size_t(slot) * tok_stride + size_t(kvh) * D + c * 8 : 0;
         cp_async16(sk + r * kRow + c * 16, p.k_cache + off, live ? 16 : 0);
         cp_async16(sv + r * kRow + c * 16, p.v_cache + off, live ? 16 : 0);
       }
@@ -161,25 +165,17 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
 #pragma unroll 4
       for (int i = lane; i < kDecTile * kByteChunks; i += 32) {
         const int r = i / kByteChunks, c = i - r * kByteChunks;
-        const int pos = key0 + r;
-        const bool live = pos < len;
-        size_t off = 0;
-        if (live) {
-          const int blk = table[pos / p.block_size];
-          off = (size_t(blk) * p.block_size + pos % p.block_size) * tok_stride + size_t(kvh) * D + c * 16;
-        }
+        const int slot = __shfl_sync(0xffffffffu, my_slot, r);
+        const bool live = slot >= 0;
+        const size_t off = live ? size_t(slot) * tok_stride + size_t(kvh) * D + c * 16 : 0;
         cp_async16(sk + r * kRow + D + c * 16, kc + off, live ? 16 : 0);
         cp_async16(sv + r * kRow + D + c * 16, vc + off, live ? 16 : 0);
       }
       // this lane's row: its slot's scales (0 for a key past the end: the codes are zeros there anyway)
       float ks = 0.f, vs = 0.f;
-      {
-        const int pos = key0 + lane;
-        if (pos < len) {
-          const size_t slot = size_t(table[pos / p.block_size]) * p.block_size + pos % p.block_size;
-          ks = p.k_scale[slot * p.Hkv + kvh];
-          vs = p.v_scale[slot * p.Hkv + kvh];
-        }
+      if (my_slot >= 0) {
+        ks = p.k_scale[size_t(my_slot) * p.Hkv + kvh];
+        vs = p.v_scale[size_t(my_slot) * p.Hkv + kvh];
       }
       cp_async_wait_all();
       __syncwarp();
