@@ -67,6 +67,9 @@ __device__ __forceinline__ void cp_async16(void* smem_dst, const void* gmem_src,
                : "memory");
 }
 __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+// wait until at most one of this thread's committed groups is still in flight (groups complete in order)
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
 
 // 16 int8 codes times a scale -> 16 bf16 values (two 16-byte words)
 __device__ __forceinline__ void dequant16(const uint4& raw, float scale, uint4& lo, uint4& hi) {
@@ -135,28 +138,40 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
   const size_t tok_stride = size_t(p.Hkv) * D;
   const int* table = p.block_table + size_t(seq) * p.max_blocks;
 
+  // lane r looks up the cache slot of key row r of a tile once (one division and one table read per lane and tile);
+  // the copy loops fetch a row's slot by shuffle, so a 16-byte copy costs a shuffle and a multiply-add, not a
+  // division, a remainder and a table read
+  auto slot_of = [&](int tile) {
+    const int pos = tile * kDecTile + lane;
+    return (tile < t1 && pos < len) ? table[pos / p.block_size] * p.block_size + pos % p.block_size : -1;
+  };
+  // one 32-key tile of K or V (bf16 cache) into a warp's buffer, one commit group
+  auto copy_rows = [&](uint8_t* dst, const __nv_bfloat16* cache, int slots) {
+#pragma unroll 4
+    for (int i = lane; i < kDecTile * kChunks; i += 32) {
+      const int r = i / kChunks, c = i - r * kChunks;                // kChunks is a power of two: shifts
+      const int slot = __shfl_sync(0xffffffffu, slots, r);
+      const bool live = slot >= 0;
+      const size_t off = live ? size_t(slot) * tok_stride + size_t(kvh) * D + c * 8 : 0;
+      cp_async16(dst + r * kRow + c * 16, cache + off, live ? 16 : 0);
+    }
+    cp_async_commit();
+  };
+  // bf16 cache: the copies run one step ahead of the arithmetic inside the warp's single pair of buffers - the keys of
+  // the next tile are requested as soon as Q K^T of this tile has read its keys (they fly during the softmax and P V),
+  // the values of the next tile once P V has read its values (they fly during the next Q K^T and softmax)
+  int next_slots = -1;
+  if (!KV8 && t0 + warp < t1) {
+    next_slots = slot_of(t0 + warp);
+    copy_rows(sk, p.k_cache, next_slots);
+    copy_rows(sv, p.v_cache, next_slots);
+  }
+
   for (int t = t0 + warp; t < t1; t += kDecWarps) {
     const int key0 = t * kDecTile;
-    // ---- stage 32 keys x D of K and V with asynchronous 16-byte copies (all in flight at once)
-    // lane r looks up the cache slot of key row r once (one division and one table read per lane and tile); the copy
-    // loops below fetch a row's slot by shuffle, so a 16-byte copy costs a shuffle and a multiply-add, not a division,
-    // a remainder and a table read
-    int my_slot = -1;
-    {
-      const int pos = key0 + lane;
-      if (pos < len) my_slot = table[pos / p.block_size] * p.block_size + pos % p.block_size;
-    }
+    int my_slot = KV8 ? slot_of(t) : next_slots;
     if (!KV8) {
-#pragma unroll 4
-      for (int i = lane; i < kDecTile * kChunks; i += 32) {
-        const int r = i / kChunks, c = i - r * kChunks;              // kChunks is a power of two: shifts
-        const int slot = __shfl_sync(0xffffffffu, my_slot, r);
-        const bool live = slot >= 0;
-        const size_t off = live ? size_t(slot) * tok_stride + size_t(kvh) * D + c * 8 : 0;
-        cp_async16(sk + r * kRow + c * 16, p.k_cache + off, live ? 16 : 0);
-        cp_async16(sv + r * kRow + c * 16, p.v_cache + off, live ? 16 : 0);
-      }
-      cp_async_wait_all();
+      cp_async_wait_but_one();                           // this tile's keys have landed; its values may still fly
       __syncwarp();
     } else {
       constexpr int kByteChunks = D / 16;                  // 16-byte chunks of int8 codes per key row
@@ -210,6 +225,11 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
         mma_bf16_16816(s[n], qa[ks + 1], kb[2], kb[3]);
       }
     }
+    if (!KV8) {
+      __syncwarp();                                      // every lane has read this tile's keys
+      next_slots = slot_of(t + kDecWarps);
+      copy_rows(sk, p.k_cache, next_slots);              // (an empty group when there is no next tile)
+    }
     // ---- mask, online softmax (log2 domain) for rows r0 = lane / 4 and r0 + 8
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -254,6 +274,10 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
     m1 = mn1;
 #pragma unroll
     for (int n = 0; n < NT; ++n) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
+    if (!KV8) {
+      cp_async_wait_but_one();                           // this tile's values have landed; the next keys may still fly
+      __syncwarp();
+    }
     // ---- O[16 x D] += P[16 x 32] · V[32 x D]: V is [key][d], so its B fragments come through transposing loads
 #pragma unroll
     for (int kk = 0; kk < 2; ++kk) {
@@ -267,7 +291,9 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
       }
     }
     __syncwarp();
+    if (!KV8) copy_rows(sv, p.v_cache, next_slots);      // every lane has read this tile's values
   }
+  cp_async_wait_all();
 
   // ---- combine the 4 warps of the CTA (in warp order), then write the split's partial or the final output
   // smerge layout: [warp][16][D + 2], over the tiles: nobody may still be reading a tile
