@@ -160,54 +160,55 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
   // bf16 cache: the copies run one step ahead of the arithmetic inside the warp's single pair of buffers - the keys of
   // the next tile are requested as soon as Q K^T of this tile has read its keys (they fly during the softmax and P V),
   // the values of the next tile once P V has read its values (they fly during the next Q K^T and softmax)
+  // int8 cache: the same, with the codes of a tile staged in the upper half of each row and expanded in place by the
+  // lane that owns the row once they have landed
+  constexpr int kByteChunks = D / 16;                    // 16-byte chunks of int8 codes per key row
+  auto copy_codes = [&](uint8_t* dst, const __nv_bfloat16* cache, int slots) {
+    const int8_t* codes = reinterpret_cast<const int8_t*>(cache);
+#pragma unroll 4
+    for (int i = lane; i < kDecTile * kByteChunks; i += 32) {
+      const int r = i / kByteChunks, c = i - r * kByteChunks;
+      const int slot = __shfl_sync(0xffffffffu, slots, r);
+      const bool live = slot >= 0;
+      const size_t off = live ? size_t(slot) * tok_stride + size_t(kvh) * D + c * 16 : 0;
+      cp_async16(dst + r * kRow + D + c * 16, codes + off, live ? 16 : 0);
+    }
+    cp_async_commit();
+  };
+  auto expand_row = [&](uint8_t* row, float scale) {     // this lane's row: codes -> bf16, front to back
+#pragma unroll
+    for (int c = 0; c < kByteChunks; ++c) {
+      const uint4 codes = *reinterpret_cast<const uint4*>(row + D + c * 16);
+      uint4 lo, hi;
+      dequant16(codes, scale, lo, hi);
+      *reinterpret_cast<uint4*>(row + c * 32) = lo;
+      *reinterpret_cast<uint4*>(row + c * 32 + 16) = hi;
+    }
+  };
   int next_slots = -1;
-  if (!KV8 && t0 + warp < t1) {
+  if (t0 + warp < t1) {
     next_slots = slot_of(t0 + warp);
-    copy_rows(sk, p.k_cache, next_slots);
-    copy_rows(sv, p.v_cache, next_slots);
+    if (!KV8) {
+      copy_rows(sk, p.k_cache, next_slots);
+      copy_rows(sv, p.v_cache, next_slots);
+    } else {
+      copy_codes(sk, p.k_cache, next_slots);
+      copy_codes(sv, p.v_cache, next_slots);
+    }
   }
 
   for (int t = t0 + warp; t < t1; t += kDecWarps) {
     const int key0 = t * kDecTile;
-    int my_slot = KV8 ? slot_of(t) : next_slots;
-    if (!KV8) {
-      cp_async_wait_but_one();                           // this tile's keys have landed; its values may still fly
-      __syncwarp();
-    } else {
-      constexpr int kByteChunks = D / 16;                  // 16-byte chunks of int8 codes per key row
-      const int8_t* kc = reinterpret_cast<const int8_t*>(p.k_cache);
-      const int8_t* vc = reinterpret_cast<const int8_t*>(p.v_cache);
-#pragma unroll 4
-      for (int i = lane; i < kDecTile * kByteChunks; i += 32) {
-        const int r = i / kByteChunks, c = i - r * kByteChunks;
-        const int slot = __shfl_sync(0xffffffffu, my_slot, r);
-        const bool live = slot >= 0;
-        const size_t off = live ? size_t(slot) * tok_stride + size_t(kvh) * D + c * 16 : 0;
-        cp_async16(sk + r * kRow + D + c * 16, kc + off, live ? 16 : 0);
-        cp_async16(sv + r * kRow + D + c * 16, vc + off, live ? 16 : 0);
-      }
-      // this lane's row: its slot's scales (0 for a key past the end: the codes are zeros there anyway)
-      float ks = 0.f, vs = 0.f;
-      if (my_slot >= 0) {
-        ks = p.k_scale[size_t(my_slot) * p.Hkv + kvh];
-        vs = p.v_scale[size_t(my_slot) * p.Hkv + kvh];
-      }
-      cp_async_wait_all();
-      __syncwarp();
-      uint8_t* rk = sk + lane * kRow;
-      uint8_t* rv = sv + lane * kRow;
-#pragma unroll
-      for (int c = 0; c < kByteChunks; ++c) {
-        const uint4 ck = *reinterpret_cast<const uint4*>(rk + D + c * 16);
-        const uint4 cv = *reinterpret_cast<const uint4*>(rv + D + c * 16);
-        uint4 lo, hi;
-        dequant16(ck, ks, lo, hi);
-        *reinterpret_cast<uint4*>(rk + c * 32) = lo;
-        *reinterpret_cast<uint4*>(rk + c * 32 + 16) = hi;
-        dequant16(cv, vs, lo, hi);
-        *reinterpret_cast<uint4*>(rv + c * 32) = lo;
-        *reinterpret_cast<uint4*>(rv + c * 32 + 16) = hi;
-      }
+    // int8 cache: this lane's row scales (0 for a key past the end: the codes are zeros there anyway)
+    float ks = 0.f, vs = 0.f;
+    if (KV8 && next_slots >= 0) {
+      ks = p.k_scale[size_t(next_slots) * p.Hkv + kvh];
+      vs = p.v_scale[size_t(next_slots) * p.Hkv + kvh];
+    }
+    cp_async_wait_but_one();                             // this tile's keys have landed; its values may still fly
+    __syncwarp();
+    if (KV8) {
+      expand_row(sk + lane * kRow, ks);
       __syncwarp();
     }
     // ---- S[16 x 32] = Q · K^T: 4 n-tiles of 8 keys
@@ -225,11 +226,10 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
         mma_bf16_16816(s[n], qa[ks + 1], kb[2], kb[3]);
       }
     }
-    if (!KV8) {
-      __syncwarp();                                      // every lane has read this tile's keys
-      next_slots = slot_of(t + kDecWarps);
-      copy_rows(sk, p.k_cache, next_slots);              // (an empty group when there is no next tile)
-    }
+    __syncwarp();                                        // every lane has read this tile's keys
+    next_slots = slot_of(t + kDecWarps);
+    if (!KV8) copy_rows(sk, p.k_cache, next_slots);      // (an empty group when there is no next tile)
+    else copy_codes(sk, p.k_cache, next_slots);
     // ---- mask, online softmax (log2 domain) for rows r0 = lane / 4 and r0 + 8
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
@@ -274,8 +274,10 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
     m1 = mn1;
 #pragma unroll
     for (int n = 0; n < NT; ++n) { o[n][0] *= a0; o[n][1] *= a0; o[n][2] *= a1; o[n][3] *= a1; }
-    if (!KV8) {
-      cp_async_wait_but_one();                           // this tile's values have landed; the next keys may still fly
+    cp_async_wait_but_one();                             // this tile's values have landed; the next keys may still fly
+    __syncwarp();
+    if (KV8) {
+      expand_row(sv + lane * kRow, vs);
       __syncwarp();
     }
     // ---- O[16 x D] += P[16 x 32] · V[32 x D]: V is [key][d], so its B fragments come through transposing loads
@@ -292,6 +294,7 @@ __global__ void __launch_bounds__(kDecWarps * 32) paged_decode_kernel(const Deco
     }
     __syncwarp();
     if (!KV8) copy_rows(sv, p.v_cache, next_slots);      // every lane has read this tile's values
+    else copy_codes(sv, p.v_cache, next_slots);
   }
   cp_async_wait_all();
 
