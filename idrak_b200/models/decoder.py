@@ -395,7 +395,11 @@ class Decoder(nn.Module):
                     normal_(blk.mlp.shared_gate, std)
 
     # ------------------------------------------------------------------ forward
-    def hidden(self, ids: torch.Tensor, positions: Optional[torch.Tensor] = None, spans=None) -> torch.Tensor:
+    def hidden(self, ids: torch.Tensor, positions: Optional[torch.Tensor] = None, spans=None,
+               embeds=None) -> torch.Tensor:
+        """Final hidden states. ``embeds``: ``(mask [B, S] bool, values [n, dim])`` - the rows of the token embedding at
+        the masked positions are replaced by ``values`` in order (image or audio features projected into the model's
+        width: the prefix a vision-language front end puts before the text)."""
         spec = self.spec
         B, S = ids.shape
         if self.pos is not None and positions is None:
@@ -406,6 +410,12 @@ class Decoder(nn.Module):
                 x = x + self.pos[positions.reshape(B, S).long()]
         if spec.embedding_scale is not None:
             x = x * spec.embedding_scale
+        if embeds is not None:
+            mask, values = embeds
+            if int(mask.sum()) != values.shape[0]:
+                raise ValueError(f"{int(mask.sum())} positions are marked for replacement but {values.shape[0]} rows were given")
+            x = x.clone()
+            x[mask] = values.to(x.dtype)
         if spec.dropout > 0 and self.training:
             x = torch.nn.functional.dropout(x, spec.dropout, True)
         if spans is not None and not torch.is_tensor(spans):
@@ -421,11 +431,11 @@ class Decoder(nn.Module):
     def head_weight(self) -> torch.Tensor:
         return self.embed if self.head is None else self.head
 
-    def forward(self, ids: torch.Tensor, positions: Optional[torch.Tensor] = None, spans=None) -> torch.Tensor:
+    def forward(self, ids: torch.Tensor, positions: Optional[torch.Tensor] = None, spans=None, embeds=None) -> torch.Tensor:
         """Logits ``[B, S, vocabulary]``. ``spans``: ``[(lo, hi), ...]`` token ranges of the sequences packed back to
         back into every row; attention stays inside each range (one kernel launch per layer: each position carries
         the start of its own sequence as a lower bound on the keys it sees)."""
-        h = self.hidden(ids, positions, spans)
+        h = self.hidden(ids, positions, spans, embeds)
         logits = ops.linear(h, self.head_weight(), self.head_bias)[..., : self.spec.vocabulary]
         if self.spec.logit_softcap:
             c = self.spec.logit_softcap
@@ -433,9 +443,9 @@ class Decoder(nn.Module):
         return logits
 
     def loss(self, ids: torch.Tensor, targets: torch.Tensor, positions: Optional[torch.Tensor] = None,
-             ignore_index: Optional[int] = None, spans=None) -> torch.Tensor:
+             ignore_index: Optional[int] = None, spans=None, embeds=None) -> torch.Tensor:
         """Mean next-token cross-entropy; the logits matrix is never materialised beyond one row chunk."""
-        h = self.hidden(ids, positions, spans)
+        h = self.hidden(ids, positions, spans, embeds)
         if self.spec.logit_softcap or self.head_bias is not None:
             logits = self.forward_from_hidden(h)
             return torch.nn.functional.cross_entropy(
