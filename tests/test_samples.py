@@ -108,3 +108,14 @@ def test_text_generation_sample_continues_the_grammar_and_the_paths_agree():
 def test_vision_sample_detects_and_segments_the_shapes():
     out = _load("idrak_vision").main(steps=120, quiet=True)
     assert out["map50"] > 0.8 and out["miou"] > 0.9
+
+
+def test_whisper_speech_sample_runs_the_whole_pipeline(tmp_path):
+    from idrak_b200.audio.flac import write_flac
+    mod = _load("whisper_speech")
+    out = mod.main(quiet=True)
+    assert out["features"] == (1, 80, 3000) and len(out["tokens"]) <= 32
+    path = tmp_path / "tone.flac"
+    write_flac(str(path), mod.synthetic_recording(1.0, 16000), 16000)
+    again = mod.main(audio=str(path), quiet=True)
+    assert again["features"] == (1, 80, 3000)
