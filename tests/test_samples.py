@@ -119,3 +119,13 @@ def test_whisper_speech_sample_runs_the_whole_pipeline(tmp_path):
     write_flac(str(path), mod.synthetic_recording(1.0, 16000), 16000)
     again = mod.main(audio=str(path), quiet=True)
     assert again["features"] == (1, 80, 3000)
+
+
+def test_chat_sample_info_chat_and_profile():
+    mod = _load("chat")
+    described = mod.main("info", quiet=True)
+    assert described["layers"] == 2 and described["kv_heads"] == 2 and described["parameters"] > 50_000
+    talked = mod.main("chat", message="hello", quiet=True)
+    assert len(talked["replies"]) == 1 and talked["messages"][-1]["role"] == "assistant"
+    timed = mod.main("profile", quiet=True)
+    assert timed["prompt_tokens"] > 50 and timed["decode_tokens_per_s"] > 0
