@@ -71,6 +71,11 @@ __device__ __forceinline__ float s8_ld_cluster(uint32_t addr) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
   return v;
 }
+__device__ __forceinline__ float4 s8_ld_cluster4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ void s8_cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -267,12 +272,23 @@ skinny8_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_consta
   if (warp >= 2) {
     const int t = threadIdx.x - 64;
     const uint32_t part_addr = smem_u32(part);
-    for (int idx = t; idx < S * NT; idx += 128) {
-      const int m = idx / S, fl = idx - m * S;
-      const uint32_t off = uint32_t((m * kS8Feat + rank * S + fl) * 4);
-      float a = 0.f;
-      for (int r = 0; r < csize; ++r) a += s8_ld_cluster(s8_map_rank(part_addr + off, r));
-      red[m * S + fl] = a;
+    // sum the cluster's partial tiles over this CTA's S rows, ranks in order, four features per 16-byte remote load
+    uint32_t peer[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) peer[r] = r < csize ? s8_map_rank(part_addr, r) : 0u;
+    const int S4 = S >> 2;                             // S is 16, 32, 64 or 128
+    for (int idx = t; idx < S4 * NT; idx += 128) {
+      const int m = idx / S4, f4 = idx - m * S4;
+      const uint32_t off = uint32_t((m * kS8Feat + rank * S + f4 * 4) * 4);
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < csize) {
+          const float4 v = s8_ld_cluster4(peer[r] + off);
+          a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+      }
+      *reinterpret_cast<float4*>(red + m * S + f4 * 4) = a;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const int outs = gated ? S / 2 : S;

@@ -79,6 +79,11 @@ __device__ __forceinline__ float sk_ld_cluster(uint32_t addr) {
   asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(addr));
   return v;
 }
+__device__ __forceinline__ float4 sk_ld_cluster4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+  return v;
+}
 __device__ __forceinline__ void sk_cluster_sync() {
   asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
   asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
@@ -264,13 +269,23 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
       for (int r = 0; r < csize; ++r) a += sk_ld_cluster(sk_map_rank(ssp_addr + t * 4, r));
       ss[t] = rsqrtf(a / float(p.K) + p.norm_eps);
     }
-    // sum the cluster's partial tiles over this CTA's S rows, ranks in order
-    for (int idx = t; idx < S * NT; idx += 128) {
-      const int m = idx / S, fl = idx - m * S;
-      const uint32_t off = uint32_t((m * kSkFeat + rank * S + fl) * 4);
-      float a = 0.f;
-      for (int r = 0; r < csize; ++r) a += sk_ld_cluster(sk_map_rank(part_addr + off, r));
-      red[m * S + fl] = a;
+    // sum the cluster's partial tiles over this CTA's S rows, ranks in order, four features per 16-byte remote load
+    uint32_t peer[8];
+#pragma unroll
+    for (int r = 0; r < 8; ++r) peer[r] = r < csize ? sk_map_rank(part_addr, r) : 0u;
+    const int S4 = S >> 2;                             // S is 16, 32, 64 or 128
+    for (int idx = t; idx < S4 * NT; idx += 128) {
+      const int m = idx / S4, f4 = idx - m * S4;
+      const uint32_t off = uint32_t((m * kSkFeat + rank * S + f4 * 4) * 4);
+      float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int r = 0; r < 8; ++r) {
+        if (r < csize) {
+          const float4 v = sk_ld_cluster4(peer[r] + off);
+          a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+        }
+      }
+      *reinterpret_cast<float4*>(red + m * S + f4 * 4) = a;
     }
     asm volatile("bar.sync 1, 128;" ::: "memory");
     const int outs = gated ? S / 2 : S;              // output features of this slice
