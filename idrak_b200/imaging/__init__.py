@@ -5,6 +5,7 @@ from .codecs import ImageFormatError, decode, decode_bmp, decode_png, decode_pnm
 from .effects import EFFECTS, PixelPass, apply, pixel_pass, random_pipeline
 from .jpeg import decode_jpeg
 from .font import FontError, TrueTypeFont, render_text
+from .shaping import base_direction, layout_line, shape_arabic, visual_order
 from .layout import Page, WordBox, compose_page, wrap
 from .raster import Path, coverage_reference, ellipse, rasterize, rect, supersample_reference
 from .resample import FILTERS, resize, taps

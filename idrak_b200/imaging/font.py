@@ -227,12 +227,22 @@ class TrueTypeFont:
                 break
 
     # ------------------------------------------------------------------ layout
-    def layout(self, text: str, size: float, kerning: bool = True) -> List[Tuple[int, float]]:
-        """(glyph id, pen x in pixels) per character, left to right on one line."""
+    def layout(self, text: str, size: float, kerning: bool = True, shape: bool = True) -> List[Tuple[int, float]]:
+        """(glyph id, pen x in pixels) per character, left to right on one line. A line with right-to-left
+        characters is shaped (Arabic contextual forms) and put into drawing order first (``imaging/shaping.py``);
+        a presentation form the font has no glyph for falls back to its base letter."""
         scale = size / self.units_per_em
         pen, prev, out = 0.0, None, []
+        if shape and any("\u0590" <= ch <= "\u08ff" or "\ufb1d" <= ch <= "\ufefc" for ch in text):
+            from .shaping import layout_line
+            text = layout_line(text)
         for ch in text:
             gid = self.glyph_index(ord(ch))
+            if gid == 0 and "\ufe70" <= ch <= "\ufefc":
+                import unicodedata
+                base = unicodedata.decomposition(ch).split()[1:]
+                if len(base) == 1:
+                    gid = self.glyph_index(int(base[0], 16))
             if kerning and prev is not None:
                 pen += self.kerning(prev, gid) * scale
             out.append((gid, pen))
