@@ -129,3 +129,14 @@ def test_chat_sample_info_chat_and_profile():
     assert len(talked["replies"]) == 1 and talked["messages"][-1]["role"] == "assistant"
     timed = mod.main("profile", quiet=True)
     assert timed["prompt_tokens"] > 50 and timed["decode_tokens_per_s"] > 0
+
+
+def test_tts_sample_trains_and_writes_a_recording(tmp_path):
+    from idrak_b200.audio import read_wav
+    mod = _load("tts_vits")
+    path = tmp_path / "said.wav"
+    out = mod.main(text="bead", out=str(path), steps=12, quiet=True)
+    first, last = out["history"][0], out["history"][-1]
+    assert last["kl"] + last["duration"] < first["kl"] + first["duration"]
+    samples, rate = read_wav(str(path))
+    assert rate == 8000 and samples.shape[-1] == out["samples"] and out["samples"] >= 4 * 32
