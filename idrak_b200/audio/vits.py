@@ -14,12 +14,15 @@ Parts, all channels-first ``[B, C, T]``:
   prior (dynamic programme over the frames, batched over sequences and tokens);
 * ``Vits.synthesize`` (text -> waveform) and ``Vits.training_losses`` (alignment, duration loss, KL divergence between
   posterior and flowed prior, generated segment for the spectral and adversarial losses);
+* ``Vits.convert_voice`` (a recording re-voiced through the flow under another speaker) with ``ReferenceEncoder``
+  (a speaker embedding from any recording's spectrogram: the tone-colour half of voice cloning);
 * ``Discriminators`` (multi-period + one multi-scale branch) with the least-squares adversarial and feature-matching
   losses.
 
 Weights load from the Hugging Face ``VitsModel`` layout (weight-normalised convolutions are folded on load); with the
-sampling noise off, ``synthesize`` reproduces that implementation's waveform (``tests/test_vits.py``). The stochastic
-duration predictor of some published checkpoints is not part of this module: such a checkpoint is refused on load.
+sampling noise off, ``synthesize`` reproduces that implementation's waveform (``tests/test_vits.py``), with either
+duration model: the deterministic ``DurationPredictor`` or the ``StochasticDurationPredictor`` (a spline flow sampled
+backwards for synthesis and trained forwards by a variational bound) that the published checkpoints use.
 On CUDA the 1-D convolutions run on this package's convolution kernels (``nn/layers.py: Conv1d``).
 
 Reference: the speech trainer's TTS / adversarial VITS modes and the VITS plugin (src/Idrak.Audio, src/Idrak.Plugins).
@@ -68,6 +71,13 @@ class VitsSpec:
     speaking_rate: float = 1.0
     sampling_rate: int = 16000
     bias: bool = True
+    stochastic_duration: bool = False
+    duration_flows: int = 4
+    duration_flow_bins: int = 10
+    duration_tail_bound: float = 5.0
+    duration_stack_layers: int = 3
+    duration_dropout: float = 0.5
+    noise_scale_duration: float = 0.8
 
     @property
     def hop(self) -> int:
@@ -76,10 +86,15 @@ class VitsSpec:
     @classmethod
     def from_hf(cls, c: Dict) -> "VitsSpec":
         """From the keys of a Hugging Face ``VitsConfig`` (a dict, e.g. the parsed ``config.json``)."""
-        if c.get("use_stochastic_duration_prediction", True):
-            raise ValueError("this checkpoint uses the stochastic duration predictor, which is not implemented here")
         g = c.get
-        return cls(vocab_size=g("vocab_size", 38), hidden=g("hidden_size", 192), layers=g("num_hidden_layers", 6),
+        if g("depth_separable_channels", 2) != 2:
+            raise ValueError("the stochastic duration predictor here carries two channels (duration and its companion)")
+        return cls(stochastic_duration=g("use_stochastic_duration_prediction", True),
+                   duration_flows=g("duration_predictor_num_flows", 4), duration_flow_bins=g("duration_predictor_flow_bins", 10),
+                   duration_tail_bound=g("duration_predictor_tail_bound", 5.0),
+                   duration_stack_layers=g("depth_separable_num_layers", 3),
+                   duration_dropout=g("duration_predictor_dropout", 0.5), noise_scale_duration=g("noise_scale_duration", 0.8),
+                   vocab_size=g("vocab_size", 38), hidden=g("hidden_size", 192), layers=g("num_hidden_layers", 6),
                    heads=g("num_attention_heads", 2), window=g("window_size", 4), ffn=g("ffn_dim", 768),
                    ffn_kernel=g("ffn_kernel_size", 3), flow_size=g("flow_size", 192),
                    spectrogram_bins=g("spectrogram_bins", 513),
@@ -302,6 +317,165 @@ class DurationPredictor(nn.Module):
         return self.proj(x * mask) * mask
 
 
+
+# ------------------------------------------------------------------------------------- stochastic duration predictor
+def rational_quadratic_spline(x: torch.Tensor, width_logits: torch.Tensor, height_logits: torch.Tensor,
+                              slope_logits: torch.Tensor, inverse: bool = False, bound: float = 5.0,
+                              min_width: float = 1e-3, min_height: float = 1e-3, min_slope: float = 1e-3):
+    """Monotone piecewise rational-quadratic map of ``[-bound, bound]`` onto itself (Durkan et al., neural spline
+    flows), the identity outside. ``width_logits`` / ``height_logits`` ``[..., K]`` give the K bins, ``slope_logits``
+    ``[..., K - 1]`` the derivatives at the inner knots (1 at both ends). Returns the mapped values and the log of the
+    derivative of the forward map at them (of the inverse map's input when ``inverse``: negate for its own)."""
+    K = width_logits.shape[-1]
+    inside = (x >= -bound) & (x <= bound)
+    xc = x.clamp(-bound, bound)
+
+    def knots(logits, floor):
+        sizes = floor + (1 - floor * K) * logits.softmax(-1)
+        edges = F.pad(sizes.cumsum(-1), (1, 0)) * 2 * bound - bound
+        edges = torch.cat([edges[..., :1] * 0 - bound, edges[..., 1:-1], edges[..., -1:] * 0 + bound], -1)
+        return edges, edges[..., 1:] - edges[..., :-1]
+
+    xk, w = knots(width_logits, min_width)
+    yk, h = knots(height_logits, min_height)
+    end = math.log(math.exp(1 - min_slope) - 1)                                   # softplus^-1(1 - min_slope)
+    d = min_slope + F.softplus(F.pad(slope_logits, (1, 1), value=end))
+    search = (yk if inverse else xk).clone()
+    search[..., -1] += 1e-6
+    k = ((xc[..., None] >= search).sum(-1) - 1).clamp(0, K - 1)[..., None]
+    pick = lambda t: t.gather(-1, k)[..., 0]
+    x0, w0, y0, h0 = pick(xk), pick(w), pick(yk), pick(h)
+    s = h0 / w0
+    d0, d1 = pick(d), pick(d[..., 1:])
+    bend = d0 + d1 - 2 * s
+    if not inverse:
+        t = (xc - x0) / w0
+        tt = t * (1 - t)
+        den = s + bend * tt
+        y = y0 + h0 * (s * t * t + d0 * tt) / den
+        logdet = torch.log(s * s * (d1 * t * t + 2 * s * tt + d0 * (1 - t) ** 2)) - 2 * torch.log(den)
+    else:
+        dy = xc - y0
+        a = h0 * (s - d0) + dy * bend
+        b = h0 * d0 - dy * bend
+        c = -s * dy
+        t = 2 * c / (-b - torch.sqrt((b * b - 4 * a * c).clamp_min(0)))
+        tt = t * (1 - t)
+        den = s + bend * tt
+        y = t * w0 + x0
+        logdet = torch.log(s * s * (d1 * t * t + 2 * s * tt + d0 * (1 - t) ** 2)) - 2 * torch.log(den)
+    return torch.where(inside, y, x), torch.where(inside, logdet, torch.zeros_like(logdet))
+
+
+class SeparableConvStack(nn.Module):
+    """Residual layers of a dilated depthwise convolution and a pointwise one, each followed by LayerNorm + GELU."""
+
+    def __init__(self, s: VitsSpec, dropout: float = 0.0):
+        super().__init__()
+        k, c = s.duration_kernel, s.hidden
+        self.convs_dilated = nn.ModuleList(Conv1d(c, c, k, groups=c, dilation=k ** i, padding=(k * k ** i - k ** i) // 2)
+                                           for i in range(s.duration_stack_layers))
+        self.convs_pointwise = nn.ModuleList(Conv1d(c, c, 1) for _ in range(s.duration_stack_layers))
+        self.norms_1 = nn.ModuleList(nn.LayerNorm(c) for _ in range(s.duration_stack_layers))
+        self.norms_2 = nn.ModuleList(nn.LayerNorm(c) for _ in range(s.duration_stack_layers))
+        self.dropout = nn.Dropout(dropout)
+
+    def forward(self, x, mask, g=None):
+        if g is not None:
+            x = x + g
+        for dw, pw, n1, n2 in zip(self.convs_dilated, self.convs_pointwise, self.norms_1, self.norms_2):
+            h = F.gelu(n1(dw(x * mask).transpose(1, 2)).transpose(1, 2))
+            h = F.gelu(n2(pw(h).transpose(1, 2)).transpose(1, 2))
+            x = x + self.dropout(h)
+        return x * mask
+
+
+class SplineCoupling(nn.Module):
+    """Two channels: the second goes through a spline whose bins come from the first (and the condition)."""
+
+    def __init__(self, s: VitsSpec):
+        super().__init__()
+        self.bins, self.bound, self.scale = s.duration_flow_bins, s.duration_tail_bound, math.sqrt(s.hidden)
+        self.conv_pre = Conv1d(1, s.hidden, 1)
+        self.conv_dds = SeparableConvStack(s)
+        self.conv_proj = Conv1d(s.hidden, 3 * s.duration_flow_bins - 1, 1)
+
+    def forward(self, x, mask, g=None, reverse: bool = False):
+        a, b = x.split(1, dim=1)
+        h = self.conv_proj(self.conv_dds(self.conv_pre(a), mask, g)) * mask        # [B, 3K-1, T]
+        h = h.transpose(1, 2).unsqueeze(1)                                         # [B, 1, T, 3K-1]
+        K = self.bins
+        b, logdet = rational_quadratic_spline(b, h[..., :K] / self.scale, h[..., K:2 * K] / self.scale, h[..., 2 * K:],
+                                              inverse=reverse, bound=self.bound)
+        return torch.cat([a, b], dim=1) * mask, (logdet * mask).sum((1, 2))
+
+
+class ChannelAffine(nn.Module):
+    def __init__(self, channels: int = 2):
+        super().__init__()
+        self.translate = nn.Parameter(torch.zeros(channels, 1))
+        self.log_scale = nn.Parameter(torch.zeros(channels, 1))
+
+    def forward(self, x, mask, g=None, reverse: bool = False):
+        if reverse:
+            return (x - self.translate) * torch.exp(-self.log_scale) * mask, None
+        return (self.translate + torch.exp(self.log_scale) * x) * mask, (self.log_scale * mask).sum((1, 2))
+
+
+class StochasticDurationPredictor(nn.Module):
+    """A flow over (log-duration, companion) pairs per token, conditioned on the text: sampled backwards for synthesis,
+    trained forwards by a variational bound in which a second flow de-quantises the integer durations."""
+
+    def __init__(self, s: VitsSpec):
+        super().__init__()
+        c = s.hidden
+        self.conv_pre, self.conv_proj = Conv1d(c, c, 1), Conv1d(c, c, 1)
+        self.conv_dds = SeparableConvStack(s, s.duration_dropout)
+        if s.speaker_dim:
+            self.cond = Conv1d(s.speaker_dim, c, 1)
+        self.flows = nn.ModuleList([ChannelAffine()] + [SplineCoupling(s) for _ in range(s.duration_flows)])
+        self.post_conv_pre, self.post_conv_proj = Conv1d(1, c, 1), Conv1d(c, c, 1)
+        self.post_conv_dds = SeparableConvStack(s, s.duration_dropout)
+        self.post_flows = nn.ModuleList([ChannelAffine()] + [SplineCoupling(s) for _ in range(s.duration_flows)])
+
+    def _condition(self, x, mask, g):
+        x = self.conv_pre(x.detach())
+        if g is not None:
+            x = x + self.cond(g.detach())
+        return self.conv_proj(self.conv_dds(x, mask)) * mask
+
+    def forward(self, x, mask, g=None, noise_scale: float = 1.0, generator: Optional[torch.Generator] = None):
+        """Sampled log-frames per token ``[B, 1, T]``."""
+        cond = self._condition(x, mask, g)
+        z = torch.randn((x.shape[0], 2, x.shape[2]), device=x.device, dtype=x.dtype, generator=generator) * noise_scale
+        order = list(reversed(self.flows))
+        order = order[:-2] + [order[-1]]                   # the published sampler skips the coupling next to the affine map
+        for f in order:
+            z, _ = f(z.flip(1), mask, cond, reverse=True)
+        return z[:, :1]
+
+    def negative_log_likelihood(self, x, mask, durations, g=None, generator: Optional[torch.Generator] = None):
+        """Variational upper bound of -log p(durations | text) per sequence ``[B]``; ``durations`` [B, 1, T] frames."""
+        cond = self._condition(x, mask, g)
+        post = self.post_conv_proj(self.post_conv_dds(self.post_conv_pre(durations), mask)) * mask
+        e = torch.randn((x.shape[0], 2, x.shape[2]), device=x.device, dtype=x.dtype, generator=generator) * mask
+        z, logdet_q = e, 0.0
+        for f in self.post_flows:
+            z, ld = f(z, mask, cond + post)
+            z, logdet_q = z.flip(1), logdet_q + ld
+        u, v = z.split(1, dim=1)
+        logdet_q = logdet_q + ((F.logsigmoid(u) + F.logsigmoid(-u)) * mask).sum((1, 2))
+        log_q = (-0.5 * (math.log(2 * math.pi) + e * e) * mask).sum((1, 2)) - logdet_q
+        first = torch.log(((durations - torch.sigmoid(u)) * mask).clamp_min(1e-5)) * mask
+        logdet = (-first).sum((1, 2))
+        z = torch.cat([first, v], dim=1)
+        for f in self.flows:
+            z, ld = f(z, mask, cond)
+            z, logdet = z.flip(1), logdet + ld
+        nll = (0.5 * (math.log(2 * math.pi) + z * z) * mask).sum((1, 2)) - logdet
+        return nll + log_q
+
+
 # --------------------------------------------------------------------------------------------------------- generator
 class ResidualBlock(nn.Module):
     def __init__(self, channels: int, kernel: int, dilations: Sequence[int], slope: float):
@@ -415,7 +589,7 @@ class Vits(nn.Module):
         self.text_encoder = TextEncoder(spec)
         self.flow = Flow(spec)
         self.decoder = Generator(spec)
-        self.duration_predictor = DurationPredictor(spec)
+        self.duration_predictor = StochasticDurationPredictor(spec) if spec.stochastic_duration else DurationPredictor(spec)
         self.posterior_encoder = PosteriorEncoder(spec)
         if spec.speakers > 1:
             self.embed_speaker = nn.Embedding(spec.speakers, spec.speaker_dim)
@@ -428,14 +602,19 @@ class Vits(nn.Module):
     @torch.no_grad()
     def synthesize(self, ids: torch.Tensor, lengths: Optional[torch.Tensor] = None, speaker: Optional[torch.Tensor] = None,
                    noise_scale: Optional[float] = None, speaking_rate: Optional[float] = None,
-                   generator: Optional[torch.Generator] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+                   generator: Optional[torch.Generator] = None,
+                   noise_scale_duration: Optional[float] = None) -> Tuple[torch.Tensor, torch.Tensor]:
         """Token ids ``[B, T]`` -> (waveform ``[B, samples]``, valid samples per sequence ``[B]``)."""
         s = self.spec
         lengths = torch.full((ids.shape[0],), ids.shape[1], device=ids.device) if lengths is None else lengths
         mask = length_mask(lengths, ids.shape[1])
         g = self._speaker(speaker)
         hidden, mean, log_dev = self.text_encoder(ids, mask)
-        log_frames = self.duration_predictor(hidden, mask, g)
+        if s.stochastic_duration:
+            nsd = s.noise_scale_duration if noise_scale_duration is None else noise_scale_duration
+            log_frames = self.duration_predictor(hidden, mask, g, nsd, generator)
+        else:
+            log_frames = self.duration_predictor(hidden, mask, g)
         rate = s.speaking_rate if speaking_rate is None else speaking_rate
         durations = torch.ceil(log_frames.exp() * mask / rate)[:, 0]
         mean, frames = expand_by_durations(mean, durations)
@@ -445,6 +624,21 @@ class Vits(nn.Module):
         noise = torch.randn(mean.shape, device=mean.device, dtype=mean.dtype, generator=generator)
         z = self.flow(mean + noise * log_dev.exp() * scale, out_mask, g, reverse=True) * out_mask
         return self.decoder(z, g)[:, 0], frames * s.hop
+
+    @torch.no_grad()
+    def convert_voice(self, spectrogram: torch.Tensor, lengths: torch.Tensor, source: torch.Tensor, target: torch.Tensor,
+                      tau: float = 0.0, generator: Optional[torch.Generator] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+        """Re-voice a recording: its spectrogram ``[B, bins, F]`` is encoded under the ``source`` speaker, carried
+        through the flow into the speaker-free prior space and back under the ``target`` speaker, then generated.
+        ``source`` / ``target`` are speaker ids ``[B]`` or embeddings ``[B, speaker_dim, 1]`` (for instance from a
+        ``ReferenceEncoder``); ``tau`` scales the posterior's sampling noise (0 = its mean)."""
+        as_g = lambda v: v if v.dim() == 3 else self.embed_speaker(v).unsqueeze(-1)
+        g_src, g_tgt = as_g(source), as_g(target)
+        mask = length_mask(lengths, spectrogram.shape[-1])
+        z, mean, _ = self.posterior_encoder(spectrogram, mask, g_src, generator)
+        z = mean + (z - mean) * tau
+        z = self.flow(self.flow(z, mask, g_src), mask, g_tgt, reverse=True) * mask
+        return self.decoder(z, g_tgt)[:, 0], lengths * self.spec.hop
 
     def training_losses(self, ids: torch.Tensor, id_lengths: torch.Tensor, spectrogram: torch.Tensor,
                         spec_lengths: torch.Tensor, speaker: Optional[torch.Tensor] = None, segment: int = 32,
@@ -461,9 +655,13 @@ class Vits(nn.Module):
         with torch.no_grad():
             align = monotonic_alignment(prior_scores(z_p, mean_p, log_dev_p), spec_lengths, id_lengths)
         frames_per_token = align.sum(1)                                               # [B, T]
-        target = torch.log(frames_per_token + 1e-6).unsqueeze(1) * mask
-        log_frames = self.duration_predictor(hidden, mask, g)
-        duration = ((log_frames - target) ** 2 * mask).sum() / mask.sum()
+        if self.spec.stochastic_duration:
+            nll = self.duration_predictor.negative_log_likelihood(hidden, mask, frames_per_token.unsqueeze(1), g, generator)
+            duration = (nll / mask.sum((1, 2))).sum()
+        else:
+            target = torch.log(frames_per_token + 1e-6).unsqueeze(1) * mask
+            log_frames = self.duration_predictor(hidden, mask, g)
+            duration = ((log_frames - target) ** 2 * mask).sum() / mask.sum()
         mean_f = mean_p @ align.transpose(1, 2)                                       # [B, C, F]
         log_dev_f = log_dev_p @ align.transpose(1, 2)
         kl = log_dev_f - log_dev_q - 0.5 + 0.5 * (z_p - mean_f) ** 2 * torch.exp(-2 * log_dev_f)
@@ -501,6 +699,29 @@ class Vits(nn.Module):
         missing, unexpected = self.load_state_dict(plain, strict=False)
         if missing or unexpected:
             raise KeyError(f"VITS state mismatch: missing {list(missing)[:5]}, unexpected {list(unexpected)[:5]}")
+
+
+class ReferenceEncoder(nn.Module):
+    """A speaker (tone colour) embedding ``[B, speaker_dim, 1]`` from a spectrogram of any length: strided 2-D
+    convolutions over (frequency, time), a GRU over the remaining frames, a projection of its last state."""
+
+    def __init__(self, bins: int, speaker_dim: int, channels: Sequence[int] = (32, 32, 64, 64, 128, 128), hidden: int = 128):
+        super().__init__()
+        layers, prev = [], 1
+        for c in channels:
+            layers += [nn.Conv2d(prev, c, 3, 2, 1), nn.ReLU()]
+            prev = c
+            bins = (bins - 1) // 2 + 1
+        self.convs = nn.Sequential(*layers)
+        self.norm = nn.LayerNorm(bins * prev)
+        self.gru = nn.GRU(bins * prev, hidden, batch_first=True)
+        self.proj = nn.Linear(hidden, speaker_dim)
+
+    def forward(self, spectrogram: torch.Tensor) -> torch.Tensor:
+        x = self.convs(spectrogram.unsqueeze(1))                                  # [B, C, bins', F']
+        x = x.permute(0, 3, 1, 2).flatten(2)                                      # [B, F', C x bins']
+        _, h = self.gru(self.norm(x))
+        return self.proj(h[-1]).unsqueeze(-1)
 
 
 # ---------------------------------------------------------------------------------------------------- discriminators

@@ -1,5 +1,5 @@
 """Text to speech with VITS. With ``--model <folder>`` (a Hugging Face VITS folder with ``config.json`` and
-``model.safetensors`` whose duration predictor is the deterministic one) the text is spoken with the checkpoint's
+``model.safetensors``) the text is spoken with the checkpoint's
 voice. Without one, a small model of the same architecture is trained for a few steps on a synthetic corpus (each
 "letter" is a tone of its own pitch, a "word" is the tones in sequence) and then asked to say a new word, so that the
 whole path - alignment search, posterior / prior / flow, generator, duration model, waveform file - runs offline.

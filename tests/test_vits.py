@@ -177,3 +177,103 @@ def test_trainer_modes(adversarial):
     assert key(reports[-1]) < key(reports[0])
     wave_out, samples = model.eval().synthesize(ids, torch.tensor([6, 3]))
     assert wave_out.shape[0] == 2 and int(samples.max()) == wave_out.shape[1]
+
+
+def test_voice_conversion_is_the_identity_for_the_same_speaker_and_changes_with_the_target():
+    spec = V.VitsSpec(vocab_size=10, hidden=16, layers=1, flow_size=8, spectrogram_bins=17, prior_flows=2,
+                      prior_wavenet_layers=2, posterior_wavenet_layers=2, wavenet_kernel=3, upsample_rates=(2, 2),
+                      upsample_kernels=(4, 4), upsample_channels=8, resblock_kernels=(3,), resblock_dilations=((1, 2),),
+                      ffn=16, duration_filter=8, speakers=3, speaker_dim=4)
+    torch.manual_seed(6)
+    model = V.Vits(spec).eval()
+    lin = torch.rand(2, 17, 12) + 0.1
+    lengths = torch.tensor([12, 9])
+    a, b = torch.tensor([0, 1]), torch.tensor([2, 2])
+    same, n = model.convert_voice(lin, lengths, a, a)
+    # same speaker in and out: the flow cancels, so it is posterior mean -> generator
+    mask = V.length_mask(lengths, 12)
+    g = model.embed_speaker(a).unsqueeze(-1)
+    _, mean, _ = model.posterior_encoder(lin, mask, g)
+    torch.testing.assert_close(same, model.decoder(mean * mask, g)[:, 0], atol=1e-5, rtol=1e-4)
+    other, _ = model.convert_voice(lin, lengths, a, b)
+    assert n.tolist() == [48, 36] and other.shape == same.shape and (other - same).abs().max() > 1e-4
+    # a tone-colour embedding taken from a recording works in place of a speaker id
+    ref = V.ReferenceEncoder(17, 4, channels=(4, 8), hidden=8)
+    emb = ref(torch.rand(2, 17, 30))
+    assert emb.shape == (2, 4, 1)
+    cloned, _ = model.convert_voice(lin, lengths, a, emb)
+    assert cloned.shape == same.shape and torch.isfinite(cloned).all()
+
+
+def _tiny_hf_stochastic():
+    from transformers import VitsConfig, VitsModel
+    cfg = VitsConfig(vocab_size=20, hidden_size=16, num_hidden_layers=1, num_attention_heads=2, window_size=2,
+                     ffn_dim=32, flow_size=8, spectrogram_bins=9, prior_encoder_num_flows=2,
+                     prior_encoder_num_wavenet_layers=2, posterior_encoder_num_wavenet_layers=2, wavenet_kernel_size=3,
+                     upsample_rates=[4, 2], upsample_kernel_sizes=[8, 4], upsample_initial_channel=16,
+                     resblock_kernel_sizes=[3], resblock_dilation_sizes=[[1, 3]], use_stochastic_duration_prediction=True,
+                     duration_predictor_num_flows=3, duration_predictor_flow_bins=5, depth_separable_num_layers=2,
+                     noise_scale=0.0, noise_scale_duration=0.0)
+    torch.manual_seed(0)
+    model = VitsModel(cfg).eval()
+    with torch.no_grad():
+        for name, p in model.duration_predictor.named_parameters():
+            if p.dim() > 1 and "norm" not in name:
+                p.mul_(3.0)
+        model.duration_predictor.flows[0].translate.add_(torch.tensor([[0.9], [0.2]]))
+        model.duration_predictor.flows[0].log_scale.add_(torch.tensor([[0.3], [-0.2]]))
+    return cfg, model
+
+
+def test_stochastic_duration_predictor_matches_hugging_face():
+    cfg, hf = _tiny_hf_stochastic()
+    mine = V.Vits(V.VitsSpec.from_hf(cfg.to_dict())).eval()
+    mine.load_hf_state(hf.state_dict())
+    ids = torch.tensor([[3, 7, 1, 12, 5, 9, 2, 15]])
+    with torch.no_grad():
+        want = hf(ids)
+    wave, samples = mine.synthesize(ids, noise_scale=0.0, noise_scale_duration=0.0)
+    assert wave.shape == want.waveform.shape and wave.shape[1] > 8 * 8
+    torch.testing.assert_close(wave, want.waveform, atol=5e-4, rtol=1e-3)
+    # the training bound, same noise
+    x, mask = torch.randn(2, 16, 6), V.length_mask(torch.tensor([6, 4]), 6)
+    durations = torch.tensor([[[2., 1, 3, 1, 4, 2]], [[1., 5, 2, 2, 0, 0]]]) * mask
+    torch.manual_seed(11)
+    with torch.no_grad():
+        want_nll = hf.duration_predictor(x, mask, None, durations=durations, reverse=False)
+    torch.manual_seed(11)
+    with torch.no_grad():
+        got_nll = mine.duration_predictor.negative_log_likelihood(x, mask, durations)
+    torch.testing.assert_close(got_nll, want_nll, atol=1e-3, rtol=1e-4)
+
+
+def test_spline_is_monotone_invertible_and_reports_its_slope():
+    torch.manual_seed(12)
+    x = (torch.randn(3, 1, 40, dtype=torch.double) * 3).requires_grad_(True)
+    w, h, d = (torch.randn(3, 1, 40, n, dtype=torch.double) for n in (6, 6, 5))
+    y, logdet = V.rational_quadratic_spline(x, w, h, d)
+    slope, = torch.autograd.grad(y.sum(), x)
+    torch.testing.assert_close(slope.log(), logdet, atol=1e-9, rtol=1e-9)
+    back, _ = V.rational_quadratic_spline(y.detach(), w, h, d, inverse=True)
+    torch.testing.assert_close(back, x.detach(), atol=1e-9, rtol=1e-9)
+    outside = x.detach().abs() > 5
+    assert bool(outside.any()) and torch.equal(y.detach()[outside], x.detach()[outside])
+
+
+def test_training_with_the_stochastic_duration_model():
+    spec = V.VitsSpec(vocab_size=12, hidden=16, layers=1, heads=2, window=2, ffn=32, flow_size=8, spectrogram_bins=17,
+                      prior_flows=2, prior_wavenet_layers=2, posterior_wavenet_layers=2, wavenet_kernel=3,
+                      upsample_rates=(4, 2), upsample_kernels=(8, 4), upsample_channels=16, resblock_kernels=(3,),
+                      resblock_dilations=((1, 3),), stochastic_duration=True, duration_flows=2, duration_flow_bins=4,
+                      duration_stack_layers=2, duration_dropout=0.0)
+    torch.manual_seed(13)
+    model = V.Vits(spec)
+    trainer = V.VitsTrainer(model, None, lr=2e-3, segment=8)
+    t = torch.arange(40 * spec.hop) / 400.0
+    wave = torch.stack([torch.sin(2 * torch.pi * 30 * t), torch.sin(2 * torch.pi * 55 * t) * 0.5])
+    ids = torch.tensor([[1, 2, 3, 4, 5, 6], [7, 8, 9, 0, 0, 0]])
+    reports = [trainer.step(ids, torch.tensor([6, 3]), wave, torch.tensor([40 * spec.hop, 30 * spec.hop])) for _ in range(15)]
+    assert all(torch.isfinite(torch.tensor(r["loss"])) for r in reports)
+    assert sum(r["duration"] for r in reports[-3:]) < sum(r["duration"] for r in reports[:3])
+    wave_out, samples = model.eval().synthesize(ids, torch.tensor([6, 3]))
+    assert int(samples.max()) == wave_out.shape[1]
