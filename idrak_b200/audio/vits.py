@@ -114,6 +114,14 @@ class VitsSpec:
                    sampling_rate=g("sampling_rate", 16000), bias=g("use_bias", True))
 
 
+def _randn(like: torch.Tensor, generator: Optional[torch.Generator], shape=None, uniform: bool = False) -> torch.Tensor:
+    """Noise of ``like``'s shape (or ``shape``), dtype and device; drawn on the generator's own device when it has one."""
+    shape = tuple(like.shape if shape is None else shape)
+    device = like.device if generator is None else generator.device
+    draw = torch.rand if uniform else torch.randn
+    return draw(shape, device=device, dtype=torch.float32, generator=generator).to(device=like.device, dtype=like.dtype)
+
+
 def length_mask(lengths: torch.Tensor, size: Optional[int] = None) -> torch.Tensor:
     """``[B, 1, T]`` float mask of the first ``lengths[b]`` positions."""
     size = int(lengths.max()) if size is None else size
@@ -259,7 +267,7 @@ class PosteriorEncoder(nn.Module):
     def forward(self, spec, mask, g=None, generator: Optional[torch.Generator] = None):
         h = self.wavenet(self.conv_pre(spec) * mask, mask, g)
         mean, log_dev = (self.conv_proj(h) * mask).split(self.size, dim=1)
-        noise = torch.randn(mean.shape, device=mean.device, dtype=mean.dtype, generator=generator)
+        noise = _randn(mean, generator)
         return (mean + noise * log_dev.exp()) * mask, mean, log_dev
 
 
@@ -447,7 +455,7 @@ class StochasticDurationPredictor(nn.Module):
     def forward(self, x, mask, g=None, noise_scale: float = 1.0, generator: Optional[torch.Generator] = None):
         """Sampled log-frames per token ``[B, 1, T]``."""
         cond = self._condition(x, mask, g)
-        z = torch.randn((x.shape[0], 2, x.shape[2]), device=x.device, dtype=x.dtype, generator=generator) * noise_scale
+        z = _randn(x, generator, (x.shape[0], 2, x.shape[2])) * noise_scale
         order = list(reversed(self.flows))
         order = order[:-2] + [order[-1]]                   # the published sampler skips the coupling next to the affine map
         for f in order:
@@ -458,7 +466,7 @@ class StochasticDurationPredictor(nn.Module):
         """Variational upper bound of -log p(durations | text) per sequence ``[B]``; ``durations`` [B, 1, T] frames."""
         cond = self._condition(x, mask, g)
         post = self.post_conv_proj(self.post_conv_dds(self.post_conv_pre(durations), mask)) * mask
-        e = torch.randn((x.shape[0], 2, x.shape[2]), device=x.device, dtype=x.dtype, generator=generator) * mask
+        e = _randn(x, generator, (x.shape[0], 2, x.shape[2])) * mask
         z, logdet_q = e, 0.0
         for f in self.post_flows:
             z, ld = f(z, mask, cond + post)
@@ -594,6 +602,10 @@ class Vits(nn.Module):
         if spec.speakers > 1:
             self.embed_speaker = nn.Embedding(spec.speakers, spec.speaker_dim)
 
+    @property
+    def dtype(self) -> torch.dtype:
+        return self.text_encoder.embed_tokens.weight.dtype
+
     def _speaker(self, speaker: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         if speaker is None or self.spec.speakers <= 1:
             return None
@@ -607,7 +619,7 @@ class Vits(nn.Module):
         """Token ids ``[B, T]`` -> (waveform ``[B, samples]``, valid samples per sequence ``[B]``)."""
         s = self.spec
         lengths = torch.full((ids.shape[0],), ids.shape[1], device=ids.device) if lengths is None else lengths
-        mask = length_mask(lengths, ids.shape[1])
+        mask = length_mask(lengths, ids.shape[1]).to(self.dtype)
         g = self._speaker(speaker)
         hidden, mean, log_dev = self.text_encoder(ids, mask)
         if s.stochastic_duration:
@@ -619,9 +631,9 @@ class Vits(nn.Module):
         durations = torch.ceil(log_frames.exp() * mask / rate)[:, 0]
         mean, frames = expand_by_durations(mean, durations)
         log_dev, _ = expand_by_durations(log_dev, durations)
-        out_mask = length_mask(frames, mean.shape[-1])
+        out_mask = length_mask(frames, mean.shape[-1]).to(self.dtype)
         scale = s.noise_scale if noise_scale is None else noise_scale
-        noise = torch.randn(mean.shape, device=mean.device, dtype=mean.dtype, generator=generator)
+        noise = _randn(mean, generator)
         z = self.flow(mean + noise * log_dev.exp() * scale, out_mask, g, reverse=True) * out_mask
         return self.decoder(z, g)[:, 0], frames * s.hop
 
@@ -634,7 +646,7 @@ class Vits(nn.Module):
         ``ReferenceEncoder``); ``tau`` scales the posterior's sampling noise (0 = its mean)."""
         as_g = lambda v: v if v.dim() == 3 else self.embed_speaker(v).unsqueeze(-1)
         g_src, g_tgt = as_g(source), as_g(target)
-        mask = length_mask(lengths, spectrogram.shape[-1])
+        mask = length_mask(lengths, spectrogram.shape[-1]).to(self.dtype)
         z, mean, _ = self.posterior_encoder(spectrogram, mask, g_src, generator)
         z = mean + (z - mean) * tau
         z = self.flow(self.flow(z, mask, g_src), mask, g_tgt, reverse=True) * mask
@@ -646,8 +658,8 @@ class Vits(nn.Module):
         """One generator-side pass: ``duration`` and ``kl`` losses, the generated waveform ``segment_wave``
         ``[B, 1, segment x hop]`` of a random window of latent frames and that window's first frame ``segment_start``
         (to cut the same samples from the recording for the spectral and adversarial losses), and the alignment."""
-        mask = length_mask(id_lengths, ids.shape[1])
-        smask = length_mask(spec_lengths, spectrogram.shape[-1])
+        mask = length_mask(id_lengths, ids.shape[1]).to(self.dtype)
+        smask = length_mask(spec_lengths, spectrogram.shape[-1]).to(self.dtype)
         g = self._speaker(speaker)
         hidden, mean_p, log_dev_p = self.text_encoder(ids, mask)
         z, mean_q, log_dev_q = self.posterior_encoder(spectrogram, smask, g, generator)
@@ -668,8 +680,7 @@ class Vits(nn.Module):
         kl = (kl * smask).sum() / smask.sum()
         seg = min(segment, int(spec_lengths.min()))
         high = (spec_lengths - seg + 1).clamp_min(1).float()
-        u = torch.rand(high.shape, device=high.device, generator=generator) if generator is None or generator.device == high.device \
-            else torch.rand(high.shape, generator=generator).to(high.device)
+        u = _randn(high, generator, uniform=True)
         start = (u * high).long()
         cols = start[:, None] + torch.arange(seg, device=z.device)[None, :]
         z_seg = z.gather(2, cols[:, None, :].expand(-1, z.shape[1], -1))
