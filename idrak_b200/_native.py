@@ -121,6 +121,7 @@ _SIGNATURES = {
     "idrak_lstm_cell_bwd": (c_int, [c_int] + [c_void_p] * 7 + [c_int, c_int, c_void_p]),
     "idrak_gru_cell": (c_int, [c_int] + [c_void_p] * 5 + [c_int, c_int, c_void_p]),
     "idrak_gru_cell_bwd": (c_int, [c_int] + [c_void_p] * 6 + [c_int, c_int, c_void_p]),
+    "idrak_monotonic_align": (c_int, [c_void_p] * 6 + [c_int, c_int, c_int, c_void_p]),
     "idrak_im2col": (c_int, [c_int, c_void_p, c_void_p, C.POINTER(c_int), c_int, c_void_p]),
     "idrak_col2im": (c_int, [c_int, c_void_p, c_void_p, C.POINTER(c_int), c_int, c_int, c_void_p]),
     "idrak_nchw_to_rows": (c_int, [c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),

@@ -538,6 +538,8 @@ def monotonic_alignment(score: torch.Tensor, frames: torch.Tensor, tokens: torch
     B, Fm, Tm = score.shape
     if bool((frames < tokens).any()):
         raise ValueError("monotonic alignment needs at least one frame per token")
+    if score.is_cuda:
+        return _monotonic_alignment_device(score, frames, tokens)
     neg = torch.finfo(score.dtype).min / 4
     tok = torch.arange(Tm, device=score.device)[None, :]
     value = torch.full((B, Fm, Tm), neg, dtype=score.dtype, device=score.device)
@@ -566,6 +568,22 @@ def monotonic_alignment(score: torch.Tensor, frames: torch.Tensor, tokens: torch
         # the first active row of a sequence is its last frame: it keeps the last token
         idx = idx - move.long()
     return path
+
+
+def _monotonic_alignment_device(score: torch.Tensor, frames: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+    """The same search as one launch (``csrc/align.cu``): one CTA per sequence, rows of best totals in shared memory."""
+    from .. import _native
+    from ..ops._util import stream_ptr
+    B, Fm, Tm = score.shape
+    sc = score.float().contiguous()
+    fr, tk = frames.to(torch.int32).contiguous(), tokens.to(torch.int32).contiguous()
+    path = torch.zeros_like(sc)
+    step = torch.empty((B, Fm, Tm), dtype=torch.uint8, device=sc.device)
+    rows = torch.empty((B, 2, Tm) if Tm > 6000 else (1,), dtype=torch.float32, device=sc.device)
+    rc = _native.lib().idrak_monotonic_align(sc.data_ptr(), fr.data_ptr(), tk.data_ptr(), path.data_ptr(), step.data_ptr(),
+                                             rows.data_ptr(), B, Fm, Tm, stream_ptr())
+    _native.check(rc, "idrak_monotonic_align")
+    return path.to(score.dtype)
 
 
 def prior_scores(z: torch.Tensor, mean: torch.Tensor, log_dev: torch.Tensor) -> torch.Tensor:

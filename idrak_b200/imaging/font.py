@@ -30,13 +30,15 @@ class TrueTypeFont:
         if len(data) < 12:
             raise FontError("not a font file")
         version, n_tables = struct.unpack(">IH", data[:6])
-        if version not in (0x00010000, 0x74727565):       # 1.0 or 'true'
-            raise FontError("only TrueType-flavoured fonts (glyf outlines) are read")
+        if version not in (0x00010000, 0x74727565, 0x4F54544F):       # 1.0, 'true' or 'OTTO' (CFF outlines)
+            raise FontError("not a TrueType / OpenType font (collections and other containers are not read)")
         self.tables: Dict[str, Tuple[int, int]] = {}
         for i in range(n_tables):
             tag, _, off, length = struct.unpack(">4sIII", data[12 + 16 * i: 28 + 16 * i])
             self.tables[tag.decode("latin-1")] = (off, length)
-        for need in ("head", "maxp", "hhea", "hmtx", "cmap", "loca", "glyf"):
+        self._cff = None
+        outlines = ("CFF ",) if version == 0x4F54544F else ("loca", "glyf")
+        for need in ("head", "maxp", "hhea", "hmtx", "cmap") + outlines:
             if need not in self.tables:
                 raise FontError(f"the font has no '{need}' table")
         head = self._table("head")
@@ -47,7 +49,12 @@ class TrueTypeFont:
         self.ascender, self.descender, self.line_gap = struct.unpack(">hhh", hhea[4:10])
         self.num_h_metrics = struct.unpack(">H", hhea[34:36])[0]
         self._cmap = self._read_cmap()
-        self._loca = self._read_loca()
+        if outlines == ("CFF ",):
+            from .cff import CffTable
+            self._cff = CffTable(self._table("CFF "))
+            self._loca = []
+        else:
+            self._loca = self._read_loca()
         self._kern = self._read_kern()
         self._paths: Dict[int, Path] = {}
 
@@ -143,7 +150,9 @@ class TrueTypeFont:
         if gid in self._paths:
             return self._paths[gid]
         path = Path()
-        if 0 <= gid < self.num_glyphs and self._loca[gid + 1] > self._loca[gid] and _depth < 8:
+        if self._cff is not None:
+            path = self._cff.glyph(gid)[0]
+        elif 0 <= gid < self.num_glyphs and self._loca[gid + 1] > self._loca[gid] and _depth < 8:
             g = self._table("glyf")[self._loca[gid]: self._loca[gid + 1]]
             n_contours = struct.unpack(">h", g[:2])[0]
             if n_contours >= 0:

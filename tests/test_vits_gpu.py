@@ -64,3 +64,16 @@ def test_training_step_and_synthesis_run_on_the_device():
     assert key(reports[-1]) < key(reports[0])
     out, samples = model.eval().synthesize(ids, lengths, generator=torch.Generator(device="cuda").manual_seed(2))
     assert out.is_cuda and int(samples.max()) == out.shape[1] and torch.isfinite(out).all()
+
+
+def test_alignment_kernel_equals_the_host_search():
+    torch.manual_seed(3)
+    score = torch.randn(5, 70, 23)
+    frames, tokens = torch.tensor([70, 51, 23, 64, 30]), torch.tensor([23, 17, 23, 1, 9])
+    want = V.monotonic_alignment(score, frames, tokens)
+    got = V.monotonic_alignment(score.cuda(), frames.cuda(), tokens.cuda())
+    assert got.is_cuda and torch.equal(got.cpu(), want)
+    # scores with many ties (the same choice on both sides)
+    tied = torch.randint(0, 3, (2, 40, 11)).float()
+    f2, t2 = torch.tensor([40, 33]), torch.tensor([11, 8])
+    assert torch.equal(V.monotonic_alignment(tied.cuda(), f2.cuda(), t2.cuda()).cpu(), V.monotonic_alignment(tied, f2, t2))
