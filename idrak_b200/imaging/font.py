@@ -25,16 +25,25 @@ class FontError(ValueError):
 
 
 class TrueTypeFont:
-    def __init__(self, data: bytes):
+    def __init__(self, data: bytes, face: int = 0):
+        """``face`` picks a member of a font collection (``ttcf`` container); a single font has face 0 only."""
         self.data = data
         if len(data) < 12:
             raise FontError("not a font file")
-        version, n_tables = struct.unpack(">IH", data[:6])
+        base = 0
+        if data[:4] == b"ttcf":
+            count = struct.unpack(">I", data[8:12])[0]
+            if not 0 <= face < count:
+                raise FontError(f"the collection has {count} faces, face {face} was asked for")
+            base = struct.unpack(">I", data[12 + 4 * face: 16 + 4 * face])[0]
+        elif face != 0:
+            raise FontError("a single font file has face 0 only")
+        version, n_tables = struct.unpack(">IH", data[base: base + 6])
         if version not in (0x00010000, 0x74727565, 0x4F54544F):       # 1.0, 'true' or 'OTTO' (CFF outlines)
-            raise FontError("not a TrueType / OpenType font (collections and other containers are not read)")
+            raise FontError("not a TrueType / OpenType font or collection")
         self.tables: Dict[str, Tuple[int, int]] = {}
         for i in range(n_tables):
-            tag, _, off, length = struct.unpack(">4sIII", data[12 + 16 * i: 28 + 16 * i])
+            tag, _, off, length = struct.unpack(">4sIII", data[base + 12 + 16 * i: base + 28 + 16 * i])
             self.tables[tag.decode("latin-1")] = (off, length)
         self._cff = None
         outlines = ("CFF ",) if version == 0x4F54544F else ("loca", "glyf")

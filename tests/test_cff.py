@@ -170,3 +170,28 @@ def test_open_type_file_with_cff_outlines_renders():
     assert abs(area - 3.14159 * 40 * 40) < 0.02 * 3.14159 * 40 * 40           # radius 200 units = 40 px: a near circle
     with pytest.raises(im.FontError):
         im.TrueTypeFont(b"wOFF" + b"\x00" * 40)
+
+
+def test_font_collection_faces():
+    chars, subrs, gsubrs = _glyphs()
+    one = build_otf(build_cff(chars[:4], subrs, gsubrs), {ord("s"): 1}, [500] * 4)
+    two = build_otf(build_cff(chars[:6], subrs, gsubrs), {ord("o"): 4}, [700] * 6, upem=2000)
+
+    def shifted(font, by):
+        n = struct.unpack(">H", font[4:6])[0]
+        out = bytearray(font)
+        for i in range(n):
+            off = struct.unpack(">I", font[12 + 16 * i + 8: 12 + 16 * i + 12])[0]
+            struct.pack_into(">I", out, 12 + 16 * i + 8, off + by)
+        return bytes(out)
+
+    header = 12 + 8
+    ttc = b"ttcf" + struct.pack(">HHIII", 1, 0, 2, header, header + len(one)) + shifted(one, header) + shifted(two, header + len(one))
+    a, b = im.TrueTypeFont(ttc), im.TrueTypeFont(ttc, face=1)
+    assert a.num_glyphs == 4 and a.glyph_index(ord("s")) == 1 and a.units_per_em == 1000
+    assert b.num_glyphs == 6 and b.glyph_index(ord("o")) == 4 and b.units_per_em == 2000 and b.advance(4) == 700
+    assert len(b.glyph_path(4).contours) == 1
+    with pytest.raises(im.FontError):
+        im.TrueTypeFont(ttc, face=2)
+    with pytest.raises(im.FontError):
+        im.TrueTypeFont(one, face=1)
