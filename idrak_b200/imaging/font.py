@@ -254,13 +254,17 @@ class TrueTypeFont:
         if shape and any("\u0590" <= ch <= "\u08ff" or "\ufb1d" <= ch <= "\ufefc" for ch in text):
             from .shaping import layout_line
             text = layout_line(text)
+        glyphs: List[int] = []
         for ch in text:
             gid = self.glyph_index(ord(ch))
             if gid == 0 and "\ufe70" <= ch <= "\ufefc":
                 import unicodedata
-                base = unicodedata.decomposition(ch).split()[1:]
-                if len(base) == 1:
-                    gid = self.glyph_index(int(base[0], 16))
+                base = [int(b, 16) for b in unicodedata.decomposition(ch).split()[1:]]
+                # a ligature the font lacks: its letters, last first (the line is already in drawing order)
+                glyphs += [self.glyph_index(b) for b in reversed(base)] or [0]
+            else:
+                glyphs.append(gid)
+        for gid in glyphs:
             if kerning and prev is not None:
                 pen += self.kerning(prev, gid) * scale
             out.append((gid, pen))
