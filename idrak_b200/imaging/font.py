@@ -65,6 +65,10 @@ class TrueTypeFont:
         else:
             self._loca = self._read_loca()
         self._kern = self._read_kern()
+        self.gsub = None
+        if "GSUB" in self.tables:
+            from .gsub import GsubTable
+            self.gsub = GsubTable(self._table("GSUB"))
         self._paths: Dict[int, Path] = {}
 
     def _table(self, tag: str) -> bytes:
@@ -251,25 +255,62 @@ class TrueTypeFont:
         a presentation form the font has no glyph for falls back to its base letter."""
         scale = size / self.units_per_em
         pen, prev, out = 0.0, None, []
-        if shape and any("\u0590" <= ch <= "\u08ff" or "\ufb1d" <= ch <= "\ufefc" for ch in text):
-            from .shaping import layout_line
-            text = layout_line(text)
         glyphs: List[int] = []
-        for ch in text:
-            gid = self.glyph_index(ord(ch))
-            if gid == 0 and "\ufe70" <= ch <= "\ufefc":
-                import unicodedata
-                base = [int(b, 16) for b in unicodedata.decomposition(ch).split()[1:]]
-                # a ligature the font lacks: its letters, last first (the line is already in drawing order)
-                glyphs += [self.glyph_index(b) for b in reversed(base)] or [0]
-            else:
-                glyphs.append(gid)
+        rtl = shape and any("\u0590" <= ch <= "\u08ff" or "\ufb1d" <= ch <= "\ufefc" for ch in text)
+        if rtl and self.gsub is not None and self.gsub.joins:
+            glyphs = self._shape_with_gsub(text)
+        else:
+            if rtl:
+                from .shaping import layout_line
+                text = layout_line(text)
+            for ch in text:
+                gid = self.glyph_index(ord(ch))
+                if gid == 0 and "\ufe70" <= ch <= "\ufefc":
+                    import unicodedata
+                    base = [int(b, 16) for b in unicodedata.decomposition(ch).split()[1:]]
+                    # a ligature the font lacks: its letters, last first (the line is already in drawing order)
+                    glyphs += [self.glyph_index(b) for b in reversed(base)] or [0]
+                else:
+                    glyphs.append(gid)
         for gid in glyphs:
             if kerning and prev is not None:
                 pen += self.kerning(prev, gid) * scale
             out.append((gid, pen))
             pen += self.advance(gid) * scale
             prev = gid
+        return out
+
+    def _shape_with_gsub(self, text: str) -> List[int]:
+        """Glyphs of a line with right-to-left text in drawing order, the positional forms and the required / standard
+        ligatures taken from the font's own substitution table."""
+        from .shaping import _MIRROR, arabic_forms, visual_indices
+        tags = {"isolated": "isol", "initial": "init", "medial": "medi", "final": "fina"}
+        per_char: List[List[int]] = []
+        for ch, form in arabic_forms(text):
+            gid = self.glyph_index(ord(ch))
+            per_char.append(list(self.gsub.single(tags[form]).get(gid, (gid,))) if form else [gid])
+        # ligatures over the logical sequence: the first character keeps the ligature, the others lose their glyphs
+        for tag in ("rlig", "liga"):
+            rules = self.gsub.ligatures(tag)
+            i = 0
+            while rules and i < len(per_char):
+                if len(per_char[i]) == 1:
+                    for rest, lig in rules.get(per_char[i][0], []):
+                        follow = per_char[i + 1: i + 1 + len(rest)]
+                        if len(follow) == len(rest) and all(len(f) == 1 and f[0] == r for f, r in zip(follow, rest)) \
+                                and (tag == "rlig" or all("\u0590" <= text[k] <= "\u08ff" for k in range(i, i + 1 + len(rest)))):
+                            per_char[i] = [lig]
+                            for k in range(i + 1, i + 1 + len(rest)):
+                                per_char[k] = []
+                            break
+                i += 1
+        out: List[int] = []
+        for i, mirrored in visual_indices(text):
+            if mirrored:
+                out.append(self.glyph_index(ord(_MIRROR[text[i]])))
+            else:
+                from .shaping import _direction
+                out += reversed(per_char[i]) if _direction(text[i]) == "R" else per_char[i]
         return out
 
     def measure(self, text: str, size: float) -> Tuple[float, float, float]:

@@ -67,9 +67,9 @@ def _joins_right(ch: str) -> bool:
     return bool(forms) and FINAL in forms
 
 
-def shape_arabic(text: str) -> str:
-    """Logical-order text with Arabic letters replaced by their contextual presentation forms."""
-    letters, ligatures = _tables()
+def arabic_forms(text: str) -> List[Tuple[str, str]]:
+    """Per character of ``text`` (logical order): (the character, its joining form or "" for anything that has none)."""
+    letters, _ = _tables()
     chars = list(text)
     n = len(chars)
 
@@ -79,34 +79,46 @@ def shape_arabic(text: str) -> str:
             j += step
         return chars[j] if 0 <= j < n else ""
 
+    out: List[Tuple[str, str]] = []
+    for i, ch in enumerate(chars):
+        forms = letters.get(ch)
+        if not forms:
+            out.append((ch, ""))
+            continue
+        prev, nxt = neighbour(i, -1), neighbour(i, +1)
+        before = bool(prev) and _joins_left(prev) and FINAL in forms
+        after = bool(nxt) and _joins_right(nxt) and INITIAL in forms
+        out.append((ch, MEDIAL if before and after and MEDIAL in forms else INITIAL if after else FINAL if before else ISOLATED))
+    return out
+
+
+def shape_arabic(text: str) -> str:
+    """Logical-order text with Arabic letters replaced by their contextual presentation forms."""
+    letters, ligatures = _tables()
+    forms = arabic_forms(text)
+    n = len(forms)
     out: List[str] = []
     i = 0
     while i < n:
-        ch = chars[i]
-        forms = letters.get(ch)
-        if not forms:
+        ch, form = forms[i]
+        if not form:
             out.append(ch)
             i += 1
             continue
-        prev = neighbour(i, -1)
-        before = bool(prev) and _joins_left(prev) and FINAL in forms
-        # lam followed (marks aside) by an alef: one ligature
-        if ch == "ل":
+        if ch == "ل":                                            # lam followed (marks aside) by an alef: one ligature
             j = i + 1
             marks = []
-            while j < n and _is_mark(chars[j]):
-                marks.append(chars[j])
+            while j < n and _is_mark(forms[j][0]):
+                marks.append(forms[j][0])
                 j += 1
-            if j < n and (ch, chars[j]) in ligatures:
-                lig = ligatures[(ch, chars[j])]
-                out.append(lig[FINAL] if before and FINAL in lig else lig[ISOLATED])
+            if j < n and (ch, forms[j][0]) in ligatures:
+                lig = ligatures[(ch, forms[j][0])]
+                joined = form in (FINAL, MEDIAL)
+                out.append(lig[FINAL] if joined and FINAL in lig else lig[ISOLATED])
                 out.extend(marks)
                 i = j + 1
                 continue
-        nxt = neighbour(i, +1)
-        after = bool(nxt) and _joins_right(nxt) and INITIAL in forms
-        form = MEDIAL if before and after and MEDIAL in forms else INITIAL if after else FINAL if before else ISOLATED
-        out.append(forms.get(form, forms.get(ISOLATED, ch)))
+        out.append(letters[ch].get(form, letters[ch].get(ISOLATED, ch)))
         i += 1
     return "".join(out)
 
@@ -130,8 +142,8 @@ def base_direction(text: str) -> str:
     return "L"
 
 
-def visual_order(text: str, base: str = "") -> str:
-    """The characters of one line in left-to-right drawing order."""
+def visual_indices(text: str, base: str = "") -> List[Tuple[int, bool]]:
+    """Drawing order of one line: (index into ``text``, whether that character is drawn mirrored), left to right."""
     base = base or base_direction(text)
     n = len(text)
     kinds = [_direction(c) for c in text]
@@ -160,14 +172,14 @@ def visual_order(text: str, base: str = "") -> str:
             level[k] = fill
         i = j
     # runs of one direction ("RN" = digits inside a right-to-left run: part of that run, kept in reading order)
-    runs: List[Tuple[str, str]] = []
+    runs: List[List[Tuple[int, bool]]] = []
     i = 0
     while i < n:
         d = level[i][0]
         j = i
         while j < n and level[j][0] == d:
             j += 1
-        seg = text[i:j]
+        seg = [(k, False) for k in range(i, j)]
         if d == "R":
             pieces, k = [], i
             while k < j:                                               # reverse, but keep each number as written
@@ -175,17 +187,22 @@ def visual_order(text: str, base: str = "") -> str:
                     m = k
                     while m < j and level[m] == "RN":
                         m += 1
-                    pieces.append(text[k:m])
+                    pieces.append([(q, False) for q in range(k, m)])
                     k = m
                 else:
-                    pieces.append(_MIRROR.get(text[k], text[k]))
+                    pieces.append([(k, text[k] in _MIRROR)])
                     k += 1
-            seg = "".join(reversed(pieces))
-        runs.append((d, seg))
+            seg = [item for piece in reversed(pieces) for item in piece]
+        runs.append(seg)
         i = j
     if base == "R":
         runs.reverse()
-    return "".join(seg for _, seg in runs)
+    return [item for seg in runs for item in seg]
+
+
+def visual_order(text: str, base: str = "") -> str:
+    """The characters of one line in left-to-right drawing order."""
+    return "".join(_MIRROR[text[i]] if mirrored else text[i] for i, mirrored in visual_indices(text, base))
 
 
 def layout_line(text: str, base: str = "") -> str:

@@ -71,7 +71,7 @@ def build_cff(charstrings, subrs=(), gsubrs=()):
     return header + names + index([top]) + strings + gsub + chars + private + index(list(subrs))
 
 
-def build_otf(cff, cmap, advances, upem=1000):
+def build_otf(cff, cmap, advances, upem=1000, extra=None):
     n = len(advances)
     head = bytearray(54)
     struct.pack_into(">H", head, 18, upem)
@@ -84,6 +84,7 @@ def build_otf(cff, cmap, advances, upem=1000):
     sub = struct.pack(">HHIII", 12, 0, 16 + len(groups), 0, len(cmap)) + groups
     cm = struct.pack(">HHHHI", 0, 1, 3, 10, 12) + sub
     tables = {b"CFF ": cff, b"cmap": cm, b"head": bytes(head), b"hhea": bytes(hhea), b"hmtx": hmtx, b"maxp": maxp}
+    tables.update(extra or {})
     out = struct.pack(">IHHHH", 0x4F54544F, len(tables), 0, 0, 0)
     at = 12 + 16 * len(tables)
     body = b""
@@ -195,3 +196,71 @@ def test_font_collection_faces():
         im.TrueTypeFont(ttc, face=2)
     with pytest.raises(im.FontError):
         im.TrueTypeFont(one, face=1)
+
+
+def build_gsub():
+    """Features init / medi / fina (single substitutions, both formats, one behind an extension lookup), isol as a
+    multiple substitution, rlig with one ligature. Glyphs: 1 beh, 2 lam, 3 alef; 4-6 beh init / medi / fina;
+    7-9 lam init / medi / fina; 10 alef fina; 11 lam-alef (from lam.init + alef.fina), 12 lam-alef joined
+    (lam.medi + alef.fina); 13 + 14 = beh isolated as a base and a dot."""
+    H = lambda *v: struct.pack(f">{len(v)}H", *v)
+    cov = lambda glyphs: H(1, len(glyphs), *glyphs)
+    single2 = lambda pairs: H(2, 6 + 2 * len(pairs), len(pairs), *[b for _, b in pairs]) + cov([a for a, _ in pairs])
+    init = single2([(1, 4), (2, 7)])
+    medi = single2([(1, 5), (2, 8)])
+    fina_sub = H(1, 6) + struct.pack(">h", 5) + cov([1])                          # beh 1 -> 6 by delta
+    fina_sub2 = single2([(2, 9), (3, 10)])
+    # multiple substitution format 1: format, coverageOffset, sequenceCount, sequenceOffsets[], then the tables
+    seq = H(2, 13, 14)
+    isol = H(1, 8 + len(seq), 1, 8) + seq + cov([1])
+    lig = lambda glyph, *rest: H(glyph, 1 + len(rest), *rest)
+    set7 = H(1, 4) + lig(11, 10)
+    set8 = H(1, 4) + lig(12, 10)
+    liga = H(1, 10 + len(set7) + len(set8), 2, 10, 10 + len(set7)) + set7 + set8 + cov([7, 8])
+
+    def lookup(kind, *subs):
+        head = H(kind, 0, len(subs))
+        offs, at = [], 6 + 2 * len(subs)
+        for sub in subs:
+            offs.append(at)
+            at += len(sub)
+        return head + H(*offs) + b"".join(subs)
+
+    ext = H(1, 1) + struct.pack(">I", 8)                                         # extension -> type 1 right behind it
+    lookups = [lookup(1, init), lookup(1, medi), lookup(1, fina_sub, fina_sub2), lookup(2, isol), lookup(4, liga),
+               lookup(7, ext + single2([(1, 6)]))]
+    offs, at = [], 2 + 2 * len(lookups)
+    for l in lookups:
+        offs.append(at)
+        at += len(l)
+    lookup_list = H(len(lookups), *offs) + b"".join(lookups)
+    feats = [(b"fina", [2, 5]), (b"init", [0]), (b"isol", [3]), (b"medi", [1]), (b"rlig", [4])]
+    records, tables, at = b"", b"", 2 + 6 * len(feats)
+    for tag, idx in feats:
+        records += tag + H(at)
+        table = H(0, len(idx), *idx)
+        tables += table
+        at += len(table)
+    feature_list = H(len(feats)) + records + tables
+    script_list = H(0)
+    return H(1, 0, 10, 10 + len(script_list), 10 + len(script_list) + len(feature_list)) + script_list + feature_list + lookup_list
+
+
+def test_gsub_forms_and_ligatures_drive_the_line_layout():
+    from idrak_b200.imaging.gsub import GsubTable
+    g = GsubTable(build_gsub())
+    assert g.joins and sorted(g.features) == ["fina", "init", "isol", "medi", "rlig"]
+    assert g.single("init") == {1: (4,), 2: (7,)} and g.single("medi") == {1: (5,), 2: (8,)}
+    assert g.single("fina") == {1: (6,), 2: (9,), 3: (10,)} and g.single("isol") == {1: (13, 14)}
+    assert g.ligatures("rlig") == {7: [((10,), 11)], 8: [((10,), 12)]} and g.single("kern") == {}
+    chars, subrs, gsubrs = _glyphs()
+    glyphs = [chars[0]] + [chars[1]] * 14
+    font = im.TrueTypeFont(build_otf(build_cff(glyphs, subrs, gsubrs), {0x628: 1, 0x644: 2, 0x627: 3, ord("a"): 1},
+                                     [500] * 15, extra={b"GSUB": build_gsub()}))
+    ids = lambda text: [gid for gid, _ in font.layout(text, 10)]
+    assert ids("ببب") == [6, 5, 4]                       # drawing order: final, medial, initial
+    assert ids("ب") == [14, 13]                           # isolated: base and dot, reversed with the run
+    assert ids("بلا") == [12, 4]                          # beh.init + (lam.medi + alef.fina -> joined ligature)
+    assert ids("لا") == [11]
+    assert ids("a بب") == [1, 0, 6, 4]                    # a left-to-right line: the Arabic run reversed inside it
+    assert ids("ab") == [1, 0]
